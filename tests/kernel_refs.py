@@ -1,0 +1,116 @@
+"""Plain PyTorch references of the kernels, one per entry point of
+``zinfer_b200.ops`` and with the same signature.  Written from the formulas (cited
+in tests/plain_qwen3.py), with 32-bit arithmetic and simple loops; they share no
+code with the kernels.  GPU tests compare each kernel with its reference; the
+CPU tests of the engine's host logic put these in the kernels' place.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+
+def embed_gather(table, ids, out=None):
+    return table[ids.long()].to(torch.float32)
+
+
+def add_rmsnorm(h, delta, weight, eps, out_dtype, rows=None, out=None):
+    if delta is not None:
+        if rows is None:
+            h += delta.to(torch.float32)
+        else:
+            h[rows.long()] += delta[rows.long()].to(torch.float32)
+    x = h if rows is None else h[rows.long()]
+    ms = (x * x).mean(dim=-1, keepdim=True)
+    inv = 1.0 / torch.sqrt(ms + torch.tensor(eps, dtype=torch.float32))
+    return (x * weight * inv).to(out_dtype)
+
+
+def residual_add(h, delta):
+    h += delta.to(torch.float32)
+
+
+def swiglu(gate_up, out=None):
+    I = gate_up.shape[1] // 2
+    g, u = gate_up[:, :I].to(torch.float32), gate_up[:, I:].to(torch.float32)
+    return (g / (1.0 + torch.exp(-g)) * u).to(gate_up.dtype)
+
+
+def rope_table(n_pos, head_dim, theta, device):
+    half = head_dim // 2
+    exponent = (np.arange(half, dtype=np.float32) * np.float32(2)) / np.float32(head_dim)
+    p = np.power(np.float64(np.float32(theta)), exponent.astype(np.float64)).astype(np.float32)
+    inv = (np.float32(1) / p).astype(np.float32)
+    ang = (np.arange(n_pos, dtype=np.float32)[:, None] * inv[None, :]).astype(np.float32)
+    cos = torch.from_numpy(np.cos(ang.astype(np.float64)).astype(np.float32)).to(device)
+    sin = torch.from_numpy(np.sin(ang.astype(np.float64)).astype(np.float32)).to(device)
+    return cos, sin
+
+
+def qk_norm_rope_store(qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weight, eps, cos, sin, positions,
+                       k_cache, v_cache, slots, page_size, write_kv=True):
+    T = qkv.shape[0]
+    nq, nkv, d = num_heads, num_kv_heads, head_dim
+    half = d // 2
+    pos = positions.long()
+
+    def norm_rope(x, w):  # x [T, heads, d] float32
+        if w is not None:
+            ms = (x * x).mean(dim=-1, keepdim=True)
+            x = x * w * (1.0 / torch.sqrt(ms + torch.tensor(eps, dtype=torch.float32)))
+        if cos is not None:
+            c, s = cos[pos][:, None, :], sin[pos][:, None, :]
+            a, b = x[..., :half], x[..., half:]
+            x = torch.cat([a * c - b * s, b * c + a * s], dim=-1)
+        return x
+
+    q = norm_rope(qkv[:, :nq * d].to(torch.float32).reshape(T, nq, d), q_weight)
+    qkv[:, :nq * d] = q.reshape(T, nq * d).to(qkv.dtype)
+    if not write_kv:
+        return
+    k = norm_rope(qkv[:, nq * d:(nq + nkv) * d].to(torch.float32).reshape(T, nkv, d), k_weight).to(qkv.dtype)
+    v = qkv[:, (nq + nkv) * d:(nq + 2 * nkv) * d].reshape(T, nkv, d)
+    for t in range(T):
+        slot = int(slots[t])
+        k_cache[slot // page_size, :, slot % page_size, :] = k[t]
+        v_cache[slot // page_size, :, slot % page_size, :] = v[t]
+
+
+def linear(x, weight, out_dtype=None, out=None):
+    y = x.to(torch.float32) @ weight.to(torch.float32).T
+    return y.to(out_dtype or x.dtype)
+
+
+def attention_tile_rows():
+    return 16
+
+
+def paged_attention(q, k_cache, v_cache, block_tables, cu_q, kv_lens, tile_seq, tile_q0, num_heads, num_kv_heads,
+                    head_dim, page_size, window, scale, out=None):
+    T = q.shape[0]
+    nq, nkv, d = num_heads, num_kv_heads, head_dim
+    g = nq // nkv
+    o = torch.zeros((T, nq * d), dtype=torch.float32, device=q.device)
+    n = kv_lens.shape[0]
+    for s in range(n):
+        a, b = int(cu_q[s]), int(cu_q[s + 1])
+        kv_len = int(kv_lens[s])
+        ctx = kv_len - (b - a)
+        for t in range(a, b):
+            pos = ctx + (t - a)
+            lo = 0 if not window else max(0, pos - window + 1)
+            js = torch.arange(lo, pos + 1, device=q.device)
+            pages = block_tables[s, (js // page_size)].long()
+            offs = js % page_size
+            K = k_cache[pages, :, offs, :].to(torch.float32)   # [keys, nkv, d]
+            V = v_cache[pages, :, offs, :].to(torch.float32)
+            qt = q[t, :nq * d].to(torch.float32).reshape(nq, d)
+            for h in range(nq):
+                sc = (K[:, h // g, :] @ qt[h]) * scale
+                p = torch.softmax(sc, dim=0)
+                o[t, h * d:(h + 1) * d] = p @ V[:, h // g, :]
+    return o.to(q.dtype)
+
+
+def argmax(logits, out=None):
+    return torch.argmax(logits, dim=-1).to(torch.int32)

@@ -1,0 +1,44 @@
+// C entry points of the kernel library.  Pointers are device pointers; `stream` is
+// the CUDA stream the caller works on.  Each returns 0 on success, a cudaError_t
+// (> 0) if the launch failed, or -1 if it refuses the sizes, with the reason in
+// zi_last_error().  dtype tags: 0 = float32, 1 = bfloat16.
+#pragma once
+#include <cuda_runtime.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+const char* zi_last_error();
+
+int zi_embed_gather(float* h, const void* table, int table_dtype, const int* ids, int T, int H, int V,
+                    cudaStream_t stream);
+int zi_add_rmsnorm(float* h, const void* delta, int delta_dtype, const float* w, float eps, void* out, int out_dtype,
+                   const int* rows, int n_rows, int H, cudaStream_t stream);
+int zi_residual_add(float* h, const void* delta, int delta_dtype, long long n, cudaStream_t stream);
+int zi_swiglu(void* out, const void* gu, int dtype, int T, int I, cudaStream_t stream);
+int zi_rope_table(float* cos_t, float* sin_t, int n_pos, int d, float theta, cudaStream_t stream);
+int zi_qk_norm_rope_store(void* qkv, int dtype, int T, int row_stride, int nq, int nkv, int d, const float* qw,
+                          const float* kw, float eps, const float* cos_t, const float* sin_t, int n_table_pos,
+                          const int* positions, void* kcache, void* vcache, const int* slots, int page_size,
+                          int write_kv, cudaStream_t stream);
+
+int zi_gemm_simt(void* out, int out_dtype, const void* x, int x_dtype, const void* w, int w_dtype, int M, int N,
+                 int K, int ldx, int ldw, int ldo, cudaStream_t stream);
+
+int zi_paged_attention_tile_rows();
+int zi_paged_attention(void* out, int out_stride, const void* q, int q_stride, int dtype, const void* kcache,
+                       const void* vcache, const int* block_tables, int bt_stride, const int* cu_q,
+                       const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv,
+                       int d, int page_size, int window, float scale, cudaStream_t stream);
+
+int zi_argmax(int* out, const float* logits, int R, int V, int ld, cudaStream_t stream);
+int zi_sample(int* out, const float* logits, int R, int V, int ld, const float* temperature, const int* top_k,
+              const float* top_p, const float* min_p, const float* rep, const float* pres, const float* freq,
+              const int* count_rows, int* counts, const unsigned long long* seeds, const int* draw_index,
+              cudaStream_t stream);
+int zi_count_tokens(int* counts, const int* tokens, int n, int V, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,62 @@
+// Shared helpers of the sm_100a kernels: dtype tags, loads that widen to 32-bit,
+// reductions with a fixed order, and the error channel of the C entry points.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define ZI_F32 0
+#define ZI_BF16 1
+
+// Entry points return 0, a cudaError_t (> 0), or ZI_REFUSED (< 0) with the reason
+// in zi_last_error().
+#define ZI_REFUSED (-1)
+
+extern "C" const char* zi_last_error();
+int zi_refuse(const char* fmt, ...);
+int zi_check_launch(const char* what);
+
+template <typename T> struct DTypeTag;
+template <> struct DTypeTag<float> { static constexpr int value = ZI_F32; };
+template <> struct DTypeTag<__nv_bfloat16> { static constexpr int value = ZI_BF16; };
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread receives the result.  The
+// order of additions depends only on blockDim, never on the data's place in a batch.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floats */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // scratch may still be read from an earlier call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarp ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+#define ZI_DISPATCH_DTYPE(dtype, T, ...)                                   \
+  do {                                                                     \
+    if ((dtype) == ZI_F32) { using T = float; __VA_ARGS__; }               \
+    else if ((dtype) == ZI_BF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+    else return zi_refuse("unknown dtype tag %d", (int)(dtype));           \
+  } while (0)

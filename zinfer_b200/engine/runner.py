@@ -1,0 +1,153 @@
+"""The step function: runs a batch of (request, next tokens) from the cache.
+
+:class:`ModelRunner` owns the model, the cache manager and the device storage.
+``step(entries)`` reserves pages for the tokens it is given, runs only those
+tokens as one batch against what earlier steps left in the cache, commits them,
+and returns the 32-bit logits at the wanted places.  Generation (the scheduler)
+and trace replay both drive this one function.
+
+The reference's unit of work is one token of one request
+(src/model/runtime/optimized_decoder/runtime.zig:103-148); its prefill is a loop
+over that (runtime.zig:150-163).
+"""
+from __future__ import annotations
+
+from typing import Hashable, Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..cache import CacheManager, CacheStorage, OutOfPages
+from ..config.registry import load_config
+from ..weights import load_tensors, random_tensors
+from .batch import StepContext, StepEntry, build_step
+from .model import DecoderModel
+
+
+class StepError(ValueError):
+    """The step's input cannot be run: bad token id, too long a request, unknown request."""
+
+
+def _require_cuda(device: torch.device) -> None:
+    if not torch.cuda.is_available() or device.type != "cuda":
+        raise RuntimeError("zinfer_b200 runs on a CUDA device only; there is no CPU path")
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, page_size: int = 16, num_pages: Optional[int] = None,
+                 max_tokens: Optional[int] = None, max_requests: int = 64):
+        """``max_tokens`` sizes each group's pool for that many cached tokens
+        (rounded up to whole pages); ``num_pages`` gives the page count directly."""
+        _require_cuda(model.device)
+        ops.lib()  # fail now, and loudly, if the kernel library cannot be built or loaded
+        self.model = model
+        self.device = model.device
+        if num_pages is None:
+            if max_tokens is None:
+                raise ValueError("give num_pages or max_tokens")
+            num_pages = -(-max_tokens // page_size)
+        kv_needs, state_needs = model.cache_needs()
+        self.manager = CacheManager(kv_needs, list(state_needs), page_size, num_pages, max_requests)
+        self.storage = CacheStorage(self.manager, state_needs, model.dtype, self.device)
+        model.attach(self.storage)
+        self.tile_rows = ops.attention_tile_rows()
+        self.steps_run = 0
+
+    # ------------------------------------------------------------- construction
+    @classmethod
+    def from_model_dir(cls, model_dir: str, dtype: torch.dtype = torch.bfloat16, device="cuda:0",
+                       max_model_len: Optional[int] = None, **kw) -> "ModelRunner":
+        family, config = load_config(model_dir)
+        model = DecoderModel(family.model_spec(config), dtype, device, max_positions=max_model_len)
+        model.bind(load_tensors(model_dir, model.tensor_specs(), dtype, model.device))
+        runner = cls(model, **kw)
+        runner.config = config
+        return runner
+
+    @classmethod
+    def from_config(cls, config, seed: int, dtype: torch.dtype = torch.bfloat16, device="cuda:0",
+                    max_model_len: Optional[int] = None, **kw) -> "ModelRunner":
+        """Random weights drawn on the device (no model folder)."""
+        from ..config.registry import family_for
+
+        family = family_for(config.to_dict())
+        model = DecoderModel(family.model_spec(config), dtype, device, max_positions=max_model_len)
+        model.bind(random_tensors(model.tensor_specs(), seed, dtype, model.device))
+        runner = cls(model, **kw)
+        runner.config = config
+        return runner
+
+    # ------------------------------------------------------------------ requests
+    def has_request(self, request_id: Hashable) -> bool:
+        return self.manager.has_request(request_id)
+
+    def add_request(self, request_id: Hashable) -> None:
+        rc = self.manager.add_request(request_id)
+        if self.storage.state:
+            self.storage.reset_slot(rc.state_slot)
+
+    def end_request(self, request_id: Hashable) -> None:
+        """Gives back everything the request holds."""
+        self.manager.free_request(request_id)
+
+    def length(self, request_id: Hashable) -> int:
+        return self.manager.length(request_id)
+
+    # ---------------------------------------------------------------------- step
+    def validate(self, entries: Sequence[StepEntry]) -> None:
+        V = self.model.spec.vocab_size
+        seen = set()
+        for e in entries:
+            if e.request_id in seen:
+                raise StepError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            if len(e.tokens) == 0:
+                raise StepError(f"request {e.request_id!r} brings no tokens")
+            bad = [t for t in e.tokens if not 0 <= int(t) < V]
+            if bad:
+                raise StepError(f"request {e.request_id!r}: token id {bad[0]} is outside the vocabulary of {V}")
+            have = self.manager.length(e.request_id) if self.manager.has_request(e.request_id) else 0
+            if have + len(e.tokens) > self.model.max_positions:
+                raise StepError(f"request {e.request_id!r} would reach {have + len(e.tokens)} tokens; "
+                                f"the limit is {self.model.max_positions}")
+            for w in e.want:
+                if not 0 <= int(w) < len(e.tokens):
+                    raise StepError(f"request {e.request_id!r}: wanted place {w} is outside its {len(e.tokens)} tokens")
+
+    def reserve(self, entries: Sequence[StepEntry]) -> None:
+        """Pages for all entries, or :class:`OutOfPages` with nothing kept."""
+        added, done = [], []
+        try:
+            for e in entries:
+                if not self.manager.has_request(e.request_id):
+                    self.add_request(e.request_id)
+                    added.append(e.request_id)
+            # all-or-nothing across entries: count first, then take
+            need = [0] * len(self.manager.groups)
+            for e in entries:
+                for gi, n in enumerate(self.manager.pages_needed(e.request_id, len(e.tokens))):
+                    need[gi] += n
+            for gi, g in enumerate(self.manager.groups):
+                if need[gi] > g.pool.num_free:
+                    raise OutOfPages(f"the step needs {need[gi]} pages in {g.pool.name}, {g.pool.num_free} are free")
+            for e in entries:
+                self.manager.reserve(e.request_id, len(e.tokens))
+                done.append(e)
+        except OutOfPages:
+            for rid in added:
+                self.manager.free_request(rid)
+            raise
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs the entries as one batch; returns logits [wanted, vocab] in the order
+        of the entries and of each entry's ``want`` (None if nothing is wanted)."""
+        if not entries:
+            return None
+        self.validate(entries)
+        self.reserve(entries)
+        ctx = build_step(self.manager, entries, self.device, self.tile_rows)
+        logits = self.model.forward(ctx)
+        for e in entries:
+            self.manager.commit(e.request_id, len(e.tokens))
+        self.steps_run += 1
+        return logits

@@ -1,0 +1,261 @@
+"""Python face of the kernel library: one function per kernel entry point.
+
+The library is built on first use (see ``csrc/build.py``) and loaded with ctypes.
+Every function takes CUDA tensors, checks what the kernel assumes, launches on the
+current torch stream and raises :class:`KernelError` with the kernel's own message
+if it refuses.  There is no fallback of any kind: without the library, or with
+tensors that are not on a CUDA device, these functions fail.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc import build as _build
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_LIB = None
+F32, BF16 = 0, 1
+
+
+def lib() -> ctypes.CDLL:
+    global _LIB
+    if _LIB is None:
+        path = _build.library_path()
+        try:
+            _LIB = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"cannot load the kernel library {path}: {e}") from None
+        _LIB.zi_last_error.restype = ctypes.c_char_p
+    return _LIB
+
+
+def library_file() -> str:
+    return _build.library_path()
+
+
+def _tag(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    if t is None:
+        return ctypes.c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError("kernels take CUDA tensors; there is no CPU path")
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        msg = lib().zi_last_error().decode("utf-8", "replace")
+        raise KernelError(f"{what}: {msg} (code {code})")
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _i32(t: torch.Tensor, name: str) -> torch.Tensor:
+    _need(t.dtype == torch.int32 and t.is_contiguous(), f"{name} must be a contiguous int32 tensor")
+    return t
+
+
+# ------------------------------------------------------------------ elementwise
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rows ``ids`` of ``table`` [V, H] as the 32-bit residual stream [T, H]."""
+    V, H = table.shape
+    T = ids.shape[0]
+    _need(table.is_contiguous(), "embedding table must be contiguous")
+    _i32(ids, "ids")
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    _check(lib().zi_embed_gather(_ptr(out), _ptr(table), _tag(table), _ptr(ids), T, H, V, _stream()), "embed_gather")
+    return out
+
+
+def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``h[row] += delta[row]`` in place (32-bit), then RMSNorm of those rows.
+
+    ``rows`` (int32) picks rows of ``h``; the result then has one row per entry."""
+    T, H = h.shape
+    _need(h.dtype == torch.float32 and h.is_contiguous(), "the residual stream is contiguous float32")
+    _need(weight.dtype == torch.float32 and weight.numel() == H, "norm weight must be float32 of the row's width")
+    if delta is not None:
+        _need(delta.shape == h.shape and delta.is_contiguous(), "delta must match the residual stream")
+    n = T if rows is None else _i32(rows, "rows").shape[0]
+    if out is None:
+        out = torch.empty((n, H), dtype=out_dtype, device=h.device)
+    _check(lib().zi_add_rmsnorm(_ptr(h), _ptr(delta), _tag(delta) if delta is not None else F32, _ptr(weight),
+                                ctypes.c_float(eps), _ptr(out), _tag(out), _ptr(rows), n, H, _stream()), "add_rmsnorm")
+    return out
+
+
+def residual_add(h: torch.Tensor, delta: torch.Tensor) -> None:
+    _need(h.dtype == torch.float32 and h.is_contiguous() and delta.is_contiguous() and delta.shape == h.shape,
+          "residual_add: shapes must match and be contiguous")
+    _check(lib().zi_residual_add(_ptr(h), _ptr(delta), _tag(delta), ctypes.c_longlong(h.numel()), _stream()),
+           "residual_add")
+
+
+def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(gate) * up`` for ``gate_up`` [T, 2I] holding gate then up."""
+    T, two_i = gate_up.shape
+    _need(two_i % 2 == 0 and gate_up.is_contiguous(), "swiglu input is contiguous [T, 2I]")
+    I = two_i // 2
+    if out is None:
+        out = torch.empty((T, I), dtype=gate_up.dtype, device=gate_up.device)
+    _check(lib().zi_swiglu(_ptr(out), _ptr(gate_up), _tag(gate_up), T, I, _stream()), "swiglu")
+    return out
+
+
+def rope_table(n_pos: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    cos = torch.empty((n_pos, head_dim // 2), dtype=torch.float32, device=device)
+    sin = torch.empty_like(cos)
+    _check(lib().zi_rope_table(_ptr(cos), _ptr(sin), n_pos, head_dim, ctypes.c_float(theta), _stream()), "rope_table")
+    return cos, sin
+
+
+def qk_norm_rope_store(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                       q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                       cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], positions: torch.Tensor,
+                       k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                       slots: Optional[torch.Tensor], page_size: int, write_kv: bool = True) -> None:
+    """In place on the fused projection rows [q heads | k heads | v heads]: per-head
+    RMSNorm of q and k (when weights are given), rotary positions (when tables are
+    given), q back into ``qkv``, k and v into their page slots."""
+    T = qkv.shape[0]
+    _need(qkv.stride(1) == 1, "qkv rows must be dense")
+    width = (num_heads + 2 * num_kv_heads) * head_dim if write_kv else num_heads * head_dim
+    _need(qkv.shape[1] >= width, "qkv is narrower than its heads")
+    for wt in (q_weight, k_weight):
+        if wt is not None:
+            _need(wt.dtype == torch.float32 and wt.numel() == head_dim, "q/k norm weights are float32 [head_dim]")
+    n_table = 0
+    if cos is not None:
+        _need(cos.shape == sin.shape and cos.shape[1] == head_dim // 2 and cos.dtype == torch.float32,
+              "rotary tables are float32 [positions, head_dim/2]")
+        n_table = cos.shape[0]
+    _i32(positions, "positions")
+    if write_kv:
+        _need(k_cache is not None and v_cache is not None and slots is not None, "writing needs pages and slots")
+        _need(k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype, "cache pages have the activations' dtype")
+        _i32(slots, "slots")
+    _check(lib().zi_qk_norm_rope_store(
+        _ptr(qkv), _tag(qkv), T, qkv.stride(0), num_heads, num_kv_heads, head_dim, _ptr(q_weight), _ptr(k_weight),
+        ctypes.c_float(eps), _ptr(cos), _ptr(sin), n_table, _ptr(positions), _ptr(k_cache), _ptr(v_cache),
+        _ptr(slots), page_size, 1 if write_kv else 0, _stream()), "qk_norm_rope_store")
+
+
+# ------------------------------------------------------------------------ matrices
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x [M, K] @ weight [N, K]^T`` with 32-bit accumulation."""
+    M, K = x.shape
+    N, K2 = weight.shape
+    _need(K == K2, f"linear: x has {K} columns, weight has {K2}")
+    _need(x.stride(1) == 1 and weight.is_contiguous(), "linear: operands must be dense along K")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+    _need(out.stride(1) == 1, "linear: output rows must be dense")
+    _check(lib().zi_gemm_simt(_ptr(out), _tag(out), _ptr(x), _tag(x), _ptr(weight), _tag(weight), M, N, K,
+                              x.stride(0), weight.stride(0), out.stride(0), _stream()), "linear")
+    return out
+
+
+# ----------------------------------------------------------------------- attention
+def attention_tile_rows() -> int:
+    return int(lib().zi_paged_attention_tile_rows())
+
+
+def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
+                    cu_q: torch.Tensor, kv_lens: torch.Tensor, tile_seq: torch.Tensor, tile_q0: torch.Tensor,
+                    num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
+                    scale: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of the step's query tokens over their requests' pages.
+
+    ``q`` [T, >= num_heads*head_dim] (row stride free), caches [pages, kv heads,
+    page_size, head_dim], ``block_tables`` [n, W], ``cu_q`` [n+1] token offsets,
+    ``kv_lens`` [n] keys per request including this step's tokens, ``tile_seq`` and
+    ``tile_q0`` the request and first token of each query tile."""
+    T = q.shape[0]
+    _need(q.stride(1) == 1, "q rows must be dense")
+    _need(k_cache.is_contiguous() and v_cache.is_contiguous(), "cache pages must be contiguous")
+    _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim), "cache pages are [pages, kv heads, page, d]")
+    _need(k_cache.dtype == q.dtype, "cache pages have the activations' dtype")
+    for name, t in (("block_tables", block_tables), ("cu_q", cu_q), ("kv_lens", kv_lens), ("tile_seq", tile_seq),
+                    ("tile_q0", tile_q0)):
+        _i32(t, name)
+    if out is None:
+        out = torch.empty((T, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    _check(lib().zi_paged_attention(
+        _ptr(out), out.stride(0), _ptr(q), q.stride(0), _tag(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+        block_tables.stride(0), _ptr(cu_q), _ptr(kv_lens), _ptr(tile_seq), _ptr(tile_q0), tile_seq.shape[0],
+        num_heads, num_kv_heads, head_dim, page_size, int(window or 0), ctypes.c_float(scale), _stream()),
+        "paged_attention")
+    return out
+
+
+# ------------------------------------------------------------------------ sampling
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    R, V = logits.shape
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "logits are float32 with dense rows")
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _check(lib().zi_argmax(_ptr(out), _ptr(logits), R, V, logits.stride(0), _stream()), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, seeds: torch.Tensor, draw_index: torch.Tensor,
+           top_k: Optional[torch.Tensor] = None, top_p: Optional[torch.Tensor] = None,
+           min_p: Optional[torch.Tensor] = None, repetition_penalty: Optional[torch.Tensor] = None,
+           presence_penalty: Optional[torch.Tensor] = None, frequency_penalty: Optional[torch.Tensor] = None,
+           count_rows: Optional[torch.Tensor] = None, counts: Optional[torch.Tensor] = None,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row.  Per-row parameters are device tensors: float32 for
+    ``temperature``/``top_p``/``min_p``/penalties, int32 for ``top_k``,
+    ``draw_index`` and ``count_rows``, int64 for ``seeds``.  ``counts`` [slots, V]
+    int32 holds how often each token occurred in a request; the row named by
+    ``count_rows`` is read for the penalties and incremented at the drawn token."""
+    R, V = logits.shape
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "logits are float32 with dense rows")
+    for t in (temperature, top_p, min_p, repetition_penalty, presence_penalty, frequency_penalty):
+        if t is not None:
+            _need(t.dtype == torch.float32 and t.numel() == R, "per-row float parameters are float32 [rows]")
+    for t in (top_k, draw_index, count_rows):
+        if t is not None:
+            _need(t.dtype == torch.int32 and t.numel() == R, "per-row integer parameters are int32 [rows]")
+    _need(seeds.dtype == torch.int64 and seeds.numel() == R, "seeds are int64 [rows]")
+    if counts is not None:
+        _need(counts.dtype == torch.int32 and counts.shape[1] == V and counts.is_contiguous(), "counts are int32 [slots, V]")
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _check(lib().zi_sample(_ptr(out), _ptr(logits), R, V, logits.stride(0), _ptr(temperature), _ptr(top_k),
+                           _ptr(top_p), _ptr(min_p), _ptr(repetition_penalty), _ptr(presence_penalty),
+                           _ptr(frequency_penalty), _ptr(count_rows), _ptr(counts), _ptr(seeds), _ptr(draw_index),
+                           _stream()), "sample")
+    return out
+
+
+def count_tokens(counts_row: torch.Tensor, tokens: torch.Tensor) -> None:
+    _need(counts_row.dtype == torch.int32 and counts_row.is_contiguous(), "counts row is contiguous int32")
+    _i32(tokens, "tokens")
+    _check(lib().zi_count_tokens(_ptr(counts_row), _ptr(tokens), tokens.numel(), counts_row.numel(), _stream()),
+           "count_tokens")
