@@ -1,0 +1,263 @@
+"""Each kernel alone against its plain PyTorch reference (tests/kernel_refs.py), in
+float32 and bfloat16, at sizes other than the engine's tiny models: widths and
+vocabularies that are no powers of two, head sizes in steps of 16, odd head counts."""
+import numpy as np
+import pytest
+import torch
+
+import kernel_refs as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def ops():
+    from zinfer_b200 import ops as o
+    return o
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-6) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1e-3)
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def test_library_is_loaded_from_the_tree():
+    import os
+    path = ops().library_file()
+    assert os.path.exists(path) and path.endswith(".so")
+    ops().lib()
+    with open("/proc/self/maps") as f:
+        assert "libzinfer_b200.so" in f.read(), "the kernel library is not mapped into the process"
+
+
+def test_no_cpu_path():
+    o = ops()
+    with pytest.raises(o.KernelError):
+        o.swiglu(torch.zeros(2, 4))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("V,H,T", [(301, 72, 9), (1000, 4096, 3), (17, 16, 33)])
+def test_embed_gather(dtype, V, H, T):
+    table = rnd(V, H, dtype=dtype)
+    ids = torch.randint(0, V, (T,), dtype=torch.int32, device=DEV)
+    got = ops().embed_gather(table, ids)
+    assert got.dtype == torch.float32
+    torch.testing.assert_close(got, ref.embed_gather(table, ids), rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H,eps", [(5, 72, 1e-6), (3, 4096, 1e-5), (130, 200, 3e-6), (2, 5120, 1e-6)])
+def test_add_rmsnorm(dtype, T, H, eps):
+    h = rnd(T, H, scale=3.0)
+    delta = rnd(T, H, dtype=dtype, seed=1)
+    w = 1 + 0.1 * rnd(H, seed=2)
+    for d in (None, delta):
+        h_ref, h_got = h.clone(), h.clone()
+        want = ref.add_rmsnorm(h_ref, d, w, eps, dtype)
+        got = ops().add_rmsnorm(h_got, d, w, eps, dtype)
+        torch.testing.assert_close(h_got, h_ref, rtol=1e-6, atol=1e-6)
+        torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+    rows = torch.tensor([T - 1, 0, T // 2], dtype=torch.int32, device=DEV)
+    h_ref, h_got = h.clone(), h.clone()
+    want = ref.add_rmsnorm(h_ref, delta, w, eps, dtype, rows=rows)
+    got = ops().add_rmsnorm(h_got, delta, w, eps, dtype, rows=rows)
+    assert got.shape == (3, H)
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+
+
+def test_rmsnorm_reference_vector():
+    # [3,4] with weights [1,2], eps 0 -> [0.84852814, 2.2627418] (src/kernel/core/cpu.zig:193-204)
+    h = torch.tensor([[3.0, 4.0]], device=DEV)
+    w = torch.tensor([1.0, 2.0], device=DEV)
+    got = ops().add_rmsnorm(h, None, w, 0.0, torch.float32)
+    torch.testing.assert_close(got.cpu(), torch.tensor([[0.84852814, 2.2627418]]), rtol=1e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,I", [(7, 200), (3, 12288), (1, 17)])
+def test_swiglu(dtype, T, I):
+    gu = rnd(T, 2 * I, dtype=dtype, scale=2.0)
+    torch.testing.assert_close(ops().swiglu(gu).float(), ref.swiglu(gu).float(), **tol(dtype))
+
+
+def test_swiglu_reference_vector():
+    # gate [0,1,-1], up [1,2,3] -> [0, 1.4621172, -0.8068243] (src/kernel/core/cpu.zig:233-245)
+    gu = torch.tensor([[0.0, 1.0, -1.0, 1.0, 2.0, 3.0]], device=DEV)
+    torch.testing.assert_close(ops().swiglu(gu).cpu(), torch.tensor([[0.0, 1.4621172, -0.8068243]]), rtol=1e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize("n_pos,d,theta", [(128, 16, 1e4), (4096, 128, 1e6), (300, 48, 5e4)])
+def test_rope_table(n_pos, d, theta):
+    cos, sin = ops().rope_table(n_pos, d, theta, DEV)
+    rc, rs = ref.rope_table(n_pos, d, theta, "cpu")
+    # same 32-bit recipe; the device's pow may differ from the host's in the last place of inv_freq,
+    # which moves the angle by at most pos * 2^-24 * inv_freq
+    np.testing.assert_allclose(cos.cpu().numpy(), rc.numpy(), atol=n_pos * 1.2e-7, rtol=0)
+    np.testing.assert_allclose(sin.cpu().numpy(), rs.numpy(), atol=n_pos * 1.2e-7, rtol=0)
+    np.testing.assert_array_equal(cos[0].cpu().numpy(), np.ones(d // 2, dtype=np.float32))  # identity at position 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,page,norm,rope", [
+    (4, 2, 16, 16, True, True), (6, 1, 32, 8, True, True), (3, 3, 48, 32, True, True),
+    (32, 8, 128, 16, True, True), (5, 5, 80, 4, False, True), (2, 1, 256, 16, True, False)])
+def test_qk_norm_rope_store(dtype, nq, nkv, d, page, norm, rope):
+    T, n_pages, n_pos = 11, 9, 200
+    qkv = rnd(T, (nq + 2 * nkv) * d, dtype=dtype)
+    qw = (1 + 0.1 * rnd(d, seed=3)) if norm else None
+    kw = (1 + 0.1 * rnd(d, seed=4)) if norm else None
+    cos, sin = ref.rope_table(n_pos, d, 1e4, DEV) if rope else (None, None)
+    positions = torch.randint(0, n_pos, (T,), dtype=torch.int32, device=DEV)
+    slots = torch.randperm(n_pages * page, device=DEV)[:T].to(torch.int32)
+    kc = torch.zeros(n_pages, nkv, page, d, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    kc_ref, vc_ref, qkv_ref = kc.clone(), vc.clone(), qkv.clone()
+    ref.qk_norm_rope_store(qkv_ref, nq, nkv, d, qw, kw, 1e-6, cos, sin, positions, kc_ref, vc_ref, slots, page)
+    ops().qk_norm_rope_store(qkv, nq, nkv, d, qw, kw, 1e-6, cos, sin, positions, kc, vc, slots, page)
+    torch.testing.assert_close(qkv[:, :nq * d].float(), qkv_ref[:, :nq * d].float(), **tol(dtype))
+    torch.testing.assert_close(kc.float(), kc_ref.float(), **tol(dtype))
+    torch.testing.assert_close(vc.float(), vc_ref.float(), rtol=0, atol=0)
+    # a reader of another layer's cache rotates q only and writes nothing
+    q_only = qkv_ref.clone()[:, :nq * d].contiguous()
+    q_in = rnd(T, nq * d, dtype=dtype, seed=9)
+    q_ref = q_in.clone()
+    ref.qk_norm_rope_store(q_ref, nq, nkv, d, qw, kw, 1e-6, cos, sin, positions, None, None, None, page, write_kv=False)
+    before = kc.clone()
+    ops().qk_norm_rope_store(q_in, nq, nkv, d, qw, kw, 1e-6, cos, sin, positions, None, None, None, page, write_kv=False)
+    torch.testing.assert_close(q_in.float(), q_ref.float(), **tol(dtype))
+    assert torch.equal(kc, before)
+
+
+def test_rope_pair_rotation_reference_vector():
+    # position 1, theta 1e4, d = 4: pairs (0,2) and (1,3) rotate by 1 and 0.01 rad (src/kernel/attention/rope.zig:145-190)
+    d = 4
+    x = torch.tensor([[1.0, 2.0, 3.0, 4.0]], device=DEV)
+    cos, sin = ops().rope_table(4, d, 1e4, DEV)
+    pos = torch.tensor([1], dtype=torch.int32, device=DEV)
+    ops().qk_norm_rope_store(x, 1, 0, d, None, None, 0.0, cos, sin, pos, None, None, None, 1, write_kv=False)
+    a0, a1 = 1.0, 0.01
+    want = [1 * np.cos(a0) - 3 * np.sin(a0), 2 * np.cos(a1) - 4 * np.sin(a1),
+            3 * np.cos(a0) + 1 * np.sin(a0), 4 * np.cos(a1) + 2 * np.sin(a1)]
+    np.testing.assert_allclose(x.cpu().numpy()[0], np.array(want, dtype=np.float32), rtol=1e-6)
+
+
+@pytest.mark.parametrize("xdt,wdt,odt", [(torch.float32,) * 3, (torch.bfloat16,) * 3,
+                                         (torch.bfloat16, torch.bfloat16, torch.float32),
+                                         (torch.bfloat16, torch.float32, torch.bfloat16)])
+@pytest.mark.parametrize("M,N,K", [(1, 301, 72), (7, 200, 96), (130, 389, 160), (64, 1000, 4096), (33, 65, 17)])
+def test_linear(xdt, wdt, odt, M, N, K):
+    x = rnd(M, K, dtype=xdt)
+    w = rnd(N, K, dtype=wdt, scale=0.05, seed=1)
+    got = ops().linear(x, w, out_dtype=odt)
+    want = (x.double() @ w.double().T)
+    t = dict(rtol=1e-5, atol=1e-5 * K ** 0.5 * 0.05) if odt == torch.float32 and xdt == torch.float32 else \
+        (dict(rtol=1e-5, atol=1e-4) if odt == torch.float32 else dict(rtol=8e-3, atol=1e-3))
+    assert got.dtype == odt
+    torch.testing.assert_close(got.double(), want, **t)
+    # strided input rows (a slice of a wider buffer)
+    wide = rnd(M, K + 24, dtype=xdt, seed=5)
+    got2 = ops().linear(wide[:, :K], w, out_dtype=odt)
+    torch.testing.assert_close(got2.double(), wide[:, :K].double() @ w.double().T, **t)
+
+
+def _paged_case(dtype, nq, nkv, d, page, q_lens, ctx_lens, seed=0):
+    """Random requests laid out in shuffled pages; returns the kernel's arguments."""
+    o = ops()
+    rng = np.random.RandomState(seed)
+    n = len(q_lens)
+    kv_lens = [c + q for c, q in zip(ctx_lens, q_lens)]
+    blocks = [-(-kv // page) for kv in kv_lens]
+    n_pages = sum(blocks) + 3
+    perm = rng.permutation(n_pages)
+    W = max(blocks)
+    bt = -np.ones((n, W), dtype=np.int32)
+    p = 0
+    for i, b in enumerate(blocks):
+        bt[i, :b] = perm[p:p + b]
+        p += b
+    kc = rnd(n_pages, nkv, page, d, dtype=dtype, seed=seed + 1)
+    vc = rnd(n_pages, nkv, page, d, dtype=dtype, seed=seed + 2)
+    T = sum(q_lens)
+    q = rnd(T, nq * d + 8, dtype=dtype, seed=seed + 3)[:, :nq * d]   # strided rows
+    cu = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+    tr = o.attention_tile_rows()
+    tseq = [i for i, ql in enumerate(q_lens) for _ in range(-(-ql // tr))]
+    tq0 = [t * tr for ql in q_lens for t in range(-(-ql // tr))]
+    dev = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=DEV)
+    return dict(q=q, k_cache=kc, v_cache=vc, block_tables=dev(bt), cu_q=dev(cu), kv_lens=dev(kv_lens),
+                tile_seq=dev(tseq), tile_q0=dev(tq0), num_heads=nq, num_kv_heads=nkv, head_dim=d, page_size=page)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,page,window", [
+    (4, 2, 16, 16, None), (6, 1, 32, 8, None), (3, 3, 48, 32, None), (8, 2, 128, 16, None),
+    (5, 1, 80, 4, 7), (4, 4, 64, 16, 33), (2, 1, 256, 16, None), (4, 2, 112, 16, 20)])
+def test_paged_attention(dtype, nq, nkv, d, page, window):
+    q_lens = [1, 37, 2, 1, 19]
+    ctx_lens = [70, 0, 15, 0, 48]
+    args = _paged_case(dtype, nq, nkv, d, page, q_lens, ctx_lens)
+    scale = float(1 / np.sqrt(d))
+    got = ops().paged_attention(window=window, scale=scale, **args)
+    want = ref.paged_attention(window=window, scale=scale, **args)
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_finds_one_far_key(dtype):
+    """One key among hundreds is made to stand out; the output must be its value.
+    A wrong page, a wrong offset or a missed tile would pick another value."""
+    nq, nkv, d, page = 4, 2, 64, 16
+    args = _paged_case(dtype, nq, nkv, d, page, q_lens=[1, 3], ctx_lens=[700, 300], seed=5)
+    for seq, far in ((0, 123), (1, 17)):
+        pg = int(args["block_tables"][seq, far // page])
+        args["k_cache"][pg, :, far % page, :] = 0
+        args["k_cache"][pg, :, far % page, 0] = 60.0
+    q = torch.zeros(4, nq * d, dtype=dtype, device=DEV)
+    q.view(4, nq, d)[:, :, 0] = 60.0
+    args["q"] = q
+    got = ops().paged_attention(window=None, scale=float(1 / np.sqrt(d)), **args).float().view(4, nq, d)
+    for t, (seq, far) in enumerate([(0, 123), (1, 17), (1, 17), (1, 17)]):
+        pg = int(args["block_tables"][seq, far // page])
+        for h in range(nq):
+            torch.testing.assert_close(got[t, h], args["v_cache"][pg, h // 2, far % page].float(), rtol=2e-2, atol=2e-2)
+
+
+def test_paged_attention_ignores_stale_page_contents():
+    """Keys beyond a request's length in its last page, and pages of other requests,
+    hold huge values; none may leak into the result."""
+    dtype = torch.float32
+    args = _paged_case(dtype, 4, 2, 32, 16, q_lens=[5], ctx_lens=[6], seed=8)
+    clean = ops().paged_attention(window=None, scale=0.17, **args).clone()
+    pg_last = int(args["block_tables"][0, 0])
+    args["k_cache"][pg_last, :, 11:, :] = 1e4
+    args["v_cache"][pg_last, :, 11:, :] = 1e4
+    used = set(args["block_tables"][0].tolist())
+    for pg in range(args["k_cache"].shape[0]):
+        if pg not in used:
+            args["k_cache"][pg] = 1e4
+            args["v_cache"][pg] = -1e4
+    dirty = ops().paged_attention(window=None, scale=0.17, **args)
+    assert torch.equal(clean, dirty)
+
+
+def test_attention_refuses_what_it_cannot_do():
+    o = ops()
+    args = _paged_case(torch.float32, 2, 1, 272, 16, [1], [3])
+    with pytest.raises(o.KernelError, match="head_dim"):
+        o.paged_attention(window=None, scale=1.0, **args)
+
+
+@pytest.mark.parametrize("R,V", [(1, 301), (5, 151936), (64, 1000)])
+def test_argmax_first_maximum_wins(R, V):
+    logits = rnd(R, V)
+    logits[0, 7] = logits[0, V - 1] = 100.0   # a tie: the lower id wins (src/sampling/sampler.zig:93-105)
+    got = ops().argmax(logits)
+    want = torch.stack([torch.tensor(int(np.argmax(row))) for row in logits.cpu().numpy()]).to(torch.int32)
+    assert torch.equal(got.cpu(), want)
+    assert int(got[0]) == 7

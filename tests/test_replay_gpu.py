@@ -1,0 +1,49 @@
+"""Trace replay on the GPU through bin/trace_run, as a user runs it: the same
+requests whole, with the tail decoded token by token, in portions of changing
+size, and mixed with other requests in a pool so small that pages are reused; in
+float32 and in bfloat16; every wanted row against the plain model."""
+import pytest
+
+import plain_qwen3
+import replay_util as ru
+
+pytestmark = pytest.mark.gpu
+
+# float32: both sides round every operation to 24 bits and the plain model runs in
+# float64, so rows agree to a few 1e-6 of the row's largest logit; 5e-5 leaves room
+# for the longer sums of the larger shapes.  bfloat16: activations are rounded to 8
+# bits between kernels (2^-9 relative each), which accumulates to about one percent
+# of the largest logit over a few layers.
+TOL = {"float32": dict(rtol=5e-5, atol=1e-6), "bfloat16": dict(rtol=3e-2, atol=1e-3)}
+LENGTHS = {"A": [5, 17, 33, 64, 100], "B": [1, 9, 40, 70, 129, 200], "C": [3, 77, 150, 31]}
+
+
+def _trace(mode, reqs):
+    return {"whole": lambda: ru.trace_whole(reqs), "tail": lambda: ru.trace_tail_decode(reqs, 32),
+            "portions": lambda: ru.trace_portions(reqs, 11), "mixed": lambda: ru.trace_mixed(reqs, 13)}[mode]()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_replay_every_way_of_cutting(model_dirs, tmp_path, name, dtype):
+    from conftest import PAGE_SIZE
+
+    model_dir = model_dirs[(name, dtype)]
+    cfg, w = plain_qwen3.load_model(model_dir)
+    reqs = ru.make_requests(cfg["vocab_size"], LENGTHS[name], seed=21)
+    plain = ru.plain_logits(cfg, w, reqs)
+    results = {}
+    for mode in ("whole", "tail", "portions", "mixed"):
+        trace = _trace(mode, reqs)
+        out = tmp_path / mode
+        results[mode] = ru.run_trace_tool(model_dir, dtype, trace, str(out), ru.max_live_tokens(trace),
+                                          cfg["vocab_size"], extra=["--page-size", str(PAGE_SIZE[name])])
+        ru.assert_close(results[mode], plain, what=f"{name}/{dtype}/{mode}", **TOL[dtype],
+                        argmax_frac=1.0 if dtype == "float32" else 0.0)
+    # the ways of cutting agree with each other far more closely than with the plain model
+    for mode in ("tail", "portions", "mixed"):
+        for key, row in results[mode].items():
+            ref = results["whole"][key]
+            scale = abs(ref).max()
+            lim = 2e-5 * scale if dtype == "float32" else 2e-2 * scale
+            assert abs(row - ref).max() <= lim, f"{name}/{dtype}: {mode} differs from whole at {key}"
