@@ -1,0 +1,147 @@
+"""The scheduler's decisions (no GPU): admission, portions under a token budget,
+decoding, finishing and freeing, and what happens when pages run out.  A fake step
+function stands for the model: it commits the fed tokens and 'samples' a token that
+is a pure function of the request and its length, as the real sampler's draws are."""
+import pytest
+
+from zinfer_b200.cache import CacheManager
+from zinfer_b200.engine.scheduler import Request, Scheduler
+from zinfer_b200.parts import KVCacheNeed
+from zinfer_b200.sampling import SamplingParams
+
+
+def make(num_pages, page=4, budget=16, chunk=None, max_running=4):
+    cache = CacheManager({"l0": KVCacheNeed(1, 16, None)}, [], page, num_pages, max_running)
+    return cache, Scheduler(cache, max_batched_tokens=budget, max_running=max_running, chunk_size=chunk)
+
+
+def fake_token(r: Request) -> int:
+    import zlib
+    return (zlib.crc32(repr(r.request_id).encode()) + 7 * r.num_tokens) % 97 + 3
+
+
+def run_step(cache, sched, log=None):
+    plan = sched.schedule()
+    sampled = []
+    for s in plan.scheduled:
+        assert cache.length(s.request.request_id) == s.start, "the fed portion does not continue the cache"
+        cache.commit(s.request.request_id, s.count)
+        if s.samples:
+            sampled.append(fake_token(s.request))
+    if log is not None:
+        log.append([(s.request.request_id, s.start, s.count, s.samples) for s in plan.scheduled])
+    done = sched.update(plan, sampled)
+    cache.check()
+    return plan, done
+
+
+def drain(cache, sched, limit=2000):
+    done, log = [], []
+    while sched.has_unfinished():
+        limit -= 1
+        assert limit > 0, "the scheduler does not terminate"
+        done += run_step(cache, sched, log)[1]
+    return done, log
+
+
+def req(rid, n_prompt, max_new, **kw):
+    return Request(rid, list(range(1, n_prompt + 1)), SamplingParams(temperature=0.0, max_new_tokens=max_new, **kw))
+
+
+def test_prompts_are_cut_under_the_budget_and_decodes_go_first():
+    cache, sched = make(num_pages=64, budget=16, chunk=10)
+    sched.add(req("a", 23, 3))
+    sched.add(req("b", 5, 2))
+    log = []
+    run_step(cache, sched, log)
+    assert log[-1] == [("a", 0, 10, False), ("b", 0, 5, True)]        # chunk 10, then b whole within the budget of 16
+    run_step(cache, sched, log)
+    assert log[-1] == [("b", 5, 1, True), ("a", 10, 10, False)]       # b decodes first, a's next portion after
+    run_step(cache, sched, log)
+    assert log[-1][0] == ("a", 20, 3, True)                           # the last portion samples; b ended after 2 tokens
+    done, _ = drain(cache, sched)
+    assert not sched.has_unfinished() and cache.free_pages() == [64] and not cache.requests
+
+
+def test_budget_is_never_exceeded_and_portions_can_be_tiny():
+    cache, sched = make(num_pages=200, budget=7, max_running=4)
+    for i in range(6):
+        sched.add(req(i, 9 + i, 4))
+    done, log = drain(cache, sched)
+    assert len(done) == 6 and all(r.finish_reason == "length" and len(r.output) == 4 for r in done)
+    assert all(sum(c for _, _, c, _ in step) <= 7 for step in log)
+    assert any(c <= 2 and not s for step in log for _, _, c, s in step), "no small portion was ever cut"
+    assert max(len(step) for step in log) <= 4
+
+
+def test_finishing_frees_pages_and_admits_the_next():
+    cache, sched = make(num_pages=4, page=4, budget=64, max_running=4)   # 16 tokens of cache in all
+    sched.add(req("a", 10, 2))
+    sched.add(req("b", 10, 2))
+    plan, _ = run_step(cache, sched)
+    assert [s.request.request_id for s in plan.scheduled] == ["a", "b"]
+    assert plan.scheduled[1].count == 4 and not plan.scheduled[1].samples   # b's portion is cut to the free page
+    done, log = drain(cache, sched)
+    assert {r.request_id for r in done} == {"a", "b"} and all(len(r.output) == 2 for r in done)
+    assert cache.free_pages() == [4]
+
+
+def test_eos_ends_a_request_and_is_not_emitted():
+    cache, sched = make(num_pages=16)
+    r = req("a", 3, 50)
+    plan = None
+    sched.add(r)
+    r.eos_token_ids = (fake_token(Request("a", [0] * 5, r.params)),)     # the token 'sampled' at length 5
+    done, _ = drain(cache, sched)
+    assert done[0].finish_reason == "stop" and len(done[0].output) == 2
+    cache2, sched2 = make(num_pages=16)
+    r2 = req("a", 3, 4, ignore_eos=True)
+    r2.eos_token_ids = r.eos_token_ids
+    sched2.add(r2)
+    done2, _ = drain(cache2, sched2)
+    assert done2[0].finish_reason == "length" and len(done2[0].output) == 4
+
+
+def test_out_of_pages_preempts_the_latest_admitted_and_output_is_unchanged():
+    def outputs(num_pages):
+        cache, sched = make(num_pages=num_pages, page=4, budget=64, max_running=3)
+        for i, n in enumerate((6, 7, 5)):
+            sched.add(req(i, n, 12))
+        done, log = drain(cache, sched)
+        return {r.request_id: (r.output, r.finish_reason, r.preemptions) for r in done}, sched.stats, log
+
+    roomy, st_roomy, _ = outputs(64)
+    tight, st_tight, log = outputs(9)       # 36 tokens of cache for 3 requests growing to 18, 19 and 17
+    assert st_roomy.preemptions == 0 and st_tight.preemptions > 0
+    assert {k: v[:2] for k, v in tight.items()} == {k: v[:2] for k, v in roomy.items()}, \
+        "preemption and recomputation changed a request's tokens"
+    assert tight[0][2] == 0, "the oldest request must never be preempted"
+    assert any(v[2] > 0 for v in tight.values())
+    # a preempted request starts again from position 0 with its generated tokens as part of the prompt
+    restarts = [e for step in log for e in step if e[1] == 0]
+    assert len(restarts) > 3
+
+
+def test_request_larger_than_the_pool_ends_with_capacity():
+    cache, sched = make(num_pages=2, page=4, budget=64)
+    sched.add(req("big", 5, 10))           # 8 tokens of cache: the prompt fits, decoding outgrows the pool
+    sched.add(req("huge", 20, 2))          # its prompt alone is larger than the pool
+    done, _ = drain(cache, sched)
+    by = {r.request_id: r for r in done}
+    assert by["big"].finish_reason == "capacity" and len(by["big"].output) == 4   # 5 + 3 fed tokens fill the 8 slots
+    assert by["huge"].finish_reason == "capacity" and by["huge"].output == []
+    assert cache.free_pages() == [2] and not cache.requests
+
+
+def test_waiting_requests_keep_their_order():
+    cache, sched = make(num_pages=64, budget=8, max_running=2)
+    for i in range(5):
+        sched.add(req(i, 4, 3))
+    _, log = drain(cache, sched)
+    first_seen = []
+    for step in log:
+        for rid, start, _, _ in step:
+            if start == 0 and rid not in first_seen:
+                first_seen.append(rid)
+    assert first_seen == [0, 1, 2, 3, 4]
+    assert max(len(step) for step in log) <= 2
