@@ -49,6 +49,7 @@ class StepContext:
     max_q_len: int = 0
     max_kv_len: int = 0
     all_decode: bool = False        # every entry brings exactly one token
+    h2d_bytes: int = 0              # size of the one host->device copy that brought these arrays
 
 
 def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile_rows: int,
@@ -129,4 +130,4 @@ def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile
         kv_lens=view("kv_lens"), state_slots=view("state_slots"), tile_seq=view("tile_seq"), tile_q0=view("tile_q0"),
         logit_rows=view("logit_rows") if R else None, kv_groups=groups, q_lens=q_lens, ctx_lens=ctx_lens,
         max_q_len=max(q_lens, default=0), max_kv_len=max((c + q for c, q in zip(ctx_lens, q_lens)), default=0),
-        all_decode=all(q == 1 for q in q_lens))
+        all_decode=all(q == 1 for q in q_lens), h2d_bytes=int(host.numel()) * 4)

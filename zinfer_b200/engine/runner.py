@@ -52,6 +52,7 @@ class ModelRunner:
         model.attach(self.storage)
         self.tile_rows = ops.attention_tile_rows()
         self.steps_run = 0
+        self.last_h2d_bytes = 0
 
     # ------------------------------------------------------------- construction
     @classmethod
@@ -146,6 +147,7 @@ class ModelRunner:
         self.validate(entries)
         self.reserve(entries)
         ctx = build_step(self.manager, entries, self.device, self.tile_rows)
+        self.last_h2d_bytes = ctx.h2d_bytes
         logits = self.model.forward(ctx)
         for e in entries:
             self.manager.commit(e.request_id, len(e.tokens))

@@ -60,7 +60,12 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+LAUNCHES = 0   # kernel launches issued through this module (graph replays are counted by their owner)
+
+
 def _check(code: int, what: str) -> None:
+    global LAUNCHES
+    LAUNCHES += 1
     if code != 0:
         msg = lib().zi_last_error().decode("utf-8", "replace")
         raise KernelError(f"{what}: {msg} (code {code})")
