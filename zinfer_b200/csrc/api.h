@@ -26,6 +26,12 @@ int zi_qk_norm_rope_store(void* qkv, int dtype, int T, int row_stride, int nq, i
 int zi_gemm_simt(void* out, int out_dtype, const void* x, int x_dtype, const void* w, int w_dtype, int M, int N,
                  int K, int ldx, int ldw, int ldo, cudaStream_t stream);
 
+int zi_gemm_tcgen05_supported(const void* x, const void* w, int K, int ldx, int ldw);
+long long zi_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* plan);
+int zi_gemm_tcgen05(void* out, int out_dtype, const void* x, const void* w, int M, int N, int K, int ldx, int ldw,
+                    int ldo, float* workspace, long long workspace_bytes, int sm_count, cudaStream_t stream);
+int zi_gemm_tcgen05_status();
+
 int zi_paged_attention_tile_rows();
 int zi_paged_attention(void* out, int out_stride, const void* q, int q_stride, int dtype, const void* kcache,
                        const void* vcache, const int* block_tables, int bt_stride, const int* cu_q,

@@ -1,0 +1,403 @@
+// out[M,N] = x[M,K] * w[N,K]^T in bfloat16 on the 5th-generation tensor cores:
+// TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) fills a ring of shared
+// memory stages, one elected thread issues tcgen05.mma with the accumulator in
+// tensor memory, and four warps read it back with tcgen05.ld for the epilogue.
+//
+// Both operands are K-major, which is how activations [tokens, K] and weights
+// [out, K] already lie in memory.  The 128 lanes of the accumulator take rows of
+// the "A side", its columns rows of the "B side":
+//   * many tokens (prefill): A side = tokens, B side = weight rows;
+//   * few tokens (decode):   A side = weight rows, B side = tokens padded to 16..256,
+//     so a CTA streams a [128, K] slab of the weight at the rate TMA can bring it
+//     and no tensor-core work is wasted on padding rows.
+// Split-K over gridDim.z writes 32-bit partial sums to a workspace; a second kernel
+// adds them in a fixed order.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner and MMA
+// issuer, warps 2..5 = epilogue (warp w reads TMEM lanes 32*(w%4)..+31).
+// Every wait on an mbarrier is bounded; when it runs out the kernel records a code
+// in `status`, lets copies in flight land, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+constexpr int TILE_A = 128;        // accumulator lanes
+constexpr int BLOCK_K = 64;        // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int A_TILE_BYTES = TILE_A * BLOCK_K * 2;
+constexpr int THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_load16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows are
+// 128 bytes, groups of 8 rows are 1024 bytes apart (stride byte offset), descriptor
+// version 1 (sm_100), layout type 2 (SWIZZLE_128B).  Addresses are in 16-byte units.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  return (uint64_t)((addr & 0x3ffffu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor of kind::f16: D = f32 (bits 4-5 = 1), A and B = bf16 (bits
+// 7-9 and 10-12 = 1), both K-major (bits 15, 16 = 0), N >> 3 at bit 17, M >> 4 at bit 24.
+__device__ __forceinline__ uint32_t instr_desc_bf16(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// -------------------------------------------------------------------- the kernel
+// A side: a_rows x K through map_a (box 64 x 128).  B side: b_rows x K through map_b
+// (box 64 x BN).  Element (a, b) goes to out[a * sa + b * sb], or, with split-K, to
+// partial[(z * a_rows + a) * b_ld + b] as float.
+template <typename TO>
+__global__ void __launch_bounds__(THREADS)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    TO* __restrict__ out, float* __restrict__ partial, int a_rows, int b_rows, int k_blocks,
+                    int k_blocks_per_split, long long sa, long long sb, int BN, int stages, int tmem_cols,
+                    int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int stage_bytes = A_TILE_BYTES + BN * BLOCK_K * 2;
+  uint64_t* full = (uint64_t*)(smem + (size_t)stages * stage_bytes);
+  uint64_t* empty = full + stages;
+  uint64_t* accum_full = empty + stages;
+  uint32_t* tmem_slot = (uint32_t*)(accum_full + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int a_tile = blockIdx.x, b_tile = blockIdx.y, split = blockIdx.z;
+  const int kb0 = split * k_blocks_per_split;
+  const int kb1 = min(k_blocks, kb0 + k_blocks_per_split);
+  const int n_kb = kb1 - kb0;  // >= 1 by construction of the grid
+  bool failed = false;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(accum_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < n_kb; ++i) {
+        const int s = i % stages;
+        const uint32_t phase = (uint32_t)(i / stages) & 1u;
+        if (!mbar_wait(&empty[s], phase ^ 1u)) { failed = true; atomicExch(status, 1); break; }
+        uint8_t* a_dst = smem + (size_t)s * stage_bytes;
+        mbar_expect_tx(&full[s], (uint32_t)stage_bytes);
+        tma_load_2d(a_dst, &map_a, &full[s], (kb0 + i) * BLOCK_K, a_tile * TILE_A);
+        tma_load_2d(a_dst + A_TILE_BYTES, &map_b, &full[s], (kb0 + i) * BLOCK_K, b_tile * BN);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc_bf16(TILE_A, BN);
+      for (int i = 0; i < n_kb; ++i) {
+        const int s = i % stages;
+        const uint32_t phase = (uint32_t)(i / stages) & 1u;
+        if (!mbar_wait(&full[s], phase)) { failed = true; atomicExch(status, 2); break; }
+        tcgen05_fence_after();
+        const uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes);
+        const uint32_t b_addr = a_addr + A_TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+          tcgen05_mma_bf16(tmem_base, smem_desc_sw128(a_addr + k * UMMA_K * 2), smem_desc_sw128(b_addr + k * UMMA_K * 2),
+                           idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        tcgen05_commit(&empty[s]);  // frees the stage when these MMAs have read it
+      }
+      if (!failed) tcgen05_commit(accum_full);
+    }
+  } else {
+    const int quarter = warp & 3;  // the TMEM lanes this warp may read
+    if (!mbar_wait(accum_full, 0)) {
+      failed = true;
+      atomicExch(status, 3);
+    } else {
+      tcgen05_fence_after();
+      const int a = a_tile * TILE_A + quarter * 32 + lane;
+      const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16];
+        tmem_load16(lane_base + (uint32_t)c0, v);
+        const int b0 = b_tile * BN + c0;
+        if (a < a_rows) {
+          if (partial) {
+            float* p = partial + ((size_t)split * a_rows + a) * (size_t)b_rows + b0;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (b0 + j < b_rows) p[j] = v[j];
+          } else {
+            TO* o = out + (long long)a * sa + (long long)b0 * sb;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (b0 + j < b_rows) o[(long long)j * sb] = from_f32<TO>(v[j]);
+          }
+        }
+      }
+    }
+  }
+  if (failed) {
+    // let copies that may still be in flight land before shared memory is given up
+    for (int i = 0; i < 64; ++i) __nanosleep(10000);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)tmem_cols)
+                 : "memory");
+  }
+}
+
+// out[a * sa + b * sb] = sum over splits of partial[(z * a_rows + a) * b_rows + b], in order of z.
+template <typename TO>
+__global__ void splitk_reduce_kernel(TO* __restrict__ out, const float* __restrict__ partial, int a_rows, int b_rows,
+                                     int splits, long long sa, long long sb) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t total = (size_t)a_rows * b_rows;
+  if (idx >= total) return;
+  float acc = 0.f;
+  for (int z = 0; z < splits; ++z) acc += partial[(size_t)z * total + idx];
+  const int a = (int)(idx / b_rows), b = (int)(idx % b_rows);
+  out[(long long)a * sa + (long long)b * sb] = from_f32<TO>(acc);
+}
+
+// ------------------------------------------------------------------- tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  int rows, cols, ld, box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = (size_t)k.ptr;
+    for (int v : {k.rows, k.cols, k.ld, k.box_rows}) h = h * 1000003u ^ (size_t)v;
+    return h;
+  }
+};
+
+// A 2-D map over a row-major bf16 matrix [rows, cols] with row pitch ld elements,
+// box [box_rows, 64], 128-byte swizzle, zero fill out of bounds.
+bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int ld, int box_rows) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{ptr, rows, cols, ld, box_rows};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *map = it->second;
+    return true;
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *map);
+  return true;
+}
+
+int round_up_bn(int n) {
+  for (int bn : {16, 32, 64, 128, 256})
+    if (n <= bn) return bn;
+  return 256;
+}
+
+int* status_word() {
+  static int* word = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    if (cudaMalloc(&word, sizeof(int)) == cudaSuccess) cudaMemset(word, 0, sizeof(int));
+  });
+  return word;
+}
+
+}  // namespace
+
+// Whether the tensor-core kernel can take these operands: bfloat16, pointers aligned
+// to 16 bytes, row pitches that are multiples of 16 bytes (TMA's rules).
+extern "C" int zi_gemm_tcgen05_supported(const void* x, const void* w, int K, int ldx, int ldw) {
+  return ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) && (ldx % 8 == 0) && (ldw % 8 == 0) && K > 0 &&
+         encode_fn() != nullptr;
+}
+
+// Size in bytes of the split-K workspace this call needs (0 when it does not split).
+// `plan` receives {swap, BN, splits}.
+extern "C" long long zi_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* plan) {
+  const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
+  const int swap = M <= 64 ? 1 : 0;
+  const int a_rows = swap ? N : M, b_rows = swap ? M : N;
+  const int BN = swap ? round_up_bn(b_rows) : (b_rows >= 256 && M >= 256 ? 256 : 128 <= b_rows ? 128 : round_up_bn(b_rows));
+  const int tiles = ((a_rows + TILE_A - 1) / TILE_A) * ((b_rows + BN - 1) / BN);
+  int splits = 1;
+  if (swap) {
+    // few tokens: the weight is streamed once; use enough CTAs that every SM pulls from memory
+    const int target = 2 * sm_count;
+    while (tiles * splits < target && splits < 16 && k_blocks / (splits * 2) >= 8) splits *= 2;
+  }
+  plan[0] = swap;
+  plan[1] = BN;
+  plan[2] = splits;
+  return splits > 1 ? (long long)splits * M * N * (long long)sizeof(float) : 0;
+}
+
+extern "C" int zi_gemm_tcgen05(void* out, int out_dtype, const void* x, const void* w, int M, int N, int K, int ldx,
+                               int ldw, int ldo, float* workspace, long long workspace_bytes, int sm_count,
+                               cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (!zi_gemm_tcgen05_supported(x, w, K, ldx, ldw))
+    return zi_refuse("gemm_tcgen05: operands must be 16-byte aligned bfloat16 with row pitches in multiples of 8");
+  int plan[3];
+  const long long need = zi_gemm_tcgen05_plan(M, N, K, sm_count, plan);
+  const int swap = plan[0], BN = plan[1], splits = plan[2];
+  if (need > workspace_bytes) return zi_refuse("gemm_tcgen05: split-K needs %lld workspace bytes, got %lld", need, workspace_bytes);
+  const int a_rows = swap ? N : M, b_rows = swap ? M : N;
+  const void* a_ptr = swap ? w : x;
+  const void* b_ptr = swap ? x : w;
+  const int lda = swap ? ldw : ldx, ldb = swap ? ldx : ldw;
+  CUtensorMap map_a, map_b;
+  if (!make_map(&map_a, a_ptr, a_rows, K, lda, TILE_A) || !make_map(&map_b, b_ptr, b_rows, K, ldb, BN))
+    return zi_refuse("gemm_tcgen05: cuTensorMapEncodeTiled failed");
+  int* status = status_word();
+  if (!status) return zi_refuse("gemm_tcgen05: cannot allocate the status word");
+
+  const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
+  const int kbps = (k_blocks + splits - 1) / splits;
+  const int real_splits = (k_blocks + kbps - 1) / kbps;
+  const int stage_bytes = A_TILE_BYTES + BN * BLOCK_K * 2;
+  int stages = swap ? 6 : (BN >= 256 ? 4 : 6);
+  if (stages > kbps) stages = kbps < 2 ? 2 : kbps;
+  const size_t smem = 1024 + (size_t)stages * stage_bytes + (2 * stages + 1) * sizeof(uint64_t) + 16;
+  const int tmem_cols = BN < 32 ? 32 : BN;
+  const long long sa = swap ? 1 : ldo, sb = swap ? ldo : 1;
+  dim3 grid((a_rows + TILE_A - 1) / TILE_A, (b_rows + BN - 1) / BN, real_splits);
+  float* partial = real_splits > 1 ? workspace : nullptr;
+
+  ZI_DISPATCH_DTYPE(out_dtype, TO, {
+    auto kern = gemm_tcgen05_kernel<TO>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return zi_refuse("gemm_tcgen05: cannot get %zu bytes of shared memory", smem);
+    kern<<<grid, THREADS, smem, stream>>>(map_a, map_b, (TO*)out, partial, a_rows, b_rows, k_blocks, kbps, sa, sb, BN,
+                                          stages, tmem_cols, status);
+    int rc = zi_check_launch("gemm_tcgen05");
+    if (rc) return rc;
+    if (partial) {
+      const size_t total = (size_t)a_rows * b_rows;
+      splitk_reduce_kernel<TO><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((TO*)out, partial, a_rows, b_rows,
+                                                                                  real_splits, sa, sb);
+      rc = zi_check_launch("splitk_reduce");
+      if (rc) return rc;
+    }
+  });
+  return 0;
+}
+
+// Reads and clears the status word of the tensor-core kernels (synchronises the
+// device).  0 = every bounded wait completed.
+extern "C" int zi_gemm_tcgen05_status() {
+  int* status = status_word();
+  if (!status) return -1;
+  int host = 0;
+  if (cudaMemcpy(&host, status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -2;
+  if (host != 0) cudaMemset(status, 0, sizeof(int));
+  return host;
+}

@@ -9,6 +9,7 @@ tensors that are not on a CUDA device, these functions fail.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -33,7 +34,14 @@ def lib() -> ctypes.CDLL:
         except OSError as e:
             raise KernelError(f"cannot load the kernel library {path}: {e}") from None
         _LIB.zi_last_error.restype = ctypes.c_char_p
+        _LIB.zi_gemm_tcgen05_plan.restype = ctypes.c_longlong
     return _LIB
+
+
+def kernel_status() -> int:
+    """Reads and clears the status word of the tensor-core kernels (synchronises).
+    0: every bounded wait inside them completed; else the code of the wait that ran out."""
+    return int(lib().zi_gemm_tcgen05_status())
 
 
 def library_file() -> str:
@@ -170,9 +178,24 @@ def qk_norm_rope_store(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, hea
 
 
 # ------------------------------------------------------------------------ matrices
+_SM_COUNT: dict[int, int] = {}
+GEMM_BACKEND = os.environ.get("ZINFER_B200_GEMM", "auto")   # auto | simt  (simt: CUDA cores only, for comparisons)
+
+
+def _sm_count(device: torch.device) -> int:
+    idx = device.index or 0
+    if idx not in _SM_COUNT:
+        _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _SM_COUNT[idx]
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
            out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``x [M, K] @ weight [N, K]^T`` with 32-bit accumulation."""
+    """``x [M, K] @ weight [N, K]^T`` with 32-bit accumulation.
+
+    bfloat16 operands that meet TMA's alignment rules go to the tcgen05 kernel; float32
+    operands (the true 32-bit path), mixed types and unaligned shapes go to the
+    CUDA-core kernel."""
     M, K = x.shape
     N, K2 = weight.shape
     _need(K == K2, f"linear: x has {K} columns, weight has {K2}")
@@ -180,6 +203,15 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
     _need(out.stride(1) == 1, "linear: output rows must be dense")
+    if (GEMM_BACKEND != "simt" and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and M > 0
+            and lib().zi_gemm_tcgen05_supported(_ptr(x), _ptr(weight), K, x.stride(0), weight.stride(0))):
+        plan = (ctypes.c_int * 3)()
+        sms = _sm_count(x.device)
+        need = lib().zi_gemm_tcgen05_plan(M, N, K, sms, plan)
+        ws = torch.empty((need // 4,), dtype=torch.float32, device=x.device) if need else None
+        _check(lib().zi_gemm_tcgen05(_ptr(out), _tag(out), _ptr(x), _ptr(weight), M, N, K, x.stride(0), weight.stride(0),
+                                     out.stride(0), _ptr(ws), ctypes.c_longlong(need), sms, _stream()), "linear (tcgen05)")
+        return out
     _check(lib().zi_gemm_simt(_ptr(out), _tag(out), _ptr(x), _tag(x), _ptr(weight), _tag(weight), M, N, K,
                               x.stride(0), weight.stride(0), out.stride(0), _stream()), "linear")
     return out
