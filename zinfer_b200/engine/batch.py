@@ -52,24 +52,38 @@ class StepContext:
     h2d_bytes: int = 0              # size of the one host->device copy that brought these arrays
 
 
-def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile_rows: int,
-               pin: bool = True) -> StepContext:
-    """Flattens ``entries``; their pages must already be reserved in ``manager``."""
-    n = len(entries)
+def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile_rows: int, pin: bool = True,
+               static: Optional["StaticStepBuffers"] = None) -> StepContext:
+    """Flattens ``entries``; their pages must already be reserved in ``manager``.
+
+    With ``static`` (decode steps replayed from a CUDA graph) the arrays have the
+    fixed capacity and addresses of those buffers: every entry brings one token, the
+    batch is padded to ``static.batch`` with requests of one key in no page whose
+    key/value write is skipped (slot -1), and block tables have ``static.width``
+    columns."""
+    n_real = len(entries)
     ps = manager.page_size
     q_lens = [len(e.tokens) for e in entries]
     ctx_lens = [manager.length(e.request_id) for e in entries]
-    T = int(sum(q_lens))
-    cu = np.zeros(n + 1, dtype=np.int64)
-    np.cumsum(q_lens, out=cu[1:])
-    n_tiles_per = [-(-q // tile_rows) for q in q_lens]
-    n_tiles = int(sum(n_tiles_per))
-    rows = [int(cu[i]) + int(w) for i, e in enumerate(entries) for w in e.want]
-    R = len(rows)
     n_groups = len(manager.groups)
-    widths = []
-    for gi in range(n_groups):
-        widths.append(max(1, max(len(manager.block_table(e.request_id, gi)) for e in entries)))
+    if static is not None:
+        assert all(q == 1 for q in q_lens) and n_real <= static.batch
+        n = static.batch
+        widths = [static.width] * n_groups
+    else:
+        n = n_real
+        widths = [max(1, max(len(manager.block_table(e.request_id, gi)) for e in entries)) for gi in range(n_groups)]
+    pad = n - n_real
+    T = int(sum(q_lens)) + pad
+    cu = np.zeros(n + 1, dtype=np.int64)
+    np.cumsum(q_lens + [1] * pad, out=cu[1:])
+    n_tiles_per = [-(-q // tile_rows) for q in q_lens] + [1] * pad
+    n_tiles = int(sum(n_tiles_per))
+    if static is not None:
+        rows = list(range(n))
+    else:
+        rows = [int(cu[i]) + int(w) for i, e in enumerate(entries) for w in e.want]
+    R = len(rows)
 
     # layout of the packed buffer
     sizes = [("token_ids", T), ("positions", T), ("cu_q", n + 1), ("kv_lens", n), ("state_slots", n),
@@ -80,7 +94,10 @@ def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile
     for name, sz in sizes:
         offs[name] = (total, sz)
         total += -(-sz // 4) * 4   # keep every array 16-byte aligned
-    host = torch.empty(max(total, 4), dtype=torch.int32, pin_memory=pin and torch.cuda.is_available())
+    if static is not None:
+        host = static.host_buffer(total)
+    else:
+        host = torch.empty(max(total, 4), dtype=torch.int32, pin_memory=pin and torch.cuda.is_available())
     buf = host.numpy()
 
     def arr(name):
@@ -89,18 +106,26 @@ def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile
 
     tok, pos = arr("token_ids"), arr("positions")
     tseq, tq0 = arr("tile_seq"), arr("tile_q0")
+    tok[:] = 0
+    pos[:] = 0
     ti = 0
-    for i, e in enumerate(entries):
+    for i in range(n):
         a, b = int(cu[i]), int(cu[i + 1])
-        tok[a:b] = np.asarray(e.tokens, dtype=np.int64)
-        pos[a:b] = np.arange(ctx_lens[i], ctx_lens[i] + q_lens[i])
+        if i < n_real:
+            tok[a:b] = np.asarray(entries[i].tokens, dtype=np.int64)
+            pos[a:b] = np.arange(ctx_lens[i], ctx_lens[i] + q_lens[i])
         for t in range(n_tiles_per[i]):
             tseq[ti] = i
             tq0[ti] = t * tile_rows
             ti += 1
     arr("cu_q")[:] = cu
-    arr("kv_lens")[:] = np.asarray(ctx_lens) + np.asarray(q_lens) if n else 0
-    arr("state_slots")[:] = [manager.requests[e.request_id].state_slot for e in entries]
+    kv = arr("kv_lens")
+    kv[:] = 1
+    if n_real:
+        kv[:n_real] = np.asarray(ctx_lens) + np.asarray(q_lens)
+    ss = arr("state_slots")
+    ss[:] = 0
+    ss[:n_real] = [manager.requests[e.request_id].state_slot for e in entries]
     if R:
         arr("logit_rows")[:] = rows
     for gi in range(n_groups):
@@ -108,6 +133,7 @@ def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile
         bt = arr(f"bt{gi}").reshape(n, W)
         bt[:] = -1
         sl = arr(f"slots{gi}")
+        sl[:] = -1
         for i, e in enumerate(entries):
             table = np.asarray(manager.block_table(e.request_id, gi), dtype=np.int64)
             bt[i, :len(table)] = table
@@ -118,7 +144,12 @@ def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile
                 raise RuntimeError(f"request {e.request_id!r}: a token would be written to a page already given back")
             sl[a:b] = pages * ps + p % ps
 
-    dev = host.to(device, non_blocking=True)
+    if static is not None:
+        dev = static.device_buffer(total)
+        dev.copy_(host[:total], non_blocking=True)
+        static.mark_copied()
+    else:
+        dev = host.to(device, non_blocking=True)
 
     def view(name):
         o, s = offs[name]
@@ -130,4 +161,38 @@ def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile
         kv_lens=view("kv_lens"), state_slots=view("state_slots"), tile_seq=view("tile_seq"), tile_q0=view("tile_q0"),
         logit_rows=view("logit_rows") if R else None, kv_groups=groups, q_lens=q_lens, ctx_lens=ctx_lens,
         max_q_len=max(q_lens, default=0), max_kv_len=max((c + q for c, q in zip(ctx_lens, q_lens)), default=0),
-        all_decode=all(q == 1 for q in q_lens), h2d_bytes=int(host.numel()) * 4)
+        all_decode=all(q == 1 for q in q_lens), h2d_bytes=int(total) * 4)
+
+
+class StaticStepBuffers:
+    """Pinned host and device buffers of fixed address for the decode steps of one
+    batch-size bucket, so that a captured CUDA graph finds every step's arrays at the
+    same place."""
+
+    def __init__(self, batch: int, width: int, device):
+        self.batch = batch
+        self.width = width
+        self.device = device
+        self._host = None
+        self._dev = None
+        self._copied = None
+
+    def host_buffer(self, total: int) -> torch.Tensor:
+        """The pinned staging buffer, safe to overwrite: the copy of the previous
+        step's arrays to the device has completed."""
+        if self._host is None:
+            self._host = torch.zeros(total, dtype=torch.int32, pin_memory=torch.cuda.is_available())
+            self._copied = torch.cuda.Event() if torch.cuda.is_available() else None
+        elif self._copied is not None:
+            self._copied.synchronize()
+        assert self._host.numel() == total, "the layout of a bucket's arrays must not change"
+        return self._host
+
+    def mark_copied(self) -> None:
+        if self._copied is not None:
+            self._copied.record()
+
+    def device_buffer(self, total: int) -> torch.Tensor:
+        if self._dev is None:
+            self._dev = torch.zeros(total, dtype=torch.int32, device=self.device)
+        return self._dev

@@ -35,7 +35,7 @@ def _require_cuda(device: torch.device) -> None:
 
 class ModelRunner:
     def __init__(self, model: DecoderModel, page_size: int = 16, num_pages: Optional[int] = None,
-                 max_tokens: Optional[int] = None, max_requests: int = 64):
+                 max_tokens: Optional[int] = None, max_requests: int = 64, cuda_graphs: bool = True):
         """``max_tokens`` sizes each group's pool for that many cached tokens
         (rounded up to whole pages); ``num_pages`` gives the page count directly."""
         _require_cuda(model.device)
@@ -53,6 +53,12 @@ class ModelRunner:
         self.tile_rows = ops.attention_tile_rows()
         self.steps_run = 0
         self.last_h2d_bytes = 0
+        # decode steps are replayed from CUDA graphs when every mixer can be captured
+        self.graphs = None
+        if cuda_graphs and model.device.type == "cuda" and all(
+                getattr(b.mixer, "graph_safe", False) for b in model.blocks):
+            from .graphs import DecodeGraphs
+            self.graphs = DecodeGraphs(self, max_requests)
 
     # ------------------------------------------------------------- construction
     @classmethod
@@ -77,6 +83,10 @@ class ModelRunner:
         runner = cls(model, **kw)
         runner.config = config
         return runner
+
+    @property
+    def graph_launches(self) -> int:
+        return self.graphs.launches if self.graphs is not None else 0
 
     # ------------------------------------------------------------------ requests
     def has_request(self, request_id: Hashable) -> bool:
@@ -146,9 +156,19 @@ class ModelRunner:
             return None
         self.validate(entries)
         self.reserve(entries)
-        ctx = build_step(self.manager, entries, self.device, self.tile_rows)
-        self.last_h2d_bytes = ctx.h2d_bytes
-        logits = self.model.forward(ctx)
+        if self.graphs is not None and self.graphs.eligible(entries):
+            all_rows = self.graphs.run(entries)
+            wanted = [i for i, e in enumerate(entries) if len(e.want)]
+            if not wanted:
+                logits = None
+            elif len(wanted) == len(entries):
+                logits = all_rows[:len(entries)]
+            else:
+                logits = all_rows[torch.tensor(wanted, device=self.device)]
+        else:
+            ctx = build_step(self.manager, entries, self.device, self.tile_rows)
+            self.last_h2d_bytes = ctx.h2d_bytes
+            logits = self.model.forward(ctx)
         for e in entries:
             self.manager.commit(e.request_id, len(e.tokens))
         self.steps_run += 1

@@ -19,6 +19,8 @@ from .base import KVCacheNeed, Mixer, TensorSpec, make_part
 
 
 class GQAttention(Mixer):
+    graph_safe = True   # forward() only launches kernels on device arrays: a decode step can be captured
+
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
         self.hidden = int(params["hidden_size"])

@@ -94,6 +94,11 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True if forward() only launches kernels that read the step's device arrays (no
+    # host-side loop over requests, no synchronisation): decode steps of a model whose
+    # mixers all say so are replayed from CUDA graphs.
+    graph_safe = False
+
     def cache_need(self):
         return None
 
