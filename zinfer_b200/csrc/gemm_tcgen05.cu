@@ -24,6 +24,7 @@
 
 #include "api.h"
 #include "common.cuh"
+#include "gemm_static_scratch.h"
 
 namespace {
 
@@ -400,4 +401,120 @@ extern "C" int zi_gemm_tcgen05_status() {
   if (cudaMemcpy(&host, status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -2;
   if (host != 0) cudaMemset(status, 0, sizeof(int));
   return host;
+}
+
+// ------------------------------------------------------------------------------
+// The same product for callers that cannot allocate device memory (declared in
+// gemm_static_scratch.h).  Split-K partial sums go to a fixed array in the
+// library's own device image instead of a caller's workspace.
+namespace {
+
+// 4 Mi floats = 16 MiB: every GPU that loads this library holds them until it exits.
+constexpr long long STATIC_SCRATCH_FLOATS = 4ll * 1024 * 1024;
+static __device__ __align__(256) float g_static_scratch[STATIC_SCRATCH_FLOATS];
+static __device__ __align__(256) int g_static_status;
+
+constexpr int MAX_DEVICES = 64;
+struct StaticScratch {
+  float* scratch = nullptr;  // device address of g_static_scratch on that device
+  int* status = nullptr;     // device address of g_static_status on that device
+};
+
+// In host code `g_static_scratch` is only a handle for the runtime, not an address
+// the GPU can use: the device address is asked for once per device, with that
+// device current.
+bool static_scratch_for_current_device(StaticScratch* out, int* device_out) {
+  static std::mutex mu;
+  static StaticScratch table[MAX_DEVICES];
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return false;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!table[dev].scratch) {
+    void* p = nullptr;
+    void* s = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) return false;
+    if (cudaGetSymbolAddress(&s, g_static_status) != cudaSuccess || !s) return false;
+    table[dev].scratch = (float*)p;
+    table[dev].status = (int*)s;
+  }
+  *out = table[dev];
+  *device_out = dev;
+  return true;
+}
+
+// The tensor map of make_map(), encoded straight into `map` (no cache, no host allocation).
+bool encode_map_direct(CUtensorMap* map, const void* ptr, int rows, int cols, int ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+extern "C" long long zi_gemm_static_scratch_capacity_bytes() { return STATIC_SCRATCH_FLOATS * (long long)sizeof(float); }
+
+extern "C" int zi_gemm_tcgen05_static_scratch(void* out, int out_dtype, const void* x, const void* w, int M, int N,
+                                              int K, int ldx, int ldw, int ldo, int sm_count, int* wait_status,
+                                              cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (!zi_gemm_tcgen05_supported(x, w, K, ldx, ldw))
+    return zi_refuse("gemm_static_scratch: operands must be 16-byte aligned bfloat16 with row pitches in multiples of 8");
+  int plan[3];
+  const long long need = zi_gemm_tcgen05_plan(M, N, K, sm_count, plan);
+  if (need > zi_gemm_static_scratch_capacity_bytes())
+    return zi_refuse("gemm_static_scratch: this product splits K and needs %lld bytes of scratch; the built-in scratch "
+                     "holds %lld (use zi_gemm_tcgen05 with a workspace of your own)",
+                     need, zi_gemm_static_scratch_capacity_bytes());
+  StaticScratch ss;
+  int dev = -1;
+  if (!static_scratch_for_current_device(&ss, &dev))
+    return zi_refuse("gemm_static_scratch: cudaGetSymbolAddress of the built-in scratch failed on the current device");
+  const int swap = plan[0], BN = plan[1], splits = plan[2];
+  const int a_rows = swap ? N : M, b_rows = swap ? M : N;
+  const int lda = swap ? ldw : ldx, ldb = swap ? ldx : ldw;
+  CUtensorMap map_a, map_b;
+  if (!encode_map_direct(&map_a, swap ? w : x, a_rows, K, lda, TILE_A) ||
+      !encode_map_direct(&map_b, swap ? x : w, b_rows, K, ldb, BN))
+    return zi_refuse("gemm_static_scratch: cuTensorMapEncodeTiled failed");
+  int* status = wait_status ? wait_status : ss.status;
+  // the status word must start at zero; the partial sums need no clearing, every
+  // element that the second kernel reads is written by the first
+  cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int), stream);
+  if (e != cudaSuccess) return zi_refuse("gemm_static_scratch: cannot clear the status word: %s", cudaGetErrorString(e));
+
+  const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
+  const int kbps = (k_blocks + splits - 1) / splits;
+  const int real_splits = (k_blocks + kbps - 1) / kbps;
+  const int stage_bytes = A_TILE_BYTES + BN * BLOCK_K * 2;
+  int stages = swap ? 6 : (BN >= 256 ? 4 : 6);
+  if (stages > kbps) stages = kbps < 2 ? 2 : kbps;
+  const size_t smem = 1024 + (size_t)stages * stage_bytes + (2 * stages + 1) * sizeof(uint64_t) + 16;
+  const int tmem_cols = BN < 32 ? 32 : BN;
+  const long long sa = swap ? 1 : ldo, sb = swap ? ldo : 1;
+  dim3 grid((a_rows + TILE_A - 1) / TILE_A, (b_rows + BN - 1) / BN, real_splits);
+  float* partial = real_splits > 1 ? ss.scratch : nullptr;
+
+  ZI_DISPATCH_DTYPE(out_dtype, TO, {
+    auto kern = gemm_tcgen05_kernel<TO>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return zi_refuse("gemm_static_scratch: cannot get %zu bytes of shared memory", smem);
+    kern<<<grid, THREADS, smem, stream>>>(map_a, map_b, (TO*)out, partial, a_rows, b_rows, k_blocks, kbps, sa, sb, BN,
+                                          stages, tmem_cols, status);
+    int rc = zi_check_launch("gemm_static_scratch");
+    if (rc) return rc;
+    if (partial) {
+      const size_t total = (size_t)a_rows * b_rows;
+      splitk_reduce_kernel<TO><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((TO*)out, partial, a_rows, b_rows,
+                                                                                  real_splits, sa, sb);
+      rc = zi_check_launch("gemm_static_scratch (reduce)");
+      if (rc) return rc;
+    }
+  });
+  return 0;
 }
