@@ -85,6 +85,10 @@ def attention_tile_rows():
     return 16
 
 
+def attention_prefill_tile_rows():
+    return 128
+
+
 def paged_attention(q, k_cache, v_cache, block_tables, cu_q, kv_lens, tile_seq, tile_q0, num_heads, num_kv_heads,
                     head_dim, page_size, window, scale, out=None):
     T = q.shape[0]
@@ -114,3 +118,8 @@ def paged_attention(q, k_cache, v_cache, block_tables, cu_q, kv_lens, tile_seq, 
 
 def argmax(logits, out=None):
     return torch.argmax(logits, dim=-1).to(torch.int32)
+
+
+def attention(q, k_cache, v_cache, block_tables, step, num_heads, num_kv_heads, head_dim, page_size, window, scale):
+    return paged_attention(q, k_cache, v_cache, block_tables, step.cu_q, step.kv_lens, step.tile_seq, step.tile_q0,
+                           num_heads, num_kv_heads, head_dim, page_size, window, scale)

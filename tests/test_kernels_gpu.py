@@ -246,6 +246,76 @@ def test_paged_attention_ignores_stale_page_contents():
     assert torch.equal(clean, dirty)
 
 
+def _as_step(args, q_lens, ctx_lens):
+    """The request arrays the dispatching `ops.attention` reads from a StepContext."""
+    from types import SimpleNamespace
+    pf = ops().attention_prefill_tile_rows()
+    dev = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    dec = [i for i, ql in enumerate(q_lens) if ql == 1]
+    tiles = [(i, t * pf) for i, ql in enumerate(q_lens) if ql > 1 for t in range(-(-ql // pf))]
+    return SimpleNamespace(cu_q=args["cu_q"], kv_lens=args["kv_lens"], tile_seq=args["tile_seq"], tile_q0=args["tile_q0"],
+                           dec_seq=dev(dec), pf_tile_seq=dev([i for i, _ in tiles]), pf_tile_q0=dev([t for _, t in tiles]),
+                           n_dec=len(dec), n_pf_tiles=len(tiles), max_kv_len=max(c + q for c, q in zip(ctx_lens, q_lens)))
+
+
+@pytest.mark.parametrize("nq,nkv,d,page,window", [
+    (8, 2, 128, 16, None), (32, 8, 128, 16, None), (6, 1, 64, 8, None), (5, 5, 64, 32, None), (4, 2, 128, 16, 100),
+    (16, 1, 128, 16, None), (6, 2, 64, 4, 37), (2, 1, 256, 16, None), (48, 3, 128, 16, None)])
+@pytest.mark.parametrize("q_lens,ctx_lens", [
+    ([1, 1, 1, 1], [0, 63, 64, 700]),                  # decode only, lengths around a tile's edge
+    ([300, 17], [0, 130]),                             # prompt portions only, one across several query tiles
+    ([1, 37, 2, 1, 129, 1], [70, 0, 15, 0, 48, 255]),  # mixed
+])
+def test_tensor_core_attention(nq, nkv, d, page, window, q_lens, ctx_lens):
+    """The bfloat16 tensor-core kernels (prefill tiles and split-key decode) through the
+    dispatcher, against the plain reference."""
+    args = _paged_case(torch.bfloat16, nq, nkv, d, page, q_lens, ctx_lens, seed=2)
+    step = _as_step(args, q_lens, ctx_lens)
+    scale = float(1 / np.sqrt(d))
+    got = ops().attention(args["q"], args["k_cache"], args["v_cache"], args["block_tables"], step, nq, nkv, d, page,
+                          window, scale)
+    want = ref.paged_attention(window=window, scale=scale, **args)
+    torch.testing.assert_close(got.float(), want.float(), rtol=1.6e-2, atol=1.5e-2)
+    # every split count gives the same answer up to rounding
+    for forced in (1, 3, 32):
+        step.max_kv_len = 64 * forced
+        again = ops().attention(args["q"], args["k_cache"], args["v_cache"], args["block_tables"], step, nq, nkv, d,
+                                page, window, scale)
+        torch.testing.assert_close(again.float(), want.float(), rtol=1.6e-2, atol=1.5e-2)
+
+
+def test_tensor_core_attention_finds_one_far_key_and_ignores_stale_pages():
+    nq, nkv, d, page = 8, 2, 128, 16
+    q_lens, ctx_lens = [1, 200, 1], [900, 100, 33]
+    args = _paged_case(torch.bfloat16, nq, nkv, d, page, q_lens, ctx_lens, seed=5)
+    used = set(int(p) for p in args["block_tables"].flatten().tolist() if p >= 0)
+    for pg in range(args["k_cache"].shape[0]):
+        if pg not in used:
+            args["k_cache"][pg] = 300.0
+            args["v_cache"][pg] = -300.0
+    last = int(args["block_tables"][2, 33 // page])            # request 2 holds 34 keys: offsets 2.. of its last page are stale
+    args["k_cache"][last, :, 2:, :] = 300.0
+    args["v_cache"][last, :, 2:, :] = -300.0
+    far = {0: 123, 1: 17, 2: 5}
+    for seq, pos in far.items():
+        pg = int(args["block_tables"][seq, pos // page])
+        args["k_cache"][pg, :, pos % page, :] = 0
+        args["k_cache"][pg, :, pos % page, 0] = 40.0
+    T = sum(q_lens)
+    q = torch.zeros(T, nq * d, dtype=torch.bfloat16, device=DEV)
+    q.view(T, nq, d)[:, :, 0] = 40.0
+    args["q"] = q
+    step = _as_step(args, q_lens, ctx_lens)
+    got = ops().attention(q, args["k_cache"], args["v_cache"], args["block_tables"], step, nq, nkv, d, page, None,
+                          float(1 / np.sqrt(d))).float().view(T, nq, d)
+    seq_of = [0] + [1] * 200 + [2]
+    for t in (0, 1, 100, 200, 201):
+        seq = seq_of[t]
+        pg = int(args["block_tables"][seq, far[seq] // page])
+        for h in range(nq):
+            torch.testing.assert_close(got[t, h], args["v_cache"][pg, h // 4, far[seq] % page].float(), rtol=2e-2, atol=3e-2)
+
+
 def test_attention_refuses_what_it_cannot_do():
     o = ops()
     args = _paged_case(torch.float32, 2, 1, 272, 16, [1], [3])

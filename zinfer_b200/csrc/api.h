@@ -38,6 +38,18 @@ int zi_paged_attention(void* out, int out_stride, const void* q, int q_stride, i
                        const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv,
                        int d, int page_size, int window, float scale, cudaStream_t stream);
 
+int zi_attention_prefill_tile_rows();
+int zi_attention_mma_supported(int nq, int nkv, int d, int decode);
+int zi_attention_prefill_mma(void* out, int out_stride, const void* q, int q_stride, const void* kcache,
+                             const void* vcache, const int* block_tables, int bt_stride, const int* cu_q,
+                             const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv,
+                             int d, int page_size, int window, float scale, cudaStream_t stream);
+long long zi_attention_decode_workspace_floats(int n_dec, int nq, int nkv, int d, int splits);
+int zi_attention_decode_mma(void* out, int out_stride, float* workspace, const void* q, int q_stride,
+                            const void* kcache, const void* vcache, const int* block_tables, int bt_stride,
+                            const int* cu_q, const int* kv_lens, const int* dec_seq, int n_dec, int nq, int nkv, int d,
+                            int page_size, int window, float scale, int splits, cudaStream_t stream);
+
 int zi_argmax(int* out, const float* logits, int R, int V, int ld, cudaStream_t stream);
 int zi_sample(int* out, const float* logits, int R, int V, int ld, const float* temperature, const int* top_k,
               const float* top_p, const float* min_p, const float* rep, const float* pres, const float* freq,

@@ -1,0 +1,533 @@
+// bfloat16 attention over the paged cache on the tensor cores (mma.sync m16n8k16,
+// 32-bit accumulation, online softmax in 32-bit), for head sizes 64 and 128
+// (decode also 256).  Two kernels share the tile code:
+//
+//  * prefill: a CTA takes 128 query tokens of one request and one query head; its
+//    8 warps own 16 query rows each and walk the keys in tiles of 64, double-buffered
+//    with cp.async.  Causal and window masks are applied only on tiles that need them.
+//  * decode: a CTA takes one request's single query token, one kv head (all the
+//    query heads of its group are the 16 rows of the MMA) and one split of the keys;
+//    its 4 warps each stream their own 16 keys per tile through a private cp.async
+//    ring (no block-wide barrier in the loop) and merge at the end.  With more than
+//    one split, partial (max, sum, output) go to a workspace and a second kernel
+//    combines them in split order.
+//
+// Keys and values lie in pages [page][kv head][offset][d]; shared-memory tiles are
+// [key][d] with the 16-byte chunks of a row XOR-swizzled by (key & 7) so that
+// ldmatrix reads are free of bank conflicts.  Keys outside the request (beyond its
+// length, in pages it does not hold) are zero-filled and masked.
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are zero-filled, nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// Byte offset of 16-byte chunk `c` of row `r` in a swizzled [rows][D] bf16 tile.
+template <int D> __device__ __forceinline__ uint32_t swz(int r, int c) {
+  return (uint32_t)(r * D * 2 + ((c ^ (r & 7)) << 4));
+}
+
+// S (16 x 16 keys) += Q (16 x D) * K^T for the 16 keys at rows key0.. of tile `ks`.
+// qf: the warp's Q fragments, [D/16][4].  s: two n-tiles of 8 keys.
+template <int D>
+__device__ __forceinline__ void qk_16keys(float (&s)[2][4], const uint32_t (&qf)[D / 16][4], uint32_t ks_addr,
+                                          int key0, int lane) {
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    uint32_t b[4];
+    const int m = lane >> 3;
+    ldmatrix_x4(b, ks_addr + swz<D>(key0 + (m >> 1) * 8 + (lane & 7), kk * 2 + (m & 1)));
+    mma_bf16(s[0], qf[kk], b[0], b[1]);
+    mma_bf16(s[1], qf[kk], b[2], b[3]);
+  }
+}
+// O (16 x D) += P (16 x 16 keys) * V for the 16 keys at rows key0.. of tile `vs`.
+template <int D>
+__device__ __forceinline__ void pv_16keys(float (&o)[D / 8][4], const uint32_t (&pf)[4], uint32_t vs_addr, int key0,
+                                          int lane) {
+#pragma unroll
+  for (int np = 0; np < D / 16; ++np) {
+    uint32_t b[4];
+    const int m = lane >> 3;
+    ldmatrix_x4_trans(b, vs_addr + swz<D>(key0 + (m & 1) * 8 + (lane & 7), np * 2 + (m >> 1)));
+    mma_bf16(o[2 * np], pf, b[0], b[1]);
+    mma_bf16(o[2 * np + 1], pf, b[2], b[3]);
+  }
+}
+
+// One step of the online softmax for the two rows a thread holds (lane/4 and lane/4+8)
+// over `NT` n-tiles of 8 keys; s holds scores already scaled to the exp2 domain, with
+// masked entries at -inf.  Rescales o, updates m and l (l is per thread; rows are
+// summed across the 4 lanes of a quad at the end), and leaves P in s.
+template <int NT, int ON>
+__device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[ON][4], float (&m)[2], float (&l)[2]) {
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    float mx = -INFINITY;
+#pragma unroll
+    for (int t = 0; t < NT; ++t) mx = fmaxf(mx, fmaxf(s[t][2 * i], s[t][2 * i + 1]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m[i], mx);
+    const float m_use = m_new == -INFINITY ? 0.f : m_new;
+    const float alpha = exp2f(m[i] - m_use);
+    float sum = 0.f;
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      s[t][2 * i] = exp2f(s[t][2 * i] - m_use);
+      s[t][2 * i + 1] = exp2f(s[t][2 * i + 1] - m_use);
+      sum += s[t][2 * i] + s[t][2 * i + 1];
+    }
+    l[i] = l[i] * alpha + sum;
+    m[i] = m_new;
+#pragma unroll
+    for (int t = 0; t < ON; ++t) {
+      o[t][2 * i] *= alpha;
+      o[t][2 * i + 1] *= alpha;
+    }
+  }
+}
+
+// Copies `n_keys` keys starting at position `key_pos0` of one kv head into a swizzled
+// tile at rows row0.., for both K and V, 16 bytes per cp.async.  `tid`/`nthreads`
+// enumerate the copying threads.  Keys outside [kv_lo, kv_hi) or in no page are zero.
+template <int D>
+__device__ __forceinline__ void load_kv_rows(uint8_t* ks, uint8_t* vs, int row0, int n_keys, int key_pos0, int kv_lo,
+                                             int kv_hi, const bf16* __restrict__ kcache,
+                                             const bf16* __restrict__ vcache, const int* __restrict__ bt, int nkv,
+                                             int kvh, int page_size, int tid, int nthreads) {
+  constexpr int CH = D / 8;
+  for (int e = tid; e < n_keys * CH; e += nthreads) {
+    const int r = e / CH, c = e % CH;
+    const int j = key_pos0 + r;
+    bool valid = j >= kv_lo && j < kv_hi;
+    size_t off = 0;
+    if (valid) {
+      const int page = bt[j / page_size];
+      valid = page >= 0;
+      if (valid) off = (((size_t)page * nkv + kvh) * page_size + (j % page_size)) * D + c * 8;
+    }
+    const uint32_t so = swz<D>(row0 + r, c);
+    cp_async16(ks + so, kcache + off, valid);
+    cp_async16(vs + so, vcache + off, valid);
+  }
+}
+
+// =============================================================================== prefill
+constexpr int PF_BQ = 128, PF_BK = 64, PF_THREADS = 256;
+
+template <int D>
+__global__ void __launch_bounds__(PF_THREADS)
+attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restrict__ q, int q_stride,
+                        const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                        const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ cu_q,
+                        const int* __restrict__ kv_lens, const int* __restrict__ tile_seq,
+                        const int* __restrict__ tile_q0, int nq, int nkv, int page_size, int window,
+                        float scale_log2) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* qs = smem;                                   // [128][D]
+  uint8_t* kbuf = qs + PF_BQ * D * 2;                   // [2][64][D]
+  uint8_t* vbuf = kbuf + 2 * PF_BK * D * 2;             // [2][64][D]
+  constexpr int TILE_BYTES = PF_BK * D * 2;
+
+  const int seq = tile_seq[blockIdx.x], q0 = tile_q0[blockIdx.x];
+  const int h = blockIdx.y, kvh = h / (nq / nkv);
+  const int tok0 = cu_q[seq], qlen = cu_q[seq + 1] - tok0, kvlen = kv_lens[seq];
+  const int ctx = kvlen - qlen;
+  const int nqv = min(PF_BQ, qlen - q0);
+  if (nqv <= 0) return;
+  const int first_pos = ctx + q0, last_pos = first_pos + nqv - 1;
+  const int kv_lo = window > 0 ? max(0, first_pos - window + 1) : 0;
+  const int kv_hi = last_pos + 1;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int* bt = block_tables + (size_t)seq * bt_stride;
+
+  // Q tile -> shared memory (rows beyond the request's tokens are zero)
+  for (int e = tid; e < PF_BQ * (D / 8); e += PF_THREADS) {
+    const int r = e / (D / 8), c = e % (D / 8);
+    const bool valid = r < nqv;
+    const bf16* src = q + (size_t)(tok0 + q0 + (valid ? r : 0)) * q_stride + (size_t)h * D + c * 8;
+    cp_async16(qs + swz<D>(r, c), src, valid);
+  }
+  const int kt0 = (kv_lo / PF_BK) * PF_BK;
+  const int n_tiles = (kv_hi - kt0 + PF_BK - 1) / PF_BK;
+  load_kv_rows<D>(kbuf, vbuf, 0, PF_BK, kt0, kv_lo, kv_hi, kcache, vcache, bt, nkv, kvh, page_size, tid, PF_THREADS);
+  cp_async_commit();
+
+  uint32_t qf[D / 16][4];
+  float o[D / 8][4];
+#pragma unroll
+  for (int t = 0; t < D / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  const int row_lo = warp * 16 + (lane >> 2);           // this thread's rows: row_lo and row_lo + 8
+  const int warp_first_pos = first_pos + warp * 16, warp_last_pos = min(last_pos, warp_first_pos + 15);
+  const bool warp_active = warp * 16 < nqv;
+
+  for (int t = 0; t < n_tiles; ++t) {
+    const int kt = kt0 + t * PF_BK;
+    const int buf = t & 1;
+    if (t + 1 < n_tiles) {
+      load_kv_rows<D>(kbuf + (buf ^ 1) * TILE_BYTES, vbuf + (buf ^ 1) * TILE_BYTES, 0, PF_BK, kt + PF_BK, kv_lo, kv_hi,
+                      kcache, vcache, bt, nkv, kvh, page_size, tid, PF_THREADS);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (t == 0) {
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const int mtx = lane >> 3;
+        ldmatrix_x4(qf[kk], smem_addr(qs) + swz<D>(warp * 16 + (mtx & 1) * 8 + (lane & 7), kk * 2 + (mtx >> 1)));
+      }
+    }
+    // a warp whose rows all lie before this tile (causal) or after it (window) has nothing to do
+    const bool tile_visible = warp_active && kt <= warp_last_pos &&
+                              (window <= 0 || kt + PF_BK - 1 > warp_first_pos - window);
+    if (tile_visible) {
+      const uint32_t ks_addr = smem_addr(kbuf + buf * TILE_BYTES), vs_addr = smem_addr(vbuf + buf * TILE_BYTES);
+      float s[PF_BK / 8][4];
+#pragma unroll
+      for (int nt = 0; nt < PF_BK / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+      for (int kp = 0; kp < PF_BK / 16; ++kp) {
+        float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        qk_16keys<D>(s2, qf, ks_addr, kp * 16, lane);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          s[2 * kp][c] = s2[0][c];
+          s[2 * kp + 1][c] = s2[1][c];
+        }
+      }
+      const bool need_mask = kt + PF_BK - 1 > warp_first_pos || window > 0 || kt < kv_lo;
+#pragma unroll
+      for (int nt = 0; nt < PF_BK / 8; ++nt) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          float v = s[nt][c] * scale_log2;
+          if (need_mask) {
+            const int j = kt + nt * 8 + 2 * (lane & 3) + (c & 1);
+            const int pos = first_pos + row_lo + (c >> 1) * 8;
+            const bool vis = j <= pos && j >= kv_lo && (window <= 0 || j > pos - window);
+            if (!vis) v = -INFINITY;
+          }
+          s[nt][c] = v;
+        }
+      }
+      softmax_step<PF_BK / 8, D / 8>(s, o, m, l);
+#pragma unroll
+      for (int kp = 0; kp < PF_BK / 16; ++kp) {
+        uint32_t pf[4] = {pack_bf16(s[2 * kp][0], s[2 * kp][1]), pack_bf16(s[2 * kp][2], s[2 * kp][3]),
+                          pack_bf16(s[2 * kp + 1][0], s[2 * kp + 1][1]), pack_bf16(s[2 * kp + 1][2], s[2 * kp + 1][3])};
+        pv_16keys<D>(o, pf, vs_addr, kp * 16, lane);
+      }
+    }
+    __syncthreads();  // the other buffer is refilled in the next iteration
+  }
+
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    float sum = l[i];
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    const int r = row_lo + i * 8;
+    if (r < nqv) {
+      const float inv = 1.0f / sum;
+      bf16* orow = out + (size_t)(tok0 + q0 + r) * out_stride + (size_t)h * D + 2 * (lane & 3);
+#pragma unroll
+      for (int t = 0; t < D / 8; ++t)
+        *reinterpret_cast<uint32_t*>(orow + t * 8) = pack_bf16(o[t][2 * i] * inv, o[t][2 * i + 1] * inv);
+    }
+  }
+}
+
+// ================================================================================ decode
+constexpr int DC_THREADS = 128, DC_WARPS = 4, DC_KEYS = 16, DC_TILE = DC_WARPS * DC_KEYS;
+template <int D> struct DecodeCfg { static constexpr int STAGES = D <= 128 ? 4 : 2; };
+
+// partial[((dec * nkv + kvh) * splits + z) * g + row] holds D output values, then max, then sum.
+template <int D>
+__global__ void __launch_bounds__(DC_THREADS)
+attn_decode_mma_kernel(bf16* __restrict__ out, int out_stride, float* __restrict__ partial,
+                       const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kcache,
+                       const bf16* __restrict__ vcache, const int* __restrict__ block_tables, int bt_stride,
+                       const int* __restrict__ cu_q, const int* __restrict__ kv_lens,
+                       const int* __restrict__ dec_seq, int nq, int nkv, int page_size, int window, float scale_log2,
+                       int splits) {
+  constexpr int STAGES = DecodeCfg<D>::STAGES;
+  constexpr int ROWS_BYTES = DC_KEYS * D * 2;                  // one warp's 16 keys of K (or V)
+  constexpr int WARP_BYTES = STAGES * 2 * ROWS_BYTES;          // a warp's private ring
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint8_t* ring = smem + warp * WARP_BYTES;
+
+  const int dec = blockIdx.x, kvh = blockIdx.y, z = blockIdx.z;
+  const int seq = dec_seq[dec];
+  const int g = nq / nkv;
+  const int token = cu_q[seq];
+  const int kvlen = kv_lens[seq];
+  const int pos = kvlen - 1;
+  const int kv_lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int kv_hi = kvlen;
+  const int* bt = block_tables + (size_t)seq * bt_stride;
+
+  const int kt0 = (kv_lo / DC_TILE) * DC_TILE;
+  const int total_tiles = max(0, (kv_hi - kt0 + DC_TILE - 1) / DC_TILE);
+  const int tps = (total_tiles + splits - 1) / splits;
+  const int t_begin = z * tps, t_end = min(total_tiles, t_begin + tps);
+  const int n_tiles = max(0, t_end - t_begin);
+
+  // Q fragments straight from global memory: row = query head within the group
+  uint32_t qf[D / 16][4];
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8;
+    const bf16* q0p = q + (size_t)token * q_stride + (size_t)(kvh * g + r0) * D + 2 * (lane & 3);
+    const bf16* q1p = q + (size_t)token * q_stride + (size_t)(kvh * g + r1) * D + 2 * (lane & 3);
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      qf[kk][0] = r0 < g ? *reinterpret_cast<const uint32_t*>(q0p + kk * 16) : 0u;
+      qf[kk][1] = r1 < g ? *reinterpret_cast<const uint32_t*>(q1p + kk * 16) : 0u;
+      qf[kk][2] = r0 < g ? *reinterpret_cast<const uint32_t*>(q0p + kk * 16 + 8) : 0u;
+      qf[kk][3] = r1 < g ? *reinterpret_cast<const uint32_t*>(q1p + kk * 16 + 8) : 0u;
+    }
+  }
+  float o[D / 8][4];
+#pragma unroll
+  for (int t = 0; t < D / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  auto issue = [&](int t) {   // this warp's 16 keys of tile t into stage t % STAGES
+    const int stage = t % STAGES;
+    uint8_t* ks = ring + stage * 2 * ROWS_BYTES;
+    const int key0 = kt0 + (t_begin + t) * DC_TILE + warp * DC_KEYS;
+    load_kv_rows<D>(ks, ks + ROWS_BYTES, 0, DC_KEYS, key0, kv_lo, kv_hi, kcache, vcache, bt, nkv, kvh, page_size, lane, 32);
+  };
+#pragma unroll
+  for (int t = 0; t < STAGES - 1; ++t) {
+    if (t < n_tiles) issue(t);
+    cp_async_commit();
+  }
+  for (int t = 0; t < n_tiles; ++t) {
+    if (t + STAGES - 1 < n_tiles) issue(t + STAGES - 1);
+    cp_async_commit();
+    cp_async_wait<STAGES - 1>();
+    __syncwarp();
+    const int key0 = kt0 + (t_begin + t) * DC_TILE + warp * DC_KEYS;
+    if (key0 < kv_hi && key0 + DC_KEYS > kv_lo) {
+      const uint32_t ks_addr = smem_addr(ring + (t % STAGES) * 2 * ROWS_BYTES), vs_addr = ks_addr + ROWS_BYTES;
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      qk_16keys<D>(s, qf, ks_addr, 0, lane);
+      const bool need_mask = key0 + DC_KEYS > kv_hi || key0 < kv_lo;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          float v = s[nt][c] * scale_log2;
+          if (need_mask) {
+            const int j = key0 + nt * 8 + 2 * (lane & 3) + (c & 1);
+            if (j >= kv_hi || j < kv_lo) v = -INFINITY;
+          }
+          s[nt][c] = v;
+        }
+      softmax_step<2, D / 8>(s, o, m, l);
+      uint32_t pf[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]), pack_bf16(s[1][0], s[1][1]),
+                        pack_bf16(s[1][2], s[1][3])};
+      pv_16keys<D>(o, pf, vs_addr, 0, lane);
+    }
+    __syncwarp();  // the stage is refilled by this warp's next issue
+  }
+  cp_async_wait<0>();
+
+  // merge the four warps: each writes (o, m, l) of its rows to its own ring, then all combine
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+  }
+  __syncwarp();
+  float* wo = reinterpret_cast<float*>(ring);               // [16][D] then m[16], l[16]
+  static_assert(WARP_BYTES >= (16 * D + 32) * 4, "a warp's ring must hold its partial result");
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = (lane >> 2) + i * 8;
+#pragma unroll
+    for (int t = 0; t < D / 8; ++t) {
+      wo[r * D + t * 8 + 2 * (lane & 3)] = o[t][2 * i];
+      wo[r * D + t * 8 + 2 * (lane & 3) + 1] = o[t][2 * i + 1];
+    }
+    if ((lane & 3) == 0) {
+      wo[16 * D + r] = m[i];
+      wo[16 * D + 16 + r] = l[i];
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < g * D; e += DC_THREADS) {
+    const int r = e / D, c = e % D;
+    float mt = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DC_WARPS; ++w) mt = fmaxf(mt, reinterpret_cast<float*>(smem + w * WARP_BYTES)[16 * D + r]);
+    float acc = 0.f, lt = 0.f;
+#pragma unroll
+    for (int w = 0; w < DC_WARPS; ++w) {
+      const float* p = reinterpret_cast<float*>(smem + w * WARP_BYTES);
+      const float mw = p[16 * D + r];
+      const float sc = mw == -INFINITY ? 0.f : exp2f(mw - mt);
+      acc += p[r * D + c] * sc;
+      lt += p[16 * D + 16 + r] * sc;
+    }
+    if (partial) {
+      float* dst = partial + ((((size_t)dec * nkv + kvh) * splits + z) * g + r) * (D + 2);
+      dst[c] = acc;
+      if (c == 0) {
+        dst[D] = mt;
+        dst[D + 1] = lt;
+      }
+    } else {
+      out[(size_t)token * out_stride + (size_t)(kvh * g + r) * D + c] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
+    }
+  }
+}
+
+template <int D>
+__global__ void attn_decode_combine_kernel(bf16* __restrict__ out, int out_stride, const float* __restrict__ partial,
+                                           const int* __restrict__ cu_q, const int* __restrict__ dec_seq, int nq,
+                                           int nkv, int splits) {
+  const int dec = blockIdx.x, h = blockIdx.y;
+  const int g = nq / nkv, kvh = h / g, r = h % g;
+  const int token = cu_q[dec_seq[dec]];
+  const float* base = partial + ((((size_t)dec * nkv + kvh) * splits) * g + r) * (D + 2);
+  const size_t zstride = (size_t)g * (D + 2);
+  float mt = -INFINITY;
+  for (int z = 0; z < splits; ++z) mt = fmaxf(mt, base[z * zstride + D]);
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    float acc = 0.f, lt = 0.f;
+    for (int z = 0; z < splits; ++z) {
+      const float mz = base[z * zstride + D];
+      const float sc = mz == -INFINITY ? 0.f : exp2f(mz - mt);
+      acc += base[z * zstride + c] * sc;
+      lt += base[z * zstride + D + 1] * sc;
+    }
+    out[(size_t)token * out_stride + (size_t)h * D + c] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
+  }
+}
+
+template <int D>
+int launch_prefill(void* out, int out_stride, const void* q, int q_stride, const void* kc, const void* vc,
+                   const int* bt, int bt_stride, const int* cu_q, const int* kv_lens, const int* tile_seq,
+                   const int* tile_q0, int n_tiles, int nq, int nkv, int page_size, int window, float scale,
+                   cudaStream_t stream) {
+  auto kern = attn_prefill_mma_kernel<D>;
+  const size_t smem = (size_t)(PF_BQ + 4 * PF_BK) * D * 2;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return zi_refuse("attention_prefill: cannot get %zu bytes of shared memory", smem);
+  dim3 grid(n_tiles, nq);
+  kern<<<grid, PF_THREADS, smem, stream>>>((bf16*)out, out_stride, (const bf16*)q, q_stride, (const bf16*)kc,
+                                           (const bf16*)vc, bt, bt_stride, cu_q, kv_lens, tile_seq, tile_q0, nq, nkv,
+                                           page_size, window, scale * 1.4426950408889634f);
+  return zi_check_launch("attention_prefill");
+}
+
+template <int D>
+int launch_decode(void* out, int out_stride, float* partial, const void* q, int q_stride, const void* kc,
+                  const void* vc, const int* bt, int bt_stride, const int* cu_q, const int* kv_lens,
+                  const int* dec_seq, int n_dec, int nq, int nkv, int page_size, int window, float scale, int splits,
+                  cudaStream_t stream) {
+  auto kern = attn_decode_mma_kernel<D>;
+  const size_t smem = (size_t)DC_WARPS * DecodeCfg<D>::STAGES * 2 * DC_KEYS * D * 2;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return zi_refuse("attention_decode: cannot get %zu bytes of shared memory", smem);
+  dim3 grid(n_dec, nkv, splits);
+  kern<<<grid, DC_THREADS, smem, stream>>>((bf16*)out, out_stride, splits > 1 ? partial : nullptr, (const bf16*)q,
+                                           q_stride, (const bf16*)kc, (const bf16*)vc, bt, bt_stride, cu_q, kv_lens,
+                                           dec_seq, nq, nkv, page_size, window, scale * 1.4426950408889634f, splits);
+  int rc = zi_check_launch("attention_decode");
+  if (rc) return rc;
+  if (splits > 1) {
+    attn_decode_combine_kernel<D><<<dim3(n_dec, nq), D >= 128 ? 128 : 64, 0, stream>>>(
+        (bf16*)out, out_stride, partial, cu_q, dec_seq, nq, nkv, splits);
+    rc = zi_check_launch("attention_decode_combine");
+  }
+  return rc;
+}
+}  // namespace
+
+extern "C" int zi_attention_prefill_tile_rows() { return PF_BQ; }
+
+// Whether the tensor-core kernels take this shape (else the caller uses zi_paged_attention).
+extern "C" int zi_attention_mma_supported(int nq, int nkv, int d, int decode) {
+  if (nkv <= 0 || nq % nkv) return 0;
+  if (decode) return (d == 64 || d == 128 || d == 256) && nq / nkv <= 16;
+  return d == 64 || d == 128;
+}
+
+extern "C" int zi_attention_prefill_mma(void* out, int out_stride, const void* q, int q_stride, const void* kcache,
+                                        const void* vcache, const int* block_tables, int bt_stride, const int* cu_q,
+                                        const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles,
+                                        int nq, int nkv, int d, int page_size, int window, float scale,
+                                        cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (!zi_attention_mma_supported(nq, nkv, d, 0)) return zi_refuse("attention_prefill: head_dim %d is not 64 or 128", d);
+  if (q_stride % 8 || ((uintptr_t)q % 16)) return zi_refuse("attention_prefill: q rows must be 16-byte aligned");
+  if (d == 64)
+    return launch_prefill<64>(out, out_stride, q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q, kv_lens,
+                              tile_seq, tile_q0, n_tiles, nq, nkv, page_size, window, scale, stream);
+  return launch_prefill<128>(out, out_stride, q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q, kv_lens,
+                             tile_seq, tile_q0, n_tiles, nq, nkv, page_size, window, scale, stream);
+}
+
+// Floats of workspace a decode launch with `splits` > 1 needs.
+extern "C" long long zi_attention_decode_workspace_floats(int n_dec, int nq, int nkv, int d, int splits) {
+  return splits > 1 ? (long long)n_dec * nq * splits * (d + 2) : 0;
+}
+
+extern "C" int zi_attention_decode_mma(void* out, int out_stride, float* workspace, const void* q, int q_stride,
+                                       const void* kcache, const void* vcache, const int* block_tables,
+                                       int bt_stride, const int* cu_q, const int* kv_lens, const int* dec_seq,
+                                       int n_dec, int nq, int nkv, int d, int page_size, int window, float scale,
+                                       int splits, cudaStream_t stream) {
+  if (n_dec <= 0) return 0;
+  if (!zi_attention_mma_supported(nq, nkv, d, 1))
+    return zi_refuse("attention_decode: head_dim %d (64, 128, 256) or group size %d (<= 16) is not supported", d, nq / nkv);
+  if (splits < 1 || (splits > 1 && !workspace)) return zi_refuse("attention_decode: %d splits need a workspace", splits);
+  if (q_stride % 2) return zi_refuse("attention_decode: q rows must be 4-byte aligned");
+  if (d == 64)
+    return launch_decode<64>(out, out_stride, workspace, q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q,
+                             kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, stream);
+  if (d == 128)
+    return launch_decode<128>(out, out_stride, workspace, q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q,
+                              kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, stream);
+  return launch_decode<256>(out, out_stride, workspace, q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q,
+                            kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, stream);
+}

@@ -39,8 +39,13 @@ class StepContext:
     cu_q: torch.Tensor              # [n+1] int32, first token of each request in the flat list
     kv_lens: torch.Tensor           # [n] int32, keys per request including this step's tokens
     state_slots: torch.Tensor       # [n] int32, the request's slot in the per-request state
-    tile_seq: torch.Tensor          # [tiles] request of each query tile
+    tile_seq: torch.Tensor          # [tiles] request of each query tile (tiles of the exact kernel)
     tile_q0: torch.Tensor           # [tiles] first token (within the request's portion) of each query tile
+    dec_seq: torch.Tensor           # [n_dec] requests that bring exactly one token
+    pf_tile_seq: torch.Tensor       # [n_pf_tiles] query tiles of the tensor-core prefill kernel, over the
+    pf_tile_q0: torch.Tensor        #              requests that bring more than one token
+    n_dec: int
+    n_pf_tiles: int
     logit_rows: Optional[torch.Tensor]   # [R] flat token indices whose logits are wanted
     kv_groups: list[KVGroupStep]
     # host copies, for parts that loop over requests
@@ -53,7 +58,7 @@ class StepContext:
 
 
 def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile_rows: int, pin: bool = True,
-               static: Optional["StaticStepBuffers"] = None) -> StepContext:
+               static: Optional["StaticStepBuffers"] = None, pf_tile_rows: int = 128) -> StepContext:
     """Flattens ``entries``; their pages must already be reserved in ``manager``.
 
     With ``static`` (decode steps replayed from a CUDA graph) the arrays have the
@@ -79,6 +84,9 @@ def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile
     np.cumsum(q_lens + [1] * pad, out=cu[1:])
     n_tiles_per = [-(-q // tile_rows) for q in q_lens] + [1] * pad
     n_tiles = int(sum(n_tiles_per))
+    all_q = q_lens + [1] * pad
+    dec_list = [i for i, ql in enumerate(all_q) if ql == 1]
+    pf_tiles = [(i, t * pf_tile_rows) for i, ql in enumerate(all_q) if ql > 1 for t in range(-(-ql // pf_tile_rows))]
     if static is not None:
         rows = list(range(n))
     else:
@@ -87,7 +95,8 @@ def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile
 
     # layout of the packed buffer
     sizes = [("token_ids", T), ("positions", T), ("cu_q", n + 1), ("kv_lens", n), ("state_slots", n),
-             ("tile_seq", n_tiles), ("tile_q0", n_tiles), ("logit_rows", R)]
+             ("tile_seq", n_tiles), ("tile_q0", n_tiles), ("logit_rows", R), ("dec_seq", len(dec_list)),
+             ("pf_tile_seq", len(pf_tiles)), ("pf_tile_q0", len(pf_tiles))]
     for gi in range(n_groups):
         sizes += [(f"slots{gi}", T), (f"bt{gi}", n * widths[gi])]
     offs, total = {}, 0
@@ -119,6 +128,9 @@ def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile
             tq0[ti] = t * tile_rows
             ti += 1
     arr("cu_q")[:] = cu
+    arr("dec_seq")[:] = dec_list
+    arr("pf_tile_seq")[:] = [i for i, _ in pf_tiles]
+    arr("pf_tile_q0")[:] = [t for _, t in pf_tiles]
     kv = arr("kv_lens")
     kv[:] = 1
     if n_real:
@@ -159,8 +171,12 @@ def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile
     return StepContext(
         n_seqs=n, n_tokens=T, token_ids=view("token_ids"), positions=view("positions"), cu_q=view("cu_q"),
         kv_lens=view("kv_lens"), state_slots=view("state_slots"), tile_seq=view("tile_seq"), tile_q0=view("tile_q0"),
+        dec_seq=view("dec_seq"), pf_tile_seq=view("pf_tile_seq"), pf_tile_q0=view("pf_tile_q0"),
+        n_dec=len(dec_list), n_pf_tiles=len(pf_tiles),
         logit_rows=view("logit_rows") if R else None, kv_groups=groups, q_lens=q_lens, ctx_lens=ctx_lens,
-        max_q_len=max(q_lens, default=0), max_kv_len=max((c + q for c, q in zip(ctx_lens, q_lens)), default=0),
+        max_q_len=max(q_lens, default=0),
+        # a captured graph serves later steps with longer requests: no host-side length may shape its launches
+        max_kv_len=0 if static is not None else max((c + q for c, q in zip(ctx_lens, q_lens)), default=0),
         all_decode=all(q == 1 for q in q_lens), h2d_bytes=int(total) * 4)
 
 

@@ -48,7 +48,8 @@ class DecodeGraphs:
         if state is None:
             state = self._buckets[b] = {"static": StaticStepBuffers(b, self.width, runner.device), "graph": None,
                                         "logits": None, "launches": 0, "warm": 0}
-        ctx = build_step(runner.manager, entries, runner.device, runner.tile_rows, static=state["static"])
+        ctx = build_step(runner.manager, entries, runner.device, runner.tile_rows, static=state["static"],
+                         pf_tile_rows=runner.pf_tile_rows)
         runner.last_h2d_bytes = ctx.h2d_bytes
         if state["graph"] is None:
             if state["warm"] < 1:

@@ -51,6 +51,7 @@ class ModelRunner:
         self.storage = CacheStorage(self.manager, state_needs, model.dtype, self.device)
         model.attach(self.storage)
         self.tile_rows = ops.attention_tile_rows()
+        self.pf_tile_rows = ops.attention_prefill_tile_rows()
         self.steps_run = 0
         self.last_h2d_bytes = 0
         # decode steps are replayed from CUDA graphs when every mixer can be captured
@@ -166,7 +167,7 @@ class ModelRunner:
             else:
                 logits = all_rows[torch.tensor(wanted, device=self.device)]
         else:
-            ctx = build_step(self.manager, entries, self.device, self.tile_rows)
+            ctx = build_step(self.manager, entries, self.device, self.tile_rows, pf_tile_rows=self.pf_tile_rows)
             self.last_h2d_bytes = ctx.h2d_bytes
             logits = self.model.forward(ctx)
         for e in entries:

@@ -35,6 +35,7 @@ def lib() -> ctypes.CDLL:
             raise KernelError(f"cannot load the kernel library {path}: {e}") from None
         _LIB.zi_last_error.restype = ctypes.c_char_p
         _LIB.zi_gemm_tcgen05_plan.restype = ctypes.c_longlong
+        _LIB.zi_attention_decode_workspace_floats.restype = ctypes.c_longlong
     return _LIB
 
 
@@ -247,6 +248,55 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         block_tables.stride(0), _ptr(cu_q), _ptr(kv_lens), _ptr(tile_seq), _ptr(tile_q0), tile_seq.shape[0],
         num_heads, num_kv_heads, head_dim, page_size, int(window or 0), ctypes.c_float(scale), _stream()),
         "paged_attention")
+    return out
+
+
+ATTENTION_BACKEND = os.environ.get("ZINFER_B200_ATTENTION", "auto")   # auto | generic
+
+
+def attention_prefill_tile_rows() -> int:
+    return int(lib().zi_attention_prefill_tile_rows())
+
+
+def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor, step,
+              num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
+              scale: float) -> torch.Tensor:
+    """Attention of a step's query tokens over their pages, by the fastest kernel that
+    takes the shape: in bfloat16 with head sizes 64/128 (decode also 256) the
+    tensor-core kernels (requests that bring one token go to the split-key decode
+    kernel, the others to the prefill kernel); otherwise, and always in float32, the
+    exact CUDA-core kernel.  ``step`` is the StepContext (its request arrays)."""
+    T = q.shape[0]
+    L = lib()
+    fast = ATTENTION_BACKEND != "generic" and q.dtype == torch.bfloat16
+    dec_ok = fast and step.n_dec > 0 and L.zi_attention_mma_supported(num_heads, num_kv_heads, head_dim, 1)
+    pf_ok = fast and step.n_pf_tiles > 0 and L.zi_attention_mma_supported(num_heads, num_kv_heads, head_dim, 0) \
+        and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
+    if (step.n_dec > 0 and not dec_ok) or (step.n_pf_tiles > 0 and not pf_ok):
+        return paged_attention(q, k_cache, v_cache, block_tables, step.cu_q, step.kv_lens, step.tile_seq, step.tile_q0,
+                               num_heads, num_kv_heads, head_dim, page_size, window, scale)
+    _need(q.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous(), "attention: dense operands")
+    _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim) and k_cache.dtype == q.dtype,
+          "cache pages are [pages, kv heads, page, d] in the activations' dtype")
+    out = torch.empty((T, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    win = int(window or 0)
+    if step.n_pf_tiles > 0:
+        _check(L.zi_attention_prefill_mma(
+            _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+            block_tables.stride(0), _ptr(step.cu_q), _ptr(step.kv_lens), _ptr(step.pf_tile_seq), _ptr(step.pf_tile_q0),
+            step.n_pf_tiles, num_heads, num_kv_heads, head_dim, page_size, win, ctypes.c_float(scale), _stream()),
+            "attention (prefill)")
+    if step.n_dec > 0:
+        sms = _sm_count(q.device)
+        splits = max(1, min(32, -(-2 * sms // (step.n_dec * num_kv_heads))))
+        if step.max_kv_len:  # known on the host: no more splits than tiles of 64 keys
+            splits = min(splits, max(1, -(-step.max_kv_len // 64)))
+        need = L.zi_attention_decode_workspace_floats(step.n_dec, num_heads, num_kv_heads, head_dim, splits)
+        ws = torch.empty((need,), dtype=torch.float32, device=q.device) if need else None
+        _check(L.zi_attention_decode_mma(
+            _ptr(out), out.stride(0), _ptr(ws), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+            block_tables.stride(0), _ptr(step.cu_q), _ptr(step.kv_lens), _ptr(step.dec_seq), step.n_dec, num_heads,
+            num_kv_heads, head_dim, page_size, win, ctypes.c_float(scale), splits, _stream()), "attention (decode)")
     return out
 
 

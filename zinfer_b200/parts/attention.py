@@ -79,7 +79,6 @@ class GQAttention(Mixer):
             qkv, self.nq, self.nkv, self.d, self.q_norm, self.k_norm,
             self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, cos, sin, step.positions,
             cache.k, cache.v, group.slot_mapping, cache.page_size, write_kv=cache.writes)
-        o = ops.paged_attention(
-            qkv, cache.k, cache.v, group.block_tables, step.cu_q, step.kv_lens, step.tile_seq, step.tile_q0,
-            self.nq, self.nkv, self.d, cache.page_size, self.window, self.scale)
+        o = ops.attention(qkv, cache.k, cache.v, group.block_tables, step, self.nq, self.nkv, self.d,
+                          cache.page_size, self.window, self.scale)
         return ops.linear(o, self.w_o, out_dtype=self.ctx.dtype)
