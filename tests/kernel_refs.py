@@ -30,7 +30,7 @@ def residual_add(h, delta):
     h += delta.to(torch.float32)
 
 
-def swiglu(gate_up, out=None):
+def swiglu(gate_up, out=None, out_dtype=None):
     I = gate_up.shape[1] // 2
     g, u = gate_up[:, :I].to(torch.float32), gate_up[:, I:].to(torch.float32)
     return (g / (1.0 + torch.exp(-g)) * u).to(gate_up.dtype)
@@ -48,7 +48,7 @@ def rope_table(n_pos, head_dim, theta, device):
 
 
 def qk_norm_rope_store(qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weight, eps, cos, sin, positions,
-                       k_cache, v_cache, slots, page_size, write_kv=True):
+                       k_cache, v_cache, slots, page_size, write_kv=True, out_dtype=None):
     T = qkv.shape[0]
     nq, nkv, d = num_heads, num_kv_heads, head_dim
     half = d // 2
@@ -67,16 +67,17 @@ def qk_norm_rope_store(qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weigh
     q = norm_rope(qkv[:, :nq * d].to(torch.float32).reshape(T, nq, d), q_weight)
     qkv[:, :nq * d] = q.reshape(T, nq * d).to(qkv.dtype)
     if not write_kv:
-        return
+        return qkv
     k = norm_rope(qkv[:, nq * d:(nq + nkv) * d].to(torch.float32).reshape(T, nkv, d), k_weight).to(qkv.dtype)
     v = qkv[:, (nq + nkv) * d:(nq + 2 * nkv) * d].reshape(T, nkv, d)
     for t in range(T):
         slot = int(slots[t])
         k_cache[slot // page_size, :, slot % page_size, :] = k[t]
         v_cache[slot // page_size, :, slot % page_size, :] = v[t]
+    return qkv
 
 
-def linear(x, weight, out_dtype=None, out=None):
+def linear(x, weight, out_dtype=None, out=None, allow_partials=False):
     y = x.to(torch.float32) @ weight.to(torch.float32).T
     return y.to(out_dtype or x.dtype)
 

@@ -166,6 +166,57 @@ def test_linear(xdt, wdt, odt, M, N, K):
     torch.testing.assert_close(got2.double(), wide[:, :K].double() @ w.double().T, **t)
 
 
+def test_split_products_and_their_consumers():
+    """A product split along K may come back as partial sums; each consumer that adds
+    them itself must agree with the product reduced first."""
+    o = ops()
+    M, K = 8, 12288
+    x = rnd(M, K, dtype=torch.bfloat16)
+    # residual add + norm
+    w = rnd(4096, K, dtype=torch.bfloat16, scale=0.05, seed=1)
+    part = o.linear(x, w, allow_partials=True)
+    assert isinstance(part, o.Partials) and part.splits > 1 and tuple(part.shape) == (M, 4096)
+    whole = o.linear(x, w)
+    torch.testing.assert_close(part.sum(torch.float32), x.float() @ w.float().T, rtol=1e-3, atol=2e-2)
+    h = rnd(M, 4096, scale=2.0, seed=2)
+    nw = 1 + 0.1 * rnd(4096, seed=3)
+    h1, h2 = h.clone(), h.clone()
+    a = o.add_rmsnorm(h1, part, nw, 1e-6, torch.bfloat16)
+    b = o.add_rmsnorm(h2, whole, nw, 1e-6, torch.bfloat16)
+    # `whole` was rounded to bfloat16 first: half an ulp (2^-9 relative) of the largest update
+    torch.testing.assert_close(h1, h2, rtol=0, atol=float(whole.float().abs().max()) * 2 ** -8 + 1e-3)
+    torch.testing.assert_close(a.float(), b.float(), rtol=1.6e-2, atol=2e-2)
+    rows = torch.tensor([5, 0], dtype=torch.int32, device=DEV)
+    h3 = h.clone()
+    c = o.add_rmsnorm(h3, part, nw, 1e-6, torch.bfloat16, rows=rows)
+    torch.testing.assert_close(c.float(), a[[5, 0]].float(), rtol=0, atol=0)
+    # SwiGLU
+    wgu = rnd(2 * 1024, K, dtype=torch.bfloat16, scale=0.02, seed=4)
+    pgu = o.linear(x, wgu, allow_partials=True)
+    assert isinstance(pgu, o.Partials)
+    torch.testing.assert_close(o.swiglu(pgu, out_dtype=torch.bfloat16).float(), o.swiglu(o.linear(x, wgu)).float(),
+                               rtol=2e-2, atol=2e-2)
+    # q/k norm + rotary + cache write
+    nq, nkv, d, page = 8, 2, 128, 16
+    wqkv = rnd((nq + 2 * nkv) * d, K, dtype=torch.bfloat16, scale=0.02, seed=5)
+    pq = o.linear(x, wqkv, allow_partials=True)
+    assert isinstance(pq, o.Partials)
+    qw, kw = 1 + 0.1 * rnd(d, seed=6), 1 + 0.1 * rnd(d, seed=7)
+    cos, sin = ref.rope_table(64, d, 1e4, DEV)
+    positions = torch.arange(M, dtype=torch.int32, device=DEV) * 3
+    slots = torch.arange(M, dtype=torch.int32, device=DEV) + 5
+    caches = [torch.zeros(4, nkv, page, d, dtype=torch.bfloat16, device=DEV) for _ in range(4)]
+    q1 = o.qk_norm_rope_store(pq, nq, nkv, d, qw, kw, 1e-6, cos, sin, positions, caches[0], caches[1], slots, page,
+                              out_dtype=torch.bfloat16)
+    q2 = o.qk_norm_rope_store(o.linear(x, wqkv), nq, nkv, d, qw, kw, 1e-6, cos, sin, positions, caches[2], caches[3],
+                              slots, page)
+    assert q1.shape == (M, nq * d)
+    torch.testing.assert_close(q1.float(), q2[:, :nq * d].float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(caches[0].float(), caches[2].float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(caches[1].float(), caches[3].float(), rtol=2e-2, atol=2e-2)
+    assert o.kernel_status() == 0
+
+
 def _paged_case(dtype, nq, nkv, d, page, q_lens, ctx_lens, seed=0):
     """Random requests laid out in shuffled pages; returns the kernel's arguments."""
     o = ops()

@@ -13,12 +13,18 @@ const char* zi_last_error();
 
 int zi_embed_gather(float* h, const void* table, int table_dtype, const int* ids, int T, int H, int V,
                     cudaStream_t stream);
-int zi_add_rmsnorm(float* h, const void* delta, int delta_dtype, const float* w, float eps, void* out, int out_dtype,
-                   const int* rows, int n_rows, int H, cudaStream_t stream);
+int zi_add_rmsnorm(float* h, const void* delta, int delta_dtype, const float* delta_partials, int splits,
+                   long long split_stride, const float* w, float eps, void* out, int out_dtype, const int* rows,
+                   int n_rows, int H, cudaStream_t stream);
 int zi_residual_add(float* h, const void* delta, int delta_dtype, long long n, cudaStream_t stream);
+int zi_residual_add_partials(float* h, const float* partials, int splits, long long split_stride, long long n,
+                             cudaStream_t stream);
 int zi_swiglu(void* out, const void* gu, int dtype, int T, int I, cudaStream_t stream);
+int zi_swiglu_partials(void* out, int dtype, const float* partials, int splits, long long split_stride, int T, int I,
+                       cudaStream_t stream);
 int zi_rope_table(float* cos_t, float* sin_t, int n_pos, int d, float theta, cudaStream_t stream);
-int zi_qk_norm_rope_store(void* qkv, int dtype, int T, int row_stride, int nq, int nkv, int d, const float* qw,
+int zi_qk_norm_rope_store(const void* src, int dtype, int T, int src_stride, const float* partials, int splits,
+                          long long split_stride, void* q_out, int q_stride, int nq, int nkv, int d, const float* qw,
                           const float* kw, float eps, const float* cos_t, const float* sin_t, int n_table_pos,
                           const int* positions, void* kcache, void* vcache, const int* slots, int page_size,
                           int write_kv, cudaStream_t stream);
@@ -29,7 +35,8 @@ int zi_gemm_simt(void* out, int out_dtype, const void* x, int x_dtype, const voi
 int zi_gemm_tcgen05_supported(const void* x, const void* w, int K, int ldx, int ldw);
 long long zi_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int* plan);
 int zi_gemm_tcgen05(void* out, int out_dtype, const void* x, const void* w, int M, int N, int K, int ldx, int ldw,
-                    int ldo, float* workspace, long long workspace_bytes, int sm_count, cudaStream_t stream);
+                    int ldo, float* workspace, long long workspace_bytes, int sm_count, int defer_reduce,
+                    cudaStream_t stream);
 int zi_gemm_tcgen05_status();
 
 int zi_paged_attention_tile_rows();

@@ -122,21 +122,24 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[ON][4
 // Copies `n_keys` keys starting at position `key_pos0` of one kv head into a swizzled
 // tile at rows row0.., for both K and V, 16 bytes per cp.async.  `tid`/`nthreads`
 // enumerate the copying threads.  Keys outside [kv_lo, kv_hi) or in no page are zero.
+// `page_shift` >= 0 says page_size == 1 << page_shift (shifts instead of divisions).
 template <int D>
 __device__ __forceinline__ void load_kv_rows(uint8_t* ks, uint8_t* vs, int row0, int n_keys, int key_pos0, int kv_lo,
                                              int kv_hi, const bf16* __restrict__ kcache,
                                              const bf16* __restrict__ vcache, const int* __restrict__ bt, int nkv,
-                                             int kvh, int page_size, int tid, int nthreads) {
-  constexpr int CH = D / 8;
+                                             int kvh, int page_size, int page_shift, int tid, int nthreads) {
+  constexpr int CH = D / 8;  // 16-byte chunks per key
   for (int e = tid; e < n_keys * CH; e += nthreads) {
     const int r = e / CH, c = e % CH;
     const int j = key_pos0 + r;
     bool valid = j >= kv_lo && j < kv_hi;
     size_t off = 0;
     if (valid) {
-      const int page = bt[j / page_size];
+      const int blk = page_shift >= 0 ? (j >> page_shift) : (j / page_size);
+      const int in_page = page_shift >= 0 ? (j & (page_size - 1)) : (j % page_size);
+      const int page = __ldg(bt + blk);
       valid = page >= 0;
-      if (valid) off = (((size_t)page * nkv + kvh) * page_size + (j % page_size)) * D + c * 8;
+      if (valid) off = (((size_t)page * nkv + kvh) * page_size + in_page) * D + c * 8;
     }
     const uint32_t so = swz<D>(row0 + r, c);
     cp_async16(ks + so, kcache + off, valid);
@@ -153,8 +156,8 @@ attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __re
                         const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                         const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ cu_q,
                         const int* __restrict__ kv_lens, const int* __restrict__ tile_seq,
-                        const int* __restrict__ tile_q0, int nq, int nkv, int page_size, int window,
-                        float scale_log2) {
+                        const int* __restrict__ tile_q0, int nq, int nkv, int page_size, int page_shift,
+                        int window, float scale_log2) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* qs = smem;                                   // [128][D]
   uint8_t* kbuf = qs + PF_BQ * D * 2;                   // [2][64][D]
@@ -182,7 +185,8 @@ attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __re
   }
   const int kt0 = (kv_lo / PF_BK) * PF_BK;
   const int n_tiles = (kv_hi - kt0 + PF_BK - 1) / PF_BK;
-  load_kv_rows<D>(kbuf, vbuf, 0, PF_BK, kt0, kv_lo, kv_hi, kcache, vcache, bt, nkv, kvh, page_size, tid, PF_THREADS);
+  load_kv_rows<D>(kbuf, vbuf, 0, PF_BK, kt0, kv_lo, kv_hi, kcache, vcache, bt, nkv, kvh, page_size, page_shift, tid,
+                  PF_THREADS);
   cp_async_commit();
 
   uint32_t qf[D / 16][4];
@@ -199,7 +203,7 @@ attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __re
     const int buf = t & 1;
     if (t + 1 < n_tiles) {
       load_kv_rows<D>(kbuf + (buf ^ 1) * TILE_BYTES, vbuf + (buf ^ 1) * TILE_BYTES, 0, PF_BK, kt + PF_BK, kv_lo, kv_hi,
-                      kcache, vcache, bt, nkv, kvh, page_size, tid, PF_THREADS);
+                      kcache, vcache, bt, nkv, kvh, page_size, page_shift, tid, PF_THREADS);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -275,7 +279,8 @@ attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __re
 
 // ================================================================================ decode
 constexpr int DC_THREADS = 128, DC_WARPS = 4, DC_KEYS = 16, DC_TILE = DC_WARPS * DC_KEYS;
-template <int D> struct DecodeCfg { static constexpr int STAGES = D <= 128 ? 4 : 2; };
+// stages of a warp's private ring: 3 x 8 KB x 4 warps = 96 KB per CTA at d = 128, two CTAs per SM
+template <int D> struct DecodeCfg { static constexpr int STAGES = D <= 64 ? 4 : (D <= 128 ? 3 : 2); };
 
 // partial[((dec * nkv + kvh) * splits + z) * g + row] holds D output values, then max, then sum.
 template <int D>
@@ -284,8 +289,8 @@ attn_decode_mma_kernel(bf16* __restrict__ out, int out_stride, float* __restrict
                        const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kcache,
                        const bf16* __restrict__ vcache, const int* __restrict__ block_tables, int bt_stride,
                        const int* __restrict__ cu_q, const int* __restrict__ kv_lens,
-                       const int* __restrict__ dec_seq, int nq, int nkv, int page_size, int window, float scale_log2,
-                       int splits) {
+                       const int* __restrict__ dec_seq, int nq, int nkv, int page_size, int page_shift, int window,
+                       float scale_log2, int splits) {
   constexpr int STAGES = DecodeCfg<D>::STAGES;
   constexpr int ROWS_BYTES = DC_KEYS * D * 2;                  // one warp's 16 keys of K (or V)
   constexpr int WARP_BYTES = STAGES * 2 * ROWS_BYTES;          // a warp's private ring
@@ -332,7 +337,8 @@ attn_decode_mma_kernel(bf16* __restrict__ out, int out_stride, float* __restrict
     const int stage = t % STAGES;
     uint8_t* ks = ring + stage * 2 * ROWS_BYTES;
     const int key0 = kt0 + (t_begin + t) * DC_TILE + warp * DC_KEYS;
-    load_kv_rows<D>(ks, ks + ROWS_BYTES, 0, DC_KEYS, key0, kv_lo, kv_hi, kcache, vcache, bt, nkv, kvh, page_size, lane, 32);
+    load_kv_rows<D>(ks, ks + ROWS_BYTES, 0, DC_KEYS, key0, kv_lo, kv_hi, kcache, vcache, bt, nkv, kvh, page_size, page_shift,
+                    lane, 32);
   };
 #pragma unroll
   for (int t = 0; t < STAGES - 1; ++t) {
@@ -443,6 +449,12 @@ __global__ void attn_decode_combine_kernel(bf16* __restrict__ out, int out_strid
   }
 }
 
+int log2_or_minus1(int v) {
+  for (int s = 0; s < 31; ++s)
+    if ((1 << s) == v) return s;
+  return -1;
+}
+
 template <int D>
 int launch_prefill(void* out, int out_stride, const void* q, int q_stride, const void* kc, const void* vc,
                    const int* bt, int bt_stride, const int* cu_q, const int* kv_lens, const int* tile_seq,
@@ -455,7 +467,7 @@ int launch_prefill(void* out, int out_stride, const void* q, int q_stride, const
   dim3 grid(n_tiles, nq);
   kern<<<grid, PF_THREADS, smem, stream>>>((bf16*)out, out_stride, (const bf16*)q, q_stride, (const bf16*)kc,
                                            (const bf16*)vc, bt, bt_stride, cu_q, kv_lens, tile_seq, tile_q0, nq, nkv,
-                                           page_size, window, scale * 1.4426950408889634f);
+                                           page_size, log2_or_minus1(page_size), window, scale * 1.4426950408889634f);
   return zi_check_launch("attention_prefill");
 }
 
@@ -471,7 +483,8 @@ int launch_decode(void* out, int out_stride, float* partial, const void* q, int 
   dim3 grid(n_dec, nkv, splits);
   kern<<<grid, DC_THREADS, smem, stream>>>((bf16*)out, out_stride, splits > 1 ? partial : nullptr, (const bf16*)q,
                                            q_stride, (const bf16*)kc, (const bf16*)vc, bt, bt_stride, cu_q, kv_lens,
-                                           dec_seq, nq, nkv, page_size, window, scale * 1.4426950408889634f, splits);
+                                           dec_seq, nq, nkv, page_size, log2_or_minus1(page_size), window,
+                                           scale * 1.4426950408889634f, splits);
   int rc = zi_check_launch("attention_decode");
   if (rc) return rc;
   if (splits > 1) {

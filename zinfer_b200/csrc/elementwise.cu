@@ -31,8 +31,10 @@ extern "C" int zi_embed_gather(float* h, const void* table, int table_dtype, con
 // ------------------------------------------------------------ residual add + RMSNorm
 // h[row] += delta[row] (when delta is given), out[r] = h[row] * w / sqrt(mean(h[row]^2) + eps).
 // One block per row; the sum of squares is taken in a fixed order.
+// The update may also come as split-K partial sums: dpart[z][row][i], z < splits, added in order.
 template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                                   const float* __restrict__ dpart, int splits, size_t zstride,
                                    const float* __restrict__ w, float eps, TO* __restrict__ out,
                                    const int* __restrict__ rows, int H) {
   __shared__ float scratch[33];
@@ -40,7 +42,16 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
   const int row = rows ? rows[r] : r;
   float* hr = h + (size_t)row * H;
   float ss = 0.f;
-  if (delta) {
+  if (dpart) {
+    const float* dr = dpart + (size_t)row * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float d = 0.f;
+      for (int z = 0; z < splits; ++z) d += dr[z * zstride + i];
+      const float v = hr[i] + d;
+      hr[i] = v;
+      ss += v * v;
+    }
+  } else if (delta) {
     const TD* dr = delta + (size_t)row * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
       float v = hr[i] + to_f32(dr[i]);
@@ -59,15 +70,114 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
   for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<TO>(hr[i] * w[i] * inv);
 }
 
-extern "C" int zi_add_rmsnorm(float* h, const void* delta, int delta_dtype, const float* w, float eps, void* out,
-                              int out_dtype, const int* rows, int n_rows, int H, cudaStream_t stream) {
-  if (n_rows <= 0) return 0;
-  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-  ZI_DISPATCH_DTYPE(delta_dtype, TD, ZI_DISPATCH_DTYPE(out_dtype, TO, {
-                      add_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(
-                          h, (const TD*)delta, w, eps, (TO*)out, rows, H);
-                    }));
+// The same with the row held in registers: one read of h and delta, one write of h and
+// of the result.  Needs H % 4 == 0 and H <= 4 * VPT * blockDim.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<uint32_t*>(&a);
+    raw.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+  }
+};
+
+template <typename TD, typename TO, int VPT>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                                       const float* __restrict__ dpart, int splits, size_t zstride,
+                                       const float* __restrict__ w, float eps, TO* __restrict__ out,
+                                       const int* __restrict__ rows, int H) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int row = rows ? rows[r] : r;
+  float* hr = h + (size_t)row * H;
+  const int nvec = H >> 2;
+  float4 v[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    if (idx < nvec) {
+      float4 a = Vec4<float>::load(hr + 4 * idx);
+      if (dpart) {
+        float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int z = 0; z < splits; ++z) {
+          const float4 p = Vec4<float>::load(dpart + z * zstride + (size_t)row * H + 4 * idx);
+          d.x += p.x; d.y += p.y; d.z += p.z; d.w += p.w;
+        }
+        a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+        Vec4<float>::store(hr + 4 * idx, a);
+      } else if (delta) {
+        const float4 d = Vec4<TD>::load(delta + (size_t)row * H + 4 * idx);
+        a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+        Vec4<float>::store(hr + 4 * idx, a);
+      }
+      v[i] = a;
+      ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+    }
+  }
+  const float total = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(total / (float)H + eps);
+  TO* o = out + (size_t)r * H;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    if (idx < nvec) {
+      const float4 ww = Vec4<float>::load(w + 4 * idx);
+      Vec4<TO>::store(o + 4 * idx, make_float4(v[i].x * ww.x * inv, v[i].y * ww.y * inv, v[i].z * ww.z * inv,
+                                               v[i].w * ww.w * inv));
+    }
+  }
+}
+
+template <typename TD, typename TO>
+static int launch_add_rmsnorm(float* h, const void* delta, const float* dpart, int splits, size_t zstride,
+                              const float* w, float eps, void* out, const int* rows, int n_rows, int H,
+                              cudaStream_t stream) {
+  const bool aligned = H % 4 == 0 && ((uintptr_t)h % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
+                       ((uintptr_t)out % 16 == 0) && ((uintptr_t)delta % 16 == 0) && ((uintptr_t)dpart % 16 == 0) &&
+                       zstride % 4 == 0;
+  const int threads = 256;
+  const int nvec = H / 4;
+  if (aligned && nvec <= threads * 8) {
+    const int vpt = (nvec + threads - 1) / threads;
+#define ZI_LAUNCH_VPT(V)                                                                                      \
+  add_rmsnorm_vec_kernel<TD, TO, V><<<n_rows, threads, 0, stream>>>(h, (const TD*)delta, dpart, splits, zstride, w, eps, \
+                                                                    (TO*)out, rows, H)
+    if (vpt <= 1) ZI_LAUNCH_VPT(1);
+    else if (vpt <= 2) ZI_LAUNCH_VPT(2);
+    else if (vpt <= 4) ZI_LAUNCH_VPT(4);
+    else ZI_LAUNCH_VPT(8);
+#undef ZI_LAUNCH_VPT
+  } else {
+    const int t2 = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    add_rmsnorm_kernel<TD, TO><<<n_rows, t2, 0, stream>>>(h, (const TD*)delta, dpart, splits, zstride, w, eps, (TO*)out,
+                                                          rows, H);
+  }
   return zi_check_launch("add_rmsnorm");
+}
+
+extern "C" int zi_add_rmsnorm(float* h, const void* delta, int delta_dtype, const float* delta_partials, int splits,
+                              long long split_stride, const float* w, float eps, void* out, int out_dtype,
+                              const int* rows, int n_rows, int H, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (delta && delta_partials) return zi_refuse("add_rmsnorm: give the update either whole or as partial sums");
+  ZI_DISPATCH_DTYPE(delta_dtype, TD, ZI_DISPATCH_DTYPE(out_dtype, TO, {
+                      return launch_add_rmsnorm<TD, TO>(h, delta, delta_partials, splits, (size_t)split_stride, w, eps,
+                                                        out, rows, n_rows, H, stream);
+                    }));
+  return 0;
 }
 
 // Plain add of the last pending update into the residual stream (rows optional).
@@ -99,10 +209,68 @@ __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int
   out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
 }
 
+// gate and up given as split-K partial sums part[z][t][2I]; four elements per thread.
+template <typename T>
+__global__ void swiglu_partials_kernel(T* __restrict__ out, const float* __restrict__ part, int splits, size_t zstride,
+                                       int I, size_t total_vec) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total_vec) return;
+  const int per_row = I >> 2;
+  const size_t t = idx / per_row;
+  const int i = (int)(idx - t * per_row) * 4;
+  float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
+  for (int z = 0; z < splits; ++z) {
+    const float* p = part + z * zstride + t * 2 * I + i;
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + I);
+    g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+    u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+  }
+  Vec4<T>::store(out + t * I + i, make_float4(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y,
+                                              g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w));
+}
+
+// Eight elements per thread (16-byte loads of bfloat16, two of float); needs I % 8 == 0.
+template <typename T>
+__global__ void swiglu_vec_kernel(T* __restrict__ out, const T* __restrict__ gu, int I, size_t total_vec) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total_vec) return;
+  const int per_row = I >> 3;
+  const size_t t = idx / per_row;
+  const int i = (int)(idx - t * per_row) * 8;
+  const T* g = gu + t * 2 * I + i;
+  const T* u = g + I;
+  T* o = out + t * I + i;
+#pragma unroll
+  for (int k = 0; k < 8; k += 4) {
+    const float4 gv = Vec4<T>::load(g + k), uv = Vec4<T>::load(u + k);
+    Vec4<T>::store(o + k, make_float4(gv.x / (1.0f + expf(-gv.x)) * uv.x, gv.y / (1.0f + expf(-gv.y)) * uv.y,
+                                      gv.z / (1.0f + expf(-gv.z)) * uv.z, gv.w / (1.0f + expf(-gv.w)) * uv.w));
+  }
+}
+
+extern "C" int zi_swiglu_partials(void* out, int dtype, const float* partials, int splits, long long split_stride,
+                                  int T, int I, cudaStream_t stream) {
+  const size_t total = (size_t)T * I;
+  if (total == 0) return 0;
+  if (I % 4 || (uintptr_t)partials % 16 || (uintptr_t)out % 8 || split_stride % 4)
+    return zi_refuse("swiglu_partials: needs I %% 4 == 0 and aligned buffers");
+  const size_t total_vec = total / 4;
+  ZI_DISPATCH_DTYPE(dtype, TT, swiglu_partials_kernel<TT><<<(unsigned)((total_vec + 255) / 256), 256, 0, stream>>>(
+                                   (TT*)out, partials, splits, (size_t)split_stride, I, total_vec));
+  return zi_check_launch("swiglu_partials");
+}
+
 extern "C" int zi_swiglu(void* out, const void* gu, int dtype, int T, int I, cudaStream_t stream) {
   const size_t total = (size_t)T * I;
   if (total == 0) return 0;
   const int threads = 256;
+  if (I % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)gu % 16 == 0) {
+    const size_t total_vec = total / 8;
+    const unsigned blocks = (unsigned)((total_vec + threads - 1) / threads);
+    ZI_DISPATCH_DTYPE(dtype, TT,
+                      swiglu_vec_kernel<TT><<<blocks, threads, 0, stream>>>((TT*)out, (const TT*)gu, I, total_vec));
+    return zi_check_launch("swiglu");
+  }
   const unsigned blocks = (unsigned)((total + threads - 1) / threads);
   ZI_DISPATCH_DTYPE(dtype, TT, swiglu_kernel<TT><<<blocks, threads, 0, stream>>>((TT*)out, (const TT*)gu, I, total));
   return zi_check_launch("swiglu");
@@ -136,27 +304,38 @@ extern "C" int zi_rope_table(float* cos_t, float* sin_t, int n_pos, int d, float
 
 // ------------------------------------------- q/k RMSNorm + rotary + write into pages
 // One warp per (token, head) of the fused projection row [q heads | k heads | v heads].
-// q heads: normed, rotated, written back in place.  k heads: normed, rotated, written
-// to the key page slot of the token.  v heads: copied to the value page slot.
-// Pages are [page][kv head][offset in page][d].
+// q heads: normed, rotated, written to q_out (which may be the source itself).  k heads:
+// normed, rotated, written to the key page slot of the token.  v heads: copied to the
+// value page slot.  The source row is either `src` (activation dtype) or split-K partial
+// sums part[z][t][width] that are added in order.  Pages are [page][kv head][offset][d].
 template <typename T>
-__global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, int nq, int nkv, int d,
-                                          const float* __restrict__ qw, const float* __restrict__ kw, float eps,
-                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                                          int n_table_pos, const int* __restrict__ positions,
-                                          T* __restrict__ kcache, T* __restrict__ vcache,
-                                          const int* __restrict__ slots, int page_size, int write_kv) {
+__global__ void qk_norm_rope_store_kernel(const T* src, int src_stride, const float* __restrict__ part,
+                                          int splits, size_t zstride, int part_width, T* q_out,
+                                          int q_stride, int nq, int nkv, int d, const float* __restrict__ qw,
+                                          const float* __restrict__ kw, float eps, const float* __restrict__ cos_t,
+                                          const float* __restrict__ sin_t, int n_table_pos,
+                                          const int* __restrict__ positions, T* __restrict__ kcache,
+                                          T* __restrict__ vcache, const int* __restrict__ slots, int page_size,
+                                          int write_kv) {
   const int t = blockIdx.x;
   const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   const int n_heads = nq + (write_kv ? 2 * nkv : 0);
   if (head >= n_heads) return;
-  T* src = qkv + (size_t)t * row_stride + (size_t)head * d;
   const int half = d >> 1;
+  auto load = [&](int i) -> float {
+    if (part) {
+      const float* p = part + (size_t)t * part_width + (size_t)head * d + i;
+      float v = 0.f;
+      for (int z = 0; z < splits; ++z) v += p[z * zstride];
+      return v;
+    }
+    return to_f32(src[(size_t)t * src_stride + (size_t)head * d + i]);
+  };
 
   T* dst;
   if (head < nq) {
-    dst = src;
+    dst = q_out + (size_t)t * q_stride + (size_t)head * d;
   } else {
     const int slot = slots[t];
     if (slot < 0) return;
@@ -165,7 +344,7 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, i
     dst = base + (((size_t)(slot / page_size) * nkv + kvh) * page_size + (slot % page_size)) * d;
   }
   if (head >= nq + nkv) {  // value head: copy
-    for (int i = lane; i < d; i += 32) dst[i] = src[i];
+    for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(load(i));
     return;
   }
   const float* w = head < nq ? qw : kw;
@@ -173,7 +352,7 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, i
   if (w) {
     float ss = 0.f;
     for (int i = lane; i < d; i += 32) {
-      const float v = to_f32(src[i]);
+      const float v = load(i);
       ss += v * v;
     }
     ss = warp_sum(ss);
@@ -182,7 +361,7 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, i
   int pos = positions[t];
   if (pos >= n_table_pos) pos = n_table_pos - 1;  // the host refuses such positions
   for (int i = lane; i < half; i += 32) {
-    float a = to_f32(src[i]), b = to_f32(src[i + half]);
+    float a = load(i), b = load(i + half);
     if (w) {
       a = a * w[i] * inv;
       b = b * w[i + half] * inv;
@@ -198,21 +377,42 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, i
   }
 }
 
-extern "C" int zi_qk_norm_rope_store(void* qkv, int dtype, int T, int row_stride, int nq, int nkv, int d,
-                                     const float* qw, const float* kw, float eps, const float* cos_t,
+extern "C" int zi_qk_norm_rope_store(const void* src, int dtype, int T, int src_stride, const float* partials,
+                                     int splits, long long split_stride, void* q_out, int q_stride, int nq, int nkv,
+                                     int d, const float* qw, const float* kw, float eps, const float* cos_t,
                                      const float* sin_t, int n_table_pos, const int* positions, void* kcache,
                                      void* vcache, const int* slots, int page_size, int write_kv,
                                      cudaStream_t stream) {
   if (T <= 0) return 0;
   if (d <= 0 || d % 2) return zi_refuse("qk_norm_rope_store: head_dim %d is not even", d);
   if ((cos_t == nullptr) != (sin_t == nullptr)) return zi_refuse("qk_norm_rope_store: cos and sin tables go together");
+  if ((src == nullptr) == (partials == nullptr)) return zi_refuse("qk_norm_rope_store: give the rows either whole or as partial sums");
   if (write_kv && (!kcache || !vcache || !slots || page_size <= 0))
     return zi_refuse("qk_norm_rope_store: writing keys and values needs pages and slots");
   const int n_heads = nq + (write_kv ? 2 * nkv : 0);
   const int warps = 4;
   dim3 grid(T, (n_heads + warps - 1) / warps);
   ZI_DISPATCH_DTYPE(dtype, TT, qk_norm_rope_store_kernel<TT><<<grid, warps * 32, 0, stream>>>(
-                                   (TT*)qkv, row_stride, nq, nkv, d, qw, kw, eps, cos_t, sin_t, n_table_pos,
-                                   positions, (TT*)kcache, (TT*)vcache, slots, page_size, write_kv));
+                                   (const TT*)src, src_stride, partials, splits, (size_t)split_stride, n_heads * d,
+                                   (TT*)q_out, q_stride, nq, nkv, d, qw, kw, eps, cos_t, sin_t, n_table_pos, positions,
+                                   (TT*)kcache, (TT*)vcache, slots, page_size, write_kv));
   return zi_check_launch("qk_norm_rope_store");
+}
+
+// h[i] += sum over splits of part[z][i], in order of z (for consumers that take no partial sums).
+__global__ void residual_add_partials_kernel(float* __restrict__ h, const float* __restrict__ part, int splits,
+                                             size_t zstride, size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float d = 0.f;
+  for (int z = 0; z < splits; ++z) d += part[z * zstride + i];
+  h[i] += d;
+}
+
+extern "C" int zi_residual_add_partials(float* h, const float* partials, int splits, long long split_stride,
+                                        long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  residual_add_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(h, partials, splits,
+                                                                             (size_t)split_stride, (size_t)n);
+  return zi_check_launch("residual_add_partials");
 }

@@ -108,14 +108,15 @@ __device__ __forceinline__ uint32_t instr_desc_bf16(int m, int n) {
 
 // -------------------------------------------------------------------- the kernel
 // A side: a_rows x K through map_a (box 64 x 128).  B side: b_rows x K through map_b
-// (box 64 x BN).  Element (a, b) goes to out[a * sa + b * sb], or, with split-K, to
-// partial[(z * a_rows + a) * b_ld + b] as float.
+// (box 64 x BN).  Element (a, b) goes to out[a * sa + b * sb], or, with split-K, as a
+// float to partial[z * a_rows * b_rows + a * pa + b * pb]: the partial sums of split z
+// lie as a [tokens, out features] matrix whichever side the tokens are on.
 template <typename TO>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     TO* __restrict__ out, float* __restrict__ partial, int a_rows, int b_rows, int k_blocks,
-                    int k_blocks_per_split, long long sa, long long sb, int BN, int stages, int tmem_cols,
-                    int* __restrict__ status) {
+                    int k_blocks_per_split, long long sa, long long sb, long long pa, long long pb, int BN, int stages,
+                    int tmem_cols, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int stage_bytes = A_TILE_BYTES + BN * BLOCK_K * 2;
@@ -197,10 +198,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int b0 = b_tile * BN + c0;
         if (a < a_rows) {
           if (partial) {
-            float* p = partial + ((size_t)split * a_rows + a) * (size_t)b_rows + b0;
+            float* p = partial + (size_t)split * a_rows * b_rows + (long long)a * pa + (long long)b0 * pb;
 #pragma unroll
             for (int j = 0; j < 16; ++j)
-              if (b0 + j < b_rows) p[j] = v[j];
+              if (b0 + j < b_rows) p[(long long)j * pb] = v[j];
           } else {
             TO* o = out + (long long)a * sa + (long long)b0 * sb;
 #pragma unroll
@@ -224,17 +225,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
 }
 
-// out[a * sa + b * sb] = sum over splits of partial[(z * a_rows + a) * b_rows + b], in order of z.
+// out[m * ldo + n] = sum over splits of partial[z][m][n], in order of z.
 template <typename TO>
-__global__ void splitk_reduce_kernel(TO* __restrict__ out, const float* __restrict__ partial, int a_rows, int b_rows,
-                                     int splits, long long sa, long long sb) {
+__global__ void splitk_reduce_kernel(TO* __restrict__ out, const float* __restrict__ partial, int M, int N,
+                                     int splits, long long ldo) {
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const size_t total = (size_t)a_rows * b_rows;
+  const size_t total = (size_t)M * N;
   if (idx >= total) return;
   float acc = 0.f;
   for (int z = 0; z < splits; ++z) acc += partial[(size_t)z * total + idx];
-  const int a = (int)(idx / b_rows), b = (int)(idx % b_rows);
-  out[(long long)a * sa + (long long)b * sb] = from_f32<TO>(acc);
+  const int m = (int)(idx / N), n = (int)(idx % N);
+  out[(long long)m * ldo + n] = from_f32<TO>(acc);
 }
 
 // ------------------------------------------------------------------- tensor maps
@@ -335,15 +336,21 @@ extern "C" long long zi_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int
     const int target = 2 * sm_count;
     while (tiles * splits < target && splits < 16 && k_blocks / (splits * 2) >= 8) splits *= 2;
   }
+  if (splits > 1) {  // the number of splits that get at least one k-block
+    const int kbps = (k_blocks + splits - 1) / splits;
+    splits = (k_blocks + kbps - 1) / kbps;
+  }
   plan[0] = swap;
   plan[1] = BN;
   plan[2] = splits;
   return splits > 1 ? (long long)splits * M * N * (long long)sizeof(float) : 0;
 }
 
+// With `defer_reduce` and a split product, the partial sums are left in `workspace` as
+// [splits, M, N] floats for a consumer that adds them itself, and `out` is not written.
 extern "C" int zi_gemm_tcgen05(void* out, int out_dtype, const void* x, const void* w, int M, int N, int K, int ldx,
                                int ldw, int ldo, float* workspace, long long workspace_bytes, int sm_count,
-                               cudaStream_t stream) {
+                               int defer_reduce, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (!zi_gemm_tcgen05_supported(x, w, K, ldx, ldw))
     return zi_refuse("gemm_tcgen05: operands must be 16-byte aligned bfloat16 with row pitches in multiples of 8");
@@ -370,6 +377,7 @@ extern "C" int zi_gemm_tcgen05(void* out, int out_dtype, const void* x, const vo
   const size_t smem = 1024 + (size_t)stages * stage_bytes + (2 * stages + 1) * sizeof(uint64_t) + 16;
   const int tmem_cols = BN < 32 ? 32 : BN;
   const long long sa = swap ? 1 : ldo, sb = swap ? ldo : 1;
+  const long long pa = swap ? 1 : N, pb = swap ? N : 1;
   dim3 grid((a_rows + TILE_A - 1) / TILE_A, (b_rows + BN - 1) / BN, real_splits);
   float* partial = real_splits > 1 ? workspace : nullptr;
 
@@ -377,14 +385,14 @@ extern "C" int zi_gemm_tcgen05(void* out, int out_dtype, const void* x, const vo
     auto kern = gemm_tcgen05_kernel<TO>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return zi_refuse("gemm_tcgen05: cannot get %zu bytes of shared memory", smem);
-    kern<<<grid, THREADS, smem, stream>>>(map_a, map_b, (TO*)out, partial, a_rows, b_rows, k_blocks, kbps, sa, sb, BN,
-                                          stages, tmem_cols, status);
+    kern<<<grid, THREADS, smem, stream>>>(map_a, map_b, (TO*)out, partial, a_rows, b_rows, k_blocks, kbps, sa, sb, pa, pb,
+                                          BN, stages, tmem_cols, status);
     int rc = zi_check_launch("gemm_tcgen05");
     if (rc) return rc;
-    if (partial) {
-      const size_t total = (size_t)a_rows * b_rows;
-      splitk_reduce_kernel<TO><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((TO*)out, partial, a_rows, b_rows,
-                                                                                  real_splits, sa, sb);
+    if (partial && !defer_reduce) {
+      const size_t total = (size_t)M * N;
+      splitk_reduce_kernel<TO><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((TO*)out, partial, M, N,
+                                                                                  real_splits, ldo);
       rc = zi_check_launch("splitk_reduce");
       if (rc) return rc;
     }
@@ -497,6 +505,7 @@ extern "C" int zi_gemm_tcgen05_static_scratch(void* out, int out_dtype, const vo
   const size_t smem = 1024 + (size_t)stages * stage_bytes + (2 * stages + 1) * sizeof(uint64_t) + 16;
   const int tmem_cols = BN < 32 ? 32 : BN;
   const long long sa = swap ? 1 : ldo, sb = swap ? ldo : 1;
+  const long long pa = swap ? 1 : N, pb = swap ? N : 1;
   dim3 grid((a_rows + TILE_A - 1) / TILE_A, (b_rows + BN - 1) / BN, real_splits);
   float* partial = real_splits > 1 ? ss.scratch : nullptr;
 
@@ -504,14 +513,14 @@ extern "C" int zi_gemm_tcgen05_static_scratch(void* out, int out_dtype, const vo
     auto kern = gemm_tcgen05_kernel<TO>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return zi_refuse("gemm_static_scratch: cannot get %zu bytes of shared memory", smem);
-    kern<<<grid, THREADS, smem, stream>>>(map_a, map_b, (TO*)out, partial, a_rows, b_rows, k_blocks, kbps, sa, sb, BN,
-                                          stages, tmem_cols, status);
+    kern<<<grid, THREADS, smem, stream>>>(map_a, map_b, (TO*)out, partial, a_rows, b_rows, k_blocks, kbps, sa, sb, pa, pb,
+                                          BN, stages, tmem_cols, status);
     int rc = zi_check_launch("gemm_static_scratch");
     if (rc) return rc;
     if (partial) {
-      const size_t total = (size_t)a_rows * b_rows;
-      splitk_reduce_kernel<TO><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((TO*)out, partial, a_rows, b_rows,
-                                                                                  real_splits, sa, sb);
+      const size_t total = (size_t)M * N;
+      splitk_reduce_kernel<TO><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((TO*)out, partial, M, N,
+                                                                                  real_splits, ldo);
       rc = zi_check_launch("gemm_static_scratch (reduce)");
       if (rc) return rc;
     }

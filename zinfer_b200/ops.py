@@ -90,6 +90,32 @@ def _i32(t: torch.Tensor, name: str) -> torch.Tensor:
     return t
 
 
+class Partials:
+    """A split-K matrix product whose partial sums have not been added yet:
+    ``data`` [splits, M, N] float32.  The consumers below (residual add + norm, SwiGLU,
+    q/k norm + rotary) add the splits themselves, in order, which saves a kernel and a
+    round trip through memory; ``sum(dtype)`` adds them for any other consumer."""
+
+    def __init__(self, data: torch.Tensor):
+        self.data = data
+
+    @property
+    def shape(self):
+        return self.data.shape[1:]
+
+    @property
+    def splits(self) -> int:
+        return self.data.shape[0]
+
+    def sum(self, dtype: torch.dtype) -> torch.Tensor:
+        out = torch.empty(tuple(self.shape), dtype=dtype, device=self.data.device)
+        S, M, N = self.data.shape
+        h = torch.zeros((M, N), dtype=torch.float32, device=self.data.device)
+        _check(lib().zi_residual_add_partials(_ptr(h), _ptr(self.data), S, ctypes.c_longlong(M * N),
+                                              ctypes.c_longlong(M * N), _stream()), "partials.sum")
+        return h if dtype == torch.float32 else h.to(dtype)
+
+
 # ------------------------------------------------------------------ elementwise
 def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Rows ``ids`` of ``table`` [V, H] as the 32-bit residual stream [T, H]."""
@@ -112,25 +138,41 @@ def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
     T, H = h.shape
     _need(h.dtype == torch.float32 and h.is_contiguous(), "the residual stream is contiguous float32")
     _need(weight.dtype == torch.float32 and weight.numel() == H, "norm weight must be float32 of the row's width")
-    if delta is not None:
+    part, splits, zstride = None, 0, 0
+    if isinstance(delta, Partials):
+        _need(tuple(delta.shape) == tuple(h.shape), "delta must match the residual stream")
+        part, splits, zstride, delta = delta.data, delta.splits, T * H, None
+    elif delta is not None:
         _need(delta.shape == h.shape and delta.is_contiguous(), "delta must match the residual stream")
     n = T if rows is None else _i32(rows, "rows").shape[0]
     if out is None:
         out = torch.empty((n, H), dtype=out_dtype, device=h.device)
-    _check(lib().zi_add_rmsnorm(_ptr(h), _ptr(delta), _tag(delta) if delta is not None else F32, _ptr(weight),
-                                ctypes.c_float(eps), _ptr(out), _tag(out), _ptr(rows), n, H, _stream()), "add_rmsnorm")
+    _check(lib().zi_add_rmsnorm(_ptr(h), _ptr(delta), _tag(delta) if delta is not None else F32, _ptr(part), splits,
+                                ctypes.c_longlong(zstride), _ptr(weight), ctypes.c_float(eps), _ptr(out), _tag(out),
+                                _ptr(rows), n, H, _stream()), "add_rmsnorm")
     return out
 
 
-def residual_add(h: torch.Tensor, delta: torch.Tensor) -> None:
+def residual_add(h: torch.Tensor, delta) -> None:
+    if isinstance(delta, Partials):
+        delta = delta.sum(torch.float32)
     _need(h.dtype == torch.float32 and h.is_contiguous() and delta.is_contiguous() and delta.shape == h.shape,
           "residual_add: shapes must match and be contiguous")
     _check(lib().zi_residual_add(_ptr(h), _ptr(delta), _tag(delta), ctypes.c_longlong(h.numel()), _stream()),
            "residual_add")
 
 
-def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def swiglu(gate_up, out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """``silu(gate) * up`` for ``gate_up`` [T, 2I] holding gate then up."""
+    if isinstance(gate_up, Partials):
+        T, two_i = gate_up.shape
+        I = two_i // 2
+        if I % 4 == 0:
+            res = torch.empty((T, I), dtype=out_dtype or torch.bfloat16, device=gate_up.data.device)
+            _check(lib().zi_swiglu_partials(_ptr(res), _tag(res), _ptr(gate_up.data), gate_up.splits,
+                                            ctypes.c_longlong(T * two_i), T, I, _stream()), "swiglu")
+            return res
+        gate_up = gate_up.sum(out_dtype or torch.bfloat16)
     T, two_i = gate_up.shape
     _need(two_i % 2 == 0 and gate_up.is_contiguous(), "swiglu input is contiguous [T, 2I]")
     I = two_i // 2
@@ -147,18 +189,29 @@ def rope_table(n_pos: int, head_dim: int, theta: float, device) -> tuple[torch.T
     return cos, sin
 
 
-def qk_norm_rope_store(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+def qk_norm_rope_store(qkv, num_heads: int, num_kv_heads: int, head_dim: int,
                        q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                        cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], positions: torch.Tensor,
                        k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
-                       slots: Optional[torch.Tensor], page_size: int, write_kv: bool = True) -> None:
-    """In place on the fused projection rows [q heads | k heads | v heads]: per-head
-    RMSNorm of q and k (when weights are given), rotary positions (when tables are
-    given), q back into ``qkv``, k and v into their page slots."""
-    T = qkv.shape[0]
-    _need(qkv.stride(1) == 1, "qkv rows must be dense")
+                       slots: Optional[torch.Tensor], page_size: int, write_kv: bool = True,
+                       out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """On the fused projection rows [q heads | k heads | v heads]: per-head RMSNorm of q
+    and k (when weights are given), rotary positions (when tables are given); k and v go
+    into their page slots.  Returns q [T, >= heads * d]: ``qkv`` itself, rewritten in
+    place, or a new tensor when ``qkv`` came as split-K partial sums."""
     width = (num_heads + 2 * num_kv_heads) * head_dim if write_kv else num_heads * head_dim
-    _need(qkv.shape[1] >= width, "qkv is narrower than its heads")
+    part, splits, zstride = None, 0, 0
+    if isinstance(qkv, Partials):
+        T = qkv.shape[0]
+        _need(qkv.shape[1] == width, "partial sums must have exactly the heads' width")
+        part, splits, zstride = qkv.data, qkv.splits, T * width
+        q_out = torch.empty((T, num_heads * head_dim), dtype=out_dtype or torch.bfloat16, device=part.device)
+        src, src_stride, dtype_tag = None, 0, _tag(q_out)
+    else:
+        T = qkv.shape[0]
+        _need(qkv.stride(1) == 1, "qkv rows must be dense")
+        _need(qkv.shape[1] >= width, "qkv is narrower than its heads")
+        q_out, src, src_stride, dtype_tag = qkv, qkv, qkv.stride(0), _tag(qkv)
     for wt in (q_weight, k_weight):
         if wt is not None:
             _need(wt.dtype == torch.float32 and wt.numel() == head_dim, "q/k norm weights are float32 [head_dim]")
@@ -170,12 +223,14 @@ def qk_norm_rope_store(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, hea
     _i32(positions, "positions")
     if write_kv:
         _need(k_cache is not None and v_cache is not None and slots is not None, "writing needs pages and slots")
-        _need(k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype, "cache pages have the activations' dtype")
+        _need(k_cache.dtype == q_out.dtype and v_cache.dtype == q_out.dtype, "cache pages have the activations' dtype")
         _i32(slots, "slots")
     _check(lib().zi_qk_norm_rope_store(
-        _ptr(qkv), _tag(qkv), T, qkv.stride(0), num_heads, num_kv_heads, head_dim, _ptr(q_weight), _ptr(k_weight),
-        ctypes.c_float(eps), _ptr(cos), _ptr(sin), n_table, _ptr(positions), _ptr(k_cache), _ptr(v_cache),
-        _ptr(slots), page_size, 1 if write_kv else 0, _stream()), "qk_norm_rope_store")
+        _ptr(src), dtype_tag, T, src_stride, _ptr(part), splits, ctypes.c_longlong(zstride), _ptr(q_out),
+        q_out.stride(0), num_heads, num_kv_heads, head_dim, _ptr(q_weight), _ptr(k_weight), ctypes.c_float(eps),
+        _ptr(cos), _ptr(sin), n_table, _ptr(positions), _ptr(k_cache), _ptr(v_cache), _ptr(slots), page_size,
+        1 if write_kv else 0, _stream()), "qk_norm_rope_store")
+    return q_out
 
 
 # ------------------------------------------------------------------------ matrices
@@ -191,8 +246,11 @@ def _sm_count(device: torch.device) -> int:
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+           out: Optional[torch.Tensor] = None, allow_partials: bool = False):
     """``x [M, K] @ weight [N, K]^T`` with 32-bit accumulation.
+
+    With ``allow_partials`` a product that was split along K may come back as
+    :class:`Partials` (its consumer adds the splits) instead of a tensor.
 
     bfloat16 operands that meet TMA's alignment rules go to the tcgen05 kernel; float32
     operands (the true 32-bit path), mixed types and unaligned shapes go to the
@@ -201,18 +259,22 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     N, K2 = weight.shape
     _need(K == K2, f"linear: x has {K} columns, weight has {K2}")
     _need(x.stride(1) == 1 and weight.is_contiguous(), "linear: operands must be dense along K")
-    if out is None:
-        out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
-    _need(out.stride(1) == 1, "linear: output rows must be dense")
     if (GEMM_BACKEND != "simt" and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and M > 0
             and lib().zi_gemm_tcgen05_supported(_ptr(x), _ptr(weight), K, x.stride(0), weight.stride(0))):
         plan = (ctypes.c_int * 3)()
         sms = _sm_count(x.device)
         need = lib().zi_gemm_tcgen05_plan(M, N, K, sms, plan)
         ws = torch.empty((need // 4,), dtype=torch.float32, device=x.device) if need else None
-        _check(lib().zi_gemm_tcgen05(_ptr(out), _tag(out), _ptr(x), _ptr(weight), M, N, K, x.stride(0), weight.stride(0),
-                                     out.stride(0), _ptr(ws), ctypes.c_longlong(need), sms, _stream()), "linear (tcgen05)")
-        return out
+        defer = allow_partials and need > 0 and out is None
+        if out is None and not defer:
+            out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+        _check(lib().zi_gemm_tcgen05(_ptr(out), _tag(out) if out is not None else BF16, _ptr(x), _ptr(weight), M, N, K,
+                                     x.stride(0), weight.stride(0), out.stride(0) if out is not None else N, _ptr(ws),
+                                     ctypes.c_longlong(need), sms, 1 if defer else 0, _stream()), "linear (tcgen05)")
+        return Partials(ws.view(plan[2], M, N)) if defer else out
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+    _need(out.stride(1) == 1, "linear: output rows must be dense")
     _check(lib().zi_gemm_simt(_ptr(out), _tag(out), _ptr(x), _tag(x), _ptr(weight), _tag(weight), M, N, K,
                               x.stride(0), weight.stride(0), out.stride(0), _stream()), "linear")
     return out
@@ -288,7 +350,8 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, blo
             "attention (prefill)")
     if step.n_dec > 0:
         sms = _sm_count(q.device)
-        splits = max(1, min(32, -(-2 * sms // (step.n_dec * num_kv_heads))))
+        # as many splits as keep all CTAs resident at once (two per SM): one wave, no tail
+        splits = max(1, min(32, (2 * sms) // (step.n_dec * num_kv_heads)))
         if step.max_kv_len:  # known on the host: no more splits than tiles of 64 keys
             splits = min(splits, max(1, -(-step.max_kv_len // 64)))
         need = L.zi_attention_decode_workspace_floats(step.n_dec, num_heads, num_kv_heads, head_dim, splits)

@@ -72,13 +72,13 @@ class GQAttention(Mixer):
     def forward(self, x, step, cache):
         q_width = self.nq * self.d
         w = self.w_qkv if cache.writes else self.w_qkv[:q_width]  # a reader of another's cache needs q only
-        qkv = ops.linear(x, w, out_dtype=self.ctx.dtype)
+        qkv = ops.linear(x, w, out_dtype=self.ctx.dtype, allow_partials=True)
         group = step.kv_groups[cache.group]
         cos, sin = self.position.tables() if self.position is not None else (None, None)
-        ops.qk_norm_rope_store(
+        q = ops.qk_norm_rope_store(
             qkv, self.nq, self.nkv, self.d, self.q_norm, self.k_norm,
             self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, cos, sin, step.positions,
-            cache.k, cache.v, group.slot_mapping, cache.page_size, write_kv=cache.writes)
-        o = ops.attention(qkv, cache.k, cache.v, group.block_tables, step, self.nq, self.nkv, self.d,
+            cache.k, cache.v, group.slot_mapping, cache.page_size, write_kv=cache.writes, out_dtype=self.ctx.dtype)
+        o = ops.attention(q, cache.k, cache.v, group.block_tables, step, self.nq, self.nkv, self.d,
                           cache.page_size, self.window, self.scale)
-        return ops.linear(o, self.w_o, out_dtype=self.ctx.dtype)
+        return ops.linear(o, self.w_o, out_dtype=self.ctx.dtype, allow_partials=True)

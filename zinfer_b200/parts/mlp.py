@@ -32,5 +32,7 @@ class SwiGLUMLP(FeedForward):
         self.w_down = tensors["down_proj.weight"].contiguous()
 
     def forward(self, x):
-        gu = ops.linear(x, self.w_gate_up, out_dtype=self.ctx.dtype)
-        return ops.linear(ops.swiglu(gu), self.w_down, out_dtype=self.ctx.dtype)
+        gu = ops.linear(x, self.w_gate_up, out_dtype=self.ctx.dtype, allow_partials=True)
+        act = ops.swiglu(gu, out_dtype=self.ctx.dtype)
+        # the product may come back as split-K partial sums; the next norm adds them with the residual
+        return ops.linear(act, self.w_down, out_dtype=self.ctx.dtype, allow_partials=True)
