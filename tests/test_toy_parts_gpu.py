@@ -1,0 +1,218 @@
+"""Generality of the parts, shown with toy parts that exist only in this test: a mixer
+with a fixed-size state of its own, a model whose layers differ (window attention, the
+stateful mixer, full attention), a schedule that names a layer twice and lets a run
+read the cache another run wrote.  Everything is registered, built and stepped through
+the framework's public interfaces, with no change to its files, and compared with a
+plain whole-sequence computation written here."""
+from dataclasses import asdict, dataclass
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+import replay_util as ru
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+F64 = torch.float64
+
+
+# ----------------------------------------------------------------- the toy mixer
+def _make_ema_mixer():
+    from zinfer_b200.parts import Mixer, StateNeed, TensorSpec
+
+    class EmaMixer(Mixer):
+        """s_t = decay * s_{t-1} + W_in x_t ; y_t = W_out s_t.  Its only memory is s, one
+        vector per request, kept in the cache manager's per-request state slots."""
+
+        def __init__(self, params, ctx):
+            super().__init__(params, ctx)
+            self.hidden = int(params["hidden_size"])
+            self.decay = float(params["decay"])
+
+        def tensor_specs(self):
+            return {"in_proj.weight": TensorSpec((self.hidden, self.hidden)),
+                    "out_proj.weight": TensorSpec((self.hidden, self.hidden))}
+
+        def bind(self, tensors):
+            self.w_in = tensors["in_proj.weight"].float()
+            self.w_out = tensors["out_proj.weight"].float()
+
+        def cache_need(self):
+            return StateNeed((self.hidden,), torch.float32)
+
+        def forward(self, x, step, cache):
+            u = x.float() @ self.w_in.T
+            y = torch.empty_like(u)
+            slots = step.state_slots.tolist()
+            start = 0
+            for i, n in enumerate(step.q_lens):        # a request's tokens are scanned in order
+                s = cache.state[slots[i]]
+                for t in range(start, start + n):
+                    s = self.decay * s + u[t]
+                    y[t] = s
+                cache.state[slots[i]] = s
+                start += n
+            return (y @ self.w_out.T).to(x.dtype)
+
+    return EmaMixer
+
+
+@dataclass(frozen=True)
+class ToyConfig:
+    vocab_size: int = 211
+    hidden_size: int = 80
+    intermediate_size: int = 112
+    num_heads: int = 5
+    num_kv_heads: int = 1
+    head_dim: int = 32
+    window: int = 9
+    decay: float = 0.7
+    eps: float = 2e-6
+    theta: float = 3000.0
+    max_positions: int = 256
+    model_type: str = "toy_hybrid"
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(**{k: v for k, v in d.items() if k in cls.__dataclass_fields__})
+
+    def to_dict(self):
+        return {**asdict(self), "architectures": ["ToyHybridForCausalLM"]}
+
+
+def toy_model_spec(cfg: ToyConfig):
+    from zinfer_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+
+    norm = PartSpec("rmsnorm", {"size": cfg.hidden_size, "eps": cfg.eps})
+    rope = PartSpec("rope", {"head_dim": cfg.head_dim, "theta": cfg.theta, "max_positions": cfg.max_positions})
+    ffn = PartSpec("swiglu_mlp", {"hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size})
+
+    def attn(window, qk_norm):
+        return PartSpec("gqa_attention", {"hidden_size": cfg.hidden_size, "num_heads": cfg.num_heads,
+                                          "num_kv_heads": cfg.num_kv_heads, "head_dim": cfg.head_dim,
+                                          "qk_norm_eps": cfg.eps if qk_norm else None, "window": window, "position": rope})
+
+    def block(mixer):
+        return PartSpec("prenorm_block", {"mixer": mixer, "mixer_norm": norm, "feed_forward": ffn, "ffn_norm": norm})
+
+    mixers = [attn(cfg.window, True), PartSpec("toy_ema_mixer", {"hidden_size": cfg.hidden_size, "decay": cfg.decay}),
+              attn(None, False)]
+    layers = tuple(LayerSpec(block(m), prefix=f"layers.{i}.") for i, m in enumerate(mixers))
+    # layer 1 runs twice (each run with a state of its own); the last run of layer 2 reads the keys
+    # and values that its first run wrote
+    schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2, cache="shared"), ScheduleEntry(1),
+                ScheduleEntry(2, cache="shared"))
+    return ModelSpec(
+        architecture="ToyHybridForCausalLM", vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size,
+        max_positions=cfg.max_positions,
+        embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size, "name": "embed"}),
+        layers=layers, schedule=schedule, final_norm=PartSpec("rmsnorm", {"size": cfg.hidden_size, "eps": cfg.eps, "name": "norm"}),
+        head=PartSpec("lm_head", {"vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size, "name": "head", "tied_to": None}))
+
+
+# -------------------------------------------------------- the plain computation
+def plain_toy_forward(cfg: ToyConfig, w, tokens):
+    S = len(tokens)
+    cos, sin = P.rope_tables(S, cfg.head_dim, cfg.theta)
+    h = w["embed.weight"][torch.as_tensor(tokens)]
+    shared_kv = {}
+
+    def attention_layer(x, i, window, qk_norm, reuse):
+        p = f"layers.{i}.mixer."
+        q = (x @ w[p + "q_proj.weight"].T).reshape(S, cfg.num_heads, cfg.head_dim)
+        if qk_norm:
+            q = P.rmsnorm(q, w[p + "q_norm.weight"], cfg.eps)
+        q = P.apply_rope(q, cos, sin)
+        if reuse and "kv" in shared_kv:
+            k, v = shared_kv["kv"]
+        else:
+            k = (x @ w[p + "k_proj.weight"].T).reshape(S, cfg.num_kv_heads, cfg.head_dim)
+            v = (x @ w[p + "v_proj.weight"].T).reshape(S, cfg.num_kv_heads, cfg.head_dim)
+            if qk_norm:
+                k = P.rmsnorm(k, w[p + "k_norm.weight"], cfg.eps)
+            k = P.apply_rope(k, cos, sin)
+            if reuse:
+                shared_kv["kv"] = (k, v)
+        o = P.attention(q, k, v, window=window).reshape(S, -1)
+        return o @ w[p + "o_proj.weight"].T
+
+    def ema_layer(x, i):
+        p = f"layers.{i}.mixer."
+        u = x @ w[p + "in_proj.weight"].T
+        s = torch.zeros(cfg.hidden_size, dtype=F64)
+        ys = []
+        for t in range(S):
+            s = cfg.decay * s + u[t]
+            ys.append(s)
+        return torch.stack(ys) @ w[p + "out_proj.weight"].T
+
+    def run(h, i):
+        p = f"layers.{i}."
+        x = P.rmsnorm(h, w[p + "mixer_norm.weight"], cfg.eps)
+        if i == 0:
+            a = attention_layer(x, 0, cfg.window, True, False)
+        elif i == 1:
+            a = ema_layer(x, 1)
+        else:
+            a = attention_layer(x, 2, None, False, True)
+        h = h + a
+        x = P.rmsnorm(h, w[p + "ffn_norm.weight"], cfg.eps)
+        g = x @ w[p + "feed_forward.gate_proj.weight"].T
+        u = x @ w[p + "feed_forward.up_proj.weight"].T
+        return h + P.swiglu(g, u) @ w[p + "feed_forward.down_proj.weight"].T
+
+    for i in (0, 1, 2, 1, 2):
+        h = run(h, i)
+    return (P.rmsnorm(h, w["norm.weight"], cfg.eps) @ w["head.weight"].T).numpy()
+
+
+@pytest.fixture
+def toy_registered():
+    from zinfer_b200.config import Family, register_family, unregister_family
+    from zinfer_b200.parts import register_part, unregister_part
+
+    register_part("toy_ema_mixer", _make_ema_mixer())
+    register_family(Family("ToyHybridForCausalLM", "toy_hybrid", ToyConfig, toy_model_spec))
+    yield
+    unregister_family("ToyHybridForCausalLM")
+    unregister_part("toy_ema_mixer")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_toy_hybrid_model_is_built_and_stepped(toy_registered, dtype):
+    from zinfer_b200.config import family_for
+    from zinfer_b200.engine import DecoderModel, ModelRunner
+    from zinfer_b200.weights import random_tensors
+
+    cfg = ToyConfig()
+    fam = family_for(cfg.to_dict())                       # found through the one registry
+    assert fam.name == "ToyHybridForCausalLM"
+    model = DecoderModel(fam.model_spec(cfg), dtype, DEV)
+    tensors = random_tensors(model.tensor_specs(), 77, dtype, DEV)
+    model.bind(tensors)
+    kv, state = model.cache_needs()
+    assert set(state) == {"run1", "run3"} and set(kv) == {"run0", "shared"}   # two states, two key caches
+    runner = ModelRunner(model, page_size=4, max_tokens=192, max_requests=3)
+    assert runner.graphs is None                           # a mixer that loops on the host is not captured
+    assert len(runner.manager.groups) == 2                 # windowed and full caches have pages of their own
+
+    w = {k: v.detach().cpu().to(F64) for k, v in tensors.items()}
+    reqs = ru.make_requests(cfg.vocab_size, [41, 7, 64, 30], seed=5)
+    plain = {rid: plain_toy_forward(cfg, w, toks) for rid, toks in reqs.items()}
+    tol = dict(rtol=5e-5, atol=1e-6) if dtype == torch.float32 else dict(rtol=3e-2, atol=1e-3)
+    for mode, trace in (("whole", ru.trace_whole(reqs)), ("tail", ru.trace_tail_decode(reqs, 20)),
+                        ("portions", ru.trace_portions(reqs, 4)), ("mixed", ru.trace_mixed(reqs, 9, max_live=3))):
+        got = ru.run_in_process(runner, trace)
+        ru.assert_close(got, plain, what=f"toy/{mode}", argmax_frac=0.0, **tol)
+        assert not runner.manager.requests
+    # the window gave pages back while requests were still running
+    runner.add_request("w")
+    from zinfer_b200.engine import StepEntry
+    runner.step([StepEntry("w", reqs["r2"][:40], [])])
+    windowed = next(i for i, g in enumerate(runner.manager.groups) if g.window is not None)
+    table = runner.manager.block_table("w", windowed)
+    assert table[:7] == [-1] * 7 and all(p >= 0 for p in table[8:])
+    runner.end_request("w")
+    runner.manager.check()
