@@ -23,6 +23,8 @@ paged_attention_kernel(T* __restrict__ out, int out_stride, const T* __restrict_
                        const int* __restrict__ kv_lens, const int* __restrict__ tile_seq,
                        const int* __restrict__ tile_q0, int nq, int nkv, int d, int page_size, int window,
                        float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float smem[];
   float* Qs = smem;                   // [BQ][d]
   float* Ks = Qs + BQ * d;            // [BK][d+1]
@@ -149,7 +151,7 @@ extern "C" int zi_paged_attention(void* out, int out_stride, const void* q, int 
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return zi_refuse("paged_attention: cannot get %zu bytes of shared memory", smem);
     }
-    kern<<<grid, THREADS, smem, stream>>>((TT*)out, out_stride, (const TT*)q, q_stride, (const TT*)kcache,
+    zi_launch(kern, dim3(grid), dim3(THREADS), smem, stream, (TT*)out, out_stride, (const TT*)q, q_stride, (const TT*)kcache,
                                           (const TT*)vcache, block_tables, bt_stride, cu_q, kv_lens, tile_seq,
                                           tile_q0, nq, nkv, d, page_size, window, scale);
   });

@@ -158,6 +158,8 @@ attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __re
                         const int* __restrict__ kv_lens, const int* __restrict__ tile_seq,
                         const int* __restrict__ tile_q0, int nq, int nkv, int page_size, int page_shift,
                         int window, float scale_log2) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* qs = smem;                                   // [128][D]
   uint8_t* kbuf = qs + PF_BQ * D * 2;                   // [2][64][D]
@@ -291,6 +293,8 @@ attn_decode_mma_kernel(bf16* __restrict__ out, int out_stride, float* __restrict
                        const int* __restrict__ cu_q, const int* __restrict__ kv_lens,
                        const int* __restrict__ dec_seq, int nq, int nkv, int page_size, int page_shift, int window,
                        float scale_log2, int splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int STAGES = DecodeCfg<D>::STAGES;
   constexpr int ROWS_BYTES = DC_KEYS * D * 2;                  // one warp's 16 keys of K (or V)
   constexpr int WARP_BYTES = STAGES * 2 * ROWS_BYTES;          // a warp's private ring
@@ -430,6 +434,8 @@ template <int D>
 __global__ void attn_decode_combine_kernel(bf16* __restrict__ out, int out_stride, const float* __restrict__ partial,
                                            const int* __restrict__ cu_q, const int* __restrict__ dec_seq, int nq,
                                            int nkv, int splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int dec = blockIdx.x, h = blockIdx.y;
   const int g = nq / nkv, kvh = h / g, r = h % g;
   const int token = cu_q[dec_seq[dec]];
@@ -465,7 +471,7 @@ int launch_prefill(void* out, int out_stride, const void* q, int q_stride, const
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return zi_refuse("attention_prefill: cannot get %zu bytes of shared memory", smem);
   dim3 grid(n_tiles, nq);
-  kern<<<grid, PF_THREADS, smem, stream>>>((bf16*)out, out_stride, (const bf16*)q, q_stride, (const bf16*)kc,
+  zi_launch(kern, dim3(grid), dim3(PF_THREADS), smem, stream, (bf16*)out, out_stride, (const bf16*)q, q_stride, (const bf16*)kc,
                                            (const bf16*)vc, bt, bt_stride, cu_q, kv_lens, tile_seq, tile_q0, nq, nkv,
                                            page_size, log2_or_minus1(page_size), window, scale * 1.4426950408889634f);
   return zi_check_launch("attention_prefill");
@@ -481,14 +487,14 @@ int launch_decode(void* out, int out_stride, float* partial, const void* q, int 
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return zi_refuse("attention_decode: cannot get %zu bytes of shared memory", smem);
   dim3 grid(n_dec, nkv, splits);
-  kern<<<grid, DC_THREADS, smem, stream>>>((bf16*)out, out_stride, splits > 1 ? partial : nullptr, (const bf16*)q,
+  zi_launch(kern, dim3(grid), dim3(DC_THREADS), smem, stream, (bf16*)out, out_stride, splits > 1 ? partial : nullptr, (const bf16*)q,
                                            q_stride, (const bf16*)kc, (const bf16*)vc, bt, bt_stride, cu_q, kv_lens,
                                            dec_seq, nq, nkv, page_size, log2_or_minus1(page_size), window,
                                            scale * 1.4426950408889634f, splits);
   int rc = zi_check_launch("attention_decode");
   if (rc) return rc;
   if (splits > 1) {
-    attn_decode_combine_kernel<D><<<dim3(n_dec, nq), D >= 128 ? 128 : 64, 0, stream>>>(
+    zi_launch(attn_decode_combine_kernel<D>, dim3(dim3(n_dec, nq)), dim3(D >= 128 ? 128 : 64), 0, stream, 
         (bf16*)out, out_stride, partial, cu_q, dec_seq, nq, nkv, splits);
     rc = zi_check_launch("attention_decode_combine");
   }

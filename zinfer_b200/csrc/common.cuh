@@ -54,6 +54,33 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
   return scratch[32];
 }
 
+// --------------------------------------------------- programmatic dependent launch
+// Every kernel is launched with programmatic stream serialization (unless switched off):
+// the next kernel of the stream may start its prologue while this one drains.  A kernel
+// therefore calls pdl_wait() before it reads anything an earlier kernel wrote (and every
+// kernel calls it once, so that completion stays transitive along the stream), and
+// pdl_launch_dependents() as soon as the next kernel may begin to start.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+extern int g_zi_pdl_enabled;
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t zi_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_zi_pdl_enabled ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 #define ZI_DISPATCH_DTYPE(dtype, T, ...)                                   \
   do {                                                                     \
     if ((dtype) == ZI_F32) { using T = float; __VA_ARGS__; }               \

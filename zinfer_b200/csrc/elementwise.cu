@@ -9,6 +9,8 @@
 template <typename T>
 __global__ void embed_gather_kernel(float* __restrict__ h, const T* __restrict__ table,
                                     const int* __restrict__ ids, int H, int V) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* out = h + (size_t)t * H;
@@ -24,7 +26,7 @@ extern "C" int zi_embed_gather(float* h, const void* table, int table_dtype, con
                                int V, cudaStream_t stream) {
   if (T <= 0) return 0;
   ZI_DISPATCH_DTYPE(table_dtype, TT,
-                    embed_gather_kernel<TT><<<T, 256, 0, stream>>>(h, (const TT*)table, ids, H, V));
+                    zi_launch(embed_gather_kernel<TT>, dim3(T), dim3(256), 0, stream, h, (const TT*)table, ids, H, V));
   return zi_check_launch("embed_gather");
 }
 
@@ -37,6 +39,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
                                    const float* __restrict__ dpart, int splits, size_t zstride,
                                    const float* __restrict__ w, float eps, TO* __restrict__ out,
                                    const int* __restrict__ rows, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   const int row = rows ? rows[r] : r;
@@ -98,6 +102,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restri
                                        const float* __restrict__ dpart, int splits, size_t zstride,
                                        const float* __restrict__ w, float eps, TO* __restrict__ out,
                                        const int* __restrict__ rows, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   const int row = rows ? rows[r] : r;
@@ -153,7 +159,7 @@ static int launch_add_rmsnorm(float* h, const void* delta, const float* dpart, i
   if (aligned && nvec <= threads * 8) {
     const int vpt = (nvec + threads - 1) / threads;
 #define ZI_LAUNCH_VPT(V)                                                                                      \
-  add_rmsnorm_vec_kernel<TD, TO, V><<<n_rows, threads, 0, stream>>>(h, (const TD*)delta, dpart, splits, zstride, w, eps, \
+  zi_launch(add_rmsnorm_vec_kernel<TD, TO, V>, dim3(n_rows), dim3(threads), 0, stream, h, (const TD*)delta, dpart, splits, zstride, w, eps, \
                                                                     (TO*)out, rows, H)
     if (vpt <= 1) ZI_LAUNCH_VPT(1);
     else if (vpt <= 2) ZI_LAUNCH_VPT(2);
@@ -162,7 +168,7 @@ static int launch_add_rmsnorm(float* h, const void* delta, const float* dpart, i
 #undef ZI_LAUNCH_VPT
   } else {
     const int t2 = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-    add_rmsnorm_kernel<TD, TO><<<n_rows, t2, 0, stream>>>(h, (const TD*)delta, dpart, splits, zstride, w, eps, (TO*)out,
+    zi_launch(add_rmsnorm_kernel<TD, TO>, dim3(n_rows), dim3(t2), 0, stream, h, (const TD*)delta, dpart, splits, zstride, w, eps, (TO*)out,
                                                           rows, H);
   }
   return zi_check_launch("add_rmsnorm");
@@ -183,6 +189,8 @@ extern "C" int zi_add_rmsnorm(float* h, const void* delta, int delta_dtype, cons
 // Plain add of the last pending update into the residual stream (rows optional).
 template <typename TD>
 __global__ void residual_add_kernel(float* __restrict__ h, const TD* __restrict__ delta, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) h[i] += to_f32(delta[i]);
 }
@@ -192,7 +200,7 @@ extern "C" int zi_residual_add(float* h, const void* delta, int delta_dtype, lon
   const int threads = 256;
   const unsigned blocks = (unsigned)((n + threads - 1) / threads);
   ZI_DISPATCH_DTYPE(delta_dtype, TD,
-                    residual_add_kernel<TD><<<blocks, threads, 0, stream>>>(h, (const TD*)delta, (size_t)n));
+                    zi_launch(residual_add_kernel<TD>, dim3(blocks), dim3(threads), 0, stream, h, (const TD*)delta, (size_t)n));
   return zi_check_launch("residual_add");
 }
 
@@ -200,6 +208,8 @@ extern "C" int zi_residual_add(float* h, const void* delta, int delta_dtype, lon
 // gu is [T, 2I]: gate in the first I columns, up in the last I.  out[t,i] = silu(g) * u.
 template <typename T>
 __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int I, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const size_t t = idx / I;
@@ -213,6 +223,8 @@ __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int
 template <typename T>
 __global__ void swiglu_partials_kernel(T* __restrict__ out, const float* __restrict__ part, int splits, size_t zstride,
                                        int I, size_t total_vec) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total_vec) return;
   const int per_row = I >> 2;
@@ -232,6 +244,8 @@ __global__ void swiglu_partials_kernel(T* __restrict__ out, const float* __restr
 // Eight elements per thread (16-byte loads of bfloat16, two of float); needs I % 8 == 0.
 template <typename T>
 __global__ void swiglu_vec_kernel(T* __restrict__ out, const T* __restrict__ gu, int I, size_t total_vec) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total_vec) return;
   const int per_row = I >> 3;
@@ -255,7 +269,7 @@ extern "C" int zi_swiglu_partials(void* out, int dtype, const float* partials, i
   if (I % 4 || (uintptr_t)partials % 16 || (uintptr_t)out % 8 || split_stride % 4)
     return zi_refuse("swiglu_partials: needs I %% 4 == 0 and aligned buffers");
   const size_t total_vec = total / 4;
-  ZI_DISPATCH_DTYPE(dtype, TT, swiglu_partials_kernel<TT><<<(unsigned)((total_vec + 255) / 256), 256, 0, stream>>>(
+  ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(swiglu_partials_kernel<TT>, dim3((unsigned)((total_vec + 255) / 256)), dim3(256), 0, stream, 
                                    (TT*)out, partials, splits, (size_t)split_stride, I, total_vec));
   return zi_check_launch("swiglu_partials");
 }
@@ -268,11 +282,11 @@ extern "C" int zi_swiglu(void* out, const void* gu, int dtype, int T, int I, cud
     const size_t total_vec = total / 8;
     const unsigned blocks = (unsigned)((total_vec + threads - 1) / threads);
     ZI_DISPATCH_DTYPE(dtype, TT,
-                      swiglu_vec_kernel<TT><<<blocks, threads, 0, stream>>>((TT*)out, (const TT*)gu, I, total_vec));
+                      zi_launch(swiglu_vec_kernel<TT>, dim3(blocks), dim3(threads), 0, stream, (TT*)out, (const TT*)gu, I, total_vec));
     return zi_check_launch("swiglu");
   }
   const unsigned blocks = (unsigned)((total + threads - 1) / threads);
-  ZI_DISPATCH_DTYPE(dtype, TT, swiglu_kernel<TT><<<blocks, threads, 0, stream>>>((TT*)out, (const TT*)gu, I, total));
+  ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(swiglu_kernel<TT>, dim3(blocks), dim3(threads), 0, stream, (TT*)out, (const TT*)gu, I, total));
   return zi_check_launch("swiglu");
 }
 
@@ -283,6 +297,8 @@ extern "C" int zi_swiglu(void* out, const void* gu, int dtype, int T, int I, cud
 // rounded value of each 32-bit step.
 __global__ void rope_table_kernel(float* __restrict__ cos_t, float* __restrict__ sin_t, int n_pos, int half,
                                   int d, float theta) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (size_t)n_pos * half) return;
   const int pos = (int)(idx / half), i = (int)(idx % half);
@@ -298,7 +314,7 @@ extern "C" int zi_rope_table(float* cos_t, float* sin_t, int n_pos, int d, float
   if (d <= 0 || d % 2) return zi_refuse("rope_table: head_dim %d is not even", d);
   const size_t total = (size_t)n_pos * (d / 2);
   if (total == 0) return 0;
-  rope_table_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(cos_t, sin_t, n_pos, d / 2, d, theta);
+  zi_launch(rope_table_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, cos_t, sin_t, n_pos, d / 2, d, theta);
   return zi_check_launch("rope_table");
 }
 
@@ -317,6 +333,8 @@ __global__ void qk_norm_rope_store_kernel(const T* src, int src_stride, const fl
                                           const int* __restrict__ positions, T* __restrict__ kcache,
                                           T* __restrict__ vcache, const int* __restrict__ slots, int page_size,
                                           int write_kv) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -392,7 +410,7 @@ extern "C" int zi_qk_norm_rope_store(const void* src, int dtype, int T, int src_
   const int n_heads = nq + (write_kv ? 2 * nkv : 0);
   const int warps = 4;
   dim3 grid(T, (n_heads + warps - 1) / warps);
-  ZI_DISPATCH_DTYPE(dtype, TT, qk_norm_rope_store_kernel<TT><<<grid, warps * 32, 0, stream>>>(
+  ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(qk_norm_rope_store_kernel<TT>, dim3(grid), dim3(warps * 32), 0, stream, 
                                    (const TT*)src, src_stride, partials, splits, (size_t)split_stride, n_heads * d,
                                    (TT*)q_out, q_stride, nq, nkv, d, qw, kw, eps, cos_t, sin_t, n_table_pos, positions,
                                    (TT*)kcache, (TT*)vcache, slots, page_size, write_kv));
@@ -402,6 +420,8 @@ extern "C" int zi_qk_norm_rope_store(const void* src, int dtype, int T, int src_
 // h[i] += sum over splits of part[z][i], in order of z (for consumers that take no partial sums).
 __global__ void residual_add_partials_kernel(float* __restrict__ h, const float* __restrict__ part, int splits,
                                              size_t zstride, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float d = 0.f;
@@ -412,7 +432,7 @@ __global__ void residual_add_partials_kernel(float* __restrict__ h, const float*
 extern "C" int zi_residual_add_partials(float* h, const float* partials, int splits, long long split_stride,
                                         long long n, cudaStream_t stream) {
   if (n <= 0) return 0;
-  residual_add_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(h, partials, splits,
+  zi_launch(residual_add_partials_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, h, partials, splits,
                                                                              (size_t)split_stride, (size_t)n);
   return zi_check_launch("residual_add_partials");
 }

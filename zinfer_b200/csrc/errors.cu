@@ -1,6 +1,7 @@
 // The error channel of the C entry points: a per-thread message for refusals.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -24,3 +25,12 @@ int zi_check_launch(const char* what) {
   }
   return 0;
 }
+
+// Programmatic dependent launch is on unless ZINFER_B200_PDL=0 (or zi_set_pdl(0)).
+int g_zi_pdl_enabled = [] {
+  const char* v = getenv("ZINFER_B200_PDL");
+  return (v && v[0] == '0') ? 0 : 1;
+}();
+
+extern "C" void zi_set_pdl(int enabled) { g_zi_pdl_enabled = enabled ? 1 : 0; }
+extern "C" int zi_get_pdl() { return g_zi_pdl_enabled; }

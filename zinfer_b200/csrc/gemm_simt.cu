@@ -13,6 +13,8 @@ template <typename TX, typename TW, typename TO>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(TO* __restrict__ out, const TX* __restrict__ x,
                                                         const TW* __restrict__ w, int M, int N, int K, int ldx,
                                                         int ldw, int ldo) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float xs[BK][BM + 4];
   __shared__ float ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -69,7 +71,7 @@ template <typename TX, typename TW, typename TO>
 int launch(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldw, int ldo,
            cudaStream_t stream) {
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  gemm_simt_kernel<TX, TW, TO><<<grid, 256, 0, stream>>>((TO*)out, (const TX*)x, (const TW*)w, M, N, K, ldx, ldw, ldo);
+  zi_launch(gemm_simt_kernel<TX, TW, TO>, dim3(grid), dim3(256), 0, stream, (TO*)out, (const TX*)x, (const TW*)w, M, N, K, ldx, ldw, ldo);
   return zi_check_launch("gemm_simt");
 }
 }  // namespace

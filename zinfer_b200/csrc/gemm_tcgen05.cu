@@ -116,7 +116,8 @@ __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     TO* __restrict__ out, float* __restrict__ partial, int a_rows, int b_rows, int k_blocks,
                     int k_blocks_per_split, long long sa, long long sb, long long pa, long long pb, int BN, int stages,
-                    int tmem_cols, int* __restrict__ status) {
+                    int tmem_cols, int a_is_weight, int* __restrict__ status) {
+  pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int stage_bytes = A_TILE_BYTES + BN * BLOCK_K * 2;
@@ -154,14 +155,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   if (warp == 0) {
     if (lane == 0) {
+      // The weight does not depend on the kernel before this one: its first tiles are
+      // requested while that kernel drains; the activations only after it has completed.
+      const int pre = min(stages, n_kb);
+      for (int i = 0; i < pre; ++i) {
+        uint8_t* a_dst = smem + (size_t)i * stage_bytes;
+        mbar_expect_tx(&full[i], (uint32_t)stage_bytes);
+        if (a_is_weight) tma_load_2d(a_dst, &map_a, &full[i], (kb0 + i) * BLOCK_K, a_tile * TILE_A);
+        else tma_load_2d(a_dst + A_TILE_BYTES, &map_b, &full[i], (kb0 + i) * BLOCK_K, b_tile * BN);
+      }
+      pdl_wait();
       for (int i = 0; i < n_kb; ++i) {
         const int s = i % stages;
         const uint32_t phase = (uint32_t)(i / stages) & 1u;
-        if (!mbar_wait(&empty[s], phase ^ 1u)) { failed = true; atomicExch(status, 1); break; }
         uint8_t* a_dst = smem + (size_t)s * stage_bytes;
-        mbar_expect_tx(&full[s], (uint32_t)stage_bytes);
-        tma_load_2d(a_dst, &map_a, &full[s], (kb0 + i) * BLOCK_K, a_tile * TILE_A);
-        tma_load_2d(a_dst + A_TILE_BYTES, &map_b, &full[s], (kb0 + i) * BLOCK_K, b_tile * BN);
+        if (i >= pre) {
+          if (!mbar_wait(&empty[s], phase ^ 1u)) { failed = true; atomicExch(status, 1); break; }
+          mbar_expect_tx(&full[s], (uint32_t)stage_bytes);
+          if (a_is_weight) tma_load_2d(a_dst, &map_a, &full[s], (kb0 + i) * BLOCK_K, a_tile * TILE_A);
+          else tma_load_2d(a_dst + A_TILE_BYTES, &map_b, &full[s], (kb0 + i) * BLOCK_K, b_tile * BN);
+        }
+        if (a_is_weight) tma_load_2d(a_dst + A_TILE_BYTES, &map_b, &full[s], (kb0 + i) * BLOCK_K, b_tile * BN);
+        else tma_load_2d(a_dst, &map_a, &full[s], (kb0 + i) * BLOCK_K, a_tile * TILE_A);
       }
     }
   } else if (warp == 1) {
@@ -229,6 +244,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 template <typename TO>
 __global__ void splitk_reduce_kernel(TO* __restrict__ out, const float* __restrict__ partial, int M, int N,
                                      int splits, long long ldo) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t total = (size_t)M * N;
   if (idx >= total) return;
@@ -385,13 +402,13 @@ extern "C" int zi_gemm_tcgen05(void* out, int out_dtype, const void* x, const vo
     auto kern = gemm_tcgen05_kernel<TO>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return zi_refuse("gemm_tcgen05: cannot get %zu bytes of shared memory", smem);
-    kern<<<grid, THREADS, smem, stream>>>(map_a, map_b, (TO*)out, partial, a_rows, b_rows, k_blocks, kbps, sa, sb, pa, pb,
-                                          BN, stages, tmem_cols, status);
+    zi_launch(kern, dim3(grid), dim3(THREADS), smem, stream, map_a, map_b, (TO*)out, partial, a_rows, b_rows, k_blocks, kbps, sa, sb, pa, pb,
+                                          BN, stages, tmem_cols, swap, status);
     int rc = zi_check_launch("gemm_tcgen05");
     if (rc) return rc;
     if (partial && !defer_reduce) {
       const size_t total = (size_t)M * N;
-      splitk_reduce_kernel<TO><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((TO*)out, partial, M, N,
+      zi_launch(splitk_reduce_kernel<TO>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (TO*)out, partial, M, N,
                                                                                   real_splits, ldo);
       rc = zi_check_launch("splitk_reduce");
       if (rc) return rc;
@@ -513,13 +530,13 @@ extern "C" int zi_gemm_tcgen05_static_scratch(void* out, int out_dtype, const vo
     auto kern = gemm_tcgen05_kernel<TO>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return zi_refuse("gemm_static_scratch: cannot get %zu bytes of shared memory", smem);
-    kern<<<grid, THREADS, smem, stream>>>(map_a, map_b, (TO*)out, partial, a_rows, b_rows, k_blocks, kbps, sa, sb, pa, pb,
-                                          BN, stages, tmem_cols, status);
+    zi_launch(kern, dim3(grid), dim3(THREADS), smem, stream, map_a, map_b, (TO*)out, partial, a_rows, b_rows, k_blocks, kbps, sa, sb, pa, pb,
+                                          BN, stages, tmem_cols, swap, status);
     int rc = zi_check_launch("gemm_static_scratch");
     if (rc) return rc;
     if (partial) {
       const size_t total = (size_t)M * N;
-      splitk_reduce_kernel<TO><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((TO*)out, partial, M, N,
+      zi_launch(splitk_reduce_kernel<TO>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (TO*)out, partial, M, N,
                                                                                   real_splits, ldo);
       rc = zi_check_launch("gemm_static_scratch (reduce)");
       if (rc) return rc;

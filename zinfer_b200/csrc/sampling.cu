@@ -79,6 +79,8 @@ __device__ void block_argmax(const RowView& row, float* best_val_out, int* best_
 
 __global__ void __launch_bounds__(THREADS) argmax_kernel(int* __restrict__ out, const float* __restrict__ logits,
                                                          int ld, int V) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sval[32];
   __shared__ int sidx[32];
   RowView row{logits + (size_t)blockIdx.x * ld, nullptr, V, 1.f, 0.f, 0.f};
@@ -147,6 +149,8 @@ struct SampleParams {
 
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int ld, int V, SampleParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sval[32];
   __shared__ int sidx[32];
   __shared__ unsigned long long hist[256];
@@ -229,6 +233,8 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int ld, i
 }
 
 __global__ void count_tokens_kernel(int* __restrict__ counts, const int* __restrict__ tokens, int n, int V) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) {
     const int t = tokens[i];
@@ -240,7 +246,7 @@ __global__ void count_tokens_kernel(int* __restrict__ counts, const int* __restr
 extern "C" int zi_argmax(int* out, const float* logits, int R, int V, int ld, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (V <= 0) return zi_refuse("argmax: empty logits");
-  argmax_kernel<<<R, THREADS, 0, stream>>>(out, logits, ld, V);
+  zi_launch(argmax_kernel, dim3(R), dim3(THREADS), 0, stream, out, logits, ld, V);
   return zi_check_launch("argmax");
 }
 
@@ -252,13 +258,13 @@ extern "C" int zi_sample(int* out, const float* logits, int R, int V, int ld, co
   if (V <= 0) return zi_refuse("sample: empty logits");
   if (!temperature || !seeds || !draw_index) return zi_refuse("sample: temperature, seeds and draw_index are required");
   SampleParams p{temperature, top_k, top_p, min_p, rep, pres, freq, count_rows, counts, seeds, draw_index};
-  sample_kernel<<<R, THREADS, 0, stream>>>(out, logits, ld, V, p);
+  zi_launch(sample_kernel, dim3(R), dim3(THREADS), 0, stream, out, logits, ld, V, p);
   return zi_check_launch("sample");
 }
 
 // counts[t] += 1 for each token (a request's prompt, when it enters with penalties on).
 extern "C" int zi_count_tokens(int* counts, const int* tokens, int n, int V, cudaStream_t stream) {
   if (n <= 0) return 0;
-  count_tokens_kernel<<<(n + 255) / 256, 256, 0, stream>>>(counts, tokens, n, V);
+  zi_launch(count_tokens_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, counts, tokens, n, V);
   return zi_check_launch("count_tokens");
 }
