@@ -5,7 +5,7 @@ its host application captures a CUDA graph, a real-time loop that forbids
 allocation, a C program that links the library without torch (which otherwise
 hands the split-K workspace to the kernel).  For them the library exports
 ``zi_gemm_tcgen05_static_scratch``: the same tensor-core product, with its split-K
-partial sums in a fixed 16 MiB array inside the library's device image.
+partial sums in a fixed 8 MiB array inside the library's device image.
 
 This test calls that function through its exported C symbol, as such a user would,
 twice in a row with different shapes (the second, smaller product must not be
@@ -39,7 +39,7 @@ def test_static_scratch_product_matches_the_ordinary_entry_point():
 
     lib = ops.lib()
     lib.zi_gemm_static_scratch_capacity_bytes.restype = ctypes.c_longlong
-    assert lib.zi_gemm_static_scratch_capacity_bytes() == 16 * 1024 * 1024
+    assert lib.zi_gemm_static_scratch_capacity_bytes() == 8 * 1024 * 1024
     g = torch.Generator().manual_seed(7)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     # two calls in a row: both split K (8 tokens x 12288 and 3 tokens x 4096), different sizes of partial sums
@@ -71,10 +71,10 @@ def test_static_scratch_refuses_what_does_not_fit():
     from zinfer_b200 import ops
 
     lib = ops.lib()
-    M, N, K = 64, 8320, 16384           # 8 splits x 64 x 8320 x 4 bytes > 16 MiB
+    M, N, K = 64, 8320, 16384           # 4 splits x 64 x 8320 x 4 bytes > 8 MiB
     plan = (ctypes.c_int * 3)()
     need = lib.zi_gemm_tcgen05_plan(M, N, K, torch.cuda.get_device_properties(0).multi_processor_count, plan)
-    if need <= 16 * 1024 * 1024:
+    if need <= 8 * 1024 * 1024:
         pytest.skip("this GPU's plan does not split the product far enough to exceed the scratch")
     x = torch.zeros(M, K, dtype=torch.bfloat16, device=DEV)
     w = torch.zeros(N, K, dtype=torch.bfloat16, device=DEV)

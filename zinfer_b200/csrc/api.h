@@ -57,7 +57,8 @@ int zi_attention_decode_mma(void* out, int out_stride, float* workspace, const v
                             const int* cu_q, const int* kv_lens, const int* dec_seq, int n_dec, int nq, int nkv, int d,
                             int page_size, int window, float scale, int splits, cudaStream_t stream);
 
-int zi_argmax(int* out, const float* logits, int R, int V, int ld, cudaStream_t stream);
+int zi_argmax_chunks(int R, int V);
+int zi_argmax(int* out, const float* logits, int R, int V, int ld, void* workspace, cudaStream_t stream);
 int zi_sample(int* out, const float* logits, int R, int V, int ld, const float* temperature, const int* top_k,
               const float* top_p, const float* min_p, const float* rep, const float* pres, const float* freq,
               const int* count_rows, int* counts, const unsigned long long* seeds, const int* draw_index,

@@ -147,6 +147,29 @@ __device__ __forceinline__ void load_kv_rows(uint8_t* ks, uint8_t* vs, int row0,
   }
 }
 
+// The same for one warp's 16 keys when the page of key r is already in lane r's
+// register `pg` (-1: no page or outside the request): no dependent load stands between
+// the loop and its copies.
+template <int D>
+__device__ __forceinline__ void load_kv_rows_pg(uint8_t* ks, uint8_t* vs, int key_pos0, int pg,
+                                                const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                                                int nkv, int kvh, int page_size, int page_shift, int lane) {
+  constexpr int CH = D / 8;
+#pragma unroll
+  for (int e0 = 0; e0 < 16 * CH; e0 += 32) {
+    const int e = e0 + lane;
+    const int r = e / CH, c = e % CH;
+    const int page = __shfl_sync(0xffffffffu, pg, r);
+    const int j = key_pos0 + r;
+    const int in_page = page_shift >= 0 ? (j & (page_size - 1)) : (j % page_size);
+    const bool valid = page >= 0;
+    const size_t off = valid ? (((size_t)page * nkv + kvh) * page_size + in_page) * D + c * 8 : 0;
+    const uint32_t so = swz<D>(r, c);
+    cp_async16(ks + so, kcache + off, valid);
+    cp_async16(vs + so, vcache + off, valid);
+  }
+}
+
 // =============================================================================== prefill
 constexpr int PF_BQ = 128, PF_BK = 64, PF_THREADS = 256;
 
@@ -337,20 +360,33 @@ attn_decode_mma_kernel(bf16* __restrict__ out, int out_stride, float* __restrict
   for (int t = 0; t < D / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-  auto issue = [&](int t) {   // this warp's 16 keys of tile t into stage t % STAGES
-    const int stage = t % STAGES;
-    uint8_t* ks = ring + stage * 2 * ROWS_BYTES;
-    const int key0 = kt0 + (t_begin + t) * DC_TILE + warp * DC_KEYS;
-    load_kv_rows<D>(ks, ks + ROWS_BYTES, 0, DC_KEYS, key0, kv_lo, kv_hi, kcache, vcache, bt, nkv, kvh, page_size, page_shift,
-                    lane, 32);
+  // Lane r (r < 16) looks up the page of key r of a tile one iteration before the tile's
+  // copies are issued, so the block-table load is never waited for inside the loop.
+  auto lookup = [&](int t) -> int {
+    const int j = kt0 + (t_begin + t) * DC_TILE + warp * DC_KEYS + (lane & 15);
+    if (t >= n_tiles || j < kv_lo || j >= kv_hi) return -1;
+    return __ldg(bt + (page_shift >= 0 ? (j >> page_shift) : (j / page_size)));
   };
+  auto issue = [&](int t, int pg) {   // this warp's 16 keys of tile t into stage t % STAGES
+    uint8_t* ks = ring + (t % STAGES) * 2 * ROWS_BYTES;
+    const int key0 = kt0 + (t_begin + t) * DC_TILE + warp * DC_KEYS;
+    load_kv_rows_pg<D>(ks, ks + ROWS_BYTES, key0, pg, kcache, vcache, nkv, kvh, page_size, page_shift, lane);
+  };
+  int pg_next = lookup(0);
 #pragma unroll
   for (int t = 0; t < STAGES - 1; ++t) {
-    if (t < n_tiles) issue(t);
+    const int pg = pg_next;
+    pg_next = lookup(t + 1);
+    if (t < n_tiles) issue(t, pg);
     cp_async_commit();
   }
   for (int t = 0; t < n_tiles; ++t) {
-    if (t + STAGES - 1 < n_tiles) issue(t + STAGES - 1);
+    {
+      const int tt = t + STAGES - 1;
+      const int pg = pg_next;
+      pg_next = lookup(tt + 1);
+      if (tt < n_tiles) issue(tt, pg);
+    }
     cp_async_commit();
     cp_async_wait<STAGES - 1>();
     __syncwarp();

@@ -117,9 +117,23 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restri
     if (idx < nvec) {
       float4 a = Vec4<float>::load(hr + 4 * idx);
       if (dpart) {
+        // the splits are read four at a time so that their loads are in flight together;
+        // they are still added in order of z
         float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int z = 0; z < splits; ++z) {
-          const float4 p = Vec4<float>::load(dpart + z * zstride + (size_t)row * H + 4 * idx);
+        const float* base = dpart + (size_t)row * H + 4 * idx;
+        int z = 0;
+        for (; z + 4 <= splits; z += 4) {
+          const float4 p0 = Vec4<float>::load(base + (size_t)z * zstride);
+          const float4 p1 = Vec4<float>::load(base + (size_t)(z + 1) * zstride);
+          const float4 p2 = Vec4<float>::load(base + (size_t)(z + 2) * zstride);
+          const float4 p3 = Vec4<float>::load(base + (size_t)(z + 3) * zstride);
+          d.x = (((d.x + p0.x) + p1.x) + p2.x) + p3.x;
+          d.y = (((d.y + p0.y) + p1.y) + p2.y) + p3.y;
+          d.z = (((d.z + p0.z) + p1.z) + p2.z) + p3.z;
+          d.w = (((d.w + p0.w) + p1.w) + p2.w) + p3.w;
+        }
+        for (; z < splits; ++z) {
+          const float4 p = Vec4<float>::load(base + (size_t)z * zstride);
           d.x += p.x; d.y += p.y; d.z += p.z; d.w += p.w;
         }
         a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
@@ -154,8 +168,9 @@ static int launch_add_rmsnorm(float* h, const void* delta, const float* dpart, i
   const bool aligned = H % 4 == 0 && ((uintptr_t)h % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
                        ((uintptr_t)out % 16 == 0) && ((uintptr_t)delta % 16 == 0) && ((uintptr_t)dpart % 16 == 0) &&
                        zstride % 4 == 0;
-  const int threads = 256;
   const int nvec = H / 4;
+  // few rows (decode): one vector per thread, so that a row's loads are all in flight at once
+  const int threads = (n_rows <= 256 && nvec > 512) ? 1024 : (nvec > 256 && n_rows <= 256 ? 512 : 256);
   if (aligned && nvec <= threads * 8) {
     const int vpt = (nvec + threads - 1) / threads;
 #define ZI_LAUNCH_VPT(V)                                                                                      \
@@ -345,7 +360,13 @@ __global__ void qk_norm_rope_store_kernel(const T* src, int src_stride, const fl
     if (part) {
       const float* p = part + (size_t)t * part_width + (size_t)head * d + i;
       float v = 0.f;
-      for (int z = 0; z < splits; ++z) v += p[z * zstride];
+      int z = 0;
+      for (; z + 4 <= splits; z += 4) {   // four loads in flight, added in order
+        const float p0 = p[(size_t)z * zstride], p1 = p[(size_t)(z + 1) * zstride];
+        const float p2 = p[(size_t)(z + 2) * zstride], p3 = p[(size_t)(z + 3) * zstride];
+        v = (((v + p0) + p1) + p2) + p3;
+      }
+      for (; z < splits; ++z) v += p[(size_t)z * zstride];
       return v;
     }
     return to_f32(src[(size_t)t * src_stride + (size_t)head * d + i]);
@@ -365,33 +386,45 @@ __global__ void qk_norm_rope_store_kernel(const T* src, int src_stride, const fl
     for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(load(i));
     return;
   }
+  // the head's pairs (i, i + d/2) this lane owns, read once into registers (d <= 256)
+  constexpr int MAXP = 4;
+  float a[MAXP], b[MAXP];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < MAXP; ++j) {
+    const int i = lane + 32 * j;
+    a[j] = b[j] = 0.f;
+    if (i < half) {
+      a[j] = load(i);
+      b[j] = load(i + half);
+      ss += a[j] * a[j] + b[j] * b[j];
+    }
+  }
   const float* w = head < nq ? qw : kw;
   float inv = 1.f;
   if (w) {
-    float ss = 0.f;
-    for (int i = lane; i < d; i += 32) {
-      const float v = load(i);
-      ss += v * v;
-    }
     ss = warp_sum(ss);
     inv = 1.0f / sqrtf(ss / (float)d + eps);
   }
   int pos = positions[t];
   if (pos >= n_table_pos) pos = n_table_pos - 1;  // the host refuses such positions
-  for (int i = lane; i < half; i += 32) {
-    float a = load(i), b = load(i + half);
+#pragma unroll
+  for (int j = 0; j < MAXP; ++j) {
+    const int i = lane + 32 * j;
+    if (i >= half) continue;
+    float x = a[j], y = b[j];
     if (w) {
-      a = a * w[i] * inv;
-      b = b * w[i + half] * inv;
+      x = x * w[i] * inv;
+      y = y * w[i + half] * inv;
     }
     if (cos_t) {
-      const float c = cos_t[(size_t)pos * half + i], s = sin_t[(size_t)pos * half + i];
-      const float ra = a * c - b * s, rb = b * c + a * s;
-      a = ra;
-      b = rb;
+      const float c = cos_t[(size_t)pos * half + i], sn = sin_t[(size_t)pos * half + i];
+      const float rx = x * c - y * sn, ry = y * c + x * sn;
+      x = rx;
+      y = ry;
     }
-    dst[i] = from_f32<T>(a);
-    dst[i + half] = from_f32<T>(b);
+    dst[i] = from_f32<T>(x);
+    dst[i + half] = from_f32<T>(y);
   }
 }
 
@@ -402,7 +435,7 @@ extern "C" int zi_qk_norm_rope_store(const void* src, int dtype, int T, int src_
                                      void* vcache, const int* slots, int page_size, int write_kv,
                                      cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (d <= 0 || d % 2) return zi_refuse("qk_norm_rope_store: head_dim %d is not even", d);
+  if (d <= 0 || d % 2 || d > 256) return zi_refuse("qk_norm_rope_store: head_dim %d is not an even number up to 256", d);
   if ((cos_t == nullptr) != (sin_t == nullptr)) return zi_refuse("qk_norm_rope_store: cos and sin tables go together");
   if ((src == nullptr) == (partials == nullptr)) return zi_refuse("qk_norm_rope_store: give the rows either whole or as partial sums");
   if (write_kv && (!kcache || !vcache || !slots || page_size <= 0))

@@ -13,8 +13,8 @@
 //   out[M, N] = x[M, K] * w[N, K]^T   (bfloat16 operands, 32-bit accumulation)
 //
 // The caller passes inputs and outputs only.  When the product is split along K,
-// the partial sums go to a 16 MiB array that is part of the library's device image:
-// every GPU that loads the library keeps those 16 MiB until the process exits.
+// the partial sums go to a 8 MiB array that is part of the library's device image:
+// every GPU that loads the library keeps those 8 MiB until the process exits.
 // Products that would need more (splits * M * N * 4 bytes; the capacity is
 // zi_gemm_static_scratch_capacity_bytes()) are refused with a message in
 // zi_last_error(), and nothing is launched.

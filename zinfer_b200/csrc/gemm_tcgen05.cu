@@ -350,7 +350,7 @@ extern "C" long long zi_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int
   int splits = 1;
   if (swap) {
     // few tokens: the weight is streamed once; use enough CTAs that every SM pulls from memory
-    const int target = 2 * sm_count;
+    const int target = sm_count + sm_count / 2;
     while (tiles * splits < target && splits < 16 && k_blocks / (splits * 2) >= 8) splits *= 2;
   }
   if (splits > 1) {  // the number of splits that get at least one k-block
@@ -434,8 +434,8 @@ extern "C" int zi_gemm_tcgen05_status() {
 // library's own device image instead of a caller's workspace.
 namespace {
 
-// 4 Mi floats = 16 MiB: every GPU that loads this library holds them until it exits.
-constexpr long long STATIC_SCRATCH_FLOATS = 4ll * 1024 * 1024;
+// 2 Mi floats = 8 MiB: every GPU that loads this library holds them until it exits.
+constexpr long long STATIC_SCRATCH_FLOATS = 2ll * 1024 * 1024;
 static __device__ __align__(256) float g_static_scratch[STATIC_SCRATCH_FLOATS];
 static __device__ __align__(256) int g_static_status;
 

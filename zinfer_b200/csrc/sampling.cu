@@ -90,6 +90,69 @@ __global__ void __launch_bounds__(THREADS) argmax_kernel(int* __restrict__ out, 
   if (threadIdx.x == 0) out[blockIdx.x] = bi;
 }
 
+// Two-stage argmax for few rows over a large vocabulary: `chunks` blocks per row each
+// find the first maximum of their slice, a second kernel picks among them.
+__global__ void __launch_bounds__(256) argmax_partial_kernel(float* __restrict__ pval, int* __restrict__ pidx,
+                                                             const float* __restrict__ logits, int ld, int V,
+                                                             int chunks) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float sval[32];
+  __shared__ int sidx[32];
+  const int r = blockIdx.x, c = blockIdx.y;
+  const int per = (V + chunks - 1) / chunks;
+  const int lo = c * per, hi = min(V, lo + per);
+  const float* row = logits + (size_t)r * ld;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int v = lo + threadIdx.x; v < hi; v += blockDim.x) {
+    float a = row[v];
+    if (a != a) a = -INFINITY;
+    if (a > bv || (a == bv && v < bi)) { bv = a; bi = v; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sval[warp] = bv; sidx[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    bv = lane < (blockDim.x >> 5) ? sval[lane] : -INFINITY;
+    bi = lane < (blockDim.x >> 5) ? sidx[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) { pval[r * chunks + c] = bv; pidx[r * chunks + c] = bi; }
+  }
+}
+
+__global__ void argmax_final_kernel(int* __restrict__ out, const float* __restrict__ pval,
+                                    const int* __restrict__ pidx, int chunks) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = threadIdx.x; c < chunks; c += 32) {
+    const float v = pval[r * chunks + c];
+    const int i = pidx[r * chunks + c];
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  if (threadIdx.x == 0) out[r] = bi == 0x7fffffff ? 0 : bi;
+}
+
 // ------------------------------------------------------------------- radix selection
 // Finds the composite key c* such that the measure of members with key > c* is
 // below `target` and the measure of members with key >= c* reaches it.
@@ -243,9 +306,22 @@ __global__ void count_tokens_kernel(int* __restrict__ counts, const int* __restr
 }
 }  // namespace
 
-extern "C" int zi_argmax(int* out, const float* logits, int R, int V, int ld, cudaStream_t stream) {
+// `workspace` (may be null) holds 2 * R * chunks 32-bit words for the two-stage form.
+extern "C" int zi_argmax_chunks(int R, int V) { return (V >= 16384 && R <= 256) ? 32 : 0; }
+
+extern "C" int zi_argmax(int* out, const float* logits, int R, int V, int ld, void* workspace, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (V <= 0) return zi_refuse("argmax: empty logits");
+  const int chunks = zi_argmax_chunks(R, V);
+  if (chunks > 0 && workspace) {
+    float* pval = (float*)workspace;
+    int* pidx = (int*)workspace + (size_t)R * chunks;
+    zi_launch(argmax_partial_kernel, dim3(R, chunks), dim3(256), 0, stream, pval, pidx, logits, ld, V, chunks);
+    int rc = zi_check_launch("argmax (partial)");
+    if (rc) return rc;
+    zi_launch(argmax_final_kernel, dim3(R), dim3(32), 0, stream, out, pval, pidx, chunks);
+    return zi_check_launch("argmax (final)");
+  }
   zi_launch(argmax_kernel, dim3(R), dim3(THREADS), 0, stream, out, logits, ld, V);
   return zi_check_launch("argmax");
 }

@@ -369,7 +369,9 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
     _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "logits are float32 with dense rows")
     if out is None:
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)
-    _check(lib().zi_argmax(_ptr(out), _ptr(logits), R, V, logits.stride(0), _stream()), "argmax")
+    chunks = lib().zi_argmax_chunks(R, V)
+    ws = torch.empty((2 * R * chunks,), dtype=torch.int32, device=logits.device) if chunks else None
+    _check(lib().zi_argmax(_ptr(out), _ptr(logits), R, V, logits.stride(0), _ptr(ws), _stream()), "argmax")
     return out
 
 
