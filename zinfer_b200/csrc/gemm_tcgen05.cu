@@ -102,35 +102,67 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
 }
 // Instruction descriptor of kind::f16: D = f32 (bits 4-5 = 1), A and B = bf16 (bits
 // 7-9 and 10-12 = 1), both K-major (bits 15, 16 = 0), N >> 3 at bit 17, M >> 4 at bit 24.
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
 __device__ __forceinline__ uint32_t instr_desc_bf16(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 // -------------------------------------------------------------------- the kernel
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+struct GemmArgs {
+  int a_rows, b_rows;        // rows of the A side (accumulator lanes) and of the B side (columns)
+  int a_tiles, b_tiles, splits;
+  int k_blocks, k_blocks_per_split;
+  long long sa, sb;          // element (a, b) goes to out[a * sa + b * sb]
+  long long pa, pb;          // or, split, as a float to partial[z * a_rows * b_rows + a * pa + b * pb]
+  int BN, stages, acc_cols;  // acc_cols: TMEM columns of one accumulator (two are allocated)
+  int a_is_weight;           // which side does not depend on the kernel before this one
+};
+
 // A side: a_rows x K through map_a (box 64 x 128).  B side: b_rows x K through map_b
-// (box 64 x BN).  Element (a, b) goes to out[a * sa + b * sb], or, with split-K, as a
-// float to partial[z * a_rows * b_rows + a * pa + b * pb]: the partial sums of split z
-// lie as a [tokens, out features] matrix whichever side the tokens are on.
+// (box 64 x BN).  Persistent: a CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...
+// (A tile fastest, so neighbouring CTAs share the B tile in L2).  Two accumulators in
+// tensor memory let the epilogue of one tile run under the MMAs of the next.
 template <typename TO>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    TO* __restrict__ out, float* __restrict__ partial, int a_rows, int b_rows, int k_blocks,
-                    int k_blocks_per_split, long long sa, long long sb, long long pa, long long pb, int BN, int stages,
-                    int tmem_cols, int a_is_weight, int* __restrict__ status) {
+                    TO* __restrict__ out, float* __restrict__ partial, const GemmArgs g, int* __restrict__ status) {
   pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int BN = g.BN, stages = g.stages;
   const int stage_bytes = A_TILE_BYTES + BN * BLOCK_K * 2;
   uint64_t* full = (uint64_t*)(smem + (size_t)stages * stage_bytes);
   uint64_t* empty = full + stages;
-  uint64_t* accum_full = empty + stages;
-  uint32_t* tmem_slot = (uint32_t*)(accum_full + 1);
+  uint64_t* accum_full = empty + stages;       // [2]
+  uint64_t* accum_empty = accum_full + 2;      // [2]
+  uint32_t* tmem_slot = (uint32_t*)(accum_empty + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int a_tile = blockIdx.x, b_tile = blockIdx.y, split = blockIdx.z;
-  const int kb0 = split * k_blocks_per_split;
-  const int kb1 = min(k_blocks, kb0 + k_blocks_per_split);
-  const int n_kb = kb1 - kb0;  // >= 1 by construction of the grid
+  const int tiles_per_split = g.a_tiles * g.b_tiles;
+  const int total_tiles = tiles_per_split * g.splits;
+  const uint32_t tmem_cols = 2u * (uint32_t)g.acc_cols;
   bool failed = false;
 
   if (threadIdx.x == 0) {
@@ -138,13 +170,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(accum_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&accum_full[i], 1);
+      mbar_init(&accum_empty[i], 4);   // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"((uint32_t)tmem_cols)
+                 "r"(tmem_cols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -153,78 +188,144 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // tile -> (a_tile, b_tile, first k-block, number of k-blocks)
+  auto decode = [&](int tile, int& a_tile, int& b_tile, int& split, int& kb0, int& n_kb) {
+    split = tile / tiles_per_split;
+    const int rem = tile - split * tiles_per_split;
+    b_tile = rem / g.a_tiles;
+    a_tile = rem - b_tile * g.a_tiles;
+    kb0 = split * g.k_blocks_per_split;
+    n_kb = min(g.k_blocks, kb0 + g.k_blocks_per_split) - kb0;
+  };
+
   if (warp == 0) {
-    if (lane == 0) {
-      // The weight does not depend on the kernel before this one: its first tiles are
-      // requested while that kernel drains; the activations only after it has completed.
+    if (lane == 0 && (int)blockIdx.x < total_tiles) {
+      int a_tile, b_tile, split, kb0, n_kb;
+      // The weight does not depend on the kernel before this one: the first tile's first
+      // weight blocks are requested while that kernel drains; activations only after it.
+      decode(blockIdx.x, a_tile, b_tile, split, kb0, n_kb);
       const int pre = min(stages, n_kb);
       for (int i = 0; i < pre; ++i) {
-        uint8_t* a_dst = smem + (size_t)i * stage_bytes;
+        uint8_t* dst = smem + (size_t)i * stage_bytes;
         mbar_expect_tx(&full[i], (uint32_t)stage_bytes);
-        if (a_is_weight) tma_load_2d(a_dst, &map_a, &full[i], (kb0 + i) * BLOCK_K, a_tile * TILE_A);
-        else tma_load_2d(a_dst + A_TILE_BYTES, &map_b, &full[i], (kb0 + i) * BLOCK_K, b_tile * BN);
+        if (g.a_is_weight) tma_load_2d(dst, &map_a, &full[i], (kb0 + i) * BLOCK_K, a_tile * TILE_A);
+        else tma_load_2d(dst + A_TILE_BYTES, &map_b, &full[i], (kb0 + i) * BLOCK_K, b_tile * BN);
       }
       pdl_wait();
-      for (int i = 0; i < n_kb; ++i) {
-        const int s = i % stages;
-        const uint32_t phase = (uint32_t)(i / stages) & 1u;
-        uint8_t* a_dst = smem + (size_t)s * stage_bytes;
-        if (i >= pre) {
-          if (!mbar_wait(&empty[s], phase ^ 1u)) { failed = true; atomicExch(status, 1); break; }
-          mbar_expect_tx(&full[s], (uint32_t)stage_bytes);
-          if (a_is_weight) tma_load_2d(a_dst, &map_a, &full[s], (kb0 + i) * BLOCK_K, a_tile * TILE_A);
-          else tma_load_2d(a_dst + A_TILE_BYTES, &map_b, &full[s], (kb0 + i) * BLOCK_K, b_tile * BN);
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
+        decode(tile, a_tile, b_tile, split, kb0, n_kb);
+        for (int i = 0; i < n_kb; ++i, ++it) {
+          const int s = it % stages;
+          const uint32_t phase = (it / stages) & 1u;
+          uint8_t* dst = smem + (size_t)s * stage_bytes;
+          const bool preloaded = tile == (int)blockIdx.x && i < pre;
+          if (!preloaded) {
+            if (!mbar_wait(&empty[s], phase ^ 1u)) { failed = true; atomicExch(status, 1); break; }
+            mbar_expect_tx(&full[s], (uint32_t)stage_bytes);
+            if (g.a_is_weight) tma_load_2d(dst, &map_a, &full[s], (kb0 + i) * BLOCK_K, a_tile * TILE_A);
+            else tma_load_2d(dst + A_TILE_BYTES, &map_b, &full[s], (kb0 + i) * BLOCK_K, b_tile * BN);
+          }
+          if (g.a_is_weight) tma_load_2d(dst + A_TILE_BYTES, &map_b, &full[s], (kb0 + i) * BLOCK_K, b_tile * BN);
+          else tma_load_2d(dst, &map_a, &full[s], (kb0 + i) * BLOCK_K, a_tile * TILE_A);
         }
-        if (a_is_weight) tma_load_2d(a_dst + A_TILE_BYTES, &map_b, &full[s], (kb0 + i) * BLOCK_K, b_tile * BN);
-        else tma_load_2d(a_dst, &map_a, &full[s], (kb0 + i) * BLOCK_K, a_tile * TILE_A);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = instr_desc_bf16(TILE_A, BN);
-      for (int i = 0; i < n_kb; ++i) {
-        const int s = i % stages;
-        const uint32_t phase = (uint32_t)(i / stages) & 1u;
-        if (!mbar_wait(&full[s], phase)) { failed = true; atomicExch(status, 2); break; }
+      uint32_t it = 0, lt = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++lt) {
+        int a_tile, b_tile, split, kb0, n_kb;
+        decode(tile, a_tile, b_tile, split, kb0, n_kb);
+        const uint32_t acc = lt & 1u, acc_phase = (lt >> 1) & 1u;
+        if (!mbar_wait(&accum_empty[acc], acc_phase ^ 1u)) { failed = true; atomicExch(status, 4); break; }
         tcgen05_fence_after();
-        const uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes);
-        const uint32_t b_addr = a_addr + A_TILE_BYTES;
+        const uint32_t d_tmem = tmem_base + acc * (uint32_t)g.acc_cols;
+        for (int i = 0; i < n_kb; ++i, ++it) {
+          const int s = it % stages;
+          const uint32_t phase = (it / stages) & 1u;
+          if (!mbar_wait(&full[s], phase)) { failed = true; atomicExch(status, 2); break; }
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes);
+          const uint32_t b_addr = a_addr + A_TILE_BYTES;
 #pragma unroll
-        for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-          tcgen05_mma_bf16(tmem_base, smem_desc_sw128(a_addr + k * UMMA_K * 2), smem_desc_sw128(b_addr + k * UMMA_K * 2),
-                           idesc, (i > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+            tcgen05_mma_bf16(d_tmem, smem_desc_sw128(a_addr + k * UMMA_K * 2), smem_desc_sw128(b_addr + k * UMMA_K * 2),
+                             idesc, (i > 0 || k > 0) ? 1u : 0u);
+          }
+          tcgen05_commit(&empty[s]);  // frees the stage when these MMAs have read it
         }
-        tcgen05_commit(&empty[s]);  // frees the stage when these MMAs have read it
+        if (!failed) tcgen05_commit(&accum_full[acc]);
       }
-      if (!failed) tcgen05_commit(accum_full);
     }
   } else {
     const int quarter = warp & 3;  // the TMEM lanes this warp may read
-    if (!mbar_wait(accum_full, 0)) {
-      failed = true;
-      atomicExch(status, 3);
-    } else {
+    uint32_t lt = 0;
+    for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++lt) {
+      int a_tile, b_tile, split, kb0, n_kb;
+      decode(tile, a_tile, b_tile, split, kb0, n_kb);
+      const uint32_t acc = lt & 1u, acc_phase = (lt >> 1) & 1u;
+      if (!mbar_wait(&accum_full[acc], acc_phase)) { failed = true; atomicExch(status, 3); break; }
       tcgen05_fence_after();
       const int a = a_tile * TILE_A + quarter * 32 + lane;
-      const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        float v[16];
-        tmem_load16(lane_base + (uint32_t)c0, v);
+      const uint32_t lane_base = tmem_base + acc * (uint32_t)g.acc_cols + ((uint32_t)(quarter * 32) << 16);
+      const bool a_ok = a < g.a_rows;
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        float v[32];
+        if (BN - c0 >= 32) {
+          tmem_load32(lane_base + (uint32_t)c0, v);
+        } else {  // BN == 16
+          float v16[16];
+          tmem_load16(lane_base + (uint32_t)c0, v16);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = j < 16 ? v16[j] : 0.f;
+        }
+        const int ncol = min(32, BN - c0);
         const int b0 = b_tile * BN + c0;
-        if (a < a_rows) {
-          if (partial) {
-            float* p = partial + (size_t)split * a_rows * b_rows + (long long)a * pa + (long long)b0 * pb;
+        if (!a_ok) continue;
+        if (partial) {
+          float* p = partial + (size_t)split * g.a_rows * g.b_rows + (long long)a * g.pa + (long long)b0 * g.pb;
+          if (g.pb == 1 && b0 + ncol <= g.b_rows && ((uintptr_t)p & 15) == 0) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (b0 + j < b_rows) p[(long long)j * pb] = v[j];
+            for (int j = 0; j < 32; j += 4)
+              if (j < ncol) *reinterpret_cast<float4*>(p + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
           } else {
-            TO* o = out + (long long)a * sa + (long long)b0 * sb;
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (b0 + j < b_rows) o[(long long)j * sb] = from_f32<TO>(v[j]);
+            for (int j = 0; j < 32; ++j)
+              if (j < ncol && b0 + j < g.b_rows) p[(long long)j * g.pb] = v[j];
+          }
+        } else {
+          TO* o = out + (long long)a * g.sa + (long long)b0 * g.sb;
+          if (g.sb == 1 && b0 + ncol <= g.b_rows && ((uintptr_t)o & 15) == 0) {
+            if (sizeof(TO) == 2) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                if (j >= ncol) break;
+                uint4 w;
+                w.x = pack2(v[j], v[j + 1]);
+                w.y = pack2(v[j + 2], v[j + 3]);
+                w.z = pack2(v[j + 4], v[j + 5]);
+                w.w = pack2(v[j + 6], v[j + 7]);
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(o) + j) = w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                if (j < ncol)
+                  *reinterpret_cast<float4*>(reinterpret_cast<float*>(o) + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < ncol && b0 + j < g.b_rows) o[(long long)j * g.sb] = from_f32<TO>(v[j]);
           }
         }
       }
+      // this accumulator may be overwritten by the MMAs of the tile after next
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&accum_empty[acc]);
     }
   }
   if (failed) {
@@ -235,8 +336,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   if (warp == 1) {
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)tmem_cols)
-                 : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
 }
 
@@ -350,8 +450,8 @@ extern "C" long long zi_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int
   int splits = 1;
   if (swap) {
     // few tokens: the weight is streamed once; use enough CTAs that every SM pulls from memory
-    const int target = sm_count + sm_count / 2;
-    while (tiles * splits < target && splits < 16 && k_blocks / (splits * 2) >= 8) splits *= 2;
+    // as many splits as still fit on the GPU at once (two CTAs per SM): one wave, no tail
+    while (tiles * splits * 2 <= 2 * sm_count && splits < 16 && k_blocks / (splits * 2) >= 8) splits *= 2;
   }
   if (splits > 1) {  // the number of splits that get at least one k-block
     const int kbps = (k_blocks + splits - 1) / splits;
@@ -363,6 +463,62 @@ extern "C" long long zi_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int
   return splits > 1 ? (long long)splits * M * N * (long long)sizeof(float) : 0;
 }
 
+namespace {
+// Launches the product (and, unless deferred, the split-K reduction) with the given
+// tensor maps, partial-sum buffer and status word.  Both entry points end here.
+int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtensorMap& map_b, int M, int N, int K,
+                int ldo, const int* plan, float* partial_buf, int* status, int sm_count, int defer_reduce,
+                const char* what, cudaStream_t stream) {
+  const int swap = plan[0], BN = plan[1], splits = plan[2];
+  GemmArgs g;
+  g.a_rows = swap ? N : M;
+  g.b_rows = swap ? M : N;
+  g.a_tiles = (g.a_rows + TILE_A - 1) / TILE_A;
+  g.b_tiles = (g.b_rows + BN - 1) / BN;
+  g.k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
+  g.k_blocks_per_split = (g.k_blocks + splits - 1) / splits;
+  g.splits = (g.k_blocks + g.k_blocks_per_split - 1) / g.k_blocks_per_split;
+  g.sa = swap ? 1 : ldo;
+  g.sb = swap ? ldo : 1;
+  g.pa = swap ? 1 : N;
+  g.pb = swap ? N : 1;
+  g.BN = BN;
+  g.acc_cols = BN < 32 ? 32 : BN;   // two accumulators: 64 .. 512 columns, a power of two
+  g.a_is_weight = swap;
+  const int stage_bytes = A_TILE_BYTES + BN * BLOCK_K * 2;
+  g.stages = swap ? 6 : (BN >= 256 ? 4 : 6);
+  if (g.stages > g.k_blocks_per_split) g.stages = g.k_blocks_per_split < 2 ? 2 : g.k_blocks_per_split;
+  const size_t smem = 1024 + (size_t)g.stages * stage_bytes + (2 * g.stages + 4) * sizeof(uint64_t) + 16;
+  const int total_tiles = g.a_tiles * g.b_tiles * g.splits;
+  float* partial = g.splits > 1 ? partial_buf : nullptr;
+
+  ZI_DISPATCH_DTYPE(out_dtype, TO, {
+    auto kern = gemm_tcgen05_kernel<TO>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return zi_refuse("%s: cannot get %zu bytes of shared memory", what, smem);
+    // CTAs that fit on the GPU at once: by shared memory, and by tensor memory (512 columns per SM)
+    int per_sm = (int)((227 * 1024) / (smem + 1024));
+    per_sm = per_sm < 1 ? 1 : per_sm;
+    const int by_tmem = 512 / (2 * g.acc_cols);
+    if (per_sm > by_tmem) per_sm = by_tmem;
+    if (per_sm > 2) per_sm = 2;
+    int grid = per_sm * (sm_count > 0 ? sm_count : 148);
+    if (grid > total_tiles) grid = total_tiles;
+    zi_launch(kern, dim3(grid), dim3(THREADS), smem, stream, map_a, map_b, (TO*)out, partial, g, status);
+    int rc = zi_check_launch(what);
+    if (rc) return rc;
+    if (partial && !defer_reduce) {
+      const size_t total = (size_t)M * N;
+      zi_launch(splitk_reduce_kernel<TO>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (TO*)out,
+                partial, M, N, g.splits, (long long)ldo);
+      rc = zi_check_launch("splitk_reduce");
+      if (rc) return rc;
+    }
+  });
+  return 0;
+}
+}  // namespace
+
 // With `defer_reduce` and a split product, the partial sums are left in `workspace` as
 // [splits, M, N] floats for a consumer that adds them itself, and `out` is not written.
 extern "C" int zi_gemm_tcgen05(void* out, int out_dtype, const void* x, const void* w, int M, int N, int K, int ldx,
@@ -373,48 +529,17 @@ extern "C" int zi_gemm_tcgen05(void* out, int out_dtype, const void* x, const vo
     return zi_refuse("gemm_tcgen05: operands must be 16-byte aligned bfloat16 with row pitches in multiples of 8");
   int plan[3];
   const long long need = zi_gemm_tcgen05_plan(M, N, K, sm_count, plan);
-  const int swap = plan[0], BN = plan[1], splits = plan[2];
   if (need > workspace_bytes) return zi_refuse("gemm_tcgen05: split-K needs %lld workspace bytes, got %lld", need, workspace_bytes);
+  const int swap = plan[0], BN = plan[1];
   const int a_rows = swap ? N : M, b_rows = swap ? M : N;
-  const void* a_ptr = swap ? w : x;
-  const void* b_ptr = swap ? x : w;
-  const int lda = swap ? ldw : ldx, ldb = swap ? ldx : ldw;
   CUtensorMap map_a, map_b;
-  if (!make_map(&map_a, a_ptr, a_rows, K, lda, TILE_A) || !make_map(&map_b, b_ptr, b_rows, K, ldb, BN))
+  if (!make_map(&map_a, swap ? w : x, a_rows, K, swap ? ldw : ldx, TILE_A) ||
+      !make_map(&map_b, swap ? x : w, b_rows, K, swap ? ldx : ldw, BN))
     return zi_refuse("gemm_tcgen05: cuTensorMapEncodeTiled failed");
   int* status = status_word();
   if (!status) return zi_refuse("gemm_tcgen05: cannot allocate the status word");
-
-  const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
-  const int kbps = (k_blocks + splits - 1) / splits;
-  const int real_splits = (k_blocks + kbps - 1) / kbps;
-  const int stage_bytes = A_TILE_BYTES + BN * BLOCK_K * 2;
-  int stages = swap ? 6 : (BN >= 256 ? 4 : 6);
-  if (stages > kbps) stages = kbps < 2 ? 2 : kbps;
-  const size_t smem = 1024 + (size_t)stages * stage_bytes + (2 * stages + 1) * sizeof(uint64_t) + 16;
-  const int tmem_cols = BN < 32 ? 32 : BN;
-  const long long sa = swap ? 1 : ldo, sb = swap ? ldo : 1;
-  const long long pa = swap ? 1 : N, pb = swap ? N : 1;
-  dim3 grid((a_rows + TILE_A - 1) / TILE_A, (b_rows + BN - 1) / BN, real_splits);
-  float* partial = real_splits > 1 ? workspace : nullptr;
-
-  ZI_DISPATCH_DTYPE(out_dtype, TO, {
-    auto kern = gemm_tcgen05_kernel<TO>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return zi_refuse("gemm_tcgen05: cannot get %zu bytes of shared memory", smem);
-    zi_launch(kern, dim3(grid), dim3(THREADS), smem, stream, map_a, map_b, (TO*)out, partial, a_rows, b_rows, k_blocks, kbps, sa, sb, pa, pb,
-                                          BN, stages, tmem_cols, swap, status);
-    int rc = zi_check_launch("gemm_tcgen05");
-    if (rc) return rc;
-    if (partial && !defer_reduce) {
-      const size_t total = (size_t)M * N;
-      zi_launch(splitk_reduce_kernel<TO>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (TO*)out, partial, M, N,
-                                                                                  real_splits, ldo);
-      rc = zi_check_launch("splitk_reduce");
-      if (rc) return rc;
-    }
-  });
-  return 0;
+  return launch_gemm(out, out_dtype, map_a, map_b, M, N, K, ldo, plan, workspace, status, sm_count, defer_reduce,
+                     "gemm_tcgen05", stream);
 }
 
 // Reads and clears the status word of the tensor-core kernels (synchronises the
@@ -500,7 +625,7 @@ extern "C" int zi_gemm_tcgen05_static_scratch(void* out, int out_dtype, const vo
   int dev = -1;
   if (!static_scratch_for_current_device(&ss, &dev))
     return zi_refuse("gemm_static_scratch: cudaGetSymbolAddress of the built-in scratch failed on the current device");
-  const int swap = plan[0], BN = plan[1], splits = plan[2];
+  const int swap = plan[0], BN = plan[1];
   const int a_rows = swap ? N : M, b_rows = swap ? M : N;
   const int lda = swap ? ldw : ldx, ldb = swap ? ldx : ldw;
   CUtensorMap map_a, map_b;
@@ -512,35 +637,6 @@ extern "C" int zi_gemm_tcgen05_static_scratch(void* out, int out_dtype, const vo
   // element that the second kernel reads is written by the first
   cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int), stream);
   if (e != cudaSuccess) return zi_refuse("gemm_static_scratch: cannot clear the status word: %s", cudaGetErrorString(e));
-
-  const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
-  const int kbps = (k_blocks + splits - 1) / splits;
-  const int real_splits = (k_blocks + kbps - 1) / kbps;
-  const int stage_bytes = A_TILE_BYTES + BN * BLOCK_K * 2;
-  int stages = swap ? 6 : (BN >= 256 ? 4 : 6);
-  if (stages > kbps) stages = kbps < 2 ? 2 : kbps;
-  const size_t smem = 1024 + (size_t)stages * stage_bytes + (2 * stages + 1) * sizeof(uint64_t) + 16;
-  const int tmem_cols = BN < 32 ? 32 : BN;
-  const long long sa = swap ? 1 : ldo, sb = swap ? ldo : 1;
-  const long long pa = swap ? 1 : N, pb = swap ? N : 1;
-  dim3 grid((a_rows + TILE_A - 1) / TILE_A, (b_rows + BN - 1) / BN, real_splits);
-  float* partial = real_splits > 1 ? ss.scratch : nullptr;
-
-  ZI_DISPATCH_DTYPE(out_dtype, TO, {
-    auto kern = gemm_tcgen05_kernel<TO>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return zi_refuse("gemm_static_scratch: cannot get %zu bytes of shared memory", smem);
-    zi_launch(kern, dim3(grid), dim3(THREADS), smem, stream, map_a, map_b, (TO*)out, partial, a_rows, b_rows, k_blocks, kbps, sa, sb, pa, pb,
-                                          BN, stages, tmem_cols, swap, status);
-    int rc = zi_check_launch("gemm_static_scratch");
-    if (rc) return rc;
-    if (partial) {
-      const size_t total = (size_t)M * N;
-      zi_launch(splitk_reduce_kernel<TO>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (TO*)out, partial, M, N,
-                                                                                  real_splits, ldo);
-      rc = zi_check_launch("gemm_static_scratch (reduce)");
-      if (rc) return rc;
-    }
-  });
-  return 0;
+  return launch_gemm(out, out_dtype, map_a, map_b, M, N, K, ldo, plan, ss.scratch, status, sm_count, 0,
+                     "gemm_static_scratch", stream);
 }
