@@ -174,7 +174,7 @@ __device__ __forceinline__ void load_kv_rows_pg(uint8_t* ks, uint8_t* vs, int ke
 constexpr int PF_BQ = 128, PF_BK = 64, PF_THREADS = 256;
 
 template <int D>
-__global__ void __launch_bounds__(PF_THREADS)
+__global__ void __launch_bounds__(PF_THREADS, 2)
 attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restrict__ q, int q_stride,
                         const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                         const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ cu_q,
@@ -189,8 +189,8 @@ attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __re
   uint8_t* vbuf = kbuf + 2 * PF_BK * D * 2;             // [2][64][D]
   constexpr int TILE_BYTES = PF_BK * D * 2;
 
-  const int seq = tile_seq[blockIdx.x], q0 = tile_q0[blockIdx.x];
-  const int h = blockIdx.y, kvh = h / (nq / nkv);
+  const int seq = tile_seq[blockIdx.y], q0 = tile_q0[blockIdx.y];
+  const int h = blockIdx.x, kvh = h / (nq / nkv);   // heads vary fastest: neighbours share K and V in L2
   const int tok0 = cu_q[seq], qlen = cu_q[seq + 1] - tok0, kvlen = kv_lens[seq];
   const int ctx = kvlen - qlen;
   const int nqv = min(PF_BQ, qlen - q0);
@@ -210,11 +210,37 @@ attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __re
   }
   const int kt0 = (kv_lo / PF_BK) * PF_BK;
   const int n_tiles = (kv_hi - kt0 + PF_BK - 1) / PF_BK;
-  load_kv_rows<D>(kbuf, vbuf, 0, PF_BK, kt0, kv_lo, kv_hi, kcache, vcache, bt, nkv, kvh, page_size, page_shift, tid,
-                  PF_THREADS);
-  cp_async_commit();
 
-  uint32_t qf[D / 16][4];
+  // Each thread copies NPER 16-byte chunks of K and of V per tile: rows r_i = tid / CH +
+  // i * (256 / CH), column c = tid % CH.  The pages of its rows are looked up one tile
+  // ahead, so the block-table load is not waited for when the copies are issued.
+  constexpr int CH = D / 8, NPER = PF_BK * CH / PF_THREADS, RSTEP = PF_THREADS / CH;
+  const int my_r = tid / CH, my_c = tid % CH;
+  int pg[NPER];
+  auto lookup = [&](int kt) {
+#pragma unroll
+    for (int i = 0; i < NPER; ++i) {
+      const int j = kt + my_r + i * RSTEP;
+      pg[i] = (j >= kv_lo && j < kv_hi) ? __ldg(bt + (page_shift >= 0 ? (j >> page_shift) : (j / page_size))) : -1;
+    }
+  };
+  auto issue = [&](int kt, int buf) {
+#pragma unroll
+    for (int i = 0; i < NPER; ++i) {
+      const int r = my_r + i * RSTEP, j = kt + r;
+      const bool valid = pg[i] >= 0;
+      const int in_page = page_shift >= 0 ? (j & (page_size - 1)) : (j % page_size);
+      const size_t off = valid ? (((size_t)pg[i] * nkv + kvh) * page_size + in_page) * D + my_c * 8 : 0;
+      const uint32_t so = swz<D>(r, my_c);
+      cp_async16(kbuf + buf * TILE_BYTES + so, kcache + off, valid);
+      cp_async16(vbuf + buf * TILE_BYTES + so, vcache + off, valid);
+    }
+  };
+  lookup(kt0);
+  issue(kt0, 0);
+  cp_async_commit();
+  if (n_tiles > 1) lookup(kt0 + PF_BK);
+
   float o[D / 8][4];
 #pragma unroll
   for (int t = 0; t < D / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
@@ -222,26 +248,20 @@ attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __re
   const int row_lo = warp * 16 + (lane >> 2);           // this thread's rows: row_lo and row_lo + 8
   const int warp_first_pos = first_pos + warp * 16, warp_last_pos = min(last_pos, warp_first_pos + 15);
   const bool warp_active = warp * 16 < nqv;
+  const uint32_t qs_addr = smem_addr(qs);
 
   for (int t = 0; t < n_tiles; ++t) {
     const int kt = kt0 + t * PF_BK;
     const int buf = t & 1;
     if (t + 1 < n_tiles) {
-      load_kv_rows<D>(kbuf + (buf ^ 1) * TILE_BYTES, vbuf + (buf ^ 1) * TILE_BYTES, 0, PF_BK, kt + PF_BK, kv_lo, kv_hi,
-                      kcache, vcache, bt, nkv, kvh, page_size, page_shift, tid, PF_THREADS);
+      issue(kt + PF_BK, buf ^ 1);
       cp_async_commit();
+      if (t + 2 < n_tiles) lookup(kt + 2 * PF_BK);
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
     __syncthreads();
-    if (t == 0) {
-#pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk) {
-        const int mtx = lane >> 3;
-        ldmatrix_x4(qf[kk], smem_addr(qs) + swz<D>(warp * 16 + (mtx & 1) * 8 + (lane & 7), kk * 2 + (mtx >> 1)));
-      }
-    }
     // a warp whose rows all lie before this tile (causal) or after it (window) has nothing to do
     const bool tile_visible = warp_active && kt <= warp_last_pos &&
                               (window <= 0 || kt + PF_BK - 1 > warp_first_pos - window);
@@ -250,14 +270,19 @@ attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __re
       float s[PF_BK / 8][4];
 #pragma unroll
       for (int nt = 0; nt < PF_BK / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+      // S = Q K^T; the Q fragments are re-read from shared memory for every 16 dims (keeps
+      // the register count low enough for two CTAs per SM)
 #pragma unroll
-      for (int kp = 0; kp < PF_BK / 16; ++kp) {
-        float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        qk_16keys<D>(s2, qf, ks_addr, kp * 16, lane);
+      for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t qf[4];
+        const int mtx = lane >> 3;
+        ldmatrix_x4(qf, qs_addr + swz<D>(warp * 16 + (mtx & 1) * 8 + (lane & 7), kk * 2 + (mtx >> 1)));
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          s[2 * kp][c] = s2[0][c];
-          s[2 * kp + 1][c] = s2[1][c];
+        for (int kp = 0; kp < PF_BK / 16; ++kp) {
+          uint32_t bfr[4];
+          ldmatrix_x4(bfr, ks_addr + swz<D>(kp * 16 + (mtx >> 1) * 8 + (lane & 7), kk * 2 + (mtx & 1)));
+          mma_bf16(s[2 * kp], qf, bfr[0], bfr[1]);
+          mma_bf16(s[2 * kp + 1], qf, bfr[2], bfr[3]);
         }
       }
       const bool need_mask = kt + PF_BK - 1 > warp_first_pos || window > 0 || kt < kv_lo;
@@ -506,7 +531,7 @@ int launch_prefill(void* out, int out_stride, const void* q, int q_stride, const
   const size_t smem = (size_t)(PF_BQ + 4 * PF_BK) * D * 2;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return zi_refuse("attention_prefill: cannot get %zu bytes of shared memory", smem);
-  dim3 grid(n_tiles, nq);
+  dim3 grid(nq, n_tiles);
   zi_launch(kern, dim3(grid), dim3(PF_THREADS), smem, stream, (bf16*)out, out_stride, (const bf16*)q, q_stride, (const bf16*)kc,
                                            (const bf16*)vc, bt, bt_stride, cu_q, kv_lens, tile_seq, tile_q0, nq, nkv,
                                            page_size, log2_or_minus1(page_size), window, scale * 1.4426950408889634f);

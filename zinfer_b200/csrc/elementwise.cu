@@ -351,11 +351,12 @@ __global__ void qk_norm_rope_store_kernel(const T* src, int src_stride, const fl
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
-  const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   const int n_heads = nq + (write_kv ? 2 * nkv : 0);
-  if (head >= n_heads) return;
   const int half = d >> 1;
+  // one block per token; its warps take the heads in turn
+  for (int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5); head < n_heads;
+       head += gridDim.y * (blockDim.x >> 5)) {
   auto load = [&](int i) -> float {
     if (part) {
       const float* p = part + (size_t)t * part_width + (size_t)head * d + i;
@@ -377,14 +378,14 @@ __global__ void qk_norm_rope_store_kernel(const T* src, int src_stride, const fl
     dst = q_out + (size_t)t * q_stride + (size_t)head * d;
   } else {
     const int slot = slots[t];
-    if (slot < 0) return;
+    if (slot < 0) continue;
     const int kvh = (head - nq) % nkv;
     T* base = head < nq + nkv ? kcache : vcache;
     dst = base + (((size_t)(slot / page_size) * nkv + kvh) * page_size + (slot % page_size)) * d;
   }
   if (head >= nq + nkv) {  // value head: copy
     for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(load(i));
-    return;
+    continue;
   }
   // the head's pairs (i, i + d/2) this lane owns, read once into registers (d <= 256)
   constexpr int MAXP = 4;
@@ -426,6 +427,7 @@ __global__ void qk_norm_rope_store_kernel(const T* src, int src_stride, const fl
     dst[i] = from_f32<T>(x);
     dst[i + half] = from_f32<T>(y);
   }
+  }  // heads
 }
 
 extern "C" int zi_qk_norm_rope_store(const void* src, int dtype, int T, int src_stride, const float* partials,
@@ -441,8 +443,9 @@ extern "C" int zi_qk_norm_rope_store(const void* src, int dtype, int T, int src_
   if (write_kv && (!kcache || !vcache || !slots || page_size <= 0))
     return zi_refuse("qk_norm_rope_store: writing keys and values needs pages and slots");
   const int n_heads = nq + (write_kv ? 2 * nkv : 0);
-  const int warps = 4;
-  dim3 grid(T, (n_heads + warps - 1) / warps);
+  // few tokens (decode): a warp per head, so that all heads run at once; many tokens: 8 warps share a token's heads
+  const int warps = T <= 256 ? 4 : 8;
+  dim3 grid(T, T <= 256 ? (n_heads + warps - 1) / warps : 1);
   ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(qk_norm_rope_store_kernel<TT>, dim3(grid), dim3(warps * 32), 0, stream, 
                                    (const TT*)src, src_stride, partials, splits, (size_t)split_stride, n_heads * d,
                                    (TT*)q_out, q_stride, nq, nkv, d, qw, kw, eps, cos_t, sin_t, n_table_pos, positions,

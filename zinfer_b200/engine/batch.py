@@ -57,8 +57,32 @@ class StepContext:
     h2d_bytes: int = 0              # size of the one host->device copy that brought these arrays
 
 
+class PinnedStaging:
+    """One pinned host buffer that the uncaptured steps reuse for their arrays (grown when
+    a step needs more).  Reusing it keeps pinned memory from being allocated and freed
+    every step; before it is overwritten, the copy of the previous step has completed."""
+
+    def __init__(self):
+        self._buf: Optional[torch.Tensor] = None
+        self._copied = None
+
+    def get(self, total: int) -> torch.Tensor:
+        cuda = torch.cuda.is_available()
+        if self._buf is None or self._buf.numel() < total:
+            self._buf = torch.empty(max(total, 4096), dtype=torch.int32, pin_memory=cuda)
+            self._copied = torch.cuda.Event() if cuda else None
+        elif self._copied is not None:
+            self._copied.synchronize()
+        return self._buf[:total]
+
+    def mark_copied(self) -> None:
+        if self._copied is not None:
+            self._copied.record()
+
+
 def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile_rows: int, pin: bool = True,
-               static: Optional["StaticStepBuffers"] = None, pf_tile_rows: int = 128) -> StepContext:
+               static: Optional["StaticStepBuffers"] = None, pf_tile_rows: int = 128,
+               staging: Optional[PinnedStaging] = None) -> StepContext:
     """Flattens ``entries``; their pages must already be reserved in ``manager``.
 
     With ``static`` (decode steps replayed from a CUDA graph) the arrays have the
@@ -87,6 +111,10 @@ def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile
     all_q = q_lens + [1] * pad
     dec_list = [i for i, ql in enumerate(all_q) if ql == 1]
     pf_tiles = [(i, t * pf_tile_rows) for i, ql in enumerate(all_q) if ql > 1 for t in range(-(-ql // pf_tile_rows))]
+    # the tiles that read the most keys come first: blocks are handed out in this order, so
+    # the long ones do not end up alone at the tail
+    all_ctx = ctx_lens + [0] * pad
+    pf_tiles.sort(key=lambda it: -(all_ctx[it[0]] + min(all_q[it[0]], it[1] + pf_tile_rows)))
     if static is not None:
         rows = list(range(n))
     else:
@@ -105,6 +133,8 @@ def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile
         total += -(-sz // 4) * 4   # keep every array 16-byte aligned
     if static is not None:
         host = static.host_buffer(total)
+    elif staging is not None:
+        host = staging.get(max(total, 4))
     else:
         host = torch.empty(max(total, 4), dtype=torch.int32, pin_memory=pin and torch.cuda.is_available())
     buf = host.numpy()
@@ -162,6 +192,8 @@ def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile
         static.mark_copied()
     else:
         dev = host.to(device, non_blocking=True)
+        if staging is not None:
+            staging.mark_copied()
 
     def view(name):
         o, s = offs[name]

@@ -20,7 +20,7 @@ from .. import ops
 from ..cache import CacheManager, CacheStorage, OutOfPages
 from ..config.registry import load_config
 from ..weights import load_tensors, random_tensors
-from .batch import StepContext, StepEntry, build_step
+from .batch import PinnedStaging, StepContext, StepEntry, build_step
 from .model import DecoderModel
 
 
@@ -54,6 +54,7 @@ class ModelRunner:
         self.pf_tile_rows = ops.attention_prefill_tile_rows()
         self.steps_run = 0
         self.last_h2d_bytes = 0
+        self._staging = PinnedStaging()
         # decode steps are replayed from CUDA graphs when every mixer can be captured
         self.graphs = None
         if cuda_graphs and model.device.type == "cuda" and all(
@@ -167,7 +168,8 @@ class ModelRunner:
             else:
                 logits = all_rows[torch.tensor(wanted, device=self.device)]
         else:
-            ctx = build_step(self.manager, entries, self.device, self.tile_rows, pf_tile_rows=self.pf_tile_rows)
+            ctx = build_step(self.manager, entries, self.device, self.tile_rows, pf_tile_rows=self.pf_tile_rows,
+                             staging=self._staging)
             self.last_h2d_bytes = ctx.h2d_bytes
             logits = self.model.forward(ctx)
         for e in entries:
