@@ -124,3 +124,9 @@ def argmax(logits, out=None):
 def attention(q, k_cache, v_cache, block_tables, step, num_heads, num_kv_heads, head_dim, page_size, window, scale):
     return paged_attention(q, k_cache, v_cache, block_tables, step.cu_q, step.kv_lens, step.tile_seq, step.tile_q0,
                            num_heads, num_kv_heads, head_dim, page_size, window, scale)
+
+
+def patch_tokens(ids, prev, dst, src):
+    for i in range(dst.numel()):
+        if int(dst[i]) >= 0:
+            ids[int(dst[i])] = prev[int(src[i])]

@@ -145,3 +145,55 @@ def test_waiting_requests_keep_their_order():
                 first_seen.append(rid)
     assert first_seen == [0, 1, 2, 3, 4]
     assert max(len(step) for step in log) <= 2
+
+
+def drain_pipelined(cache, sched, limit=2000):
+    """The engine's pipelined order: a step is launched (advance) before the tokens of the
+    step before it are read (resolve), so end-of-sequence is noticed one step late."""
+    done, pending = [], None
+    while sched.has_unfinished() or pending is not None:
+        limit -= 1
+        assert limit > 0
+        plan = sched.schedule()
+        sampled = []
+        for s in plan.scheduled:
+            assert cache.length(s.request.request_id) == s.start
+            cache.commit(s.request.request_id, s.count)
+            if s.samples:
+                # the fake token depends on the request and its length only, like a seeded draw
+                r = s.request
+                sampled.append(fake_token(Request(r.request_id, [0] * (s.start + s.count), r.params)))
+        sched.advance(plan)
+        if pending is not None:
+            done += sched.resolve(*pending)
+        pending = (plan, sampled) if plan.scheduled else None
+        if not plan.scheduled:
+            done += sched.resolve(plan, [])
+        cache.check()
+    return done
+
+
+def test_pipelined_resolution_gives_the_same_tokens_and_reasons():
+    def build(num_pages):
+        cache, sched = make(num_pages=num_pages, page=4, budget=32, max_running=3)
+        reqs = [req(i, n, 10) for i, n in enumerate((6, 7, 5, 9))]
+        # request 1 stops at its 4th token, request 3 at its 1st
+        reqs[1].eos_token_ids = (fake_token(Request(1, [0] * (7 + 3), reqs[1].params)),)
+        reqs[3].eos_token_ids = (fake_token(Request(3, [0] * 9, reqs[3].params)),)
+        for r in reqs:
+            sched.add(r)
+        return cache, sched
+
+    for pages in (64, 9):
+        cache, sched = build(pages)
+        sync, _ = drain(cache, sched)
+        cache2, sched2 = build(pages)
+        piped = drain_pipelined(cache2, sched2)
+        key = lambda rs: sorted((r.request_id, tuple(r.output), r.finish_reason) for r in rs)
+        assert key(piped) == key(sync)
+        assert all(-1 not in r.output for r in piped), "a placeholder was left in an output"
+        by = {r.request_id: r for r in piped}
+        assert by[1].finish_reason == "stop" and len(by[1].output) == 3
+        assert by[3].finish_reason == "stop" and by[3].output == []
+        assert by[0].finish_reason == "length" and len(by[0].output) == 10
+        assert not cache2.requests and cache2.free_pages() == [pages]

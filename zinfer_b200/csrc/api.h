@@ -19,6 +19,7 @@ int zi_add_rmsnorm(float* h, const void* delta, int delta_dtype, const float* de
 int zi_residual_add(float* h, const void* delta, int delta_dtype, long long n, cudaStream_t stream);
 int zi_residual_add_partials(float* h, const float* partials, int splits, long long split_stride, long long n,
                              cudaStream_t stream);
+int zi_patch_tokens(int* ids, const int* prev, const int* dst, const int* src, int n, cudaStream_t stream);
 int zi_swiglu(void* out, const void* gu, int dtype, int T, int I, cudaStream_t stream);
 int zi_swiglu_partials(void* out, int dtype, const float* partials, int splits, long long split_stride, int T, int I,
                        cudaStream_t stream);

@@ -472,3 +472,19 @@ extern "C" int zi_residual_add_partials(float* h, const float* partials, int spl
                                                                              (size_t)split_stride, (size_t)n);
   return zi_check_launch("residual_add_partials");
 }
+
+// ids[dst[i]] = prev[src[i]] for i < n with dst[i] >= 0: the tokens a step feeds that were
+// sampled by the step before it are taken on the device, so the host need not wait for them.
+__global__ void patch_tokens_kernel(int* __restrict__ ids, const int* __restrict__ prev, const int* __restrict__ dst,
+                                    const int* __restrict__ src, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n && dst[i] >= 0) ids[dst[i]] = prev[src[i]];
+}
+
+extern "C" int zi_patch_tokens(int* ids, const int* prev, const int* dst, const int* src, int n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  zi_launch(patch_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, ids, prev, dst, src, n);
+  return zi_check_launch("patch_tokens");
+}

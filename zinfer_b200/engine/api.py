@@ -21,6 +21,17 @@ from .scheduler import Request, Scheduler, StepPlan
 
 
 @dataclass
+class _InFlight:
+    """A launched step whose sampled tokens the host has not read yet."""
+
+    plan: StepPlan
+    tokens_dev: Optional[torch.Tensor]     # [rows] int32 on the device
+    tokens_host: Optional[torch.Tensor]    # the pinned copy (valid once `done` has completed)
+    done: Optional[object]
+    row_of: dict                           # request id -> row of tokens_dev
+
+
+@dataclass
 class GenerationResult:
     request_id: object
     prompt_token_ids: list[int]
@@ -44,7 +55,8 @@ class Engine:
     def __init__(self, model_dir: Optional[str] = None, *, config=None, random_weights_seed: Optional[int] = None,
                  dtype="bfloat16", device="cuda:0", page_size: int = 16, kv_cache_tokens: Optional[int] = None,
                  num_pages: Optional[int] = None, max_model_len: Optional[int] = None,
-                 max_batched_tokens: int = 2048, chunk_size: Optional[int] = None, max_requests: int = 64):
+                 max_batched_tokens: int = 2048, chunk_size: Optional[int] = None, max_requests: int = 64,
+                 pipelined: bool = True):
         tdtype = _DTYPES.get(dtype)
         if tdtype is None:
             raise ValueError(f"dtype must be bfloat16 or float32, got {dtype!r}")
@@ -65,6 +77,12 @@ class Engine:
         self.sampler = Sampler(model.spec.vocab_size, max_requests, model.device)
         self._ids = itertools.count()
         self._live: dict[object, Request] = {}
+        self.pipelined = pipelined
+        self._inflight: Optional[_InFlight] = None
+        self._finished_early: list[GenerationResult] = []
+        pin = torch.cuda.is_available() and model.device.type == "cuda"
+        self._token_buffers = [torch.zeros(max_requests, dtype=torch.int32, pin_memory=pin) for _ in range(3)]
+        self._token_turn = 0
 
     def _size_pool(self, model_dir, config, dtype, device, page_size, max_model_len, max_requests) -> int:
         kv_cache_tokens, num_pages = self._pool_args
@@ -92,34 +110,75 @@ class Engine:
         self._live[rid] = req
         return rid
 
-    def has_unfinished(self) -> bool:
-        return self.scheduler.has_unfinished()
-
     # ---------------------------------------------------------------------- step
-    def step(self) -> list[GenerationResult]:
-        """One scheduler decision, one step of the model, one token for every request
-        that reached its end.  Returns the requests that finished."""
-        plan: StepPlan = self.scheduler.schedule()
+    def _launch(self, plan: StepPlan) -> Optional[_InFlight]:
+        """Builds the plan's batch, runs the model and the sampler, and starts the copy of
+        the sampled tokens to the host.  Does not wait for anything."""
+        prev = self._inflight
+        entries, rows = [], []
+        for s in plan.scheduled:
+            r = s.request
+            toks = r.tokens[s.start:s.start + s.count]
+            src = None
+            if Scheduler.PLACEHOLDER in toks:
+                if s.count == 1 and prev is not None and r.request_id in prev.row_of:
+                    src = prev.row_of[r.request_id]      # sampled by the step in flight: taken on the device
+                else:
+                    # a longer portion holds a token the host has not read yet: read it first
+                    self._finished_early += self._resolve()
+                    prev = None
+                    toks = r.tokens[s.start:s.start + s.count]
+            entries.append(StepEntry(r.request_id, toks, [s.count - 1] if s.samples else [], token_src=src))
+            if s.samples:
+                rows.append(r)
+        logits = self.runner.step(entries, prev_tokens=prev.tokens_dev if prev is not None else None)
+        if not rows:
+            return _InFlight(plan, None, None, None, {})
+        tokens = self.sampler.sample(logits, [r.request_id for r in rows], [r.params for r in rows],
+                                     [len(r.output) for r in rows])
+        host = self._token_buffers[self._token_turn % len(self._token_buffers)]
+        self._token_turn += 1
+        host[:len(rows)].copy_(tokens, non_blocking=True)     # the step's one read back to the host
+        done = torch.cuda.Event() if tokens.is_cuda else None
+        if done is not None:
+            done.record()
+        return _InFlight(plan, tokens, host[:len(rows)], done, {r.request_id: i for i, r in enumerate(rows)})
+
+    def _resolve(self) -> list[GenerationResult]:
+        """Waits for the tokens of the step in flight and hands them to the scheduler."""
+        fl, self._inflight = self._inflight, None
+        if fl is None:
+            return []
         sampled: list[int] = []
-        if plan.scheduled:
-            entries, rows = [], []
-            for s in plan.scheduled:
-                toks = s.request.tokens[s.start:s.start + s.count]
-                entries.append(StepEntry(s.request.request_id, toks, [s.count - 1] if s.samples else []))
-                if s.samples:
-                    rows.append(s.request)
-            logits = self.runner.step(entries)
-            if rows:
-                tokens = self.sampler.sample(logits, [r.request_id for r in rows], [r.params for r in rows],
-                                             [len(r.output) for r in rows])
-                sampled = tokens.cpu().tolist()   # the step's one read back to the host
-        finished = self.scheduler.update(plan, sampled)
+        if fl.tokens_host is not None:
+            if fl.done is not None:
+                fl.done.synchronize()
+            sampled = fl.tokens_host.tolist()
         out = []
-        for r in finished:
+        for r in self.scheduler.resolve(fl.plan, sampled):
             self.sampler.end_request(r.request_id)
             self._live.pop(r.request_id, None)
             out.append(GenerationResult(r.request_id, r.prompt, list(r.output), r.finish_reason, r.preemptions))
         return out
+
+    def step(self) -> list[GenerationResult]:
+        """One scheduler decision and one step of the model.  With ``pipelined`` (the
+        default) the step is launched before the tokens of the step before it have been
+        read: decoded tokens are fed on the device, the host prepares the next batch while
+        the GPU works, and requests are reported finished one call later.  Returns the
+        requests that finished."""
+        plan: StepPlan = self.scheduler.schedule()
+        self._finished_early = []
+        launched = self._launch(plan) if plan.scheduled else _InFlight(plan, None, None, None, {})
+        self.scheduler.advance(plan)
+        finished = self._finished_early + self._resolve()       # the step before this one
+        self._inflight = launched
+        if not self.pipelined or not plan.scheduled:
+            finished += self._resolve()
+        return finished
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_unfinished() or self._inflight is not None
 
     # ------------------------------------------------------------------ generate
     def generate(self, prompt_ids: Sequence[Sequence[int]], params=None, **options) -> list[GenerationResult]:

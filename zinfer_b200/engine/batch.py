@@ -22,6 +22,9 @@ class StepEntry:
     request_id: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()        # indices into `tokens` whose logits are returned
+    # For an entry of one token whose value is not yet known on the host: the row of the
+    # previous step's sampled-token tensor that holds it (the token in `tokens` is a placeholder).
+    token_src: Optional[int] = None
 
 
 @dataclass
@@ -55,6 +58,9 @@ class StepContext:
     max_kv_len: int = 0
     all_decode: bool = False        # every entry brings exactly one token
     h2d_bytes: int = 0              # size of the one host->device copy that brought these arrays
+    patch_dst: Optional[torch.Tensor] = None   # flat token positions to fill from the previous step's tokens
+    patch_src: Optional[torch.Tensor] = None   # rows of the previous step's sampled tokens
+    n_patch: int = 0
 
 
 class PinnedStaging:
@@ -125,6 +131,9 @@ def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile
     sizes = [("token_ids", T), ("positions", T), ("cu_q", n + 1), ("kv_lens", n), ("state_slots", n),
              ("tile_seq", n_tiles), ("tile_q0", n_tiles), ("logit_rows", R), ("dec_seq", len(dec_list)),
              ("pf_tile_seq", len(pf_tiles)), ("pf_tile_q0", len(pf_tiles))]
+    patches = [(int(cu[i]), int(e.token_src)) for i, e in enumerate(entries) if e.token_src is not None]
+    n_patch_cap = n if static is not None else len(patches)
+    sizes += [("patch_dst", n_patch_cap), ("patch_src", n_patch_cap)]
     for gi in range(n_groups):
         sizes += [(f"slots{gi}", T), (f"bt{gi}", n * widths[gi])]
     offs, total = {}, 0
@@ -151,7 +160,7 @@ def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile
     for i in range(n):
         a, b = int(cu[i]), int(cu[i + 1])
         if i < n_real:
-            tok[a:b] = np.asarray(entries[i].tokens, dtype=np.int64)
+            tok[a:b] = np.maximum(np.asarray(entries[i].tokens, dtype=np.int64), 0)   # placeholders are patched on the device
             pos[a:b] = np.arange(ctx_lens[i], ctx_lens[i] + q_lens[i])
         for t in range(n_tiles_per[i]):
             tseq[ti] = i
@@ -159,6 +168,11 @@ def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile
             ti += 1
     arr("cu_q")[:] = cu
     arr("dec_seq")[:] = dec_list
+    if n_patch_cap:
+        arr("patch_dst")[:] = -1
+        arr("patch_src")[:] = 0
+        arr("patch_dst")[:len(patches)] = [d for d, _ in patches]
+        arr("patch_src")[:len(patches)] = [s_ for _, s_ in patches]
     arr("pf_tile_seq")[:] = [i for i, _ in pf_tiles]
     arr("pf_tile_q0")[:] = [t for _, t in pf_tiles]
     kv = arr("kv_lens")
@@ -205,6 +219,8 @@ def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile
         kv_lens=view("kv_lens"), state_slots=view("state_slots"), tile_seq=view("tile_seq"), tile_q0=view("tile_q0"),
         dec_seq=view("dec_seq"), pf_tile_seq=view("pf_tile_seq"), pf_tile_q0=view("pf_tile_q0"),
         n_dec=len(dec_list), n_pf_tiles=len(pf_tiles),
+        patch_dst=view("patch_dst") if n_patch_cap else None, patch_src=view("patch_src") if n_patch_cap else None,
+        n_patch=len(patches),
         logit_rows=view("logit_rows") if R else None, kv_groups=groups, q_lens=q_lens, ctx_lens=ctx_lens,
         max_q_len=max(q_lens, default=0),
         # a captured graph serves later steps with longer requests: no host-side length may shape its launches

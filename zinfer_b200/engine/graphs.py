@@ -39,7 +39,7 @@ class DecodeGraphs:
         return (len(entries) <= self.max_batch and all(len(e.tokens) == 1 for e in entries)
                 and self.bucket_for(len(entries)) is not None)
 
-    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def run(self, entries: Sequence[StepEntry], prev_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Logits [bucket, vocab] (a buffer that the next replay overwrites); the
         first len(entries) rows belong to the entries, in order."""
         runner = self.runner
@@ -51,6 +51,8 @@ class DecodeGraphs:
         ctx = build_step(runner.manager, entries, runner.device, runner.tile_rows, static=state["static"],
                          pf_tile_rows=runner.pf_tile_rows)
         runner.last_h2d_bytes = ctx.h2d_bytes
+        if ctx.n_patch:   # outside the graph: which rows are patched changes from step to step
+            ops.patch_tokens(ctx.token_ids, prev_tokens, ctx.patch_dst, ctx.patch_src)
         if state["graph"] is None:
             if state["warm"] < 1:
                 # first use: run uncaptured, so that one-time set-up (function attributes,

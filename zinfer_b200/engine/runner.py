@@ -116,7 +116,12 @@ class ModelRunner:
             seen.add(e.request_id)
             if len(e.tokens) == 0:
                 raise StepError(f"request {e.request_id!r} brings no tokens")
-            bad = [t for t in e.tokens if not 0 <= int(t) < V]
+            if e.token_src is not None:
+                if len(e.tokens) != 1:
+                    raise StepError(f"request {e.request_id!r}: only a single token can come from the step before")
+                bad = []
+            else:
+                bad = [t for t in e.tokens if not 0 <= int(t) < V]
             if bad:
                 raise StepError(f"request {e.request_id!r}: token id {bad[0]} is outside the vocabulary of {V}")
             have = self.manager.length(e.request_id) if self.manager.has_request(e.request_id) else 0
@@ -151,15 +156,18 @@ class ModelRunner:
                 self.manager.free_request(rid)
             raise
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], prev_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Runs the entries as one batch; returns logits [wanted, vocab] in the order
-        of the entries and of each entry's ``want`` (None if nothing is wanted)."""
+        of the entries and of each entry's ``want`` (None if nothing is wanted).
+        ``prev_tokens`` (int32, on the device) is read by entries with ``token_src``."""
         if not entries:
             return None
         self.validate(entries)
+        if any(e.token_src is not None for e in entries) and prev_tokens is None:
+            raise StepError("an entry takes its token from the step before, but no such tokens were given")
         self.reserve(entries)
         if self.graphs is not None and self.graphs.eligible(entries):
-            all_rows = self.graphs.run(entries)
+            all_rows = self.graphs.run(entries, prev_tokens)
             wanted = [i for i, e in enumerate(entries) if len(e.want)]
             if not wanted:
                 logits = None
@@ -171,6 +179,8 @@ class ModelRunner:
             ctx = build_step(self.manager, entries, self.device, self.tile_rows, pf_tile_rows=self.pf_tile_rows,
                              staging=self._staging)
             self.last_h2d_bytes = ctx.h2d_bytes
+            if ctx.n_patch:
+                ops.patch_tokens(ctx.token_ids, prev_tokens, ctx.patch_dst, ctx.patch_src)
             logits = self.model.forward(ctx)
         for e in entries:
             self.manager.commit(e.request_id, len(e.tokens))

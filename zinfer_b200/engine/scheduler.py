@@ -228,11 +228,13 @@ class Scheduler:
         return plan
 
     # --------------------------------------------------------------------- update
-    def update(self, plan: StepPlan, sampled: Sequence[int]) -> list[Request]:
-        """Takes the tokens sampled for the plan's sampling entries (in plan order),
-        appends them and finishes what has ended.  Returns the finished requests."""
-        finished = list(plan.finished)
-        it = iter(sampled)
+    PLACEHOLDER = -1   # a token that has been sampled on the device but not yet read by the host
+
+    def advance(self, plan: StepPlan) -> None:
+        """Call when the plan's step has been launched: the fed tokens count as computed,
+        every sampling request gets a placeholder for the token being sampled, and requests
+        that thereby reach their length limit leave the running set (their pages are given
+        back; later work on the same stream cannot overtake the step that still reads them)."""
         for s in plan.scheduled:
             r = s.request
             was_decode = s.count == 1 and s.start >= len(r.prompt)
@@ -243,13 +245,39 @@ class Scheduler:
                 self.stats.prompt_tokens += s.count
             if not s.samples:
                 continue
-            tok = int(next(it))
-            if not r.params.ignore_eos and tok in r.eos_token_ids:
-                self._finish(r, "stop")              # the end token is neither emitted nor fed
-                finished.append(r)
-                continue
-            r.output.append(tok)
+            r.output.append(self.PLACEHOLDER)
             if len(r.output) >= r.params.max_new_tokens or r.num_tokens >= self.max_model_len:
                 self._finish(r, "length")
+
+    def resolve(self, plan: StepPlan, sampled: Sequence[int]) -> list[Request]:
+        """Call when the plan's sampled tokens (in plan order) have reached the host: fills
+        the placeholders in, ends requests that drew an end-of-sequence token (which is
+        neither emitted nor fed), and returns all requests that this plan finished."""
+        finished = list(plan.finished)
+        it = iter(sampled)
+        for s in plan.scheduled:
+            if not s.samples:
+                continue
+            r = s.request
+            tok = int(next(it))
+            if r.finish_reason == "stop":
+                continue                                 # ended by an earlier token; this one is dropped
+            idx = s.start + s.count - len(r.prompt)      # which output this step sampled
+            if not r.params.ignore_eos and tok in r.eos_token_ids:
+                del r.output[idx:]                       # the end token and anything in flight after it
+                if r.status != "finished":
+                    self._finish(r, "stop")
+                else:                                    # had also reached its length limit with this token
+                    r.finish_reason = "stop"
+                finished.append(r)
+                continue
+            if idx < len(r.output):
+                r.output[idx] = tok
+            if r.status == "finished" and r.finish_reason == "length" and idx == len(r.output) - 1:
                 finished.append(r)
         return finished
+
+    def update(self, plan: StepPlan, sampled: Sequence[int]) -> list[Request]:
+        """The two phases back to back, for a host that waits for each step's tokens."""
+        self.advance(plan)
+        return self.resolve(plan, sampled)

@@ -129,6 +129,14 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Ten
     return out
 
 
+def patch_tokens(ids: torch.Tensor, prev: torch.Tensor, dst: torch.Tensor, src: torch.Tensor) -> None:
+    """``ids[dst[i]] = prev[src[i]]`` where ``dst[i] >= 0``: feeds tokens sampled by the
+    step before without a round trip through the host."""
+    for t, name in ((ids, "ids"), (prev, "prev"), (dst, "dst"), (src, "src")):
+        _i32(t, name)
+    _check(lib().zi_patch_tokens(_ptr(ids), _ptr(prev), _ptr(dst), _ptr(src), dst.numel(), _stream()), "patch_tokens")
+
+
 def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                 out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
