@@ -15,12 +15,14 @@ def embed_gather(table, ids, out=None):
 
 
 def add_rmsnorm(h, delta, weight, eps, out_dtype, rows=None, out=None):
-    if delta is not None:
-        if rows is None:
+    if rows is None:
+        if delta is not None:
             h += delta.to(torch.float32)
-        else:
-            h[rows.long()] += delta[rows.long()].to(torch.float32)
-    x = h if rows is None else h[rows.long()]
+        x = h
+    else:   # picked rows (repeats allowed): h itself stays as it is
+        x = h[rows.long()]
+        if delta is not None:
+            x = x + delta[rows.long()].to(torch.float32)
     ms = (x * x).mean(dim=-1, keepdim=True)
     inv = 1.0 / torch.sqrt(ms + torch.tensor(eps, dtype=torch.float32))
     return (x * weight * inv).to(out_dtype)
@@ -30,8 +32,23 @@ def residual_add(h, delta):
     h += delta.to(torch.float32)
 
 
-def swiglu(gate_up, out=None, out_dtype=None):
+SWIGLU_INTERLEAVE = 64
+
+
+def interleave_gate_up(gate, up, block=64):
+    I, K = gate.shape
+    return torch.stack([gate.view(I // block, block, K), up.view(I // block, block, K)], dim=1).reshape(2 * I, K).contiguous()
+
+
+def linear_swiglu(x, w_interleaved, out_dtype=None):
+    return swiglu(linear(x, w_interleaved, out_dtype=torch.float32), interleave=64).to(out_dtype or x.dtype)
+
+
+def swiglu(gate_up, out=None, out_dtype=None, interleave=0):
     I = gate_up.shape[1] // 2
+    if interleave:
+        blocks = gate_up.reshape(gate_up.shape[0], I // interleave, 2, interleave)
+        gate_up = torch.cat([blocks[:, :, 0].reshape(-1, I), blocks[:, :, 1].reshape(-1, I)], dim=1)
     g, u = gate_up[:, :I].to(torch.float32), gate_up[:, I:].to(torch.float32)
     return (g / (1.0 + torch.exp(-g)) * u).to(gate_up.dtype)
 

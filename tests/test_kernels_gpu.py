@@ -69,6 +69,7 @@ def test_add_rmsnorm(dtype, T, H, eps):
     got = ops().add_rmsnorm(h_got, delta, w, eps, dtype, rows=rows)
     assert got.shape == (3, H)
     torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+    assert torch.equal(h_got, h) and torch.equal(h_ref, h)     # picking rows (even twice) leaves the residual alone
 
 
 def test_rmsnorm_reference_vector():
@@ -214,6 +215,29 @@ def test_split_products_and_their_consumers():
     torch.testing.assert_close(q1.float(), q2[:, :nq * d].float(), rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(caches[0].float(), caches[2].float(), rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(caches[1].float(), caches[3].float(), rtol=2e-2, atol=2e-2)
+    assert o.kernel_status() == 0
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 256, 128), (8, 3072, 4096), (33, 640, 200), (64, 1024, 512), (65, 192, 72),
+                                   (300, 512, 264), (2048, 1536, 1024), (130, 64, 64)])
+def test_linear_swiglu_fused_epilogue(M, I, K):
+    """gate_up product with the SwiGLU in its epilogue, few tokens (weight rows on the MMA
+    lanes, exchange through shared memory) and many (tokens on the lanes)."""
+    o = ops()
+    x = rnd(M, K, dtype=torch.bfloat16)
+    wg = rnd(I, K, dtype=torch.bfloat16, scale=0.05, seed=1)
+    wu = rnd(I, K, dtype=torch.bfloat16, scale=0.05, seed=2)
+    w = o.interleave_gate_up(wg, wu)
+    assert torch.equal(w[:64], wg[:64]) and torch.equal(w[64:128], wu[:64]) and torch.equal(w[128:192], wg[64:128])
+    got = o.linear_swiglu(x, w)
+    g = x.float() @ wg.float().T
+    u = x.float() @ wu.float().T
+    want = g / (1 + torch.exp(-g)) * u
+    assert got.shape == (M, I) and got.dtype == torch.bfloat16
+    torch.testing.assert_close(got.float(), want, rtol=1.6e-2, atol=2e-3 * K ** 0.5 * 0.05 + 1e-3)
+    # the unfused route (product, then the SwiGLU kernel on the interleaved columns) agrees
+    unfused = o.swiglu(o.linear(x, w), interleave=64)
+    torch.testing.assert_close(unfused.float(), want, rtol=2e-2, atol=2e-3 * K ** 0.5 * 0.05 + 2e-3)
     assert o.kernel_status() == 0
 
 

@@ -20,9 +20,11 @@ int zi_residual_add(float* h, const void* delta, int delta_dtype, long long n, c
 int zi_residual_add_partials(float* h, const float* partials, int splits, long long split_stride, long long n,
                              cudaStream_t stream);
 int zi_patch_tokens(int* ids, const int* prev, const int* dst, const int* src, int n, cudaStream_t stream);
-int zi_swiglu(void* out, const void* gu, int dtype, int T, int I, cudaStream_t stream);
+int zi_swiglu(void* out, const void* gu, int dtype, int T, int I, int interleave, cudaStream_t stream);
 int zi_swiglu_partials(void* out, int dtype, const float* partials, int splits, long long split_stride, int T, int I,
-                       cudaStream_t stream);
+                       int interleave, cudaStream_t stream);
+int zi_gemm_tcgen05_swiglu(void* out, int out_dtype, const void* x, const void* w, int M, int N2, int K, int ldx,
+                           int ldw, int ldo, int sm_count, cudaStream_t stream);
 int zi_rope_table(float* cos_t, float* sin_t, int n_pos, int d, float theta, cudaStream_t stream);
 int zi_qk_norm_rope_store(const void* src, int dtype, int T, int src_stride, const float* partials, int splits,
                           long long split_stride, void* q_out, int q_stride, int nq, int nkv, int d, const float* qw,

@@ -32,6 +32,7 @@ extern "C" int zi_embed_gather(float* h, const void* table, int table_dtype, con
 
 // ------------------------------------------------------------ residual add + RMSNorm
 // h[row] += delta[row] (when delta is given), out[r] = h[row] * w / sqrt(mean(h[row]^2) + eps).
+// With `rows` (a gather of picked rows, possibly with repeats) h itself is not modified.
 // One block per row; the sum of squares is taken in a fixed order.
 // The update may also come as split-K partial sums: dpart[z][row][i], z < splits, added in order.
 template <typename TD, typename TO>
@@ -52,14 +53,14 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
       float d = 0.f;
       for (int z = 0; z < splits; ++z) d += dr[z * zstride + i];
       const float v = hr[i] + d;
-      hr[i] = v;
+      if (!rows) hr[i] = v;
       ss += v * v;
     }
   } else if (delta) {
     const TD* dr = delta + (size_t)row * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
       float v = hr[i] + to_f32(dr[i]);
-      hr[i] = v;
+      if (!rows) hr[i] = v;
       ss += v * v;
     }
   } else {
@@ -71,7 +72,22 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
   const float total = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(total / (float)H + eps);
   TO* o = out + (size_t)r * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<TO>(hr[i] * w[i] * inv);
+  if (!rows) {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<TO>(hr[i] * w[i] * inv);
+  } else {
+    // picked rows: h is left as it is (a row may be picked twice), the sum is formed again
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float v = hr[i];
+      if (dpart) {
+        float d = 0.f;
+        for (int z = 0; z < splits; ++z) d += dpart[z * zstride + (size_t)row * H + i];
+        v += d;
+      } else if (delta) {
+        v += to_f32(delta[(size_t)row * H + i]);
+      }
+      o[i] = from_f32<TO>(v * w[i] * inv);
+    }
+  }
 }
 
 // The same with the row held in registers: one read of h and delta, one write of h and
@@ -137,11 +153,11 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restri
           d.x += p.x; d.y += p.y; d.z += p.z; d.w += p.w;
         }
         a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
-        Vec4<float>::store(hr + 4 * idx, a);
+        if (!rows) Vec4<float>::store(hr + 4 * idx, a);   // picked rows leave h as it is (a row may be picked twice)
       } else if (delta) {
         const float4 d = Vec4<TD>::load(delta + (size_t)row * H + 4 * idx);
         a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
-        Vec4<float>::store(hr + 4 * idx, a);
+        if (!rows) Vec4<float>::store(hr + 4 * idx, a);
       }
       v[i] = a;
       ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
@@ -220,24 +236,38 @@ extern "C" int zi_residual_add(float* h, const void* delta, int delta_dtype, lon
 }
 
 // --------------------------------------------------------------------------- SwiGLU
-// gu is [T, 2I]: gate in the first I columns, up in the last I.  out[t,i] = silu(g) * u.
+// gu is [T, 2I].  interleave == 0: gate in the first I columns, up in the last I.
+// interleave == 64: blocks of 128 columns hold 64 gate then the 64 up values of the same
+// features.  out[t,i] = silu(g) * u.
+__device__ __forceinline__ void gate_up_columns(int i, int I, int interleave, int& gcol, int& ucol) {
+  if (interleave) {
+    gcol = (i / interleave) * 2 * interleave + (i % interleave);
+    ucol = gcol + interleave;
+  } else {
+    gcol = i;
+    ucol = i + I;
+  }
+}
+
 template <typename T>
-__global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int I, size_t total) {
+__global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int I, size_t total, int interleave) {
   pdl_launch_dependents();
   pdl_wait();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const size_t t = idx / I;
   const int i = (int)(idx - t * I);
-  const float g = to_f32(gu[t * 2 * I + i]);
-  const float u = to_f32(gu[t * 2 * I + I + i]);
+  int gc, uc;
+  gate_up_columns(i, I, interleave, gc, uc);
+  const float g = to_f32(gu[t * 2 * I + gc]);
+  const float u = to_f32(gu[t * 2 * I + uc]);
   out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
 }
 
 // gate and up given as split-K partial sums part[z][t][2I]; four elements per thread.
 template <typename T>
 __global__ void swiglu_partials_kernel(T* __restrict__ out, const float* __restrict__ part, int splits, size_t zstride,
-                                       int I, size_t total_vec) {
+                                       int I, size_t total_vec, int interleave) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -246,9 +276,11 @@ __global__ void swiglu_partials_kernel(T* __restrict__ out, const float* __restr
   const size_t t = idx / per_row;
   const int i = (int)(idx - t * per_row) * 4;
   float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
+  int gc, uc;
+  gate_up_columns(i, I, interleave, gc, uc);
   for (int z = 0; z < splits; ++z) {
-    const float* p = part + z * zstride + t * 2 * I + i;
-    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + I);
+    const float* p = part + z * zstride + t * 2 * I;
+    const float4 a = *reinterpret_cast<const float4*>(p + gc), b = *reinterpret_cast<const float4*>(p + uc);
     g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
     u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
   }
@@ -258,7 +290,8 @@ __global__ void swiglu_partials_kernel(T* __restrict__ out, const float* __restr
 
 // Eight elements per thread (16-byte loads of bfloat16, two of float); needs I % 8 == 0.
 template <typename T>
-__global__ void swiglu_vec_kernel(T* __restrict__ out, const T* __restrict__ gu, int I, size_t total_vec) {
+__global__ void swiglu_vec_kernel(T* __restrict__ out, const T* __restrict__ gu, int I, size_t total_vec,
+                                  int interleave) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -266,8 +299,10 @@ __global__ void swiglu_vec_kernel(T* __restrict__ out, const T* __restrict__ gu,
   const int per_row = I >> 3;
   const size_t t = idx / per_row;
   const int i = (int)(idx - t * per_row) * 8;
-  const T* g = gu + t * 2 * I + i;
-  const T* u = g + I;
+  int gc, uc;
+  gate_up_columns(i, I, interleave, gc, uc);
+  const T* g = gu + t * 2 * I + gc;
+  const T* u = gu + t * 2 * I + uc;
   T* o = out + t * I + i;
 #pragma unroll
   for (int k = 0; k < 8; k += 4) {
@@ -278,18 +313,19 @@ __global__ void swiglu_vec_kernel(T* __restrict__ out, const T* __restrict__ gu,
 }
 
 extern "C" int zi_swiglu_partials(void* out, int dtype, const float* partials, int splits, long long split_stride,
-                                  int T, int I, cudaStream_t stream) {
+                                  int T, int I, int interleave, cudaStream_t stream) {
   const size_t total = (size_t)T * I;
   if (total == 0) return 0;
   if (I % 4 || (uintptr_t)partials % 16 || (uintptr_t)out % 8 || split_stride % 4)
     return zi_refuse("swiglu_partials: needs I %% 4 == 0 and aligned buffers");
   const size_t total_vec = total / 4;
   ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(swiglu_partials_kernel<TT>, dim3((unsigned)((total_vec + 255) / 256)), dim3(256), 0, stream, 
-                                   (TT*)out, partials, splits, (size_t)split_stride, I, total_vec));
+                                   (TT*)out, partials, splits, (size_t)split_stride, I, total_vec, interleave));
   return zi_check_launch("swiglu_partials");
 }
 
-extern "C" int zi_swiglu(void* out, const void* gu, int dtype, int T, int I, cudaStream_t stream) {
+extern "C" int zi_swiglu(void* out, const void* gu, int dtype, int T, int I, int interleave, cudaStream_t stream) {
+  if (interleave && (interleave % 8 || I % interleave)) return zi_refuse("swiglu: interleave %d does not fit I = %d", interleave, I);
   const size_t total = (size_t)T * I;
   if (total == 0) return 0;
   const int threads = 256;
@@ -297,11 +333,11 @@ extern "C" int zi_swiglu(void* out, const void* gu, int dtype, int T, int I, cud
     const size_t total_vec = total / 8;
     const unsigned blocks = (unsigned)((total_vec + threads - 1) / threads);
     ZI_DISPATCH_DTYPE(dtype, TT,
-                      zi_launch(swiglu_vec_kernel<TT>, dim3(blocks), dim3(threads), 0, stream, (TT*)out, (const TT*)gu, I, total_vec));
+                      zi_launch(swiglu_vec_kernel<TT>, dim3(blocks), dim3(threads), 0, stream, (TT*)out, (const TT*)gu, I, total_vec, interleave));
     return zi_check_launch("swiglu");
   }
   const unsigned blocks = (unsigned)((total + threads - 1) / threads);
-  ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(swiglu_kernel<TT>, dim3(blocks), dim3(threads), 0, stream, (TT*)out, (const TT*)gu, I, total));
+  ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(swiglu_kernel<TT>, dim3(blocks), dim3(threads), 0, stream, (TT*)out, (const TT*)gu, I, total, interleave));
   return zi_check_launch("swiglu");
 }
 

@@ -138,13 +138,20 @@ struct GemmArgs {
   long long pa, pb;          // or, split, as a float to partial[z * a_rows * b_rows + a * pa + b * pb]
   int BN, stages, acc_cols;  // acc_cols: TMEM columns of one accumulator (two are allocated)
   int a_is_weight;           // which side does not depend on the kernel before this one
+  // SwiGLU epilogue (tokens on the lanes): the weight's rows are interleaved in blocks of 64
+  // (64 gate rows, then the 64 up rows of the same features); the kernel writes
+  // silu(gate) * up, half as many columns, with this row pitch.
+  long long act_ld;
 };
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
 // A side: a_rows x K through map_a (box 64 x 128).  B side: b_rows x K through map_b
 // (box 64 x BN).  Persistent: a CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...
 // (A tile fastest, so neighbouring CTAs share the B tile in L2).  Two accumulators in
 // tensor memory let the epilogue of one tile run under the MMAs of the next.
-template <typename TO>
+// SWIGLU: the epilogue writes silu(gate) * up (tokens on the lanes only).
+template <typename TO, bool SWIGLU>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     TO* __restrict__ out, float* __restrict__ partial, const GemmArgs g, int* __restrict__ status) {
@@ -271,6 +278,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int a = a_tile * TILE_A + quarter * 32 + lane;
       const uint32_t lane_base = tmem_base + acc * (uint32_t)g.acc_cols + ((uint32_t)(quarter * 32) << 16);
       const bool a_ok = a < g.a_rows;
+      if (SWIGLU) {
+        // Tokens on the lanes; of every 128 columns the first 64 are gate and the next 64 up.
+        for (int c0 = 0; c0 < BN; c0 += 128) {
+#pragma unroll
+          for (int h = 0; h < 64; h += 32) {
+            float gv[32], uv[32];
+            tmem_load32(lane_base + (uint32_t)(c0 + h), gv);
+            tmem_load32(lane_base + (uint32_t)(c0 + 64 + h), uv);
+            const int f0 = (b_tile * BN + c0) / 2 + h;                 // first output feature of this chunk
+            if (!a_ok) continue;
+            TO* o = out + (long long)a * g.act_ld + f0;
+            if (f0 + 32 <= g.b_rows / 2 && ((uintptr_t)o & 15) == 0 && sizeof(TO) == 2) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 w;
+                w.x = pack2(silu_mul(gv[j], uv[j]), silu_mul(gv[j + 1], uv[j + 1]));
+                w.y = pack2(silu_mul(gv[j + 2], uv[j + 2]), silu_mul(gv[j + 3], uv[j + 3]));
+                w.z = pack2(silu_mul(gv[j + 4], uv[j + 4]), silu_mul(gv[j + 5], uv[j + 5]));
+                w.w = pack2(silu_mul(gv[j + 6], uv[j + 6]), silu_mul(gv[j + 7], uv[j + 7]));
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(o) + j) = w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (f0 + j < g.b_rows / 2) o[j] = from_f32<TO>(silu_mul(gv[j], uv[j]));
+            }
+          }
+        }
+      } else
       for (int c0 = 0; c0 < BN; c0 += 32) {
         float v[32];
         if (BN - c0 >= 32) {
@@ -468,7 +504,7 @@ namespace {
 // tensor maps, partial-sum buffer and status word.  Both entry points end here.
 int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtensorMap& map_b, int M, int N, int K,
                 int ldo, const int* plan, float* partial_buf, int* status, int sm_count, int defer_reduce,
-                const char* what, cudaStream_t stream) {
+                const char* what, cudaStream_t stream, int swiglu = 0) {
   const int swap = plan[0], BN = plan[1], splits = plan[2];
   GemmArgs g;
   g.a_rows = swap ? N : M;
@@ -485,6 +521,7 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
   g.BN = BN;
   g.acc_cols = BN < 32 ? 32 : BN;   // two accumulators: 64 .. 512 columns, a power of two
   g.a_is_weight = swap;
+  g.act_ld = ldo;
   const int stage_bytes = A_TILE_BYTES + BN * BLOCK_K * 2;
   g.stages = swap ? 6 : (BN >= 256 ? 4 : 6);
   if (g.stages > g.k_blocks_per_split) g.stages = g.k_blocks_per_split < 2 ? 2 : g.k_blocks_per_split;
@@ -493,7 +530,7 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
   float* partial = g.splits > 1 ? partial_buf : nullptr;
 
   ZI_DISPATCH_DTYPE(out_dtype, TO, {
-    auto kern = gemm_tcgen05_kernel<TO>;
+    auto kern = swiglu ? gemm_tcgen05_kernel<TO, true> : gemm_tcgen05_kernel<TO, false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return zi_refuse("%s: cannot get %zu bytes of shared memory", what, smem);
     // CTAs that fit on the GPU at once: by shared memory, and by tensor memory (512 columns per SM)
@@ -540,6 +577,37 @@ extern "C" int zi_gemm_tcgen05(void* out, int out_dtype, const void* x, const vo
   if (!status) return zi_refuse("gemm_tcgen05: cannot allocate the status word");
   return launch_gemm(out, out_dtype, map_a, map_b, M, N, K, ldo, plan, workspace, status, sm_count, defer_reduce,
                      "gemm_tcgen05", stream);
+}
+
+// gate_up product with the SwiGLU applied in the epilogue: w is [2I, K] with rows interleaved
+// in blocks of 64 (64 gate rows, then the 64 up rows of the same features); out is [M, I].
+// Returns -2 (without launching) when the plan would split K: the caller then uses the
+// plain product and the separate SwiGLU kernel.
+extern "C" int zi_gemm_tcgen05_swiglu(void* out, int out_dtype, const void* x, const void* w, int M, int N2, int K,
+                                      int ldx, int ldw, int ldo, int sm_count, cudaStream_t stream) {
+  if (M <= 0 || N2 <= 0) return 0;
+  if (N2 % 128) return zi_refuse("gemm_swiglu: the interleaved weight needs a multiple of 128 rows, got %d", N2);
+  if (!zi_gemm_tcgen05_supported(x, w, K, ldx, ldw))
+    return zi_refuse("gemm_swiglu: operands must be 16-byte aligned bfloat16 with row pitches in multiples of 8");
+  int plan[3];
+  zi_gemm_tcgen05_plan(M, N2, K, sm_count, plan);
+  if (plan[2] > 1) return -2;
+  const int swap = plan[0];
+  // Few tokens: the separate SwiGLU kernel is the better schedule.  While it runs, the CTAs of
+  // the down product are already resident and prefetch their weights, which they cannot do
+  // while this product's CTAs still hold the shared memory.  (Measured: fused is 6 us per layer slower.)
+  if (swap) return -2;
+  if (plan[1] < 128) return -2;
+  const int BN = plan[1];
+  const int a_rows = swap ? N2 : M, b_rows = swap ? M : N2;
+  CUtensorMap map_a, map_b;
+  if (!make_map(&map_a, swap ? w : x, a_rows, K, swap ? ldw : ldx, TILE_A) ||
+      !make_map(&map_b, swap ? x : w, b_rows, K, swap ? ldx : ldw, BN))
+    return zi_refuse("gemm_swiglu: cuTensorMapEncodeTiled failed");
+  int* status = status_word();
+  if (!status) return zi_refuse("gemm_swiglu: cannot allocate the status word");
+  return launch_gemm(out, out_dtype, map_a, map_b, M, N2, K, ldo, plan, nullptr, status, sm_count, 0, "gemm_swiglu",
+                     stream, 1);
 }
 
 // Reads and clears the status word of the tensor-core kernels (synchronises the

@@ -140,9 +140,10 @@ def patch_tokens(ids: torch.Tensor, prev: torch.Tensor, dst: torch.Tensor, src: 
 def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                 out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``h[row] += delta[row]`` in place (32-bit), then RMSNorm of those rows.
+    """``h += delta`` in place (32-bit), then RMSNorm of every row.
 
-    ``rows`` (int32) picks rows of ``h``; the result then has one row per entry."""
+    ``rows`` (int32, repeats allowed) picks rows instead: the result has one row per entry,
+    the norm of ``h[row] + delta[row]``, and ``h`` is left unchanged."""
     T, H = h.shape
     _need(h.dtype == torch.float32 and h.is_contiguous(), "the residual stream is contiguous float32")
     _need(weight.dtype == torch.float32 and weight.numel() == H, "norm weight must be float32 of the row's width")
@@ -170,15 +171,18 @@ def residual_add(h: torch.Tensor, delta) -> None:
            "residual_add")
 
 
-def swiglu(gate_up, out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """``silu(gate) * up`` for ``gate_up`` [T, 2I] holding gate then up."""
+def swiglu(gate_up, out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+           interleave: int = 0) -> torch.Tensor:
+    """``silu(gate) * up`` for ``gate_up`` [T, 2I]: gate then up (``interleave`` 0), or blocks
+    of 2 * ``interleave`` columns holding ``interleave`` gate values and then the up values of
+    the same features."""
     if isinstance(gate_up, Partials):
         T, two_i = gate_up.shape
         I = two_i // 2
         if I % 4 == 0:
             res = torch.empty((T, I), dtype=out_dtype or torch.bfloat16, device=gate_up.data.device)
             _check(lib().zi_swiglu_partials(_ptr(res), _tag(res), _ptr(gate_up.data), gate_up.splits,
-                                            ctypes.c_longlong(T * two_i), T, I, _stream()), "swiglu")
+                                            ctypes.c_longlong(T * two_i), T, I, interleave, _stream()), "swiglu")
             return res
         gate_up = gate_up.sum(out_dtype or torch.bfloat16)
     T, two_i = gate_up.shape
@@ -186,8 +190,38 @@ def swiglu(gate_up, out: Optional[torch.Tensor] = None, out_dtype: Optional[torc
     I = two_i // 2
     if out is None:
         out = torch.empty((T, I), dtype=gate_up.dtype, device=gate_up.device)
-    _check(lib().zi_swiglu(_ptr(out), _ptr(gate_up), _tag(gate_up), T, I, _stream()), "swiglu")
+    _check(lib().zi_swiglu(_ptr(out), _ptr(gate_up), _tag(gate_up), T, I, interleave, _stream()), "swiglu")
     return out
+
+
+SWIGLU_INTERLEAVE = 64   # block of gate rows followed by the up rows of the same features
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, block: int = SWIGLU_INTERLEAVE) -> torch.Tensor:
+    """[2I, K] with rows in blocks of 2 * block: ``block`` gate rows, then the up rows of the
+    same features (what the fused SwiGLU epilogue of the tensor-core product reads)."""
+    I, K = gate.shape
+    _need(I % block == 0, f"interleaving needs the width {I} to be a multiple of {block}")
+    return torch.stack([gate.view(I // block, block, K), up.view(I // block, block, K)], dim=1).reshape(2 * I, K).contiguous()
+
+
+def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``silu(x Wg^T) * (x Wu^T)`` for a gate/up weight interleaved by :func:`interleave_gate_up`.
+    On the tensor-core path without a K split the SwiGLU runs in the product's epilogue;
+    otherwise the product is followed by the SwiGLU kernel."""
+    M, K = x.shape
+    N2 = w_interleaved.shape[0]
+    if (GEMM_BACKEND != "simt" and x.dtype == torch.bfloat16 and w_interleaved.dtype == torch.bfloat16 and M > 0
+            and x.stride(1) == 1 and w_interleaved.is_contiguous()
+            and lib().zi_gemm_tcgen05_supported(_ptr(x), _ptr(w_interleaved), K, x.stride(0), w_interleaved.stride(0))):
+        out = torch.empty((M, N2 // 2), dtype=out_dtype or x.dtype, device=x.device)
+        code = lib().zi_gemm_tcgen05_swiglu(_ptr(out), _tag(out), _ptr(x), _ptr(w_interleaved), M, N2, K, x.stride(0),
+                                            w_interleaved.stride(0), out.stride(0), _sm_count(x.device), _stream())
+        if code != -2:
+            _check(code, "linear_swiglu")
+            return out
+    gu = linear(x, w_interleaved, out_dtype=out_dtype or x.dtype, allow_partials=True)
+    return swiglu(gu, out_dtype=out_dtype or x.dtype, interleave=SWIGLU_INTERLEAVE)
 
 
 def rope_table(n_pos: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:

@@ -7,9 +7,10 @@ them by name.
 
 Kinds of part and what each must provide:
 
-``Norm``            ``forward(h, delta, out_rows=None)``: adds ``delta`` (may be None)
-                    into the 32-bit residual ``h`` in place and returns the normed
-                    rows in the activation dtype.
+``Norm``            ``forward(h, delta, rows=None)``: adds ``delta`` (may be None) into
+                    the 32-bit residual ``h`` in place and returns the normed rows in
+                    the activation dtype; with ``rows`` it returns the norm of the
+                    picked rows of ``h + delta`` and leaves ``h`` alone.
 ``PositionEncoding````tables()``: what the mixer's kernels need to place a token.
 ``Mixer``           ``cache_need()``: a :class:`KVCacheNeed`, a :class:`StateNeed`
                     or None; ``forward(x, step, cache)`` mixes tokens of the same

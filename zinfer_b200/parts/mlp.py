@@ -28,11 +28,17 @@ class SwiGLUMLP(FeedForward):
         g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
         if g.dtype != u.dtype:
             g, u = g.to(torch.float32), u.to(torch.float32)
-        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
+        # rows interleaved in blocks of 64 (gate block, up block) when the width allows it: the
+        # tensor-core product can then apply the SwiGLU in its epilogue
+        self.interleaved = self.inter % ops.SWIGLU_INTERLEAVE == 0
+        self.w_gate_up = ops.interleave_gate_up(g, u) if self.interleaved else torch.cat([g, u], dim=0).contiguous()
         self.w_down = tensors["down_proj.weight"].contiguous()
 
     def forward(self, x):
-        gu = ops.linear(x, self.w_gate_up, out_dtype=self.ctx.dtype, allow_partials=True)
-        act = ops.swiglu(gu, out_dtype=self.ctx.dtype)
+        if self.interleaved:
+            act = ops.linear_swiglu(x, self.w_gate_up, out_dtype=self.ctx.dtype)
+        else:
+            gu = ops.linear(x, self.w_gate_up, out_dtype=self.ctx.dtype, allow_partials=True)
+            act = ops.swiglu(gu, out_dtype=self.ctx.dtype)
         # the product may come back as split-K partial sums; the next norm adds them with the residual
         return ops.linear(act, self.w_down, out_dtype=self.ctx.dtype, allow_partials=True)
