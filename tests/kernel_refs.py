@@ -147,3 +147,7 @@ def patch_tokens(ids, prev, dst, src):
     for i in range(dst.numel()):
         if int(dst[i]) >= 0:
             ids[int(dst[i])] = prev[int(src[i])]
+
+
+def decode_fused_ok(dtype, num_heads, num_kv_heads, head_dim, step):
+    return False

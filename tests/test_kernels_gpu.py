@@ -359,6 +359,48 @@ def test_tensor_core_attention(nq, nkv, d, page, window, q_lens, ctx_lens):
         torch.testing.assert_close(again.float(), want.float(), rtol=1.6e-2, atol=1.5e-2)
 
 
+@pytest.mark.parametrize("nq,nkv,d,page,window,norm,rope,partial", [
+    (32, 8, 128, 16, None, True, True, True), (8, 2, 128, 16, None, True, True, False), (6, 1, 64, 8, 50, True, True, False),
+    (5, 5, 64, 32, None, False, True, False), (16, 1, 128, 16, None, True, False, False), (2, 1, 256, 16, None, True, True, False)])
+def test_fused_decode_attention_equals_the_two_kernels(nq, nkv, d, page, window, norm, rope, partial):
+    """q/k norm + rotary + cache write + attention in one kernel against the same done by
+    qk_norm_rope_store followed by the decode attention: outputs and cache contents agree."""
+    o = ops()
+    ctx_lens = [0, 1, 63, 64, 700, 129, 15, 300]       # the token is the first, crosses tiles, ...
+    q_lens = [1] * len(ctx_lens)
+    args = _paged_case(torch.bfloat16, nq, nkv, d, page, q_lens, ctx_lens, seed=4)
+    step = _as_step(args, q_lens, ctx_lens)
+    T = len(q_lens)
+    step.n_seqs = T
+    step.positions = torch.tensor(ctx_lens, dtype=torch.int32, device=DEV)
+    slots = torch.tensor([int(args["block_tables"][i, c // page]) * page + c % page for i, c in enumerate(ctx_lens)],
+                         dtype=torch.int32, device=DEV)
+    width = (nq + 2 * nkv) * d
+    if partial:
+        x = rnd(T, 4096, dtype=torch.bfloat16, seed=8)
+        w = rnd(width, 4096, dtype=torch.bfloat16, scale=0.02, seed=9)
+        qkv = o.linear(x, w, allow_partials=True)
+        assert isinstance(qkv, o.Partials)
+        qkv2 = o.Partials(qkv.data.clone())
+    else:
+        qkv = rnd(T, width, dtype=torch.bfloat16, seed=8)
+        qkv2 = qkv.clone()
+    qw = (1 + 0.1 * rnd(d, seed=3)) if norm else None
+    kw = (1 + 0.1 * rnd(d, seed=4)) if norm else None
+    cos, sin = ref.rope_table(1024, d, 1e4, DEV) if rope else (None, None)
+    scale = float(1 / np.sqrt(d))
+    k1, v1 = args["k_cache"].clone(), args["v_cache"].clone()
+    k2, v2 = args["k_cache"].clone(), args["v_cache"].clone()
+    assert o.decode_fused_ok(torch.bfloat16, nq, nkv, d, step)
+    fused = o.attention_decode_fused(qkv, nq, nkv, d, qw, kw, 1e-6, cos, sin, k1, v1, slots, args["block_tables"], step,
+                                     page, window, scale)
+    q = o.qk_norm_rope_store(qkv2, nq, nkv, d, qw, kw, 1e-6, cos, sin, step.positions, k2, v2, slots, page,
+                             out_dtype=torch.bfloat16)
+    two = o.attention(q, k2, v2, args["block_tables"], step, nq, nkv, d, page, window, scale)
+    assert torch.equal(k1, k2) and torch.equal(v1, v2), "the fused kernel wrote other keys or values"
+    torch.testing.assert_close(fused.float(), two.float(), rtol=1.6e-2, atol=1e-2)
+
+
 def test_tensor_core_attention_finds_one_far_key_and_ignores_stale_pages():
     nq, nkv, d, page = 8, 2, 128, 16
     q_lens, ctx_lens = [1, 200, 1], [900, 100, 33]

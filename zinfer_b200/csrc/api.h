@@ -60,6 +60,14 @@ int zi_attention_decode_mma(void* out, int out_stride, float* workspace, const v
                             const int* cu_q, const int* kv_lens, const int* dec_seq, int n_dec, int nq, int nkv, int d,
                             int page_size, int window, float scale, int splits, cudaStream_t stream);
 
+int zi_attention_decode_fused(void* out, int out_stride, float* workspace, const void* qkv, int qkv_stride,
+                              const float* partials, int part_splits, long long part_zstride, const float* qw,
+                              const float* kw, float eps, const float* cos_t, const float* sin_t, int n_table_pos,
+                              const int* positions, const int* slots, void* kcache, void* vcache,
+                              const int* block_tables, int bt_stride, const int* cu_q, const int* kv_lens,
+                              const int* dec_seq, int n_dec, int nq, int nkv, int d, int page_size, int window,
+                              float scale, int splits, cudaStream_t stream);
+
 int zi_argmax_chunks(int R, int V);
 int zi_argmax(int* out, const float* logits, int R, int V, int ld, void* workspace, cudaStream_t stream);
 int zi_sample(int* out, const float* logits, int R, int V, int ld, const float* temperature, const int* top_k,

@@ -332,15 +332,40 @@ constexpr int DC_THREADS = 128, DC_WARPS = 4, DC_KEYS = 16, DC_TILE = DC_WARPS *
 // stages of a warp's private ring: 3 x 8 KB x 4 warps = 96 KB per CTA at d = 128, two CTAs per SM
 template <int D> struct DecodeCfg { static constexpr int STAGES = D <= 64 ? 4 : (D <= 128 ? 3 : 2); };
 
+// What the fused form needs to make q, k and v of the step's token itself from the fused
+// projection row [q heads | k heads | v heads] (bfloat16, or split-K partial sums).
+struct FusedQK {
+  const bf16* qkv;          // [T, >= width] or null
+  int qkv_stride;
+  const float* part;        // [part_splits][T][width] or null
+  int part_splits;
+  long long part_zstride;
+  int width;                // (nq + 2 nkv) * d
+  const float* qw;          // per-head RMSNorm weights of q and k, or null
+  const float* kw;
+  float eps;
+  const float* cos_t;       // rotary tables [n_table_pos][d/2], or null
+  const float* sin_t;
+  int n_table_pos;
+  const int* positions;     // [T]
+  const int* slots;         // [T] where the token's k and v go (page * page_size + offset)
+  bf16* kcache_w;           // the same pages as kcache / vcache, written here
+  bf16* vcache_w;
+};
+
 // partial[((dec * nkv + kvh) * splits + z) * g + row] holds D output values, then max, then sum.
-template <int D>
+// FUSED: the kernel also does what qk_norm_rope_store does for its token: every block makes
+// the q heads of its group (RMSNorm, rotary) in shared memory; the block of the last split
+// makes the token's key and value, writes them to their page, and folds them into its result
+// as one more key (the streamed keys then end before the token's own position).
+template <int D, bool FUSED>
 __global__ void __launch_bounds__(DC_THREADS)
 attn_decode_mma_kernel(bf16* __restrict__ out, int out_stride, float* __restrict__ partial,
                        const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kcache,
                        const bf16* __restrict__ vcache, const int* __restrict__ block_tables, int bt_stride,
                        const int* __restrict__ cu_q, const int* __restrict__ kv_lens,
                        const int* __restrict__ dec_seq, int nq, int nkv, int page_size, int page_shift, int window,
-                       float scale_log2, int splits) {
+                       float scale_log2, int splits, const FusedQK fq) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int STAGES = DecodeCfg<D>::STAGES;
@@ -357,7 +382,7 @@ attn_decode_mma_kernel(bf16* __restrict__ out, int out_stride, float* __restrict
   const int kvlen = kv_lens[seq];
   const int pos = kvlen - 1;
   const int kv_lo = window > 0 ? max(0, pos - window + 1) : 0;
-  const int kv_hi = kvlen;
+  const int kv_hi = FUSED ? pos : kvlen;     // fused: the token's own key is not in the cache yet
   const int* bt = block_tables + (size_t)seq * bt_stride;
 
   const int kt0 = (kv_lo / DC_TILE) * DC_TILE;
@@ -366,9 +391,9 @@ attn_decode_mma_kernel(bf16* __restrict__ out, int out_stride, float* __restrict
   const int t_begin = z * tps, t_end = min(total_tiles, t_begin + tps);
   const int n_tiles = max(0, t_end - t_begin);
 
-  // Q fragments straight from global memory: row = query head within the group
+  // Q fragments: row = query head within the group
   uint32_t qf[D / 16][4];
-  {
+  if (!FUSED) {
     const int r0 = lane >> 2, r1 = r0 + 8;
     const bf16* q0p = q + (size_t)token * q_stride + (size_t)(kvh * g + r0) * D + 2 * (lane & 3);
     const bf16* q1p = q + (size_t)token * q_stride + (size_t)(kvh * g + r1) * D + 2 * (lane & 3);
@@ -405,6 +430,106 @@ attn_decode_mma_kernel(bf16* __restrict__ out, int out_stride, float* __restrict
     if (t < n_tiles) issue(t, pg);
     cp_async_commit();
   }
+  // ---- fused: q (all blocks) and the token's own k, v (block of the last split), while the
+  // first tiles are on their way
+  uint8_t* fused_smem = smem + DC_WARPS * WARP_BYTES;           // q tile [16][D] bf16 (swizzled), then floats
+  float* knew = reinterpret_cast<float*>(fused_smem + 16 * D * 2);   // [D] own key, as stored (bf16-rounded)
+  float* vnew = knew + D;                                            // [D] own value, as stored
+  float* snew = vnew + D;                                            // [16] own key's score per head, exp2 domain
+  const bool owner = FUSED && z == splits - 1;
+  if (FUSED) {
+    constexpr int HALF = D / 2, MAXP = HALF / 32 > 0 ? HALF / 32 : 1;
+    const int my_pos = min(fq.positions[token], fq.n_table_pos - 1);
+    auto load = [&](int head_col, int i) -> float {   // element i of the head starting at column head_col
+      if (fq.part) {
+        const float* p = fq.part + (size_t)token * fq.width + head_col + i;
+        float v = 0.f;
+        for (int zz = 0; zz < fq.part_splits; ++zz) v += p[(size_t)zz * fq.part_zstride];
+        return v;
+      }
+      return __bfloat162float(fq.qkv[(size_t)token * fq.qkv_stride + head_col + i]);
+    };
+    // heads of this block: g query heads, then (owner only) the key head and the value head
+    for (int hh = warp; hh < 16 + 2; hh += DC_WARPS) {
+      if (hh >= g && hh < 16) {   // rows of the q tile beyond the group are zero
+        for (int c = lane; c < D / 8; c += 32) *reinterpret_cast<uint4*>(fused_smem + swz<D>(hh, c)) = make_uint4(0, 0, 0, 0);
+        continue;
+      }
+      const int which = hh < g ? 0 : (hh == 16 ? 1 : 2);   // 0 q head, 1 key, 2 value
+      if (which != 0 && !owner) continue;
+      const int head_col = which == 0 ? (kvh * g + hh) * D : (which == 1 ? (nq + kvh) * D : (nq + nkv + kvh) * D);
+      if (which == 2) {
+        for (int i = lane; i < D; i += 32) vnew[i] = __bfloat162float(__float2bfloat16_rn(load(head_col, i)));
+        continue;
+      }
+      float a[MAXP], b[MAXP], ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < MAXP; ++j) {
+        const int i = lane + 32 * j;
+        a[j] = b[j] = 0.f;
+        if (i < HALF) {
+          a[j] = load(head_col, i);
+          b[j] = load(head_col, i + HALF);
+          ss += a[j] * a[j] + b[j] * b[j];
+        }
+      }
+      const float* w = which == 0 ? fq.qw : fq.kw;
+      float inv = 1.f;
+      if (w) {
+        ss = warp_sum(ss);
+        inv = 1.0f / sqrtf(ss / (float)D + fq.eps);
+      }
+#pragma unroll
+      for (int j = 0; j < MAXP; ++j) {
+        const int i = lane + 32 * j;
+        if (i >= HALF) continue;
+        float x = a[j], y = b[j];
+        if (w) {
+          x = x * w[i] * inv;
+          y = y * w[i + HALF] * inv;
+        }
+        if (fq.cos_t) {
+          const float c = fq.cos_t[(size_t)my_pos * HALF + i], sn = fq.sin_t[(size_t)my_pos * HALF + i];
+          const float rx = x * c - y * sn, ry = y * c + x * sn;
+          x = rx;
+          y = ry;
+        }
+        if (which == 0) {
+          // element i of row hh lies in chunk i / 8 at offset i % 8 of the swizzled tile
+          *reinterpret_cast<bf16*>(fused_smem + swz<D>(hh, i >> 3) + (i & 7) * 2) = __float2bfloat16_rn(x);
+          *reinterpret_cast<bf16*>(fused_smem + swz<D>(hh, (i + HALF) >> 3) + ((i + HALF) & 7) * 2) = __float2bfloat16_rn(y);
+        } else {
+          knew[i] = __bfloat162float(__float2bfloat16_rn(x));
+          knew[i + HALF] = __bfloat162float(__float2bfloat16_rn(y));
+        }
+      }
+    }
+    __syncthreads();
+    if (owner) {
+      // the token's key and value go to their page; their score against every head of the group
+      const int slot = fq.slots[token];
+      if (slot >= 0) {
+        const size_t off = (((size_t)(slot / page_size) * nkv + kvh) * page_size + (slot % page_size)) * D;
+        for (int i = tid; i < D; i += DC_THREADS) {
+          fq.kcache_w[off + i] = __float2bfloat16_rn(knew[i]);
+          fq.vcache_w[off + i] = __float2bfloat16_rn(vnew[i]);
+        }
+      }
+      for (int r = warp; r < g; r += DC_WARPS) {
+        float dot = 0.f;
+        for (int i = lane; i < D; i += 32)
+          dot += __bfloat162float(*reinterpret_cast<const bf16*>(fused_smem + swz<D>(r, i >> 3) + (i & 7) * 2)) * knew[i];
+        dot = warp_sum(dot);
+        if (lane == 0) snew[r] = dot * scale_log2;
+      }
+    }
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      const int mtx = lane >> 3;
+      ldmatrix_x4(qf[kk], smem_addr(fused_smem) + swz<D>((mtx & 1) * 8 + (lane & 7), kk * 2 + (mtx >> 1)));
+    }
+  }
+
   for (int t = 0; t < n_tiles; ++t) {
     {
       const int tt = t + STAGES - 1;
@@ -469,6 +594,7 @@ attn_decode_mma_kernel(bf16* __restrict__ out, int out_stride, float* __restrict
     float mt = -INFINITY;
 #pragma unroll
     for (int w = 0; w < DC_WARPS; ++w) mt = fmaxf(mt, reinterpret_cast<float*>(smem + w * WARP_BYTES)[16 * D + r]);
+    if (owner) mt = fmaxf(mt, snew[r]);
     float acc = 0.f, lt = 0.f;
 #pragma unroll
     for (int w = 0; w < DC_WARPS; ++w) {
@@ -477,6 +603,11 @@ attn_decode_mma_kernel(bf16* __restrict__ out, int out_stride, float* __restrict
       const float sc = mw == -INFINITY ? 0.f : exp2f(mw - mt);
       acc += p[r * D + c] * sc;
       lt += p[16 * D + 16 + r] * sc;
+    }
+    if (owner) {   // the token's own key: one more partial with sum 1 and its value as output
+      const float sc = exp2f(snew[r] - mt);
+      acc += vnew[c] * sc;
+      lt += sc;
     }
     if (partial) {
       float* dst = partial + ((((size_t)dec * nkv + kvh) * splits + z) * g + r) * (D + 2);
@@ -538,28 +669,43 @@ int launch_prefill(void* out, int out_stride, const void* q, int q_stride, const
   return zi_check_launch("attention_prefill");
 }
 
-template <int D>
+template <int D, bool FUSED>
 int launch_decode(void* out, int out_stride, float* partial, const void* q, int q_stride, const void* kc,
                   const void* vc, const int* bt, int bt_stride, const int* cu_q, const int* kv_lens,
                   const int* dec_seq, int n_dec, int nq, int nkv, int page_size, int window, float scale, int splits,
-                  cudaStream_t stream) {
-  auto kern = attn_decode_mma_kernel<D>;
-  const size_t smem = (size_t)DC_WARPS * DecodeCfg<D>::STAGES * 2 * DC_KEYS * D * 2;
+                  const FusedQK& fq, cudaStream_t stream) {
+  auto kern = attn_decode_mma_kernel<D, FUSED>;
+  const size_t smem = (size_t)DC_WARPS * DecodeCfg<D>::STAGES * 2 * DC_KEYS * D * 2 +
+                      (FUSED ? (size_t)16 * D * 2 + (2 * D + 16) * sizeof(float) : 0);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return zi_refuse("attention_decode: cannot get %zu bytes of shared memory", smem);
   dim3 grid(n_dec, nkv, splits);
-  zi_launch(kern, dim3(grid), dim3(DC_THREADS), smem, stream, (bf16*)out, out_stride, splits > 1 ? partial : nullptr, (const bf16*)q,
-                                           q_stride, (const bf16*)kc, (const bf16*)vc, bt, bt_stride, cu_q, kv_lens,
-                                           dec_seq, nq, nkv, page_size, log2_or_minus1(page_size), window,
-                                           scale * 1.4426950408889634f, splits);
+  zi_launch(kern, dim3(grid), dim3(DC_THREADS), smem, stream, (bf16*)out, out_stride, splits > 1 ? partial : nullptr,
+            (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, bt, bt_stride, cu_q, kv_lens, dec_seq, nq, nkv,
+            page_size, log2_or_minus1(page_size), window, scale * 1.4426950408889634f, splits, fq);
   int rc = zi_check_launch("attention_decode");
   if (rc) return rc;
   if (splits > 1) {
-    zi_launch(attn_decode_combine_kernel<D>, dim3(dim3(n_dec, nq)), dim3(D >= 128 ? 128 : 64), 0, stream, 
-        (bf16*)out, out_stride, partial, cu_q, dec_seq, nq, nkv, splits);
+    zi_launch(attn_decode_combine_kernel<D>, dim3(n_dec, nq), dim3(D >= 128 ? 128 : 64), 0, stream, (bf16*)out,
+              out_stride, partial, cu_q, dec_seq, nq, nkv, splits);
     rc = zi_check_launch("attention_decode_combine");
   }
   return rc;
+}
+
+template <bool FUSED>
+int dispatch_decode(int d, void* out, int out_stride, float* partial, const void* q, int q_stride, const void* kc,
+                    const void* vc, const int* bt, int bt_stride, const int* cu_q, const int* kv_lens,
+                    const int* dec_seq, int n_dec, int nq, int nkv, int page_size, int window, float scale, int splits,
+                    const FusedQK& fq, cudaStream_t stream) {
+  if (d == 64)
+    return launch_decode<64, FUSED>(out, out_stride, partial, q, q_stride, kc, vc, bt, bt_stride, cu_q, kv_lens, dec_seq,
+                                    n_dec, nq, nkv, page_size, window, scale, splits, fq, stream);
+  if (d == 128)
+    return launch_decode<128, FUSED>(out, out_stride, partial, q, q_stride, kc, vc, bt, bt_stride, cu_q, kv_lens,
+                                     dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, fq, stream);
+  return launch_decode<256, FUSED>(out, out_stride, partial, q, q_stride, kc, vc, bt, bt_stride, cu_q, kv_lens, dec_seq,
+                                   n_dec, nq, nkv, page_size, window, scale, splits, fq, stream);
 }
 }  // namespace
 
@@ -602,12 +748,46 @@ extern "C" int zi_attention_decode_mma(void* out, int out_stride, float* workspa
     return zi_refuse("attention_decode: head_dim %d (64, 128, 256) or group size %d (<= 16) is not supported", d, nq / nkv);
   if (splits < 1 || (splits > 1 && !workspace)) return zi_refuse("attention_decode: %d splits need a workspace", splits);
   if (q_stride % 2) return zi_refuse("attention_decode: q rows must be 4-byte aligned");
-  if (d == 64)
-    return launch_decode<64>(out, out_stride, workspace, q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q,
-                             kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, stream);
-  if (d == 128)
-    return launch_decode<128>(out, out_stride, workspace, q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q,
-                              kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, stream);
-  return launch_decode<256>(out, out_stride, workspace, q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q,
-                            kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, stream);
+  FusedQK none = {};
+  return dispatch_decode<false>(d, out, out_stride, workspace, q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q,
+                                kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, none, stream);
+}
+
+// Decode attention that also makes q, k and v of each request's token from the fused
+// projection row (per-head RMSNorm when weights are given, rotary when tables are given) and
+// writes k and v into their page slots: qk_norm_rope_store and attention in one kernel.  The
+// row comes either as bfloat16 `qkv` or as split-K partial sums `partials`.
+extern "C" int zi_attention_decode_fused(void* out, int out_stride, float* workspace, const void* qkv, int qkv_stride,
+                                         const float* partials, int part_splits, long long part_zstride,
+                                         const float* qw, const float* kw, float eps, const float* cos_t,
+                                         const float* sin_t, int n_table_pos, const int* positions,
+                                         const int* slots, void* kcache, void* vcache, const int* block_tables,
+                                         int bt_stride, const int* cu_q, const int* kv_lens, const int* dec_seq,
+                                         int n_dec, int nq, int nkv, int d, int page_size, int window, float scale,
+                                         int splits, cudaStream_t stream) {
+  if (n_dec <= 0) return 0;
+  if (!zi_attention_mma_supported(nq, nkv, d, 1))
+    return zi_refuse("attention_decode: head_dim %d (64, 128, 256) or group size %d (<= 16) is not supported", d, nq / nkv);
+  if (splits < 1 || (splits > 1 && !workspace)) return zi_refuse("attention_decode: %d splits need a workspace", splits);
+  if ((qkv == nullptr) == (partials == nullptr)) return zi_refuse("attention_decode: give the rows either whole or as partial sums");
+  if ((cos_t == nullptr) != (sin_t == nullptr)) return zi_refuse("attention_decode: cos and sin tables go together");
+  FusedQK fq;
+  fq.qkv = (const bf16*)qkv;
+  fq.qkv_stride = qkv_stride;
+  fq.part = partials;
+  fq.part_splits = part_splits;
+  fq.part_zstride = part_zstride;
+  fq.width = (nq + 2 * nkv) * d;
+  fq.qw = qw;
+  fq.kw = kw;
+  fq.eps = eps;
+  fq.cos_t = cos_t;
+  fq.sin_t = sin_t;
+  fq.n_table_pos = n_table_pos > 0 ? n_table_pos : 1;
+  fq.positions = positions;
+  fq.slots = slots;
+  fq.kcache_w = (bf16*)kcache;
+  fq.vcache_w = (bf16*)vcache;
+  return dispatch_decode<true>(d, out, out_stride, workspace, nullptr, 0, kcache, vcache, block_tables, bt_stride, cu_q,
+                               kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, fq, stream);
 }

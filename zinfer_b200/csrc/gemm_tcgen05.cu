@@ -523,7 +523,8 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
   g.a_is_weight = swap;
   g.act_ld = ldo;
   const int stage_bytes = A_TILE_BYTES + BN * BLOCK_K * 2;
-  g.stages = swap ? 6 : (BN >= 256 ? 4 : 6);
+  // few tokens: as many stages (up to 6) as still let two CTAs share an SM's shared memory
+  g.stages = swap ? (111 * 1024 / stage_bytes > 6 ? 6 : 111 * 1024 / stage_bytes) : (BN >= 256 ? 4 : 6);
   if (g.stages > g.k_blocks_per_split) g.stages = g.k_blocks_per_split < 2 ? 2 : g.k_blocks_per_split;
   const size_t smem = 1024 + (size_t)g.stages * stage_bytes + (2 * g.stages + 4) * sizeof(uint64_t) + 16;
   const int total_tiles = g.a_tiles * g.b_tiles * g.splits;

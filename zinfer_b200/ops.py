@@ -405,6 +405,67 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, blo
     return out
 
 
+def decode_fused_ok(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int, step) -> bool:
+    """Whether a step can use :func:`attention_decode_fused`: bfloat16, every request brings
+    one token, and the split-key decode kernel takes the shape."""
+    if not (ATTENTION_BACKEND != "generic" and dtype == torch.bfloat16 and step.n_pf_tiles == 0
+            and step.n_dec > 0 and step.n_dec == step.n_seqs and torch.cuda.is_available()
+            and lib().zi_attention_mma_supported(num_heads, num_kv_heads, head_dim, 1)):
+        return False
+    # Worth it while all blocks run at once (few requests: the step is a chain of short
+    # kernels and one kernel less counts).  With more blocks than fit, the work every block
+    # repeats before it streams its keys costs more than the separate kernel (measured at 64 requests).
+    return step.n_dec * num_kv_heads <= 2 * _sm_count(torch.device("cuda", torch.cuda.current_device()))
+
+
+def attention_decode_fused(qkv, num_heads: int, num_kv_heads: int, head_dim: int, q_weight: Optional[torch.Tensor],
+                           k_weight: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
+                           sin: Optional[torch.Tensor], k_cache: torch.Tensor, v_cache: torch.Tensor,
+                           slots: torch.Tensor, block_tables: torch.Tensor, step, page_size: int,
+                           window: Optional[int], scale: float) -> torch.Tensor:
+    """q/k RMSNorm, rotary positions, the write of each token's key and value into its page
+    and the attention itself in ONE kernel, for steps in which every request brings a single
+    token.  ``qkv`` is the fused projection row as a tensor or as split-K partial sums."""
+    L = lib()
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    if isinstance(qkv, Partials):
+        T = qkv.shape[0]
+        _need(qkv.shape[1] == width, "partial sums must have exactly the heads' width")
+        src, src_stride, part, psplits, pz = None, 0, qkv.data, qkv.splits, T * width
+        device = qkv.data.device
+    else:
+        T = qkv.shape[0]
+        _need(qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and qkv.shape[1] >= width, "qkv rows are dense bfloat16")
+        src, src_stride, part, psplits, pz = qkv, qkv.stride(0), None, 0, 0
+        device = qkv.device
+    _need(T == step.n_dec, "every request brings exactly one token")
+    for wt in (q_weight, k_weight):
+        if wt is not None:
+            _need(wt.dtype == torch.float32 and wt.numel() == head_dim, "q/k norm weights are float32 [head_dim]")
+    n_table = 0
+    if cos is not None:
+        _need(cos.shape == sin.shape and cos.shape[1] == head_dim // 2 and cos.dtype == torch.float32,
+              "rotary tables are float32 [positions, head_dim/2]")
+        n_table = cos.shape[0]
+    _need(k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.dtype == torch.bfloat16
+          and tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim), "cache pages are bfloat16 [pages, kv heads, page, d]")
+    _i32(slots, "slots")
+    out = torch.empty((T, num_heads * head_dim), dtype=torch.bfloat16, device=device)
+    sms = _sm_count(device)
+    splits = max(1, min(32, (2 * sms) // (step.n_dec * num_kv_heads)))
+    if step.max_kv_len:
+        splits = min(splits, max(1, -(-step.max_kv_len // 64)))
+    need = L.zi_attention_decode_workspace_floats(step.n_dec, num_heads, num_kv_heads, head_dim, splits)
+    ws = torch.empty((need,), dtype=torch.float32, device=device) if need else None
+    _check(L.zi_attention_decode_fused(
+        _ptr(out), out.stride(0), _ptr(ws), _ptr(src), src_stride, _ptr(part), psplits, ctypes.c_longlong(pz),
+        _ptr(q_weight), _ptr(k_weight), ctypes.c_float(eps), _ptr(cos), _ptr(sin), n_table, _ptr(step.positions),
+        _ptr(slots), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), block_tables.stride(0), _ptr(step.cu_q),
+        _ptr(step.kv_lens), _ptr(step.dec_seq), step.n_dec, num_heads, num_kv_heads, head_dim, page_size,
+        int(window or 0), ctypes.c_float(scale), splits, _stream()), "attention (fused decode)")
+    return out
+
+
 # ------------------------------------------------------------------------ sampling
 def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     R, V = logits.shape

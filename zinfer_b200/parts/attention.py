@@ -75,6 +75,13 @@ class GQAttention(Mixer):
         qkv = ops.linear(x, w, out_dtype=self.ctx.dtype, allow_partials=True)
         group = step.kv_groups[cache.group]
         cos, sin = self.position.tables() if self.position is not None else (None, None)
+        if cache.writes and ops.decode_fused_ok(self.ctx.dtype, self.nq, self.nkv, self.d, step):
+            # every request brings one token: norm, rotation, cache write and attention are one kernel
+            o = ops.attention_decode_fused(
+                qkv, self.nq, self.nkv, self.d, self.q_norm, self.k_norm,
+                self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, cos, sin, cache.k, cache.v,
+                group.slot_mapping, group.block_tables, step, cache.page_size, self.window, self.scale)
+            return ops.linear(o, self.w_o, out_dtype=self.ctx.dtype, allow_partials=True)
         q = ops.qk_norm_rope_store(
             qkv, self.nq, self.nkv, self.d, self.q_norm, self.k_norm,
             self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, cos, sin, step.positions,
