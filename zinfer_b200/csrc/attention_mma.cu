@@ -90,8 +90,16 @@ __device__ __forceinline__ void pv_16keys(float (&o)[D / 8][4], const uint32_t (
 // over `NT` n-tiles of 8 keys; s holds scores already scaled to the exp2 domain, with
 // masked entries at -inf.  Rescales o, updates m and l (l is per thread; rows are
 // summed across the 4 lanes of a quad at the end), and leaves P in s.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int NT, int ON>
 __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[ON][4], float (&m)[2], float (&l)[2]) {
+  float alpha[2];
+  bool grew = false;
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     float mx = -INFINITY;
@@ -101,20 +109,27 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[ON][4
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
     const float m_new = fmaxf(m[i], mx);
     const float m_use = m_new == -INFINITY ? 0.f : m_new;
-    const float alpha = exp2f(m[i] - m_use);
+    alpha[i] = fast_exp2(m[i] - m_use);
+    grew |= m_new != m[i];
     float sum = 0.f;
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
-      s[t][2 * i] = exp2f(s[t][2 * i] - m_use);
-      s[t][2 * i + 1] = exp2f(s[t][2 * i + 1] - m_use);
+      s[t][2 * i] = fast_exp2(s[t][2 * i] - m_use);
+      s[t][2 * i + 1] = fast_exp2(s[t][2 * i + 1] - m_use);
       sum += s[t][2 * i] + s[t][2 * i + 1];
     }
-    l[i] = l[i] * alpha + sum;
+    l[i] = l[i] * alpha[i] + sum;
     m[i] = m_new;
+  }
+  // the running maximum rarely moves after the first tiles: skip the rescale of the
+  // output accumulators when no row of the warp needs it
+  if (__any_sync(0xffffffffu, grew)) {
 #pragma unroll
     for (int t = 0; t < ON; ++t) {
-      o[t][2 * i] *= alpha;
-      o[t][2 * i + 1] *= alpha;
+      o[t][0] *= alpha[0];
+      o[t][1] *= alpha[0];
+      o[t][2] *= alpha[1];
+      o[t][3] *= alpha[1];
     }
   }
 }
