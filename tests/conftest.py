@@ -35,8 +35,18 @@ TINY_C = dict(
     architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=301, hidden_size=72, intermediate_size=200,
     num_hidden_layers=2, num_attention_heads=3, num_key_value_heads=3, head_dim=48, max_position_embeddings=512,
     rms_norm_eps=3e-6, rope_theta=50000.0, tie_word_embeddings=False, torch_dtype="bfloat16")
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-PAGE_SIZE = {"A": 16, "B": 8, "C": 32}
+# two with the head sizes the tensor-core kernels take (64 and 128), grouped and not, with a
+# feed-forward width that is a multiple of 64 (D) and one that is not (E)
+TINY_D = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=1000, hidden_size=256, intermediate_size=512,
+    num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2, head_dim=64, max_position_embeddings=1024,
+    rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False, torch_dtype="bfloat16")
+TINY_E = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=777, hidden_size=320, intermediate_size=456,
+    num_hidden_layers=2, num_attention_heads=3, num_key_value_heads=3, head_dim=128, max_position_embeddings=640,
+    rms_norm_eps=2e-5, rope_theta=20000.0, tie_word_embeddings=True, torch_dtype="bfloat16")
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
+PAGE_SIZE = {"A": 16, "B": 8, "C": 32, "D": 16, "E": 64}
 
 
 @pytest.fixture(scope="session")

@@ -27,7 +27,7 @@ def _engine(d, name, dtype, **kw):
     return Engine(d, **opts)
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_greedy_generation_through_the_entry_point(model_dirs, name):
     from zinfer_b200.sampling import SamplingParams
 

@@ -15,7 +15,8 @@ pytestmark = pytest.mark.gpu
 # bits between kernels (2^-9 relative each), which accumulates to about one percent
 # of the largest logit over a few layers.
 TOL = {"float32": dict(rtol=5e-5, atol=1e-6), "bfloat16": dict(rtol=3e-2, atol=1e-3)}
-LENGTHS = {"A": [5, 17, 33, 64, 100], "B": [1, 9, 40, 70, 129, 200], "C": [3, 77, 150, 31]}
+LENGTHS = {"A": [5, 17, 33, 64, 100], "B": [1, 9, 40, 70, 129, 200], "C": [3, 77, 150, 31],
+           "D": [2, 65, 130, 300, 47], "E": [1, 129, 64, 200]}
 
 
 def _trace(mode, reqs):
@@ -24,7 +25,7 @@ def _trace(mode, reqs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_replay_every_way_of_cutting(model_dirs, tmp_path, name, dtype):
     from conftest import PAGE_SIZE
 
