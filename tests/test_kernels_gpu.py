@@ -341,9 +341,13 @@ def _as_step(args, q_lens, ctx_lens):
     ([300, 17], [0, 130]),                             # prompt portions only, one across several query tiles
     ([1, 37, 2, 1, 129, 1], [70, 0, 15, 0, 48, 255]),  # mixed
 ])
-def test_tensor_core_attention(nq, nkv, d, page, window, q_lens, ctx_lens):
-    """The bfloat16 tensor-core kernels (prefill tiles and split-key decode) through the
-    dispatcher, against the plain reference."""
+@pytest.mark.parametrize("prefill_kernel", ["mma", "tcgen05"])
+def test_tensor_core_attention(nq, nkv, d, page, window, q_lens, ctx_lens, prefill_kernel, monkeypatch):
+    """The bfloat16 tensor-core kernels (prefill tiles by mma.sync or by tcgen05 with S and O
+    in tensor memory, and split-key decode) through the dispatcher, against the plain reference."""
+    if prefill_kernel == "tcgen05" and (d != 128 or max(q_lens) == 1):
+        pytest.skip("the tcgen05 prefill kernel takes head size 128")
+    monkeypatch.setattr(ops(), "PREFILL_ATTENTION", prefill_kernel)
     args = _paged_case(torch.bfloat16, nq, nkv, d, page, q_lens, ctx_lens, seed=2)
     step = _as_step(args, q_lens, ctx_lens)
     scale = float(1 / np.sqrt(d))

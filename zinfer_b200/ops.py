@@ -40,9 +40,11 @@ def lib() -> ctypes.CDLL:
 
 
 def kernel_status() -> int:
-    """Reads and clears the status word of the tensor-core kernels (synchronises).
+    """Reads and clears the status words of the tcgen05 kernels (synchronises).
     0: every bounded wait inside them completed; else the code of the wait that ran out."""
-    return int(lib().zi_gemm_tcgen05_status())
+    a = int(lib().zi_gemm_tcgen05_status())
+    b = int(lib().zi_attention_tcgen05_status())
+    return a if a else b
 
 
 def library_file() -> str:
@@ -356,6 +358,10 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
 
 
 ATTENTION_BACKEND = os.environ.get("ZINFER_B200_ATTENTION", "auto")   # auto | generic
+# Which tensor-core prefill kernel: "mma" (mma.sync flash attention, the faster one today) or
+# "tcgen05" (S and O tiles in tensor memory, TMA-fed; correct, but its single softmax group
+# leaves the tensor core idle while it works: 0.39 ms against 0.22 ms for 2,048 tokens).
+PREFILL_ATTENTION = os.environ.get("ZINFER_B200_PREFILL_ATTENTION", "mma")
 
 
 def attention_prefill_tile_rows() -> int:
@@ -384,7 +390,14 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, blo
           "cache pages are [pages, kv heads, page, d] in the activations' dtype")
     out = torch.empty((T, num_heads * head_dim), dtype=q.dtype, device=q.device)
     win = int(window or 0)
-    if step.n_pf_tiles > 0:
+    if step.n_pf_tiles > 0 and PREFILL_ATTENTION == "tcgen05" and L.zi_attention_prefill_tcgen05_supported(
+            num_heads, num_kv_heads, head_dim, page_size, _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache)):
+        _check(L.zi_attention_prefill_tcgen05(
+            _ptr(out), out.stride(0), _ptr(q), q.stride(0), T, _ptr(k_cache), _ptr(v_cache),
+            ctypes.c_longlong(k_cache.shape[0]), _ptr(block_tables), block_tables.stride(0), _ptr(step.cu_q),
+            _ptr(step.kv_lens), _ptr(step.pf_tile_seq), _ptr(step.pf_tile_q0), step.n_pf_tiles, num_heads, num_kv_heads,
+            head_dim, page_size, win, ctypes.c_float(scale), _stream()), "attention (prefill, tcgen05)")
+    elif step.n_pf_tiles > 0:
         _check(L.zi_attention_prefill_mma(
             _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
             block_tables.stride(0), _ptr(step.cu_q), _ptr(step.kv_lens), _ptr(step.pf_tile_seq), _ptr(step.pf_tile_q0),
