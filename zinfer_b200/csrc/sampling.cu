@@ -2,18 +2,18 @@
 // reference's chain of penalties, top-k, temperature, min-p, top-p and one draw
 // (src/sampling/sampler.zig:18-91), one block per row.
 //
-// The reference sorts candidates by descending logit and cuts prefixes of that
-// order.  Here every cut is a threshold on a 64-bit composite key (order-preserving
-// bits of the adjusted logit, then the inverted token id, so ties go to the lower
-// id and keys are unique), found by radix selection over histograms.  Weights
-// exp(z - max) are accumulated as 2^-40 fixed-point integers, so sums do not
-// depend on the order of the additions and a draw is reproducible bit for bit.
+// The reference sorts candidates by descending logit and cuts prefixes of that order.
+// Here every cut is a threshold in the order (adjusted logit descending, token id
+// ascending), found by radix selection four bits at a time with the bins in registers
+// (no atomics, so sums do not depend on timing and a draw is reproducible bit for bit).
+#include <type_traits>
+
 #include "api.h"
 #include "common.cuh"
 
 namespace {
 constexpr int THREADS = 1024;
-constexpr double FIXED_ONE = 1099511627776.0;  // 2^40
+constexpr int SMALL_K = 1024;   // top-k up to this many candidates are listed, sorted and walked as the reference does
 
 __device__ __forceinline__ float adjusted_logit(float logit, int count, float rep, float pres, float freq) {
   // src/sampling/sampler.zig:186-201
@@ -23,13 +23,6 @@ __device__ __forceinline__ float adjusted_logit(float logit, int count, float re
   a -= pres;
   a -= (float)count * freq;
   return a;
-}
-
-__device__ __forceinline__ unsigned long long composite_key(float a, int v) {
-  unsigned int b = __float_as_uint(a);
-  if (a != a) b = 0xff800000u;  // NaN sorts as -inf
-  b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
-  return ((unsigned long long)b << 32) | (unsigned long long)(0xffffffffu - (unsigned int)v);
 }
 
 struct RowView {
@@ -154,39 +147,191 @@ __global__ void argmax_final_kernel(int* __restrict__ out, const float* __restri
 }
 
 // ------------------------------------------------------------------- radix selection
-// Finds the composite key c* such that the measure of members with key > c* is
-// below `target` and the measure of members with key >= c* reaches it.
-template <typename Member>
-__device__ unsigned long long radix_select(const Member& member, int V, unsigned long long target,
-                                           unsigned long long* hist, unsigned long long* bcast) {
-  unsigned long long prefix = 0, mask = 0;
-  for (int pass = 0; pass < 8; ++pass) {
-    const int shift = 56 - 8 * pass;
-    __syncthreads();
-    for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
-    __syncthreads();
-    for (int v = threadIdx.x; v < V; v += blockDim.x) {
-      unsigned long long key, meas;
-      if (member(v, key, meas) && (key & mask) == prefix && meas)
-        atomicAdd(&hist[(key >> shift) & 255], meas);
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      unsigned long long cum = 0;
-      int digit = 0;
-      for (int b = 255; b >= 0; --b) {
-        if (cum + hist[b] >= target) { digit = b; break; }
-        cum += hist[b];
-      }
-      bcast[0] = (unsigned long long)digit;
-      bcast[1] = target - cum;
-    }
-    __syncthreads();
-    prefix |= bcast[0] << shift;
-    mask |= 0xffull << shift;
-    target = bcast[1];
+// Candidates are ordered by (key descending, token id ascending), key being the
+// order-preserving bits of the adjusted logit.  A cut of that order is a pair (key threshold,
+// id limit): a token is inside if its key is above the threshold, or equal to it with an id
+// up to the limit.  Thresholds are found four bits at a time: every thread counts (or sums
+// weights of) its tokens into 16 bins held in registers, the block adds the bins up in a
+// fixed order, and all threads walk the 16 totals from the top.  No atomics: the sums do not
+// depend on timing, so a draw is reproducible bit for bit.
+__device__ __forceinline__ unsigned int order_key(float a) {
+  unsigned int b = __float_as_uint(a);
+  if (a != a) b = 0xff800000u;  // NaN sorts as -inf
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+struct Cut {
+  unsigned int key;   // threshold on the key
+  int id_limit;       // among tokens with exactly that key, ids up to this are inside
+};
+__device__ __forceinline__ bool inside(const Cut& c, unsigned int key, int v) {
+  return key > c.key || (key == c.key && v <= c.id_limit);
+}
+
+// Adds 16 per-thread bins over the block; every thread receives the 16 totals in `tot`.
+template <typename T>
+__device__ __forceinline__ void block_sum16(T (&bins)[16], T* smem /* [32][16] */, T (&tot)[16]) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+#pragma unroll
+  for (int b = 0; b < 16; ++b) {
+    T v = bins[b];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    bins[b] = v;
   }
-  return prefix;
+  __syncthreads();
+  if (lane == 0)
+#pragma unroll
+    for (int b = 0; b < 16; ++b) smem[warp * 16 + b] = bins[b];
+  __syncthreads();
+#pragma unroll
+  for (int b = 0; b < 16; ++b) {
+    T t = 0;
+    for (int w = 0; w < nwarp; ++w) t += smem[w * 16 + b];   // fixed order
+    tot[b] = t;
+  }
+}
+
+// The cut with `target` measure inside it (measure(above the cut) < target <= measure(with
+// the cut's own key)).  F(v, key&, weight&) -> bool says whether token v is a candidate and
+// gives its key and weight; WEIGHTED false counts candidates instead.
+template <bool WEIGHTED, typename F>
+__device__ Cut select_cut(const F& cand, int V, double target, void* smem) {
+  using T = typename std::conditional<WEIGHTED, float, int>::type;
+  unsigned int prefix = 0, mask = 0;
+  double remaining = target;
+  double eq_total = 0.0;
+  for (int pass = 0; pass < 8; ++pass) {
+    const int shift = 28 - 4 * pass;
+    T bins[16];
+#pragma unroll
+    for (int b = 0; b < 16; ++b) bins[b] = 0;
+    for (int v = threadIdx.x; v < V; v += blockDim.x) {
+      unsigned int key;
+      float w;
+      if (!cand(v, key, w) || (key & mask) != prefix) continue;
+      const unsigned int d = (key >> shift) & 15u;
+      const T inc = WEIGHTED ? (T)w : (T)1;
+#pragma unroll
+      for (int b = 0; b < 16; ++b) bins[b] += (d == (unsigned)b) ? inc : (T)0;
+    }
+    T tot[16];
+    block_sum16<T>(bins, reinterpret_cast<T*>(smem), tot);
+    double cum = 0.0;
+    int digit = 0;
+#pragma unroll
+    for (int b = 15; b >= 0; --b) {
+      if (cum + (double)tot[b] >= remaining || b == 0) {
+        digit = b;
+        eq_total = (double)tot[b];
+        break;
+      }
+      cum += (double)tot[b];
+    }
+    remaining -= cum;
+    prefix |= (unsigned)digit << shift;
+    mask |= 15u << shift;
+  }
+  // `remaining` of the measure must come from the tokens whose key equals the threshold
+  Cut cut{prefix, 0x7fffffff};
+  // how many of those tokens (all of equal weight): all of them unless fewer suffice
+  int n_eq = 0, need = 0;
+  {
+    int bins[16];
+#pragma unroll
+    for (int b = 0; b < 16; ++b) bins[b] = 0;
+    for (int v = threadIdx.x; v < V; v += blockDim.x) {
+      unsigned int key;
+      float w;
+      if (cand(v, key, w) && key == prefix) bins[0] += 1;
+    }
+    int tot[16];
+    block_sum16<int>(bins, reinterpret_cast<int*>(smem), tot);
+    n_eq = tot[0];
+  }
+  if (n_eq <= 1) return cut;
+  if (WEIGHTED) {
+    const double w_each = eq_total / (double)n_eq;
+    need = w_each > 0.0 ? (int)ceil(remaining / w_each - 1e-9) : n_eq;
+  } else {
+    need = (int)remaining;
+  }
+  if (need >= n_eq) return cut;
+  if (need < 1) need = 1;
+  // the need-th smallest id among the tokens with the threshold key (ids below 2^20)
+  unsigned int iprefix = 0, imask = 0;
+  int left = need;
+  for (int pass = 0; pass < 5; ++pass) {
+    const int shift = 16 - 4 * pass;
+    int bins[16];
+#pragma unroll
+    for (int b = 0; b < 16; ++b) bins[b] = 0;
+    for (int v = threadIdx.x; v < V; v += blockDim.x) {
+      unsigned int key;
+      float w;
+      if (!cand(v, key, w) || key != prefix || ((unsigned)v & imask) != iprefix) continue;
+      const unsigned int d = ((unsigned)v >> shift) & 15u;
+#pragma unroll
+      for (int b = 0; b < 16; ++b) bins[b] += (d == (unsigned)b) ? 1 : 0;
+    }
+    int tot[16];
+    block_sum16<int>(bins, reinterpret_cast<int*>(smem), tot);
+    int cum = 0, digit = 15;
+#pragma unroll
+    for (int b = 0; b < 16; ++b) {
+      if (cum + tot[b] >= left) {
+        digit = b;
+        break;
+      }
+      cum += tot[b];
+    }
+    left -= cum;
+    iprefix |= (unsigned)digit << shift;
+    imask |= 15u << shift;
+  }
+  cut.id_limit = (int)iprefix;
+  return cut;
+}
+
+// A key lower bound `lb` with at least k and (if the data allow) at most `limit` tokens at
+// or above it: the radix descent of select_cut, stopped as soon as the surviving bin is small
+// enough to be listed.  Returns the number of tokens with key >= lb.
+template <typename F>
+__device__ int coarse_lower_bound(const F& key_of, int V, int k, int limit, void* smem, unsigned int& lb) {
+  unsigned int prefix = 0, mask = 0;
+  int remaining = k, above = 0, n_ge = V;
+  for (int pass = 0; pass < 8; ++pass) {
+    const int shift = 28 - 4 * pass;
+    int bins[16];
+#pragma unroll
+    for (int b = 0; b < 16; ++b) bins[b] = 0;
+    for (int v = threadIdx.x; v < V; v += blockDim.x) {
+      const unsigned int key = key_of(v);
+      if ((key & mask) != prefix) continue;
+      const unsigned int d = (key >> shift) & 15u;
+#pragma unroll
+      for (int b = 0; b < 16; ++b) bins[b] += (d == (unsigned)b) ? 1 : 0;
+    }
+    int tot[16];
+    block_sum16<int>(bins, reinterpret_cast<int*>(smem), tot);
+    int cum = 0, digit = 0;
+#pragma unroll
+    for (int b = 15; b >= 0; --b) {
+      if (cum + tot[b] >= remaining || b == 0) {
+        digit = b;
+        break;
+      }
+      cum += tot[b];
+    }
+    remaining -= cum;
+    above += cum;
+    prefix |= (unsigned)digit << shift;
+    mask |= 15u << shift;
+    n_ge = above + tot[digit];
+    if (n_ge <= limit) break;
+  }
+  lb = prefix;
+  return n_ge;
 }
 
 __device__ __forceinline__ unsigned long long splitmix64(unsigned long long x) {
@@ -216,9 +361,7 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int ld, i
   pdl_wait();
   __shared__ float sval[32];
   __shared__ int sidx[32];
-  __shared__ unsigned long long hist[256];
-  __shared__ unsigned long long bcast[2];
-  __shared__ unsigned long long ssum;
+  __shared__ double sred[32 * 16 / 2 + 34];   // 32 x 16 four-byte bins, then room for the draw's scan
   const int r = blockIdx.x;
   int* my_counts = (p.counts && p.count_rows && p.count_rows[r] >= 0) ? p.counts + (size_t)p.count_rows[r] * V : nullptr;
   RowView row{logits + (size_t)r * ld, my_counts, V, p.rep ? p.rep[r] : 1.f, p.pres ? p.pres[r] : 0.f,
@@ -230,64 +373,186 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int ld, i
   block_argmax(row, &amax, &token, sval, sidx);
 
   if (temperature > 0.f && top_k != 1) {
-    // top-k: threshold on the composite key with exactly k members at or above it
-    unsigned long long t_topk = 0;
-    if (top_k > 0 && top_k < V) {
-      auto member = [&](int v, unsigned long long& key, unsigned long long& meas) {
-        key = composite_key(row.adjusted(v), v);
-        meas = 1;
-        return true;
-      };
-      t_topk = radix_select(member, V, (unsigned long long)top_k, hist, bcast);
-    }
     const float zmax = amax / temperature;
     const float min_p = fminf(fmaxf(p.min_p ? p.min_p[r] : 0.f, 0.f), 1.f);
     const float top_p = fminf(fmaxf(p.top_p ? p.top_p[r] : 1.f, 0.f), 1.f);
-    // members after top-k and min-p, with fixed-point weight exp(z - zmax)
-    auto member1 = [&](int v, unsigned long long& key, unsigned long long& meas) {
-      const float a = row.adjusted(v);
-      key = composite_key(a, v);
-      if (key < t_topk) return false;
-      const float e = expf(a / temperature - zmax);
-      if (min_p > 0.f && !(e >= min_p) && v != token) return false;
-      meas = (unsigned long long)((double)e * FIXED_ONE);
-      return true;
-    };
-    auto total_of = [&](auto& mem) {
+    // top-k with few candidates: a coarse key bound that leaves a short list (at least k long)
+    unsigned int lb = 0;
+    int n_listed = V;
+    if (top_k > 0 && top_k <= SMALL_K && top_k < V) {
+      auto key_of = [&](int v) { return order_key(row.adjusted(v)); };
+      n_listed = coarse_lower_bound(key_of, V, top_k, SMALL_K, sred, lb);
+    }
+    const unsigned long long bits = splitmix64(splitmix64(p.seeds[r]) ^ (unsigned long long)(unsigned int)p.draw_index[r]);
+    const double u = (double)(bits >> 11) * (1.0 / 9007199254740992.0);
+    if (top_k > 0 && top_k < V && n_listed <= SMALL_K) {
+      // Few candidates: gather them, order them as the reference does (logit descending, id
+      // ascending), and let one thread run the reference's loop over that short list.
+      __shared__ float cand_a[SMALL_K];
+      __shared__ int cand_v[SMALL_K];
+      __shared__ float sort_a[SMALL_K];
+      __shared__ int sort_v[SMALL_K];
+      __shared__ int n_cand;
+      if (threadIdx.x == 0) n_cand = 0;
       __syncthreads();
-      if (threadIdx.x == 0) ssum = 0;
-      __syncthreads();
-      unsigned long long local = 0;
       for (int v = threadIdx.x; v < V; v += blockDim.x) {
-        unsigned long long key, meas;
-        if (mem(v, key, meas)) local += meas;
+        const float a = row.adjusted(v);
+        if (order_key(a) >= lb) {
+          const int slot = atomicAdd(&n_cand, 1);   // the order of arrival does not matter: the list is sorted next
+          if (slot < SMALL_K) {
+            cand_a[slot] = a;
+            cand_v[slot] = v;
+          }
+        }
       }
-      if (local) atomicAdd(&ssum, local);
       __syncthreads();
-      return ssum;
+      const int n_all = min(n_cand, SMALL_K);
+      const int n = min(n_all, top_k);                       // the list is sorted: its first k are the top k
+      for (int i = threadIdx.x; i < n_all; i += blockDim.x) {   // rank sort: the place of i is the number of candidates before it
+        const unsigned int ki = order_key(cand_a[i]);
+        const int vi = cand_v[i];
+        int rank = 0;
+        for (int j = 0; j < n_all; ++j) {
+          const unsigned int kj = order_key(cand_a[j]);
+          rank += (kj > ki || (kj == ki && cand_v[j] < vi)) ? 1 : 0;
+        }
+        sort_a[rank] = cand_a[i];
+        sort_v[rank] = vi;
+      }
+      __syncthreads();
+      if (threadIdx.x == 0 && n > 0) {
+        // src/sampling/sampler.zig:38-90 on the sorted candidates
+        double sum = 0.0;
+        for (int i = 0; i < n; ++i) {
+          const float e = expf(sort_a[i] / temperature - zmax);
+          cand_a[i] = e;
+          sum += (double)e;
+        }
+        int keep = n;
+        if (min_p > 0.f) {
+          const float thr = cand_a[0] * min_p;
+          keep = 0;
+          while (keep < n && cand_a[keep] >= thr) ++keep;
+          keep = max(keep, 1);
+          sum = 0.0;
+          for (int i = 0; i < keep; ++i) sum += (double)cand_a[i];
+        }
+        if (top_p < 1.f) {
+          double cum = 0.0;
+          int np = 0;
+          while (np < keep) {
+            cum += (double)cand_a[np] / sum;
+            ++np;
+            if (cum >= (double)top_p) break;
+          }
+          keep = min(max(np, 1), keep);
+        }
+        double kept = 0.0;
+        for (int i = 0; i < keep; ++i) kept += (double)cand_a[i];
+        int pick = sort_v[0];
+        if (kept > 0.0) {
+          double thr = u * kept;
+          pick = sort_v[keep - 1];
+          for (int i = 0; i < keep; ++i) {
+            thr -= (double)cand_a[i];
+            if (thr <= 0.0) {
+              pick = sort_v[i];
+              break;
+            }
+          }
+        }
+        cand_v[0] = pick;
+      }
+      __syncthreads();
+      if (n > 0) token = cand_v[0];
+    } else {
+    // many candidates: the cut with exactly k of them inside, then thresholds over the whole row
+    Cut cut_k{0u, 0x7fffffff};
+    if (top_k > 0 && top_k < V) {
+      auto all = [&](int v, unsigned int& key, float& w) {
+        key = order_key(row.adjusted(v));
+        w = 1.f;
+        return true;
+      };
+      cut_k = select_cut<false>(all, V, (double)top_k, sred);
+    }
+    // candidates after top-k and min-p, with weight exp(z - zmax)
+    auto cand1 = [&](int v, unsigned int& key, float& w) {
+      const float a = row.adjusted(v);
+      key = order_key(a);
+      if (!inside(cut_k, key, v)) return false;
+      w = expf(a / temperature - zmax);
+      return !(min_p > 0.f) || w >= min_p || v == token;
     };
-    unsigned long long t_topp = 0;
+    // block sum of a candidate set's weights, in a fixed order
+    auto total_of = [&](auto& cand) -> double {
+      float bins[16];
+#pragma unroll
+      for (int b = 0; b < 16; ++b) bins[b] = 0.f;
+      for (int v = threadIdx.x; v < V; v += blockDim.x) {
+        unsigned int key;
+        float w;
+        if (cand(v, key, w)) bins[0] += w;
+      }
+      float tot[16];
+      block_sum16<float>(bins, reinterpret_cast<float*>(sred), tot);
+      return (double)tot[0];
+    };
+    Cut cut_p{0u, 0x7fffffff};
     if (top_p < 1.f) {
-      const unsigned long long sum1 = total_of(member1);
-      unsigned long long target = (unsigned long long)ceil((double)top_p * (double)sum1);
-      if (target < 1) target = 1;
-      if (target > sum1) target = sum1;
-      t_topp = radix_select(member1, V, target, hist, bcast);
+      const double sum1 = total_of(cand1);
+      cut_p = select_cut<true>(cand1, V, fmax((double)top_p * sum1, 1e-30), sred);
     }
-    auto member2 = [&](int v, unsigned long long& key, unsigned long long& meas) {
-      return member1(v, key, meas) && key >= t_topp;
-    };
-    const unsigned long long kept = total_of(member2);
-    if (kept > 0) {
-      const unsigned long long bits = splitmix64(splitmix64(p.seeds[r]) ^ (unsigned long long)(unsigned int)p.draw_index[r]);
-      const double u = (double)(bits >> 11) * (1.0 / 9007199254740992.0);
-      unsigned long long rdraw = (unsigned long long)(u * (double)kept);
-      if (rdraw >= kept) rdraw = kept - 1;
-      const unsigned long long chosen = radix_select(member2, V, rdraw + 1, hist, bcast);
-      const unsigned int inv = (unsigned int)(chosen & 0xffffffffull);
-      const int cand = (int)(0xffffffffu - inv);
-      if (cand >= 0 && cand < V) token = cand;
+    auto cand2 = [&](int v, unsigned int& key, float& w) { return cand1(v, key, w) && inside(cut_p, key, v); };
+    // the draw: tokens in the order (thread, then its strided tokens); find where the running
+    // sum of weights passes u * total
+    float mine = 0.f;
+    for (int v = threadIdx.x; v < V; v += blockDim.x) {
+      unsigned int key;
+      float w;
+      if (cand2(v, key, w)) mine += w;
     }
+    double* scan = sred;                      // [blockDim.x / 32] warp totals after the per-warp scan
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float incl = mine;                        // inclusive scan within the warp
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    const float excl = __shfl_up_sync(0xffffffffu, incl, 1);   // the lane below's end is this lane's start, exactly
+    __syncthreads();
+    if (lane == 31) scan[warp] = (double)incl;
+    __syncthreads();
+    double before = 0.0, kept = 0.0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) {
+      if (w < warp) before += scan[w];
+      kept += scan[w];
+    }
+    if (kept > 0.0) {
+      const double target = u * kept;
+      const double lo = before + (lane > 0 ? (double)excl : 0.0), hi = before + (double)incl;
+      __shared__ int chosen;
+      if (threadIdx.x == 0) chosen = -1;
+      __syncthreads();
+      // exactly one thread's interval [lo, hi) holds the target (the last non-empty one takes hi == kept)
+      if (mine > 0.f && target >= lo && (target < hi || hi >= kept)) {
+        double run = lo;
+        int pick = -1;
+        for (int v = threadIdx.x; v < V; v += blockDim.x) {
+          unsigned int key;
+          float w;
+          if (!cand2(v, key, w)) continue;
+          pick = v;
+          run += (double)w;
+          if (run > target) break;
+        }
+        if (pick >= 0) atomicMax(&chosen, pick >= 0 ? pick : -1);
+      }
+      __syncthreads();
+      if (chosen >= 0) token = chosen;
+    }
+    }  // many candidates
   }
   if (threadIdx.x == 0) {
     out[r] = token;

@@ -47,6 +47,20 @@ class Sampler:
             self._rows.free([row])
 
     # ----------------------------------------------------------------- sampling
+    _FIELDS = ("temperature", "top_p", "min_p", "rep", "pres", "freq", "top_k", "draw_index", "count_rows", "seed_lo", "seed_hi")
+
+    def _staging(self, rows: int):
+        """A pinned buffer [fields, rows] of 32-bit words from a small ring (so a buffer is
+        not overwritten while its copy to the device may still be in flight)."""
+        if not hasattr(self, "_ring"):
+            pin = torch.cuda.is_available() and self.device.type == "cuda"
+            self._ring = [torch.zeros((len(self._FIELDS), self.max_requests), dtype=torch.int32, pin_memory=pin)
+                          for _ in range(4)]
+            self._turn = 0
+        buf = self._ring[self._turn % len(self._ring)]
+        self._turn += 1
+        return buf
+
     def sample(self, logits: torch.Tensor, request_ids: Sequence[Hashable], params: Sequence[SamplingParams],
                draw_index: Sequence[int]) -> torch.Tensor:
         """One token (int32, on the device) per row of ``logits``."""
@@ -54,20 +68,29 @@ class Sampler:
         assert R == len(request_ids) == len(params) == len(draw_index)
         if all(p.greedy and not p.has_penalties for p in params):
             return ops.argmax(logits)
-        f32 = lambda vals: torch.tensor(vals, dtype=torch.float32, device=self.device)
-        i32 = lambda vals: torch.tensor(vals, dtype=torch.int32, device=self.device)
         any_pen = any(p.has_penalties for p in params)
-        count_rows = i32([self._row_of.get(rid, -1) if p.has_penalties else -1 for rid, p in zip(request_ids, params)])
+        # all per-row parameters travel in one pinned buffer and one copy
+        host = self._staging(R)
+        f = host.view(torch.float32)
+        for i, (rid, p) in enumerate(zip(request_ids, params)):
+            f[0, i] = 0.0 if p.greedy else p.temperature
+            f[1, i] = p.top_p
+            f[2, i] = p.min_p
+            f[3, i] = p.repetition_penalty
+            f[4, i] = p.presence_penalty
+            f[5, i] = p.frequency_penalty
+            host[6, i] = p.top_k
+            host[7, i] = int(draw_index[i])
+            host[8, i] = self._row_of.get(rid, -1) if p.has_penalties else -1
+            host[9, i] = (p.seed & 0xFFFFFFFF) - (1 << 32 if p.seed & 0x80000000 else 0)
+            host[10, i] = (p.seed >> 32) & 0x7FFFFFFF
+        dev = host[:, :R].to(self.device, non_blocking=True) if self.device.type == "cuda" else host[:, :R].clone()
+        dev = dev.contiguous()
+        fl = dev.view(torch.float32)
+        # seeds as int64 [R]: low and high words side by side
+        seeds = torch.stack([dev[9], dev[10]], dim=1).contiguous().view(torch.int64).reshape(R)
         return ops.sample(
-            logits,
-            temperature=f32([0.0 if p.greedy else p.temperature for p in params]),
-            seeds=torch.tensor([p.seed for p in params], dtype=torch.int64, device=self.device),
-            draw_index=i32(list(draw_index)),
-            top_k=i32([p.top_k for p in params]),
-            top_p=f32([p.top_p for p in params]),
-            min_p=f32([p.min_p for p in params]),
-            repetition_penalty=f32([p.repetition_penalty for p in params]) if any_pen else None,
-            presence_penalty=f32([p.presence_penalty for p in params]) if any_pen else None,
-            frequency_penalty=f32([p.frequency_penalty for p in params]) if any_pen else None,
-            count_rows=count_rows if any_pen else None,
+            logits, temperature=fl[0], seeds=seeds, draw_index=dev[7], top_k=dev[6], top_p=fl[1], min_p=fl[2],
+            repetition_penalty=fl[3] if any_pen else None, presence_penalty=fl[4] if any_pen else None,
+            frequency_penalty=fl[5] if any_pen else None, count_rows=dev[8] if any_pen else None,
             counts=self._counts if any_pen else None)
