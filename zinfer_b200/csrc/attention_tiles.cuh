@@ -1,0 +1,505 @@
+// Tile code of the tensor-core attention kernels (mma.sync m16n8k16 on bfloat16, 32-bit
+// accumulation and softmax): fragment loads from XOR-swizzled shared-memory tiles, the online
+// softmax step, cp.async copies of paged keys and values, and the decode unit (one request's
+// token, one kv head, one split of the keys) that both the decode kernel and the kernel that
+// runs whole layers of a decode step are made of.
+#pragma once
+#include "common.cuh"
+
+namespace {
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are zero-filled, nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// Byte offset of 16-byte chunk `c` of row `r` in a swizzled [rows][D] bf16 tile.
+template <int D> __device__ __forceinline__ uint32_t swz(int r, int c) {
+  return (uint32_t)(r * D * 2 + ((c ^ (r & 7)) << 4));
+}
+
+// S (16 x 16 keys) += Q (16 x D) * K^T for the 16 keys at rows key0.. of tile `ks`.
+// qf: the warp's Q fragments, [D/16][4].  s: two n-tiles of 8 keys.
+template <int D>
+__device__ __forceinline__ void qk_16keys(float (&s)[2][4], const uint32_t (&qf)[D / 16][4], uint32_t ks_addr,
+                                          int key0, int lane) {
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    uint32_t b[4];
+    const int m = lane >> 3;
+    ldmatrix_x4(b, ks_addr + swz<D>(key0 + (m >> 1) * 8 + (lane & 7), kk * 2 + (m & 1)));
+    mma_bf16(s[0], qf[kk], b[0], b[1]);
+    mma_bf16(s[1], qf[kk], b[2], b[3]);
+  }
+}
+// O (16 x D) += P (16 x 16 keys) * V for the 16 keys at rows key0.. of tile `vs`.
+template <int D>
+__device__ __forceinline__ void pv_16keys(float (&o)[D / 8][4], const uint32_t (&pf)[4], uint32_t vs_addr, int key0,
+                                          int lane) {
+#pragma unroll
+  for (int np = 0; np < D / 16; ++np) {
+    uint32_t b[4];
+    const int m = lane >> 3;
+    ldmatrix_x4_trans(b, vs_addr + swz<D>(key0 + (m & 1) * 8 + (lane & 7), np * 2 + (m >> 1)));
+    mma_bf16(o[2 * np], pf, b[0], b[1]);
+    mma_bf16(o[2 * np + 1], pf, b[2], b[3]);
+  }
+}
+
+// One step of the online softmax for the two rows a thread holds (lane/4 and lane/4+8)
+// over `NT` n-tiles of 8 keys; s holds scores already scaled to the exp2 domain, with
+// masked entries at -inf.  Rescales o, updates m and l (l is per thread; rows are
+// summed across the 4 lanes of a quad at the end), and leaves P in s.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int NT, int ON>
+__device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[ON][4], float (&m)[2], float (&l)[2]) {
+  float alpha[2];
+  bool grew = false;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    float mx = -INFINITY;
+#pragma unroll
+    for (int t = 0; t < NT; ++t) mx = fmaxf(mx, fmaxf(s[t][2 * i], s[t][2 * i + 1]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m[i], mx);
+    const float m_use = m_new == -INFINITY ? 0.f : m_new;
+    alpha[i] = fast_exp2(m[i] - m_use);
+    grew |= m_new != m[i];
+    float sum = 0.f;
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      s[t][2 * i] = fast_exp2(s[t][2 * i] - m_use);
+      s[t][2 * i + 1] = fast_exp2(s[t][2 * i + 1] - m_use);
+      sum += s[t][2 * i] + s[t][2 * i + 1];
+    }
+    l[i] = l[i] * alpha[i] + sum;
+    m[i] = m_new;
+  }
+  // the running maximum rarely moves after the first tiles: skip the rescale of the
+  // output accumulators when no row of the warp needs it
+  if (__any_sync(0xffffffffu, grew)) {
+#pragma unroll
+    for (int t = 0; t < ON; ++t) {
+      o[t][0] *= alpha[0];
+      o[t][1] *= alpha[0];
+      o[t][2] *= alpha[1];
+      o[t][3] *= alpha[1];
+    }
+  }
+}
+
+// Copies `n_keys` keys starting at position `key_pos0` of one kv head into a swizzled
+// tile at rows row0.., for both K and V, 16 bytes per cp.async.  `tid`/`nthreads`
+// enumerate the copying threads.  Keys outside [kv_lo, kv_hi) or in no page are zero.
+// `page_shift` >= 0 says page_size == 1 << page_shift (shifts instead of divisions).
+template <int D>
+__device__ __forceinline__ void load_kv_rows(uint8_t* ks, uint8_t* vs, int row0, int n_keys, int key_pos0, int kv_lo,
+                                             int kv_hi, const bf16* __restrict__ kcache,
+                                             const bf16* __restrict__ vcache, const int* __restrict__ bt, int nkv,
+                                             int kvh, int page_size, int page_shift, int tid, int nthreads) {
+  constexpr int CH = D / 8;  // 16-byte chunks per key
+  for (int e = tid; e < n_keys * CH; e += nthreads) {
+    const int r = e / CH, c = e % CH;
+    const int j = key_pos0 + r;
+    bool valid = j >= kv_lo && j < kv_hi;
+    size_t off = 0;
+    if (valid) {
+      const int blk = page_shift >= 0 ? (j >> page_shift) : (j / page_size);
+      const int in_page = page_shift >= 0 ? (j & (page_size - 1)) : (j % page_size);
+      const int page = __ldg(bt + blk);
+      valid = page >= 0;
+      if (valid) off = (((size_t)page * nkv + kvh) * page_size + in_page) * D + c * 8;
+    }
+    const uint32_t so = swz<D>(row0 + r, c);
+    cp_async16(ks + so, kcache + off, valid);
+    cp_async16(vs + so, vcache + off, valid);
+  }
+}
+
+// The same for one warp's 16 keys when the page of key r is already in lane r's
+// register `pg` (-1: no page or outside the request): no dependent load stands between
+// the loop and its copies.
+template <int D>
+__device__ __forceinline__ void load_kv_rows_pg(uint8_t* ks, uint8_t* vs, int key_pos0, int pg,
+                                                const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                                                int nkv, int kvh, int page_size, int page_shift, int lane) {
+  constexpr int CH = D / 8;
+#pragma unroll
+  for (int e0 = 0; e0 < 16 * CH; e0 += 32) {
+    const int e = e0 + lane;
+    const int r = e / CH, c = e % CH;
+    const int page = __shfl_sync(0xffffffffu, pg, r);
+    const int j = key_pos0 + r;
+    const int in_page = page_shift >= 0 ? (j & (page_size - 1)) : (j % page_size);
+    const bool valid = page >= 0;
+    const size_t off = valid ? (((size_t)page * nkv + kvh) * page_size + in_page) * D + c * 8 : 0;
+    const uint32_t so = swz<D>(r, c);
+    cp_async16(ks + so, kcache + off, valid);
+    cp_async16(vs + so, vcache + off, valid);
+  }
+}
+
+// ================================================================================ decode
+constexpr int DC_THREADS = 128, DC_WARPS = 4, DC_KEYS = 16, DC_TILE = DC_WARPS * DC_KEYS;
+// stages of a warp's private ring: 3 x 8 KB x 4 warps = 96 KB per CTA at d = 128, two CTAs per SM
+template <int D> struct DecodeCfg { static constexpr int STAGES = D <= 64 ? 4 : (D <= 128 ? 3 : 2); };
+
+// What the fused form needs to make q, k and v of the step's token itself from the fused
+// projection row [q heads | k heads | v heads] (bfloat16, or split-K partial sums).
+struct FusedQK {
+  const bf16* qkv;          // [T, >= width] or null
+  int qkv_stride;
+  const float* part;        // [part_splits][T][width] or null
+  int part_splits;
+  long long part_zstride;
+  int width;                // (nq + 2 nkv) * d
+  const float* qw;          // per-head RMSNorm weights of q and k, or null
+  const float* kw;
+  float eps;
+  const float* cos_t;       // rotary tables [n_table_pos][d/2], or null
+  const float* sin_t;
+  int n_table_pos;
+  const int* positions;     // [T]
+  const int* slots;         // [T] where the token's k and v go (page * page_size + offset)
+  bf16* kcache_w;           // the same pages as kcache / vcache, written here
+  bf16* vcache_w;
+  const float* row_scale;   // [T] a factor on each token's row before anything else, or null
+};
+
+// partial[((dec * nkv + kvh) * splits + z) * g + row] holds D output values, then max, then sum.
+// FUSED: the kernel also does what qk_norm_rope_store does for its token: every block makes
+// the q heads of its group (RMSNorm, rotary) in shared memory; the block of the last split
+// makes the token's key and value, writes them to their page, and folds them into its result
+// as one more key (the streamed keys then end before the token's own position).
+// One unit of decode attention: request `dec`'s token, kv head `kvh`, split `z` of `splits`
+// of its keys, by DC_THREADS threads (`tid`) with DC_WARPS private rings in `smem`.
+// Sync::sync() is a barrier of exactly these threads.  A caller that runs several units one
+// after the other puts a barrier between them (the merge at the end reads all rings).
+// STAGES: tiles of a warp's ring (STAGES - 1 in flight); shared memory needed:
+// DC_WARPS * STAGES * 2 * DC_KEYS * D * 2 bytes, and for FUSED 16 * D * 2 + (2 D + 16) * 4 more.
+template <int D, bool FUSED, class Sync, int STAGES = DecodeCfg<D>::STAGES>
+__device__ __forceinline__ void attn_decode_unit(
+    uint8_t* smem, int tid, int dec, int kvh, int z, bf16* __restrict__ out, int out_stride,
+    float* __restrict__ partial, const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kcache,
+    const bf16* __restrict__ vcache, const int* __restrict__ block_tables, int bt_stride,
+    const int* __restrict__ cu_q, const int* __restrict__ kv_lens, const int* __restrict__ dec_seq, int nq, int nkv,
+    int page_size, int page_shift, int window, float scale_log2, int splits, const FusedQK& fq) {
+
+  constexpr int ROWS_BYTES = DC_KEYS * D * 2;                  // one warp's 16 keys of K (or V)
+  constexpr int WARP_BYTES = STAGES * 2 * ROWS_BYTES;          // a warp's private ring
+  const int lane = tid & 31, warp = tid >> 5;
+  uint8_t* ring = smem + warp * WARP_BYTES;
+
+  const int seq = dec_seq[dec];
+  const int g = nq / nkv;
+  const int token = cu_q[seq];
+  const int kvlen = kv_lens[seq];
+  const int pos = kvlen - 1;
+  const int kv_lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int kv_hi = FUSED ? pos : kvlen;     // fused: the token's own key is not in the cache yet
+  const int* bt = block_tables + (size_t)seq * bt_stride;
+
+  const int kt0 = (kv_lo / DC_TILE) * DC_TILE;
+  const int total_tiles = max(0, (kv_hi - kt0 + DC_TILE - 1) / DC_TILE);
+  const int tps = (total_tiles + splits - 1) / splits;
+  const int t_begin = z * tps, t_end = min(total_tiles, t_begin + tps);
+  const int n_tiles = max(0, t_end - t_begin);
+
+  // Q fragments: row = query head within the group
+  uint32_t qf[D / 16][4];
+  if (!FUSED) {
+    const int r0 = lane >> 2, r1 = r0 + 8;
+    const bf16* q0p = q + (size_t)token * q_stride + (size_t)(kvh * g + r0) * D + 2 * (lane & 3);
+    const bf16* q1p = q + (size_t)token * q_stride + (size_t)(kvh * g + r1) * D + 2 * (lane & 3);
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      qf[kk][0] = r0 < g ? *reinterpret_cast<const uint32_t*>(q0p + kk * 16) : 0u;
+      qf[kk][1] = r1 < g ? *reinterpret_cast<const uint32_t*>(q1p + kk * 16) : 0u;
+      qf[kk][2] = r0 < g ? *reinterpret_cast<const uint32_t*>(q0p + kk * 16 + 8) : 0u;
+      qf[kk][3] = r1 < g ? *reinterpret_cast<const uint32_t*>(q1p + kk * 16 + 8) : 0u;
+    }
+  }
+  float o[D / 8][4];
+#pragma unroll
+  for (int t = 0; t < D / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  // Lane r (r < 16) looks up the page of key r of a tile one iteration before the tile's
+  // copies are issued, so the block-table load is never waited for inside the loop.
+  auto lookup = [&](int t) -> int {
+    const int j = kt0 + (t_begin + t) * DC_TILE + warp * DC_KEYS + (lane & 15);
+    if (t >= n_tiles || j < kv_lo || j >= kv_hi) return -1;
+    return __ldg(bt + (page_shift >= 0 ? (j >> page_shift) : (j / page_size)));
+  };
+  auto issue = [&](int t, int pg) {   // this warp's 16 keys of tile t into stage t % STAGES
+    uint8_t* ks = ring + (t % STAGES) * 2 * ROWS_BYTES;
+    const int key0 = kt0 + (t_begin + t) * DC_TILE + warp * DC_KEYS;
+    load_kv_rows_pg<D>(ks, ks + ROWS_BYTES, key0, pg, kcache, vcache, nkv, kvh, page_size, page_shift, lane);
+  };
+  int pg_next = lookup(0);
+#pragma unroll
+  for (int t = 0; t < STAGES - 1; ++t) {
+    const int pg = pg_next;
+    pg_next = lookup(t + 1);
+    if (t < n_tiles) issue(t, pg);
+    cp_async_commit();
+  }
+  // ---- fused: q (all blocks) and the token's own k, v (block of the last split), while the
+  // first tiles are on their way
+  uint8_t* fused_smem = smem + DC_WARPS * WARP_BYTES;           // q tile [16][D] bf16 (swizzled), then floats
+  float* knew = reinterpret_cast<float*>(fused_smem + 16 * D * 2);   // [D] own key, as stored (bf16-rounded)
+  float* vnew = knew + D;                                            // [D] own value, as stored
+  float* snew = vnew + D;                                            // [16] own key's score per head, exp2 domain
+  const bool owner = FUSED && z == splits - 1;
+  if (FUSED) {
+    constexpr int HALF = D / 2, MAXP = HALF / 32 > 0 ? HALF / 32 : 1;
+    const int my_pos = min(fq.positions[token], fq.n_table_pos - 1);
+    const float row_scale = fq.row_scale ? fq.row_scale[token] : 1.0f;
+    auto load = [&](int head_col, int i) -> float {   // element i of the head starting at column head_col
+      if (fq.part) {
+        const float* p = fq.part + (size_t)token * fq.width + head_col + i;
+        float v = 0.f;
+        for (int zz = 0; zz < fq.part_splits; ++zz) v += p[(size_t)zz * fq.part_zstride];
+        return v * row_scale;
+      }
+      return __bfloat162float(fq.qkv[(size_t)token * fq.qkv_stride + head_col + i]) * row_scale;
+    };
+    // heads of this block: g query heads, then (owner only) the key head and the value head
+    for (int hh = warp; hh < 16 + 2; hh += DC_WARPS) {
+      if (hh >= g && hh < 16) {   // rows of the q tile beyond the group are zero
+        for (int c = lane; c < D / 8; c += 32) *reinterpret_cast<uint4*>(fused_smem + swz<D>(hh, c)) = make_uint4(0, 0, 0, 0);
+        continue;
+      }
+      const int which = hh < g ? 0 : (hh == 16 ? 1 : 2);   // 0 q head, 1 key, 2 value
+      if (which != 0 && !owner) continue;
+      const int head_col = which == 0 ? (kvh * g + hh) * D : (which == 1 ? (nq + kvh) * D : (nq + nkv + kvh) * D);
+      if (which == 2) {
+        for (int i = lane; i < D; i += 32) vnew[i] = __bfloat162float(__float2bfloat16_rn(load(head_col, i)));
+        continue;
+      }
+      float a[MAXP], b[MAXP], ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < MAXP; ++j) {
+        const int i = lane + 32 * j;
+        a[j] = b[j] = 0.f;
+        if (i < HALF) {
+          a[j] = load(head_col, i);
+          b[j] = load(head_col, i + HALF);
+          ss += a[j] * a[j] + b[j] * b[j];
+        }
+      }
+      const float* w = which == 0 ? fq.qw : fq.kw;
+      float inv = 1.f;
+      if (w) {
+        ss = warp_sum(ss);
+        inv = 1.0f / sqrtf(ss / (float)D + fq.eps);
+      }
+#pragma unroll
+      for (int j = 0; j < MAXP; ++j) {
+        const int i = lane + 32 * j;
+        if (i >= HALF) continue;
+        float x = a[j], y = b[j];
+        if (w) {
+          x = x * w[i] * inv;
+          y = y * w[i + HALF] * inv;
+        }
+        if (fq.cos_t) {
+          const float c = fq.cos_t[(size_t)my_pos * HALF + i], sn = fq.sin_t[(size_t)my_pos * HALF + i];
+          const float rx = x * c - y * sn, ry = y * c + x * sn;
+          x = rx;
+          y = ry;
+        }
+        if (which == 0) {
+          // element i of row hh lies in chunk i / 8 at offset i % 8 of the swizzled tile
+          *reinterpret_cast<bf16*>(fused_smem + swz<D>(hh, i >> 3) + (i & 7) * 2) = __float2bfloat16_rn(x);
+          *reinterpret_cast<bf16*>(fused_smem + swz<D>(hh, (i + HALF) >> 3) + ((i + HALF) & 7) * 2) = __float2bfloat16_rn(y);
+        } else {
+          knew[i] = __bfloat162float(__float2bfloat16_rn(x));
+          knew[i + HALF] = __bfloat162float(__float2bfloat16_rn(y));
+        }
+      }
+    }
+    Sync::sync();
+    if (owner) {
+      // the token's key and value go to their page; their score against every head of the group
+      const int slot = fq.slots[token];
+      if (slot >= 0) {
+        const size_t off = (((size_t)(slot / page_size) * nkv + kvh) * page_size + (slot % page_size)) * D;
+        for (int i = tid; i < D; i += DC_THREADS) {
+          fq.kcache_w[off + i] = __float2bfloat16_rn(knew[i]);
+          fq.vcache_w[off + i] = __float2bfloat16_rn(vnew[i]);
+        }
+      }
+      for (int r = warp; r < g; r += DC_WARPS) {
+        float dot = 0.f;
+        for (int i = lane; i < D; i += 32)
+          dot += __bfloat162float(*reinterpret_cast<const bf16*>(fused_smem + swz<D>(r, i >> 3) + (i & 7) * 2)) * knew[i];
+        dot = warp_sum(dot);
+        if (lane == 0) snew[r] = dot * scale_log2;
+      }
+    }
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      const int mtx = lane >> 3;
+      ldmatrix_x4(qf[kk], smem_addr(fused_smem) + swz<D>((mtx & 1) * 8 + (lane & 7), kk * 2 + (mtx >> 1)));
+    }
+  }
+
+  for (int t = 0; t < n_tiles; ++t) {
+    {
+      const int tt = t + STAGES - 1;
+      const int pg = pg_next;
+      pg_next = lookup(tt + 1);
+      if (tt < n_tiles) issue(tt, pg);
+    }
+    cp_async_commit();
+    cp_async_wait<STAGES - 1>();
+    __syncwarp();
+    const int key0 = kt0 + (t_begin + t) * DC_TILE + warp * DC_KEYS;
+    if (key0 < kv_hi && key0 + DC_KEYS > kv_lo) {
+      const uint32_t ks_addr = smem_addr(ring + (t % STAGES) * 2 * ROWS_BYTES), vs_addr = ks_addr + ROWS_BYTES;
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      qk_16keys<D>(s, qf, ks_addr, 0, lane);
+      const bool need_mask = key0 + DC_KEYS > kv_hi || key0 < kv_lo;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          float v = s[nt][c] * scale_log2;
+          if (need_mask) {
+            const int j = key0 + nt * 8 + 2 * (lane & 3) + (c & 1);
+            if (j >= kv_hi || j < kv_lo) v = -INFINITY;
+          }
+          s[nt][c] = v;
+        }
+      softmax_step<2, D / 8>(s, o, m, l);
+      uint32_t pf[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]), pack_bf16(s[1][0], s[1][1]),
+                        pack_bf16(s[1][2], s[1][3])};
+      pv_16keys<D>(o, pf, vs_addr, 0, lane);
+    }
+    __syncwarp();  // the stage is refilled by this warp's next issue
+  }
+  cp_async_wait<0>();
+
+  // merge the four warps: each writes (o, m, l) of its rows to its own ring, then all combine
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+  }
+  __syncwarp();
+  float* wo = reinterpret_cast<float*>(ring);               // [16][D] then m[16], l[16]
+  static_assert(WARP_BYTES >= (16 * D + 32) * 4, "a warp's ring must hold its partial result");
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = (lane >> 2) + i * 8;
+#pragma unroll
+    for (int t = 0; t < D / 8; ++t) {
+      wo[r * D + t * 8 + 2 * (lane & 3)] = o[t][2 * i];
+      wo[r * D + t * 8 + 2 * (lane & 3) + 1] = o[t][2 * i + 1];
+    }
+    if ((lane & 3) == 0) {
+      wo[16 * D + r] = m[i];
+      wo[16 * D + 16 + r] = l[i];
+    }
+  }
+  Sync::sync();
+  for (int e = tid; e < g * D; e += DC_THREADS) {
+    const int r = e / D, c = e % D;
+    float mt = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DC_WARPS; ++w) mt = fmaxf(mt, reinterpret_cast<float*>(smem + w * WARP_BYTES)[16 * D + r]);
+    if (owner) mt = fmaxf(mt, snew[r]);
+    float acc = 0.f, lt = 0.f;
+#pragma unroll
+    for (int w = 0; w < DC_WARPS; ++w) {
+      const float* p = reinterpret_cast<float*>(smem + w * WARP_BYTES);
+      const float mw = p[16 * D + r];
+      const float sc = mw == -INFINITY ? 0.f : exp2f(mw - mt);
+      acc += p[r * D + c] * sc;
+      lt += p[16 * D + 16 + r] * sc;
+    }
+    if (owner) {   // the token's own key: one more partial with sum 1 and its value as output
+      const float sc = exp2f(snew[r] - mt);
+      acc += vnew[c] * sc;
+      lt += sc;
+    }
+    if (partial) {
+      float* dst = partial + ((((size_t)dec * nkv + kvh) * splits + z) * g + r) * (D + 2);
+      dst[c] = acc;
+      if (c == 0) {
+        dst[D] = mt;
+        dst[D + 1] = lt;
+      }
+    } else {
+      out[(size_t)token * out_stride + (size_t)(kvh * g + r) * D + c] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
+    }
+  }
+}
+
+// Combines the splits of one (request, query head) in split order; `nthreads` threads.
+// (`partial` may have been written earlier in the same kernel: no read-only loads of it.)
+template <int D>
+__device__ __forceinline__ void attn_decode_combine_item(int dec, int h, int tid, int nthreads, bf16* __restrict__ out,
+                                                         int out_stride, const float* partial,
+                                                         const int* __restrict__ cu_q,
+                                                         const int* __restrict__ dec_seq, int nq, int nkv,
+                                                         int splits) {
+  const int g = nq / nkv, kvh = h / g, r = h % g;
+  const int token = cu_q[dec_seq[dec]];
+  const float* base = partial + ((((size_t)dec * nkv + kvh) * splits) * g + r) * (D + 2);
+  const size_t zstride = (size_t)g * (D + 2);
+  float mt = -INFINITY;
+  for (int z = 0; z < splits; ++z) mt = fmaxf(mt, base[z * zstride + D]);
+  for (int c = tid; c < D; c += nthreads) {
+    float acc = 0.f, lt = 0.f;
+    for (int z = 0; z < splits; ++z) {
+      const float mz = base[z * zstride + D];
+      const float sc = mz == -INFINITY ? 0.f : exp2f(mz - mt);
+      acc += base[z * zstride + c] * sc;
+      lt += base[z * zstride + D + 1] * sc;
+    }
+    out[(size_t)token * out_stride + (size_t)h * D + c] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
+  }
+}
+
+inline int log2_or_minus1(int v) {
+  for (int s = 0; s < 31; ++s)
+    if ((1 << s) == v) return s;
+  return -1;
+}
+
+}  // namespace
