@@ -79,6 +79,7 @@ int zi_attention_decode_fused(void* out, int out_stride, float* workspace, const
 // Whole layers of a decode step in one persistent kernel (decode_layers.cu).
 int zi_decode_layers_supported(int hidden, int nq, int nkv, int d, int inter);
 long long zi_decode_layers_desc_bytes();
+int zi_decode_layers_grid(int sm_count);
 int zi_decode_layers_layout(int hidden, int nq, int nkv, int d, int inter, int grid, long long* out);
 int zi_decode_layers_fill_desc(void* desc, const void* w_qkv, const void* w_o, const void* w_gu, const void* w_down,
                                int hidden, int nq, int nkv, int d, int inter, const float* norm1_w,

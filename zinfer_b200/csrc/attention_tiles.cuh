@@ -209,14 +209,16 @@ struct FusedQK {
 // Sync::sync() is a barrier of exactly these threads.  A caller that runs several units one
 // after the other puts a barrier between them (the merge at the end reads all rings).
 // STAGES: tiles of a warp's ring (STAGES - 1 in flight); shared memory needed:
-// DC_WARPS * STAGES * 2 * DC_KEYS * D * 2 bytes, and for FUSED 16 * D * 2 + (2 D + 16) * 4 more.
+// DC_WARPS * STAGES * 2 * DC_KEYS * D * 2 bytes, and for FUSED 16 * D * 2 + (2 D + 16) * 4 more
+// (behind the rings, or at `fused_area`, 128-byte aligned).
 template <int D, bool FUSED, class Sync, int STAGES = DecodeCfg<D>::STAGES>
 __device__ __forceinline__ void attn_decode_unit(
     uint8_t* smem, int tid, int dec, int kvh, int z, bf16* __restrict__ out, int out_stride,
     float* __restrict__ partial, const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kcache,
     const bf16* __restrict__ vcache, const int* __restrict__ block_tables, int bt_stride,
     const int* __restrict__ cu_q, const int* __restrict__ kv_lens, const int* __restrict__ dec_seq, int nq, int nkv,
-    int page_size, int page_shift, int window, float scale_log2, int splits, const FusedQK& fq) {
+    int page_size, int page_shift, int window, float scale_log2, int splits, const FusedQK& fq,
+    uint8_t* fused_area = nullptr) {
 
   constexpr int ROWS_BYTES = DC_KEYS * D * 2;                  // one warp's 16 keys of K (or V)
   constexpr int WARP_BYTES = STAGES * 2 * ROWS_BYTES;          // a warp's private ring
@@ -279,7 +281,8 @@ __device__ __forceinline__ void attn_decode_unit(
   }
   // ---- fused: q (all blocks) and the token's own k, v (block of the last split), while the
   // first tiles are on their way
-  uint8_t* fused_smem = smem + DC_WARPS * WARP_BYTES;           // q tile [16][D] bf16 (swizzled), then floats
+  // q tile [16][D] bf16 (swizzled), then floats: behind the rings unless the caller has another place
+  uint8_t* fused_smem = fused_area ? fused_area : smem + DC_WARPS * WARP_BYTES;
   float* knew = reinterpret_cast<float*>(fused_smem + 16 * D * 2);   // [D] own key, as stored (bf16-rounded)
   float* vnew = knew + D;                                            // [D] own value, as stored
   float* snew = vnew + D;                                            // [16] own key's score per head, exp2 domain

@@ -13,9 +13,9 @@
 // The ring takes nearly all of shared memory (what is in flight per SM bounds the rate at which
 // HBM can be read); the attention phase borrows it for its own rings of keys and values.
 //
-// Warps: 0 = TMA producer (weights ahead of time; activations once their phase is open),
-// 1 = tensor-memory owner and tcgen05.mma issuer, 2..5 = compute (accumulator read-back,
-// residual + norm, attention over the paged cache, SwiGLU, and the grid barriers).
+// Warps: 0..3 = compute (accumulator read-back, residual + norm, attention over the paged cache,
+// SwiGLU, and the grid barriers), 4 = tensor-memory owner and tcgen05.mma issuer, 5..7 = TMA
+// producers (weights ahead of time; activations once their phase is open).
 //
 // A layer is h += attn(norm1(h)); h += mlp(norm2(h)) with RMSNorm, grouped-query attention
 // (optional per-head q/k RMSNorm, optional rotary tables) and a SwiGLU feed-forward.  Phases
@@ -48,8 +48,15 @@
 
 namespace {
 
-constexpr int DL_THREADS = 192;
+#ifndef DL_CTAS_PER_SM
+#define DL_CTAS_PER_SM 2
+#endif
+#ifndef DL_PRODUCERS
+#define DL_PRODUCERS 2
+#endif
 constexpr int DL_COMPUTE = 128;
+constexpr int DL_THREADS = DL_COMPUTE + 32 + 32 * DL_PRODUCERS;
+constexpr size_t DL_SMEM_BUDGET = (size_t)227 * 1024 / DL_CTAS_PER_SM - (DL_CTAS_PER_SM > 1 ? 1024 : 0);
 constexpr int TILE_A = 128, BLOCK_K = 64, UMMA_K = 16, A_TILE_BYTES = TILE_A * BLOCK_K * 2;
 constexpr int CHUNK = 256;            // columns of one elementwise item, two per compute thread
 constexpr int MAX_TOKENS = 64;
@@ -85,6 +92,7 @@ struct Args {
   const LayerDesc* layers;
   int n_layers;
   int B, BN, stages, acc_cols;
+  int fused_off;               // where the attention keeps its q tile and the token's own k, v (bytes from the ring's start)
   int hidden, nq, nkv, inter, n_qkv, n_gu, interleave;
   int n[4], k[4], tiles[4], kb[4], splits[4];   // the four products: rows, depth, 128-row tiles, k-blocks, k splits
   int att_splits, page_size, page_shift, chunks;  // chunks: CHUNK-column pieces of a row of h
@@ -118,7 +126,7 @@ struct Ctl {
 };
 
 // Tiles of an attention warp's ring while the attention phase has the whole ring's memory.
-template <int D> struct AttCfg { static constexpr int STAGES = D <= 64 ? 8 : 6; };
+template <int D> struct AttCfg { static constexpr int STAGES = (D <= 64 ? 8 : 6) / DL_CTAS_PER_SM; };
 
 struct ComputeSync {
   static __device__ __forceinline__ void sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -357,7 +365,7 @@ __device__ __forceinline__ void phase_epilogue(const Args& a, Ctl* ctl, int j, u
 }
 
 template <int D>
-__global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __grid_constant__ Args a) {
+__global__ void __launch_bounds__(DL_THREADS, DL_CTAS_PER_SM) decode_layers_kernel(const __grid_constant__ Args a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int stages = a.stages;
@@ -382,7 +390,7 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 1) {
+  if (warp == 4) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem)),
                  "r"(tmem_cols)
                  : "memory");
@@ -393,13 +401,19 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
   tcgen05_fence_after();
   const uint32_t tmem_base = ctl->tmem;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+  if (warp >= 5) {
+    // ----------------------------------------------------------------- TMA producers
+    // Issuing a tensor copy costs its thread a few hundred nanoseconds whatever the box's size,
+    // more than HBM needs to deliver a weight tile to one SM: DL_PRODUCERS threads (lane 0 of as
+    // many warps) share the items, producer p taking items p, p + DL_PRODUCERS, ...
     if (lane == 0) {
+      const int p = warp - 5;
       Cursor ca, cb;
       ca.start(a, blockIdx.x, gridDim.x);
-      cb.start(a, blockIdx.x, gridDim.x);
-      uint32_t ia = 0, ib = 0, idle = 0;
+      for (int k = 0; k < p && !ca.done; ++k) ca.next_kb(a);
+      cb = ca;
+      uint32_t ia = p, ib = p, idle = 0;
+      int fenced_att = 0, fenced_open = 0;
       long long t_idle = 0;
       while (!cb.done && !ctl->failed) {
         bool progressed = false;
@@ -409,7 +423,8 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
         if (!ca.done && ctl->att_done >= ca.layer + (ca.j > 0 ? 1 : 0)) {
           const int s = ia % stages;
           if (mbar_test(&ctl->empty[s], ((ia / stages) & 1u) ^ 1u)) {
-            if (ca.j > 0) {
+            if (fenced_att < ctl->att_done) {
+              fenced_att = ctl->att_done;
               __threadfence_block();
               fence_proxy_async();   // the attention's reads and writes of this memory come first
             }
@@ -417,20 +432,24 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
             mbar_expect_tx(&ctl->full[s], (uint32_t)stage_bytes);
             tma_load_2d(smem + (size_t)s * stage_bytes, &a.layers[ca.layer].w[ca.j], &ctl->full[s], ca.kb * BLOCK_K,
                         ca.tile * TILE_A);
-            ca.next_kb(a);
-            ++ia;
+            for (int k = 0; k < DL_PRODUCERS && !ca.done; ++k) ca.next_kb(a);
+            ia += DL_PRODUCERS;
             progressed = true;
           }
         }
         if (ib < ia) {
-          if (ctl->opened >= opens_after(a, cb.layer, cb.j)) {
-            __threadfence_block();
-            fence_proxy_async();
+          const int need = opens_after(a, cb.layer, cb.j);
+          if (ctl->opened >= need) {
+            if (fenced_open < need) {   // once per phase: what other CTAs wrote before the barrier, then TMA reads
+              __threadfence_block();
+              fence_proxy_async();
+              fenced_open = need;
+            }
             const int s = ib % stages;
             const CUtensorMap* bmap = (cb.j == 1) ? &a.map_xo : (cb.j == 3 ? &a.map_act : &a.map_hw);
             tma_load_2d(smem + (size_t)s * stage_bytes + A_TILE_BYTES, bmap, &ctl->full[s], cb.kb * BLOCK_K, 0);
-            cb.next_kb(a);
-            ++ib;
+            for (int k = 0; k < DL_PRODUCERS && !cb.done; ++k) cb.next_kb(a);
+            ib += DL_PRODUCERS;
             progressed = true;
           }
         }
@@ -447,7 +466,7 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 4) {
     // ------------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       const uint32_t idesc = instr_desc_bf16(TILE_A, a.BN);
@@ -488,7 +507,7 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
     }
   } else {
     // ---------------------------------------------------------------- compute warps
-    const int ctid = threadIdx.x - 64;
+    const int ctid = threadIdx.x;
     const int P = barriers_per_layer(a);
     const int xo_stride = a.nq * D;
     uint32_t lt = 0;
@@ -530,7 +549,8 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
           attn_decode_unit<D, true, ComputeSync, AttCfg<D>::STAGES>(att_smem, ctid, dec, kvh, z, a.xo, xo_stride,
                                                  S > 1 ? a.attn_part : nullptr, nullptr, 0, L.kcache, L.vcache,
                                                  grp.block_tables, grp.bt_stride, a.cu_q, a.kv_lens, a.dec_seq, a.nq,
-                                                 a.nkv, a.page_size, a.page_shift, L.window, L.scale_log2, S, fq);
+                                                 a.nkv, a.page_size, a.page_shift, L.window, L.scale_log2, S, fq,
+                                                 smem + a.fused_off);
           ComputeSync::sync();
         }
         // the ring goes back to the producer
@@ -572,7 +592,7 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
   }
   tcgen05_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 4) {
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
@@ -648,16 +668,32 @@ Layout make_layout(int hidden, int nq, int nkv, int d, int inter, int grid) {
 
 size_t attention_smem(int d) {
   const int st = d <= 64 ? AttCfg<64>::STAGES : AttCfg<128>::STAGES;
-  return (size_t)DC_WARPS * st * 2 * DC_KEYS * d * 2 + (size_t)16 * d * 2 + (2 * d + 16) * sizeof(float);
+  return (size_t)DC_WARPS * st * 2 * DC_KEYS * d * 2;   // the rings
 }
+size_t attention_fused_bytes(int d) { return (size_t)16 * d * 2 + (2 * d + 16) * sizeof(float); }
 
-// As many stages as shared memory holds; 0 if the attention phase would not fit into them.
-int choose_stages(int d, int BN) {
-  const size_t fixed = 1024 + sizeof(Ctl) + 128;
+// Shared memory of a CTA: [ring][Ctl][the attention's small arrays, unless they fit behind its
+// rings inside the ring's memory].  stages == 0: does not fit.
+struct SmemPlan {
+  int stages;
+  size_t fused_off, total;
+};
+SmemPlan plan_smem(int d, int BN) {
+  SmemPlan p = {0, 0, 0};
   const size_t stage = A_TILE_BYTES + (size_t)BN * BLOCK_K * 2;
-  int st = (int)((227 * 1024 - fixed) / stage);
-  st = st > MAX_STAGES ? MAX_STAGES : st;
-  return (size_t)st * stage >= attention_smem(d) ? st : 0;
+  const size_t ctl = ((sizeof(Ctl) + 127) / 128) * 128 + 128;
+  for (int st = MAX_STAGES; st >= 2; --st) {
+    const size_t ring = (size_t)st * stage;
+    if (ring < attention_smem(d)) break;
+    const bool inside = ring >= attention_smem(d) + attention_fused_bytes(d);
+    const size_t total = 1024 + ring + ctl + (inside ? 0 : attention_fused_bytes(d));
+    if (total > DL_SMEM_BUDGET) continue;
+    p.stages = st;
+    p.fused_off = inside ? attention_smem(d) : ring + ctl;
+    p.total = total;
+    return p;
+  }
+  return p;
 }
 
 }  // namespace
@@ -666,10 +702,13 @@ extern "C" int zi_decode_layers_supported(int hidden, int nq, int nkv, int d, in
   if (!(d == 64 || d == 128)) return 0;
   if (nkv <= 0 || nq % nkv || nq / nkv > 16) return 0;
   if (hidden % 8 || inter % 8 || hidden <= 0 || inter <= 0) return 0;
-  return choose_stages(d, 64) >= 2 ? 1 : 0;
+  return (plan_smem(d, 16).stages >= 2 && plan_smem(d, 32).stages >= 2 && plan_smem(d, 64).stages >= 2) ? 1 : 0;
 }
 
 extern "C" long long zi_decode_layers_desc_bytes() { return (long long)sizeof(LayerDesc); }
+
+// CTAs of a launch on a device with `sm_count` SMs (the `grid` of the calls below).
+extern "C" int zi_decode_layers_grid(int sm_count) { return sm_count * DL_CTAS_PER_SM; }
 
 // out[0..2]: workspace bytes, byte offset of the last product's partial sums, its split count;
 // out[3..15]: for inspection, the byte offsets of hw, xo, act, ssq, the four products' partial sums
@@ -766,7 +805,9 @@ extern "C" int zi_decode_layers(const void* descs, int n_layers, int B, int hidd
   a.layers = (const LayerDesc*)descs;
   a.n_layers = n_layers;
   a.B = B;
-  a.stages = choose_stages(d, a.BN);
+  const SmemPlan sp = plan_smem(d, a.BN);
+  a.stages = sp.stages;
+  a.fused_off = (int)sp.fused_off;
   a.acc_cols = a.BN < 32 ? 32 : a.BN;
   a.hidden = hidden;
   a.nq = nq;
@@ -804,19 +845,28 @@ extern "C" int zi_decode_layers(const void* descs, int n_layers, int B, int hidd
   a.counter = (unsigned*)(ws + l.off_counter);
   a.status = status;
 
-  const size_t stage_bytes = A_TILE_BYTES + (size_t)a.BN * BLOCK_K * 2;
-  const size_t smem = 1024 + (size_t)a.stages * stage_bytes + sizeof(Ctl) + 128;
+  const size_t smem = sp.total;
   auto kern = d == 64 ? decode_layers_kernel<64> : decode_layers_kernel<128>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return zi_refuse("decode_layers: cannot get %zu bytes of shared memory", smem);
-  // every CTA must be resident at once (they meet at grid barriers): one per SM at most
-  int per_sm = 0;
-  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, DL_THREADS, smem);
-  int dev = 0, sms = 0;
+  cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  // every CTA must be resident at once (they meet at grid barriers)
+  // (The runtime's occupancy query answers 1 for this kernel whatever its size; the count is made here
+  // from the same resources: registers, shared memory with its 1 KB per block, threads.)
+  cudaFuncAttributes fa;
+  int dev = 0, sms = 0, regs_sm = 0, smem_sm = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (e != cudaSuccess || per_sm < 1 || grid > sms * per_sm)
-    return zi_refuse("decode_layers: a grid of %d blocks cannot be resident at once on %d SMs", grid, sms);
+  cudaDeviceGetAttribute(&regs_sm, cudaDevAttrMaxRegistersPerMultiprocessor, dev);
+  cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
+  if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess) return zi_refuse("decode_layers: cannot read the kernel's attributes");
+  const int warps = (DL_THREADS + 31) / 32;
+  const long long regs_block = (long long)((fa.numRegs + 7) / 8 * 8) * 32 * ((warps + 3) / 4 * 4);
+  const bool fits = regs_block * DL_CTAS_PER_SM <= regs_sm &&
+                    (long long)(smem + fa.sharedSizeBytes + 1024) * DL_CTAS_PER_SM <= smem_sm;
+  if (!fits || grid > sms * DL_CTAS_PER_SM)
+    return zi_refuse("decode_layers: %d blocks (%d registers, %zu bytes of shared memory each) cannot be resident at once on %d SMs",
+                     grid, fa.numRegs, smem, sms);
   e = cudaMemsetAsync(a.counter, 0, sizeof(unsigned), stream);
   if (e != cudaSuccess) return zi_refuse("decode_layers: cannot clear the barrier counter: %s", cudaGetErrorString(e));
   // a plain launch (no programmatic early start): the kernel before it has drained, so every SM is free

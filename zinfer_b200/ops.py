@@ -510,7 +510,7 @@ class DecodeLayers:
         self.hidden, self.nq, self.nkv, self.d, self.inter, self.interleave, self.page_size = sig
         self.n_layers = len(layers)
         self.device = layers[0]["mixer"]["w_qkv"].device
-        self.grid = _sm_count(self.device)
+        self.grid = int(L.zi_decode_layers_grid(_sm_count(self.device)))
         nbytes = int(L.zi_decode_layers_desc_bytes())
         host = (ctypes.c_uint8 * (nbytes * self.n_layers))()
         self._keep = []   # the tensors the descriptors point into
