@@ -291,42 +291,97 @@ __device__ __forceinline__ void attn_decode_unit(
     constexpr int HALF = D / 2, MAXP = HALF / 32 > 0 ? HALF / 32 : 1;
     const int my_pos = min(fq.positions[token], fq.n_table_pos - 1);
     const float row_scale = fq.row_scale ? fq.row_scale[token] : 1.0f;
-    auto load = [&](int head_col, int i) -> float {   // element i of the head starting at column head_col
-      if (fq.part) {
-        const float* p = fq.part + (size_t)token * fq.width + head_col + i;
-        float v = 0.f;
-        for (int zz = 0; zz < fq.part_splits; ++zz) v += p[(size_t)zz * fq.part_zstride];
-        return v * row_scale;
-      }
-      return __bfloat162float(fq.qkv[(size_t)token * fq.qkv_stride + head_col + i]) * row_scale;
+    // Heads of this block: g query heads, then (owner only) the key head and the value head.
+    // Warp w takes heads w, w + 4, ...: first ALL loads of all its heads (one trip to memory, not
+    // one per head), then the norms and rotations.
+    constexpr int MAXH = (16 + 2 + DC_WARPS - 1) / DC_WARPS;
+    float a[MAXH][MAXP], b[MAXH][MAXP];
+    int which[MAXH];   // 0 q head, 1 key, 2 value, -1 nothing
+#pragma unroll
+    for (int k = 0; k < MAXH; ++k) {
+      const int hh = warp + k * DC_WARPS;
+      which[k] = hh < g ? 0 : (hh == 16 && owner ? 1 : (hh == 17 && owner ? 2 : -1));
+#pragma unroll
+      for (int j = 0; j < MAXP; ++j) a[k][j] = b[k][j] = 0.f;
+    }
+    auto head_col_of = [&](int k) -> int {
+      const int hh = warp + k * DC_WARPS;
+      return which[k] == 0 ? (kvh * g + hh) * D : (which[k] == 1 ? (nq + kvh) * D : (nq + nkv + kvh) * D);
     };
-    // heads of this block: g query heads, then (owner only) the key head and the value head
-    for (int hh = warp; hh < 16 + 2; hh += DC_WARPS) {
+    if (fq.part) {
+      for (int zz = 0; zz < fq.part_splits; ++zz) {
+        const float* p = fq.part + (size_t)zz * fq.part_zstride + (size_t)token * fq.width;
+#pragma unroll
+        for (int k = 0; k < MAXH; ++k) {
+          if (which[k] < 0) continue;
+          const float* ph = p + head_col_of(k);
+#pragma unroll
+          for (int j = 0; j < MAXP; ++j) {
+            const int i = lane + 32 * j;
+            if (i < HALF) {
+              a[k][j] += ph[i];
+              b[k][j] += ph[i + HALF];
+            }
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < MAXH; ++k) {
+        if (which[k] < 0) continue;
+        const bf16* ph = fq.qkv + (size_t)token * fq.qkv_stride + head_col_of(k);
+#pragma unroll
+        for (int j = 0; j < MAXP; ++j) {
+          const int i = lane + 32 * j;
+          if (i < HALF) {
+            a[k][j] = __bfloat162float(ph[i]);
+            b[k][j] = __bfloat162float(ph[i + HALF]);
+          }
+        }
+      }
+    }
+    // norm weights and rotation of this lane's elements (the same for every head of a kind)
+    float wq[2][MAXP], wk[2][MAXP], cs[MAXP], sn[MAXP];
+#pragma unroll
+    for (int j = 0; j < MAXP; ++j) {
+      const int i = lane + 32 * j;
+      const bool in = i < HALF;
+      wq[0][j] = in && fq.qw ? fq.qw[i] : 1.f;
+      wq[1][j] = in && fq.qw ? fq.qw[i + HALF] : 1.f;
+      wk[0][j] = in && fq.kw ? fq.kw[i] : 1.f;
+      wk[1][j] = in && fq.kw ? fq.kw[i + HALF] : 1.f;
+      cs[j] = in && fq.cos_t ? fq.cos_t[(size_t)my_pos * HALF + i] : 1.f;
+      sn[j] = in && fq.cos_t ? fq.sin_t[(size_t)my_pos * HALF + i] : 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < MAXH; ++k) {
+      const int hh = warp + k * DC_WARPS;
       if (hh >= g && hh < 16) {   // rows of the q tile beyond the group are zero
         for (int c = lane; c < D / 8; c += 32) *reinterpret_cast<uint4*>(fused_smem + swz<D>(hh, c)) = make_uint4(0, 0, 0, 0);
         continue;
       }
-      const int which = hh < g ? 0 : (hh == 16 ? 1 : 2);   // 0 q head, 1 key, 2 value
-      if (which != 0 && !owner) continue;
-      const int head_col = which == 0 ? (kvh * g + hh) * D : (which == 1 ? (nq + kvh) * D : (nq + nkv + kvh) * D);
-      if (which == 2) {
-        for (int i = lane; i < D; i += 32) vnew[i] = __bfloat162float(__float2bfloat16_rn(load(head_col, i)));
+      if (which[k] < 0) continue;
+      if (which[k] == 2) {
+#pragma unroll
+        for (int j = 0; j < MAXP; ++j) {
+          const int i = lane + 32 * j;
+          if (i < HALF) {
+            vnew[i] = __bfloat162float(__float2bfloat16_rn(a[k][j] * row_scale));
+            vnew[i + HALF] = __bfloat162float(__float2bfloat16_rn(b[k][j] * row_scale));
+          }
+        }
         continue;
       }
-      float a[MAXP], b[MAXP], ss = 0.f;
+      float ss = 0.f;
 #pragma unroll
       for (int j = 0; j < MAXP; ++j) {
-        const int i = lane + 32 * j;
-        a[j] = b[j] = 0.f;
-        if (i < HALF) {
-          a[j] = load(head_col, i);
-          b[j] = load(head_col, i + HALF);
-          ss += a[j] * a[j] + b[j] * b[j];
-        }
+        a[k][j] *= row_scale;
+        b[k][j] *= row_scale;
+        ss = sum_squares_step(ss, a[k][j], b[k][j]);   // lanes beyond HALF hold zeros
       }
-      const float* w = which == 0 ? fq.qw : fq.kw;
+      const bool normed = which[k] == 0 ? fq.qw != nullptr : fq.kw != nullptr;
       float inv = 1.f;
-      if (w) {
+      if (normed) {
         ss = warp_sum(ss);
         inv = 1.0f / sqrtf(ss / (float)D + fq.eps);
       }
@@ -334,18 +389,13 @@ __device__ __forceinline__ void attn_decode_unit(
       for (int j = 0; j < MAXP; ++j) {
         const int i = lane + 32 * j;
         if (i >= HALF) continue;
-        float x = a[j], y = b[j];
-        if (w) {
-          x = x * w[i] * inv;
-          y = y * w[i + HALF] * inv;
+        float x = a[k][j], y = b[k][j];
+        if (normed) {
+          x = norm_scale(x, which[k] == 0 ? wq[0][j] : wk[0][j], inv);
+          y = norm_scale(y, which[k] == 0 ? wq[1][j] : wk[1][j], inv);
         }
-        if (fq.cos_t) {
-          const float c = fq.cos_t[(size_t)my_pos * HALF + i], sn = fq.sin_t[(size_t)my_pos * HALF + i];
-          const float rx = x * c - y * sn, ry = y * c + x * sn;
-          x = rx;
-          y = ry;
-        }
-        if (which == 0) {
+        if (fq.cos_t) rotate_pair(x, y, cs[j], sn[j]);
+        if (which[k] == 0) {
           // element i of row hh lies in chunk i / 8 at offset i % 8 of the swizzled tile
           *reinterpret_cast<bf16*>(fused_smem + swz<D>(hh, i >> 3) + (i & 7) * 2) = __float2bfloat16_rn(x);
           *reinterpret_cast<bf16*>(fused_smem + swz<D>(hh, (i + HALF) >> 3) + ((i + HALF) & 7) * 2) = __float2bfloat16_rn(y);

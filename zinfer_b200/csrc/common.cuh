@@ -37,6 +37,18 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// The arithmetic of the per-head norm and the rotation, with every rounding spelled out, so that
+// the kernels that make keys (alone, or fused into the decode attention) store the same bits
+// whatever the compiler would contract.
+__device__ __forceinline__ float sum_squares_step(float ss, float a, float b) { return __fmaf_rn(b, b, __fmaf_rn(a, a, ss)); }
+__device__ __forceinline__ float norm_scale(float v, float w, float inv) { return __fmul_rn(__fmul_rn(v, w), inv); }
+__device__ __forceinline__ void rotate_pair(float& x, float& y, float c, float s) {
+  const float rx = __fsub_rn(__fmul_rn(x, c), __fmul_rn(y, s));
+  const float ry = __fadd_rn(__fmul_rn(y, c), __fmul_rn(x, s));
+  x = rx;
+  y = ry;
+}
+
 // Sum over a block of up to 1024 threads; every thread receives the result.  The
 // order of additions depends only on blockDim, never on the data's place in a batch.
 __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floats */) {

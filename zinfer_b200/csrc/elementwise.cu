@@ -434,7 +434,7 @@ __global__ void qk_norm_rope_store_kernel(const T* src, int src_stride, const fl
     if (i < half) {
       a[j] = load(i);
       b[j] = load(i + half);
-      ss += a[j] * a[j] + b[j] * b[j];
+      ss = sum_squares_step(ss, a[j], b[j]);
     }
   }
   const float* w = head < nq ? qw : kw;
@@ -451,15 +451,10 @@ __global__ void qk_norm_rope_store_kernel(const T* src, int src_stride, const fl
     if (i >= half) continue;
     float x = a[j], y = b[j];
     if (w) {
-      x = x * w[i] * inv;
-      y = y * w[i + half] * inv;
+      x = norm_scale(x, w[i], inv);
+      y = norm_scale(y, w[i + half], inv);
     }
-    if (cos_t) {
-      const float c = cos_t[(size_t)pos * half + i], sn = sin_t[(size_t)pos * half + i];
-      const float rx = x * c - y * sn, ry = y * c + x * sn;
-      x = rx;
-      y = ry;
-    }
+    if (cos_t) rotate_pair(x, y, cos_t[(size_t)pos * half + i], sin_t[(size_t)pos * half + i]);
     dst[i] = from_f32<T>(x);
     dst[i + half] = from_f32<T>(y);
   }

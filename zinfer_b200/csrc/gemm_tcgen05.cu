@@ -397,10 +397,23 @@ extern "C" long long zi_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int
   const int BN = swap ? round_up_bn(b_rows) : (b_rows >= 256 && M >= 256 ? 256 : 128 <= b_rows ? 128 : round_up_bn(b_rows));
   const int tiles = ((a_rows + TILE_A - 1) / TILE_A) * ((b_rows + BN - 1) / BN);
   int splits = 1;
-  if (swap) {
-    // few tokens: the weight is streamed once; use enough CTAs that every SM pulls from memory
-    // as many splits as still fit on the GPU at once (two CTAs per SM): one wave, no tail
-    while (tiles * splits * 2 <= 2 * sm_count && splits < 16 && k_blocks / (splits * 2) >= 8) splits *= 2;
+  const int slots = 2 * (sm_count > 0 ? sm_count : 148);   // CTAs resident at once, two per SM
+  if (swap && 2 * tiles <= slots) {
+    // few tokens, few tiles: the weight is streamed once; as many splits as still fit on the GPU
+    // at once, so that every SM pulls from memory: one wave, no tail
+    while (tiles * splits * 2 <= slots && splits < 16 && k_blocks / (splits * 2) >= 8) splits *= 2;
+  } else if (swap && tiles < slots) {
+    // between half a wave and a whole one (192 tiles on 296 slots): without a split a third of the
+    // slots idle; take the split count whose units (tile x split) fill whole waves best
+    double best = 0.0;
+    for (int s = 1; s <= 4 && k_blocks / s >= 8; ++s) {
+      const int units = tiles * s;
+      const double eff = (double)units / ((double)((units + slots - 1) / slots) * slots);
+      if (eff > best + 0.02) {
+        best = eff;
+        splits = s;
+      }
+    }
   }
   if (splits > 1) {  // the number of splits that get at least one k-block
     const int kbps = (k_blocks + splits - 1) / splits;
