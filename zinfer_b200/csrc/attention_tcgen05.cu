@@ -1,22 +1,10 @@
 // Paged causal flash attention for prompt portions on the 5th-generation tensor cores
-// (head size 128, bfloat16): S = Q K^T and O_tile = P V are tcgen05.mma products with
-// their accumulators in tensor memory; Q, K and V tiles come by TMA (128-byte swizzle,
-// no multicast) straight from the activation buffer and the cache pages.
-//
-// A CTA takes 128 query tokens of one request and one query head and walks the keys in
-// tiles of 128.  Warp roles (192 threads):
-//   warp 0      TMA producer: Q once, then K and V tiles (one box per page and half of d)
-//               through a two-stage ring;
-//   warp 1      owns tensor memory and issues the MMAs: S[j+1] = Q K[j+1]^T is issued
-//               before O_tile[j] = P[j] V[j], so it runs under the softmax of tile j;
-//   warps 2..5  softmax: thread r owns query row r.  It reads its row of S from tensor
-//               memory (tcgen05.ld), masks, keeps the running maximum and sum in 32-bit,
-//               writes P as bfloat16 into shared memory in the swizzled K-major layout the
-//               next MMA reads, then adds O_tile (read back from tensor memory) into its
-//               32-bit output row: O = O * alpha + O_tile.
-// V is read as an MN-major operand (its rows are keys, the contraction dimension), K and
-// Q as K-major.  Every mbarrier wait is bounded; a timeout records a code in `status`,
-// lets copies land, frees the tensor memory and returns.
+// (head size 128, bfloat16): S = Q K^T and O += P V are tcgen05.mma products with S, P and O in
+// tensor memory; Q, K and V tiles come by TMA (128-byte swizzle, no multicast) straight from the
+// activation buffer and the cache pages.  V is read as an MN-major operand (its rows are keys,
+// the contraction dimension), K and Q as K-major, P from tensor memory.  The kernel and its warp
+// roles are described at the kernel.  Every mbarrier wait is bounded; a timeout records a code
+// in `status`, lets copies land, frees the tensor memory and returns.
 #include <cuda.h>
 
 #include <mutex>
@@ -27,7 +15,7 @@
 namespace {
 using bf16 = __nv_bfloat16;
 
-constexpr int BQ = 128, BK = 128, D = 128, THREADS = 192;
+constexpr int BQ = 128, BK = 128, D = 128, THREADS = 320;
 constexpr int HALF_BYTES = 128 * 128;          // 128 rows x 64 bf16: one swizzled half tile
 constexpr int TILE_BYTES = 2 * HALF_BYTES;     // a [128, 128] bf16 tile as two halves of d (or of keys)
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
@@ -54,6 +42,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         : "r"(addr), "r"(parity)
         : "memory");
     if (done) return true;
+    __nanosleep(64);   // a waiting warp must not take issue slots from the working ones
   }
   return false;
 }
@@ -118,15 +107,62 @@ __device__ __forceinline__ uint32_t idesc_bf16(int n, bool b_mn) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
+__device__ __forceinline__ void tmem_store16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_store32(uint32_t taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+        "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])),
+        "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+        "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+        "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])),
+        "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D += A * B with A in tensor memory (128 lanes = rows, two bfloat16 of K per 32-bit column).
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 struct Barriers {
   uint64_t q_full;
   uint64_t k_full[2], v_full[2], kv_empty[2];
-  uint64_t s_full[2], s_empty[2];
-  uint64_t p_full, p_empty;
-  uint64_t o_full, o_empty;
+  uint64_t s_full[2], p_full[2], pv_done[2];   // per query tile of the CTA
   uint32_t tmem_slot;
 };
 
+// A CTA takes TWO neighbouring tiles of 128 query tokens (a, b) of one request and one query
+// head and walks the keys in tiles of 128 once for both: while the softmax warps of one tile
+// work on their scores, the tensor core runs the other tile's products.
+//   warp 0      TMA producer: both Q tiles once, then K and V tiles through a two-stage ring
+//   warp 1      owns tensor memory and issues the MMAs, per key tile j and query tile x:
+//               O_x += P_x[j] V[j] (P read from tensor memory), then S_x[j+1] = Q_x K[j+1]^T
+//   warps 2..5  softmax of tile a, warps 6..9 of tile b: thread r owns query row r = its TMEM
+//               lane.  It reads its row of S (tcgen05.ld), masks, exponentiates against a
+//               reference maximum and writes P as bfloat16 over the first half of S's own
+//               columns (tcgen05.st).  O stays in tensor memory for the whole walk: the
+//               reference maximum only moves when the row's maximum outgrows it by 2^8, and
+//               only then is O read, rescaled and written back (sum and output use the same
+//               reference, so the result is exact).
+// The kernel is launched over the list of 128-row tiles: the CTA of an even tile of a request
+// takes the next one too, the CTA of an odd tile leaves at once.
 __global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, int out_stride,
@@ -135,25 +171,32 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ tile_q0, int nq, int nkv, int page_size, int window,
                             float scale_log2, int* __restrict__ status) {
   pdl_launch_dependents();
+  const int seq = tile_seq[blockIdx.y], q0 = tile_q0[blockIdx.y];
+  if ((q0 / BQ) & 1) return;   // the CTA of the tile before this one takes both
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* q_s = smem;                       // [2 halves of d][128 rows][128 B]
-  uint8_t* k_s = q_s + TILE_BYTES;           // [2 stages][2 halves of d][128 keys][128 B]
+  uint8_t* q_s = smem;                       // [2 query tiles][2 halves of d][128 rows][128 B]
+  uint8_t* k_s = q_s + 2 * TILE_BYTES;       // [2 stages][2 halves of d][128 keys][128 B]
   uint8_t* v_s = k_s + 2 * TILE_BYTES;       // [2 stages][2 halves of d][128 keys][128 B]
-  uint8_t* p_s = v_s + 2 * TILE_BYTES;       // [2 halves of keys][128 rows][128 B]
-  Barriers* bar = reinterpret_cast<Barriers*>(p_s + TILE_BYTES);
+  Barriers* bar = reinterpret_cast<Barriers*>(v_s + 2 * TILE_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int seq = tile_seq[blockIdx.y], q0 = tile_q0[blockIdx.y];
   const int h = blockIdx.x, kvh = h / (nq / nkv);
   const int tok0 = cu_q[seq], qlen = cu_q[seq + 1] - tok0, kvlen = kv_lens[seq];
   const int ctx = kvlen - qlen;
-  const int nqv = min(BQ, qlen - q0);
-  const int first_pos = ctx + q0, last_pos = first_pos + nqv - 1;
-  const int kv_lo = window > 0 ? max(0, first_pos - window + 1) : 0;
-  const int kv_hi = last_pos + 1;
-  const int kt0 = (kv_lo / BK) * BK;
-  const int n_tiles = nqv > 0 ? (kv_hi - kt0 + BK - 1) / BK : 0;
+  int nqv[2], first_pos[2], kv_lo[2], kv_hi[2], n_t[2];
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    nqv[x] = max(0, min(BQ, qlen - (q0 + x * BQ)));
+    first_pos[x] = ctx + q0 + x * BQ;
+    kv_lo[x] = window > 0 ? max(0, first_pos[x] - window + 1) : 0;
+    kv_hi[x] = first_pos[x] + nqv[x];
+  }
+  const int kt0 = (kv_lo[0] / BK) * BK;      // tile a starts lowest
+#pragma unroll
+  for (int x = 0; x < 2; ++x) n_t[x] = nqv[x] > 0 ? (kv_hi[x] - kt0 + BK - 1) / BK : 0;
+  const int n_max = max(n_t[0], n_t[1]);
+  const int lo_all = kv_lo[0], hi_all = max(kv_hi[0], kv_hi[1]);
   const int* bt = block_tables + (size_t)seq * bt_stride;
   bool failed = false;
 
@@ -164,12 +207,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_init(&bar->v_full[i], 1);
       mbar_init(&bar->kv_empty[i], 1);
       mbar_init(&bar->s_full[i], 1);
-      mbar_init(&bar->s_empty[i], 4);
+      mbar_init(&bar->p_full[i], 4);    // one arrival per softmax warp of the tile
+      mbar_init(&bar->pv_done[i], 1);
     }
-    mbar_init(&bar->p_full, 4);
-    mbar_init(&bar->p_empty, 1);
-    mbar_init(&bar->o_full, 1);
-    mbar_init(&bar->o_empty, 4);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -183,20 +223,40 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __syncthreads();
   fence_after();
   const uint32_t tmem_base = bar->tmem_slot;
-  const uint32_t tmem_s[2] = {tmem_base, tmem_base + 128u};
-  const uint32_t tmem_o = tmem_base + 256u;
+  const uint32_t tmem_s[2] = {tmem_base, tmem_base + 128u};          // scores, then P over their first 64 columns
+  const uint32_t tmem_o[2] = {tmem_base + 256u, tmem_base + 384u};
   pdl_wait();   // q and the cache pages were written by the kernels before
 
   if (warp == 0) {
-    if (lane == 0 && n_tiles > 0) {
-      mbar_expect_tx(&bar->q_full, TILE_BYTES);
-      tma_load_2d(q_s, &map_q, &bar->q_full, h * D, tok0 + q0);
-      tma_load_2d(q_s + HALF_BYTES, &map_q, &bar->q_full, h * D + 64, tok0 + q0);
+    if (n_max > 0) {
+      if (lane == 0) {
+        mbar_expect_tx(&bar->q_full, (uint32_t)(nqv[1] > 0 ? 2 * TILE_BYTES : TILE_BYTES));
+        for (int x = 0; x < 2; ++x) {
+          if (nqv[x] <= 0) continue;
+          tma_load_2d(q_s + x * TILE_BYTES, &map_q, &bar->q_full, h * D, tok0 + q0 + x * BQ);
+          tma_load_2d(q_s + x * TILE_BYTES + HALF_BYTES, &map_q, &bar->q_full, h * D + 64, tok0 + q0 + x * BQ);
+        }
+      }
+      // A key tile is 4 boxes per page (K and V, two halves of d).  Issuing a tensor copy costs its
+      // thread a few hundred nanoseconds, so the boxes of a tile are issued by the warp's lanes
+      // side by side, not by one thread one after the other.
       const int box_bytes = page_size * 128;
       const int pages_per_tile = BK / page_size;
-      for (int j = 0; j < n_tiles; ++j) {
+      const int n_boxes = 4 * pages_per_tile;
+      for (int j = 0; j < n_max; ++j) {
         const int s = j & 1;
-        if (!mbar_wait(&bar->kv_empty[s], ((uint32_t)(j >> 1) & 1u) ^ 1u)) { failed = true; atomicExch(status, 11); break; }
+        int ok = 1;
+        if (lane == 0) {
+          ok = mbar_wait(&bar->kv_empty[s], ((uint32_t)(j >> 1) & 1u) ^ 1u) ? 1 : 0;
+          if (ok) {
+            mbar_expect_tx(&bar->k_full[s], (uint32_t)TILE_BYTES);
+            mbar_expect_tx(&bar->v_full[s], (uint32_t)TILE_BYTES);
+          } else {
+            atomicExch(status, 11);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) { failed = true; break; }
         const int kt = kt0 + j * BK;
         // A tile may reach past the request's last page, or start in pages a window has given
         // back.  Such boxes are filled from a page the request does hold: their keys are masked
@@ -204,165 +264,190 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         int fallback = -1;
         for (int p = 0; p < pages_per_tile && fallback < 0; ++p) {
           const int key = kt + p * page_size;
-          if (key < kv_hi && key + page_size > kv_lo) fallback = __ldg(bt + key / page_size);
+          if (key < hi_all && key + page_size > lo_all) fallback = __ldg(bt + key / page_size);
         }
         if (fallback < 0) fallback = 0;
-        mbar_expect_tx(&bar->k_full[s], (uint32_t)TILE_BYTES);
-        mbar_expect_tx(&bar->v_full[s], (uint32_t)TILE_BYTES);
-        for (int p = 0; p < pages_per_tile; ++p) {
+        for (int b = lane; b < n_boxes; b += 32) {
+          const int p = b >> 2, which = b & 3;   // 0, 1: K halves; 2, 3: V halves
           const int key = kt + p * page_size;
-          int page = (key < kv_hi && key + page_size > kv_lo) ? __ldg(bt + key / page_size) : -1;
+          int page = (key < hi_all && key + page_size > lo_all) ? __ldg(bt + key / page_size) : -1;
           if (page < 0) page = fallback;
           const int row = (page * nkv + kvh) * page_size;
-          uint8_t* kd = k_s + s * TILE_BYTES + p * box_bytes;
-          uint8_t* vd = v_s + s * TILE_BYTES + p * box_bytes;
-          tma_load_2d(kd, &map_k, &bar->k_full[s], 0, row);
-          tma_load_2d(kd + HALF_BYTES, &map_k, &bar->k_full[s], 64, row);
-          tma_load_2d(vd, &map_v, &bar->v_full[s], 0, row);
-          tma_load_2d(vd + HALF_BYTES, &map_v, &bar->v_full[s], 64, row);
+          uint8_t* dst = (which < 2 ? k_s : v_s) + s * TILE_BYTES + p * box_bytes + (which & 1) * HALF_BYTES;
+          tma_load_2d(dst, which < 2 ? &map_k : &map_v, which < 2 ? &bar->k_full[s] : &bar->v_full[s], (which & 1) * 64, row);
         }
+        __syncwarp();
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && n_tiles > 0) {
+    if (lane == 0 && n_max > 0) {
       const uint32_t idesc_s = idesc_bf16(BK, false), idesc_o = idesc_bf16(D, true);
-      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
-      auto issue_qk = [&](int j) -> bool {
-        const int s = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        if (!mbar_wait(&bar->k_full[s], ph)) { atomicExch(status, 12); return false; }
-        if (!mbar_wait(&bar->s_empty[s], ph ^ 1u)) { atomicExch(status, 13); return false; }
-        fence_after();
-        const uint32_t k_addr = smem_u32(k_s + s * TILE_BYTES);
+      // S_x[j] = Q_x K[j]^T (K[j] must have arrived: the caller has waited for it)
+      auto issue_qk = [&](int x, int j) {
+        const uint32_t q_addr = smem_u32(q_s + x * TILE_BYTES), k_addr = smem_u32(k_s + (j & 1) * TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (uint32_t)((kk >> 2) * HALF_BYTES + (kk & 3) * 32);
-          umma_bf16(tmem_s[s], desc_kmajor(q_addr + off), desc_kmajor(k_addr + off), idesc_s, kk > 0 ? 1u : 0u);
+          umma_bf16(tmem_s[x], desc_kmajor(q_addr + off), desc_kmajor(k_addr + off), idesc_s, kk > 0 ? 1u : 0u);
         }
-        umma_commit(&bar->s_full[s]);
-        return true;
+        umma_commit(&bar->s_full[x]);
       };
       if (!mbar_wait(&bar->q_full, 0)) { failed = true; atomicExch(status, 14); }
-      if (!failed && !issue_qk(0)) failed = true;
-      for (int j = 0; j < n_tiles && !failed; ++j) {
-        if (j + 1 < n_tiles && !issue_qk(j + 1)) { failed = true; break; }
-        const int s = j & 1;
-        if (!mbar_wait(&bar->p_full, (uint32_t)j & 1u)) { failed = true; atomicExch(status, 15); break; }
-        if (!mbar_wait(&bar->v_full[s], (uint32_t)(j >> 1) & 1u)) { failed = true; atomicExch(status, 16); break; }
-        if (!mbar_wait(&bar->o_empty, ((uint32_t)j & 1u) ^ 1u)) { failed = true; atomicExch(status, 17); break; }
+      if (!failed && !mbar_wait(&bar->k_full[0], 0)) { failed = true; atomicExch(status, 12); }
+      if (!failed) {
         fence_after();
-        const uint32_t v_addr = smem_u32(v_s + s * TILE_BYTES);
+        for (int x = 0; x < 2; ++x)
+          if (n_t[x] > 0) issue_qk(x, 0);
+      }
+      for (int j = 0; j < n_max && !failed; ++j) {
+        const int s = j & 1;
+        bool have_v = false, have_k = false;
+        for (int x = 0; x < 2 && !failed; ++x) {
+          if (j >= n_t[x]) continue;
+          if (!mbar_wait(&bar->p_full[x], (uint32_t)j & 1u)) { failed = true; atomicExch(status, 15); break; }
+          if (!have_v) {
+            if (!mbar_wait(&bar->v_full[s], (uint32_t)(j >> 1) & 1u)) { failed = true; atomicExch(status, 16); break; }
+            have_v = true;
+          }
+          fence_after();
+          const uint32_t v_addr = smem_u32(v_s + s * TILE_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < BK / 16; ++kk) {
-          // P: keys kk*16.. of the K-major P tile; V: key rows kk*16.. of the MN-major V tile
-          const uint32_t p_off = (uint32_t)((kk >> 2) * HALF_BYTES + (kk & 3) * 32);
-          umma_bf16(tmem_o, desc_kmajor(p_addr + p_off), desc_mnmajor(v_addr + (uint32_t)kk * 16u * 128u), idesc_o,
-                    kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            // P: keys kk*16.. = 8 columns of packed pairs; V: key rows kk*16.. of the MN-major V tile
+            umma_bf16_ts(tmem_o[x], tmem_s[x] + (uint32_t)kk * 8u, desc_mnmajor(v_addr + (uint32_t)kk * 16u * 128u), idesc_o,
+                         (j > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&bar->pv_done[x]);
+          if (j + 1 < n_t[x]) {   // the next scores of this tile run under the other tile's softmax
+            if (!have_k) {
+              if (!mbar_wait(&bar->k_full[(j + 1) & 1], (uint32_t)((j + 1) >> 1) & 1u)) { failed = true; atomicExch(status, 12); break; }
+              have_k = true;
+              fence_after();
+            }
+            issue_qk(x, j + 1);
+          }
         }
-        umma_commit(&bar->o_full);
-        umma_commit(&bar->p_empty);
-        umma_commit(&bar->kv_empty[s]);
+        if (!failed) umma_commit(&bar->kv_empty[s]);
       }
     }
   } else {
+    const int x = (warp - 2) >> 2;               // which query tile
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;           // this thread's query row = its TMEM lane
-    const int pos = first_pos + r;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-    float o_acc[D];
-#pragma unroll
-    for (int c = 0; c < D; ++c) o_acc[c] = 0.f;
-    float m = -INFINITY, l = 0.f;
-    for (int j = 0; j < n_tiles && !failed; ++j) {
-      const int s = j & 1;
+    // this tile's numbers in registers (the arrays are indexed by x, which only this branch knows)
+    const int nt = x ? n_t[1] : n_t[0];
+    const int my_first = x ? first_pos[1] : first_pos[0];
+    const int my_lo = x ? kv_lo[1] : kv_lo[0];
+    const int pos = my_first + r;
+    const int row_lo = window > 0 ? max(my_lo, pos - window + 1) : my_lo;   // keys row_lo .. pos are visible
+    const uint32_t s_addr = (x ? tmem_s[1] : tmem_s[0]) + lane_off, o_addr = (x ? tmem_o[1] : tmem_o[0]) + lane_off;
+    uint64_t* s_full = &bar->s_full[x];
+    uint64_t* p_full = &bar->p_full[x];
+    uint64_t* pv_done = &bar->pv_done[x];
+    float m_ref = -INFINITY, l = 0.f;
+    for (int j = 0; j < nt && !failed; ++j) {
       const int kt = kt0 + j * BK;
-      if (!mbar_wait(&bar->s_full[s], (uint32_t)(j >> 1) & 1u)) { failed = true; atomicExch(status, 18); break; }
+      if (!mbar_wait(s_full, (uint32_t)j & 1u)) { failed = true; atomicExch(status, 18); break; }
       fence_after();
-      const bool need_mask = kt + BK - 1 > first_pos || window > 0 || kt < kv_lo;
+      // Columns c_lo .. c_hi - 1 of this tile are visible to this row; only tiles on the diagonal,
+      // at a window's edge or below the first visible key need the test at all (a warp-uniform
+      // choice between two loops, so that the common tile pays nothing for the mask).
+      const bool need_mask = kt + BK - 1 > my_first || window > 0 || kt < my_lo;
+      const int c_hi = min(BK, pos - kt + 1), c_lo = max(0, row_lo - kt);
       // pass 1: the row's maximum over the visible keys
       float mx = -INFINITY;
+      if (need_mask) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BK; c0 += 32) {
+          float v[32];
+          tmem_load32(s_addr + (uint32_t)c0, v);
 #pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, (c0 + i >= c_lo && c0 + i < c_hi) ? v[i] : -INFINITY);
+        }
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BK; c0 += 32) {
+          float v[32];
+          tmem_load32(s_addr + (uint32_t)c0, v);
+          float m4[4] = {v[0], v[1], v[2], v[3]};
+#pragma unroll
+          for (int i = 4; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], v[i]);
+          mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
+        }
+      }
+      // The reference maximum moves only when the row's maximum has outgrown it by 2^8
+      // (p stays below 256); then the sum and the output in tensor memory are rescaled.
+      const float cand = mx * scale_log2;
+      const bool need = cand > m_ref + 8.0f;
+      if (__any_sync(0xffffffffu, need)) {
+        float f = 1.0f;
+        if (need) {
+          f = m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - cand);
+          m_ref = cand;
+        }
+        l *= f;
+        if (j > 0) {
+          if (!mbar_wait(pv_done, ((uint32_t)j & 1u) ^ 1u)) { failed = true; atomicExch(status, 20); break; }
+          fence_after();
+#pragma unroll 1
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            float v[32];
+            tmem_load32(o_addr + (uint32_t)c0, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= f;
+            tmem_store32(o_addr + (uint32_t)c0, v);
+          }
+        }
+      }
+      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+      // pass 2: p = exp2(s * scale - reference), the row sum, P as bfloat16 pairs over S's first columns
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
       for (int c0 = 0; c0 < BK; c0 += 32) {
         float v[32];
-        tmem_load32(tmem_s[s] + lane_off + (uint32_t)c0, v);
+        tmem_load32(s_addr + (uint32_t)c0, v);
+        uint32_t packed[16];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = v[i];
-          if (need_mask) {
-            const int key = kt + c0 + i;
-            if (key > pos || key < kv_lo || (window > 0 && key <= pos - window)) x = -INFINITY;
-          }
-          mx = fmaxf(mx, x);
+        for (int i = 0; i < 32; ++i) v[i] = fast_exp2(fmaf(v[i], scale_log2, -m_use));
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = (c0 + i >= c_lo && c0 + i < c_hi) ? v[i] : 0.f;
         }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sum4[i & 3] += v[i];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) packed[i] = pack2(v[2 * i], v[2 * i + 1]);
+        tmem_store16(s_addr + (uint32_t)(c0 >> 1), packed);
       }
-      const float m_new = fmaxf(m, mx * scale_log2);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = fast_exp2(m - m_use);
-      // P of the tile before must have been read by its MMA before it is overwritten
-      if (!mbar_wait(&bar->p_empty, ((uint32_t)j & 1u) ^ 1u)) { failed = true; atomicExch(status, 19); break; }
-      // pass 2: p = exp2(s * scale - max), the row sum, P to shared memory as bfloat16
-      float sum = 0.f;
-#pragma unroll
-      for (int c0 = 0; c0 < BK; c0 += 32) {
-        float v[32];
-        tmem_load32(tmem_s[s] + lane_off + (uint32_t)c0, v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float p = fast_exp2(fmaf(v[i], scale_log2, -m_use));
-          if (need_mask) {
-            const int key = kt + c0 + i;
-            if (key > pos || key < kv_lo || (window > 0 && key <= pos - window)) p = 0.f;
-          }
-          v[i] = p;
-          sum += p;
-        }
-        uint8_t* prow = p_s + (c0 >> 6) * HALF_BYTES + r * 128;
-#pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          const int chunk = ((c0 & 63) + i) >> 3;
-          uint4 w;
-          w.x = pack2(v[i], v[i + 1]);
-          w.y = pack2(v[i + 2], v[i + 3]);
-          w.z = pack2(v[i + 4], v[i + 5]);
-          w.w = pack2(v[i + 6], v[i + 7]);
-          *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = w;
-        }
-      }
-      l = l * alpha + sum;
-      m = m_new;
-      // S[s] has been read; P is written: make it visible to the tensor core's reads
-      fence_before();
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&bar->s_empty[s]);
-        mbar_arrive(&bar->p_full);
-      }
-      // O = O * alpha + P V
-      if (!mbar_wait(&bar->o_full, (uint32_t)j & 1u)) { failed = true; atomicExch(status, 20); break; }
-      fence_after();
-#pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        float v[32];
-        tmem_load32(tmem_o + lane_off + (uint32_t)c0, v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o_acc[c0 + i] = fmaf(o_acc[c0 + i], alpha, v[i]);
-      }
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      tmem_wait_st();
       fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bar->o_empty);
+      if (lane == 0) mbar_arrive(p_full);
     }
-    if (!failed && r < nqv) {
-      const float inv = l > 0.f ? 1.0f / l : 0.f;
-      bf16* orow = out + (size_t)(tok0 + q0 + r) * out_stride + (size_t)h * D;
+    if (!failed && nt > 0) {
+      if (!mbar_wait(pv_done, (uint32_t)(nt - 1) & 1u)) { failed = true; atomicExch(status, 21); }
+      fence_after();
+      if (!failed) {
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        bf16* orow = out + (size_t)(tok0 + q0 + x * BQ + r) * out_stride + (size_t)h * D;
 #pragma unroll
-      for (int c = 0; c < D; c += 8) {
-        uint4 w;
-        w.x = pack2(o_acc[c] * inv, o_acc[c + 1] * inv);
-        w.y = pack2(o_acc[c + 2] * inv, o_acc[c + 3] * inv);
-        w.z = pack2(o_acc[c + 4] * inv, o_acc[c + 5] * inv);
-        w.w = pack2(o_acc[c + 6] * inv, o_acc[c + 7] * inv);
-        *reinterpret_cast<uint4*>(orow + c) = w;
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          float v[32];
+          tmem_load32(o_addr + (uint32_t)c0, v);
+          if (r < (x ? nqv[1] : nqv[0])) {
+#pragma unroll
+            for (int c = 0; c < 32; c += 8) {
+              uint4 w;
+              w.x = pack2(v[c] * inv, v[c + 1] * inv);
+              w.y = pack2(v[c + 2] * inv, v[c + 3] * inv);
+              w.z = pack2(v[c + 4] * inv, v[c + 5] * inv);
+              w.w = pack2(v[c + 6] * inv, v[c + 7] * inv);
+              *reinterpret_cast<uint4*>(orow + c0 + c) = w;
+            }
+          }
+        }
       }
     }
   }
