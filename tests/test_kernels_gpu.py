@@ -108,8 +108,9 @@ def test_rope_table(n_pos, d, theta):
 @pytest.mark.parametrize("nq,nkv,d,page,norm,rope", [
     (4, 2, 16, 16, True, True), (6, 1, 32, 8, True, True), (3, 3, 48, 32, True, True),
     (32, 8, 128, 16, True, True), (5, 5, 80, 4, False, True), (2, 1, 256, 16, True, False)])
-def test_qk_norm_rope_store(dtype, nq, nkv, d, page, norm, rope):
-    T, n_pages, n_pos = 11, 9, 200
+@pytest.mark.parametrize("T", [11, 300])   # a few tokens; a prompt portion (bfloat16 rows then take the 16-byte kernel)
+def test_qk_norm_rope_store(dtype, nq, nkv, d, page, norm, rope, T):
+    n_pages, n_pos = -(-T // page) + 3, 200
     qkv = rnd(T, (nq + 2 * nkv) * d, dtype=dtype)
     qw = (1 + 0.1 * rnd(d, seed=3)) if norm else None
     kw = (1 + 0.1 * rnd(d, seed=4)) if norm else None

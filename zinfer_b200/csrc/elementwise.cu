@@ -461,6 +461,98 @@ __global__ void qk_norm_rope_store_kernel(const T* src, int src_stride, const fl
   }  // heads
 }
 
+// The same for many tokens of bfloat16 rows (prompt portions), 16 bytes per access: HALF / 8
+// lanes share a (token, head), each with 8 consecutive elements of the head's first half and
+// the 8 that pair with them in the second; a warp works on 32 / (HALF / 8) heads at once.
+// d in {16, 32, 64, 128, 256}.
+template <int D>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_store_vec_kernel(const __nv_bfloat16* src, int src_stride, __nv_bfloat16* q_out,   // may be the same rows
+                              int q_stride, int nq, int nkv, const float* __restrict__ qw,
+                              const float* __restrict__ kw, float eps, const float* __restrict__ cos_t,
+                              const float* __restrict__ sin_t, int n_table_pos, const int* __restrict__ positions,
+                              __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache,
+                              const int* __restrict__ slots, int page_size, int n_heads, long long n_items) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int HALF = D / 2, LPI = HALF / 8;            // lanes per (token, head)
+  const long long item_raw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LPI;
+  const bool in_range = item_raw < n_items;
+  const long long item = in_range ? item_raw : n_items - 1;   // lanes past the end load a valid row and store nothing
+  const int sub = threadIdx.x % LPI;
+  const int t = (int)(item / n_heads), head = (int)(item % n_heads);
+  const int i0 = sub * 8;
+  const __nv_bfloat16* sp = src + (size_t)t * src_stride + (size_t)head * D + i0;
+  const uint4 ra = *reinterpret_cast<const uint4*>(sp), rb = *reinterpret_cast<const uint4*>(sp + HALF);
+  float a[8], b[8];
+  const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&ra);
+  const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&rb);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 fa = __bfloat1622float2(pa[j]), fb = __bfloat1622float2(pb[j]);
+    a[2 * j] = fa.x;
+    a[2 * j + 1] = fa.y;
+    b[2 * j] = fb.x;
+    b[2 * j + 1] = fb.y;
+  }
+  // the sum of squares of the head, by every lane of the warp (no lane leaves before the shuffles)
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ss = sum_squares_step(ss, a[j], b[j]);
+#pragma unroll
+  for (int o = LPI / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o, LPI);
+  if (!in_range) return;
+  __nv_bfloat16* dst;
+  if (head < nq) {
+    dst = q_out + (size_t)t * q_stride + (size_t)head * D + i0;
+  } else {
+    const int slot = slots[t];
+    if (slot < 0) return;
+    const int kvh = (head - nq) % nkv;
+    __nv_bfloat16* base = head < nq + nkv ? kcache : vcache;
+    dst = base + (((size_t)(slot / page_size) * nkv + kvh) * page_size + (slot % page_size)) * D + i0;
+  }
+  if (head >= nq + nkv) {        // value head: copy
+    *reinterpret_cast<uint4*>(dst) = ra;
+    *reinterpret_cast<uint4*>(dst + HALF) = rb;
+    return;
+  }
+  const float* w = head < nq ? qw : kw;
+  const float inv = w ? 1.0f / sqrtf(ss / (float)D + eps) : 1.f;
+  int pos = positions[t];
+  if (pos >= n_table_pos) pos = n_table_pos - 1;  // the host refuses such positions
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (w) {
+      a[j] = norm_scale(a[j], w[i0 + j], inv);
+      b[j] = norm_scale(b[j], w[i0 + j + HALF], inv);
+    }
+    if (cos_t) rotate_pair(a[j], b[j], cos_t[(size_t)pos * HALF + i0 + j], sin_t[(size_t)pos * HALF + i0 + j]);
+  }
+  uint4 oa, ob;
+  __nv_bfloat162* qa = reinterpret_cast<__nv_bfloat162*>(&oa);
+  __nv_bfloat162* qb = reinterpret_cast<__nv_bfloat162*>(&ob);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    qa[j] = __floats2bfloat162_rn(a[2 * j], a[2 * j + 1]);
+    qb[j] = __floats2bfloat162_rn(b[2 * j], b[2 * j + 1]);
+  }
+  *reinterpret_cast<uint4*>(dst) = oa;
+  *reinterpret_cast<uint4*>(dst + HALF) = ob;
+}
+
+template <int D>
+static void launch_qk_vec(const void* src, int T, int src_stride, void* q_out, int q_stride, int nq, int nkv,
+                          const float* qw, const float* kw, float eps, const float* cos_t, const float* sin_t,
+                          int n_table_pos, const int* positions, void* kcache, void* vcache, const int* slots,
+                          int page_size, int n_heads, cudaStream_t stream) {
+  const long long n_items = (long long)T * n_heads;
+  const long long threads = n_items * (D / 16);
+  zi_launch(qk_norm_rope_store_vec_kernel<D>, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, stream,
+            (const __nv_bfloat16*)src, src_stride, (__nv_bfloat16*)q_out, q_stride, nq, nkv, qw, kw, eps, cos_t, sin_t,
+            n_table_pos, positions, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, slots, page_size, n_heads, n_items);
+}
+
 extern "C" int zi_qk_norm_rope_store(const void* src, int dtype, int T, int src_stride, const float* partials,
                                      int splits, long long split_stride, void* q_out, int q_stride, int nq, int nkv,
                                      int d, const float* qw, const float* kw, float eps, const float* cos_t,
@@ -474,6 +566,23 @@ extern "C" int zi_qk_norm_rope_store(const void* src, int dtype, int T, int src_
   if (write_kv && (!kcache || !vcache || !slots || page_size <= 0))
     return zi_refuse("qk_norm_rope_store: writing keys and values needs pages and slots");
   const int n_heads = nq + (write_kv ? 2 * nkv : 0);
+  // many tokens of bfloat16 rows: the kernel with 16-byte accesses
+  const bool vec = T > 256 && dtype == ZI_BF16 && src && (d == 16 || d == 32 || d == 64 || d == 128 || d == 256) &&
+                   src_stride % 8 == 0 && q_stride % 8 == 0 && (uintptr_t)src % 16 == 0 && (uintptr_t)q_out % 16 == 0 &&
+                   (!write_kv || ((uintptr_t)kcache % 16 == 0 && (uintptr_t)vcache % 16 == 0)) &&
+                   (!qw || (uintptr_t)qw % 16 == 0) && (!kw || (uintptr_t)kw % 16 == 0);
+  if (vec) {
+#define ZI_QK_VEC(DD)                                                                                            \
+  launch_qk_vec<DD>(src, T, src_stride, q_out, q_stride, nq, nkv, qw, kw, eps, cos_t, sin_t, n_table_pos, positions, \
+                    kcache, vcache, slots, page_size, n_heads, stream)
+    if (d == 16) ZI_QK_VEC(16);
+    else if (d == 32) ZI_QK_VEC(32);
+    else if (d == 64) ZI_QK_VEC(64);
+    else if (d == 128) ZI_QK_VEC(128);
+    else ZI_QK_VEC(256);
+#undef ZI_QK_VEC
+    return zi_check_launch("qk_norm_rope_store");
+  }
   // few tokens (decode): a warp per head, so that all heads run at once; many tokens: 8 warps share a token's heads
   const int warps = T <= 256 ? 4 : 8;
   dim3 grid(T, T <= 256 ? (n_heads + warps - 1) / warps : 1);
