@@ -566,8 +566,8 @@ extern "C" int zi_qk_norm_rope_store(const void* src, int dtype, int T, int src_
   if (write_kv && (!kcache || !vcache || !slots || page_size <= 0))
     return zi_refuse("qk_norm_rope_store: writing keys and values needs pages and slots");
   const int n_heads = nq + (write_kv ? 2 * nkv : 0);
-  // many tokens of bfloat16 rows: the kernel with 16-byte accesses
-  const bool vec = T > 256 && dtype == ZI_BF16 && src && (d == 16 || d == 32 || d == 64 || d == 128 || d == 256) &&
+  // more than a few tokens of bfloat16 rows: the kernel with 16-byte accesses
+  const bool vec = T > 16 && dtype == ZI_BF16 && src && (d == 16 || d == 32 || d == 64 || d == 128 || d == 256) &&
                    src_stride % 8 == 0 && q_stride % 8 == 0 && (uintptr_t)src % 16 == 0 && (uintptr_t)q_out % 16 == 0 &&
                    (!write_kv || ((uintptr_t)kcache % 16 == 0 && (uintptr_t)vcache % 16 == 0)) &&
                    (!qw || (uintptr_t)qw % 16 == 0) && (!kw || (uintptr_t)kw % 16 == 0);

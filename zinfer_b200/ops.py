@@ -405,11 +405,7 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, blo
             step.n_pf_tiles, num_heads, num_kv_heads, head_dim, page_size, win, ctypes.c_float(scale), _stream()),
             "attention (prefill)")
     if step.n_dec > 0:
-        sms = _sm_count(q.device)
-        # as many splits as keep all CTAs resident at once (two per SM): one wave, no tail
-        splits = max(1, min(32, (2 * sms) // (step.n_dec * num_kv_heads)))
-        if step.max_kv_len:  # known on the host: no more splits than tiles of 64 keys
-            splits = min(splits, max(1, -(-step.max_kv_len // 64)))
+        splits = decode_splits(step.n_dec, num_kv_heads, _sm_count(q.device), step.max_kv_len)
         need = L.zi_attention_decode_workspace_floats(step.n_dec, num_heads, num_kv_heads, head_dim, splits)
         ws = torch.empty((need,), dtype=torch.float32, device=q.device) if need else None
         _check(L.zi_attention_decode_mma(
@@ -417,6 +413,26 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, blo
             block_tables.stride(0), _ptr(step.cu_q), _ptr(step.kv_lens), _ptr(step.dec_seq), step.n_dec, num_heads,
             num_kv_heads, head_dim, page_size, win, ctypes.c_float(scale), splits, _stream()), "attention (decode)")
     return out
+
+
+def decode_splits(n_dec: int, num_kv_heads: int, sm_count: int, max_kv_len: Optional[int] = None,
+                  fixed_us: float = 3.0) -> int:
+    """Key splits of the decode attention.  Its blocks are (request, kv head, split), two fit on
+    an SM at once, and a block costs a fixed time (``fixed_us``: launch, prologue, merge; more in
+    the fused kernel, which also makes q, k and v) plus its share of the walk over the keys
+    (about 0.025 us a key for a block's four warps).  The split count (at most 32, never more
+    than tiles of 64 keys) that makes waves x block time smallest."""
+    slots, units = 2 * sm_count, max(1, n_dec * num_kv_heads)
+    keys = max_kv_len if max_kv_len and max_kv_len > 0 else 2048
+    limit = max(1, min(32, -(-keys // 64)))
+    walk = 0.025 * keys
+    best, best_cost = 1, float("inf")
+    for s in range(1, limit + 1):
+        waves = -(-units * s // slots)
+        cost = waves * (fixed_us + walk / s)
+        if cost < best_cost * 0.98:     # more splits only for a clear gain
+            best, best_cost = s, cost
+    return best
 
 
 def decode_fused_ok(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int, step) -> bool:
@@ -465,10 +481,7 @@ def attention_decode_fused(qkv, num_heads: int, num_kv_heads: int, head_dim: int
           and tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim), "cache pages are bfloat16 [pages, kv heads, page, d]")
     _i32(slots, "slots")
     out = torch.empty((T, num_heads * head_dim), dtype=torch.bfloat16, device=device)
-    sms = _sm_count(device)
-    splits = max(1, min(32, (2 * sms) // (step.n_dec * num_kv_heads)))
-    if step.max_kv_len:
-        splits = min(splits, max(1, -(-step.max_kv_len // 64)))
+    splits = decode_splits(step.n_dec, num_kv_heads, _sm_count(device), step.max_kv_len, fixed_us=8.0)
     need = L.zi_attention_decode_workspace_floats(step.n_dec, num_heads, num_kv_heads, head_dim, splits)
     ws = torch.empty((need,), dtype=torch.float32, device=device) if need else None
     _check(L.zi_attention_decode_fused(
