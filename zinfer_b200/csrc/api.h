@@ -61,7 +61,6 @@ int zi_attention_prefill_tcgen05(void* out, int out_stride, const void* q, int q
                                  int bt_stride, const int* cu_q, const int* kv_lens, const int* tile_seq,
                                  const int* tile_q0, int n_tiles, int nq, int nkv, int d, int page_size, int window,
                                  float scale, cudaStream_t stream);
-int zi_attention_tcgen05_status();
 long long zi_attention_decode_workspace_floats(int n_dec, int nq, int nkv, int d, int splits);
 int zi_attention_decode_mma(void* out, int out_stride, float* workspace, const void* q, int q_stride,
                             const void* kcache, const void* vcache, const int* block_tables, int bt_stride,

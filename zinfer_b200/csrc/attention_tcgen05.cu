@@ -7,10 +7,10 @@
 // in `status`, lets copies land, frees the tensor memory and returns.
 #include <cuda.h>
 
-#include <mutex>
-
 #include "api.h"
 #include "common.cuh"
+#include "gemm_internal.h"
+#include "tcgen05_ptx.cuh"
 
 namespace {
 using bf16 = __nv_bfloat16;
@@ -18,83 +18,11 @@ using bf16 = __nv_bfloat16;
 constexpr int BQ = 128, BK = 128, D = 128, THREADS = 320;
 constexpr int HALF_BYTES = 128 * 128;          // 128 rows x 64 bf16: one swizzled half tile
 constexpr int TILE_BYTES = 2 * HALF_BYTES;     // a [128, 128] bf16 tile as two halves of d (or of keys)
-constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done) return true;
-    __nanosleep(64);   // a waiting warp must not take issue slots from the working ones
-  }
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_load32(uint32_t taddr, float* v) {
-  uint32_t r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-}
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-
-// K-major operand with 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
-  return (uint64_t)((addr & 0x3ffffu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 // MN-major operand with 128-byte swizzle: 64 MN elements (128 bytes) per row, the next 64 MN
 // elements `HALF_BYTES` further (leading byte offset); groups of 8 K rows 1024 bytes apart.
@@ -219,9 +147,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  fence_before();
+  tcgen05_fence_before();
   __syncthreads();
-  fence_after();
+  tcgen05_fence_after();
   const uint32_t tmem_base = bar->tmem_slot;
   const uint32_t tmem_s[2] = {tmem_base, tmem_base + 128u};          // scores, then P over their first 64 columns
   const uint32_t tmem_o[2] = {tmem_base + 256u, tmem_base + 384u};
@@ -288,14 +216,14 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (uint32_t)((kk >> 2) * HALF_BYTES + (kk & 3) * 32);
-          umma_bf16(tmem_s[x], desc_kmajor(q_addr + off), desc_kmajor(k_addr + off), idesc_s, kk > 0 ? 1u : 0u);
+          tcgen05_mma_bf16(tmem_s[x], smem_desc_sw128(q_addr + off), smem_desc_sw128(k_addr + off), idesc_s, kk > 0 ? 1u : 0u);
         }
-        umma_commit(&bar->s_full[x]);
+        tcgen05_commit(&bar->s_full[x]);
       };
       if (!mbar_wait(&bar->q_full, 0)) { failed = true; atomicExch(status, 14); }
       if (!failed && !mbar_wait(&bar->k_full[0], 0)) { failed = true; atomicExch(status, 12); }
       if (!failed) {
-        fence_after();
+        tcgen05_fence_after();
         for (int x = 0; x < 2; ++x)
           if (n_t[x] > 0) issue_qk(x, 0);
       }
@@ -309,7 +237,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (!mbar_wait(&bar->v_full[s], (uint32_t)(j >> 1) & 1u)) { failed = true; atomicExch(status, 16); break; }
             have_v = true;
           }
-          fence_after();
+          tcgen05_fence_after();
           const uint32_t v_addr = smem_u32(v_s + s * TILE_BYTES);
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk) {
@@ -317,17 +245,17 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             umma_bf16_ts(tmem_o[x], tmem_s[x] + (uint32_t)kk * 8u, desc_mnmajor(v_addr + (uint32_t)kk * 16u * 128u), idesc_o,
                          (j > 0 || kk > 0) ? 1u : 0u);
           }
-          umma_commit(&bar->pv_done[x]);
+          tcgen05_commit(&bar->pv_done[x]);
           if (j + 1 < n_t[x]) {   // the next scores of this tile run under the other tile's softmax
             if (!have_k) {
               if (!mbar_wait(&bar->k_full[(j + 1) & 1], (uint32_t)((j + 1) >> 1) & 1u)) { failed = true; atomicExch(status, 12); break; }
               have_k = true;
-              fence_after();
+              tcgen05_fence_after();
             }
             issue_qk(x, j + 1);
           }
         }
-        if (!failed) umma_commit(&bar->kv_empty[s]);
+        if (!failed) tcgen05_commit(&bar->kv_empty[s]);
       }
     }
   } else {
@@ -349,7 +277,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     for (int j = 0; j < nt && !failed; ++j) {
       const int kt = kt0 + j * BK;
       if (!mbar_wait(s_full, (uint32_t)j & 1u)) { failed = true; atomicExch(status, 18); break; }
-      fence_after();
+      tcgen05_fence_after();
       // Columns c_lo .. c_hi - 1 of this tile are visible to this row; only tiles on the diagonal,
       // at a window's edge or below the first visible key need the test at all (a warp-uniform
       // choice between two loops, so that the common tile pays nothing for the mask).
@@ -389,7 +317,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         l *= f;
         if (j > 0) {
           if (!mbar_wait(pv_done, ((uint32_t)j & 1u) ^ 1u)) { failed = true; atomicExch(status, 20); break; }
-          fence_after();
+          tcgen05_fence_after();
 #pragma unroll 1
           for (int c0 = 0; c0 < D; c0 += 32) {
             float v[32];
@@ -422,13 +350,13 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       tmem_wait_st();
-      fence_before();
+      tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
     }
     if (!failed && nt > 0) {
       if (!mbar_wait(pv_done, (uint32_t)(nt - 1) & 1u)) { failed = true; atomicExch(status, 21); }
-      fence_after();
+      tcgen05_fence_after();
       if (!failed) {
         const float inv = l > 0.f ? 1.0f / l : 0.f;
         bf16* orow = out + (size_t)(tok0 + q0 + x * BQ + r) * out_stride + (size_t)h * D;
@@ -454,52 +382,14 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   if (failed) {
     for (int i = 0; i < 64; ++i) __nanosleep(10000);   // copies in flight land before shared memory is given up
   }
-  fence_before();
+  tcgen05_fence_before();
   __syncthreads();
   if (warp == 1) {
-    fence_after();
+    tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  });
-  return fn;
-}
-
-// A 2-D map over row-major bf16 [rows, cols] with row pitch `ld` elements, box [box_rows, 64].
-bool make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, long long ld, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
-  const cuuint32_t elem[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-int* status_word() {
-  static int* word = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    if (cudaMalloc(&word, sizeof(int)) == cudaSuccess) cudaMemset(word, 0, sizeof(int));
-  });
-  return word;
-}
 }  // namespace
 
 // Whether the tcgen05 prefill kernel takes this shape: head size 128, pages of 8..128 tokens
@@ -509,7 +399,7 @@ extern "C" int zi_attention_prefill_tcgen05_supported(int nq, int nkv, int d, in
   if (d != 128 || nkv <= 0 || nq % nkv) return 0;
   if (page_size < 8 || page_size > 128 || 128 % page_size || page_size % 8) return 0;
   if (((uintptr_t)q % 16) || (q_stride % 8) || ((uintptr_t)kcache % 16) || ((uintptr_t)vcache % 16)) return 0;
-  return encode_fn() != nullptr;
+  return 1;
 }
 
 extern "C" int zi_attention_prefill_tcgen05(void* out, int out_stride, const void* q, int q_stride, int n_tokens,
@@ -523,10 +413,12 @@ extern "C" int zi_attention_prefill_tcgen05(void* out, int out_stride, const voi
     return zi_refuse("attention_prefill_tcgen05: needs head_dim 128, pages of 8..128 tokens dividing 128, aligned q and pages");
   CUtensorMap map_q, map_k, map_v;
   const long long cache_rows = n_pages * nkv * page_size;
-  if (!make_map(&map_q, q, n_tokens, nq * d, q_stride, BQ) || !make_map(&map_k, kcache, cache_rows, d, d, page_size) ||
-      !make_map(&map_v, vcache, cache_rows, d, d, page_size))
+  if (cache_rows > 0x7fffffffll) return zi_refuse("attention_prefill_tcgen05: the cache has too many rows for a tensor map");
+  if (!zi_internal_make_map(&map_q, q, n_tokens, nq * d, q_stride, BQ) ||
+      !zi_internal_make_map(&map_k, kcache, (int)cache_rows, d, d, page_size) ||
+      !zi_internal_make_map(&map_v, vcache, (int)cache_rows, d, d, page_size))
     return zi_refuse("attention_prefill_tcgen05: cuTensorMapEncodeTiled failed");
-  int* status = status_word();
+  int* status = zi_internal_status_word();
   if (!status) return zi_refuse("attention_prefill_tcgen05: cannot allocate the status word");
   const size_t smem = 1024 + (size_t)6 * TILE_BYTES + sizeof(Barriers) + 64;
   auto kern = attn_prefill_tcgen05_kernel;
@@ -536,13 +428,4 @@ extern "C" int zi_attention_prefill_tcgen05(void* out, int out_stride, const voi
             block_tables, bt_stride, cu_q, kv_lens, tile_seq, tile_q0, nq, nkv, page_size, window,
             scale * 1.4426950408889634f, status);
   return zi_check_launch("attention_prefill_tcgen05");
-}
-
-extern "C" int zi_attention_tcgen05_status() {
-  int* status = status_word();
-  if (!status) return -1;
-  int host = 0;
-  if (cudaMemcpy(&host, status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -2;
-  if (host != 0) cudaMemset(status, 0, sizeof(int));
-  return host;
 }

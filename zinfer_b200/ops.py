@@ -42,9 +42,7 @@ def lib() -> ctypes.CDLL:
 def kernel_status() -> int:
     """Reads and clears the status words of the tcgen05 kernels (synchronises).
     0: every bounded wait inside them completed; else the code of the wait that ran out."""
-    a = int(lib().zi_gemm_tcgen05_status())
-    b = int(lib().zi_attention_tcgen05_status())
-    return a if a else b
+    return int(lib().zi_gemm_tcgen05_status())   # one word for the products, the attention and the whole-layer kernel
 
 
 def library_file() -> str:
