@@ -71,7 +71,7 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, u
 
 struct Barriers {
   uint64_t q_full;
-  uint64_t k_full[2], v_full[2], kv_empty[2];
+  uint64_t k_full[2], v_full[2], k_empty[2], v_empty[2];
   uint64_t s_full[2], p_full[2], pv_done[2];   // per query tile of the CTA
   uint32_t tmem_slot;
 };
@@ -133,7 +133,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar->k_full[i], 1);
       mbar_init(&bar->v_full[i], 1);
-      mbar_init(&bar->kv_empty[i], 1);
+      mbar_init(&bar->k_empty[i], 1);
+      mbar_init(&bar->v_empty[i], 1);
       mbar_init(&bar->s_full[i], 1);
       mbar_init(&bar->p_full[i], 4);    // one arrival per softmax warp of the tile
       mbar_init(&bar->pv_done[i], 1);
@@ -170,21 +171,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // side by side, not by one thread one after the other.
       const int box_bytes = page_size * 128;
       const int pages_per_tile = BK / page_size;
-      const int n_boxes = 4 * pages_per_tile;
       for (int j = 0; j < n_max; ++j) {
         const int s = j & 1;
-        int ok = 1;
-        if (lane == 0) {
-          ok = mbar_wait(&bar->kv_empty[s], ((uint32_t)(j >> 1) & 1u) ^ 1u) ? 1 : 0;
-          if (ok) {
-            mbar_expect_tx(&bar->k_full[s], (uint32_t)TILE_BYTES);
-            mbar_expect_tx(&bar->v_full[s], (uint32_t)TILE_BYTES);
-          } else {
-            atomicExch(status, 11);
-          }
-        }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) { failed = true; break; }
         const int kt = kt0 + j * BK;
         // A tile may reach past the request's last page, or start in pages a window has given
         // back.  Such boxes are filled from a page the request does hold: their keys are masked
@@ -195,16 +183,30 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           if (key < hi_all && key + page_size > lo_all) fallback = __ldg(bt + key / page_size);
         }
         if (fallback < 0) fallback = 0;
-        for (int b = lane; b < n_boxes; b += 32) {
-          const int p = b >> 2, which = b & 3;   // 0, 1: K halves; 2, 3: V halves
-          const int key = kt + p * page_size;
-          int page = (key < hi_all && key + page_size > lo_all) ? __ldg(bt + key / page_size) : -1;
-          if (page < 0) page = fallback;
-          const int row = (page * nkv + kvh) * page_size;
-          uint8_t* dst = (which < 2 ? k_s : v_s) + s * TILE_BYTES + p * box_bytes + (which & 1) * HALF_BYTES;
-          tma_load_2d(dst, which < 2 ? &map_k : &map_v, which < 2 ? &bar->k_full[s] : &bar->v_full[s], (which & 1) * 64, row);
+        // K's slot is free as soon as the scores of the tile two before have been computed, a whole
+        // iteration before V's: K[j] is requested early enough to be there when S[j] is issued
+        for (int which_kv = 0; which_kv < 2; ++which_kv) {
+          int ok = 1;
+          if (lane == 0) {
+            uint64_t* empty = which_kv ? &bar->v_empty[s] : &bar->k_empty[s];
+            ok = mbar_wait(empty, ((uint32_t)(j >> 1) & 1u) ^ 1u) ? 1 : 0;
+            if (ok) mbar_expect_tx(which_kv ? &bar->v_full[s] : &bar->k_full[s], (uint32_t)TILE_BYTES);
+            else atomicExch(status, 11);
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) { failed = true; break; }
+          for (int b = lane; b < 2 * pages_per_tile; b += 32) {
+            const int p = b >> 1, half = b & 1;
+            const int key = kt + p * page_size;
+            int page = (key < hi_all && key + page_size > lo_all) ? __ldg(bt + key / page_size) : -1;
+            if (page < 0) page = fallback;
+            const int row = (page * nkv + kvh) * page_size;
+            uint8_t* dst = (which_kv ? v_s : k_s) + s * TILE_BYTES + p * box_bytes + half * HALF_BYTES;
+            tma_load_2d(dst, which_kv ? &map_v : &map_k, which_kv ? &bar->v_full[s] : &bar->k_full[s], half * 64, row);
+          }
+          __syncwarp();
         }
-        __syncwarp();
+        if (failed) break;
       }
     }
   } else if (warp == 1) {
@@ -226,6 +228,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         tcgen05_fence_after();
         for (int x = 0; x < 2; ++x)
           if (n_t[x] > 0) issue_qk(x, 0);
+        tcgen05_commit(&bar->k_empty[0]);   // K[0] is free when these products have read it
       }
       for (int j = 0; j < n_max && !failed; ++j) {
         const int s = j & 1;
@@ -255,7 +258,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             issue_qk(x, j + 1);
           }
         }
-        if (!failed) tcgen05_commit(&bar->kv_empty[s]);
+        if (!failed) {
+          tcgen05_commit(&bar->v_empty[s]);                 // V[j] has been read by this iteration's products
+          tcgen05_commit(&bar->k_empty[(j + 1) & 1]);       // and K[j+1] by the scores issued in it
+        }
       }
     }
   } else {
