@@ -337,7 +337,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
       // pass 2: p = exp2(s * scale - reference), the row sum, P as bfloat16 pairs over S's first columns
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
+#pragma unroll 2
       for (int c0 = 0; c0 < BK; c0 += 32) {
         float v[32];
         tmem_load32(s_addr + (uint32_t)c0, v);
