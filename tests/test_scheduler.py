@@ -197,3 +197,21 @@ def test_pipelined_resolution_gives_the_same_tokens_and_reasons():
         assert by[3].finish_reason == "stop" and by[3].output == []
         assert by[0].finish_reason == "length" and len(by[0].output) == 10
         assert not cache2.requests and cache2.free_pages() == [pages]
+
+
+def test_decode_attention_split_choice():
+    """The split count of the decode attention (a host decision): one wave of blocks when the
+    requests are few, whole waves when they are many, never more splits than tiles of 64 keys."""
+    from zinfer_b200.ops import decode_splits
+
+    sms = 148
+    assert decode_splits(1, 8, sms, 2048) >= 16            # one request: many splits fill the GPU
+    assert decode_splits(8, 8, sms, 2048) == 4             # 64 (request, head) pairs x 4 = 256 blocks on 296 slots
+    assert decode_splits(32, 8, sms, 2048) == 1            # 256 pairs already fill a wave
+    assert decode_splits(48, 8, sms, 2048) in (2, 3)       # 384 pairs: 2 waves whole, 1.3 split in three
+    assert decode_splits(8, 8, sms, 100) <= 2              # 100 keys are two tiles of 64
+    assert decode_splits(8, 8, sms, 0) >= 1 and decode_splits(8, 8, sms, None) >= 1
+    for n in range(1, 130):
+        for keys in (1, 63, 64, 65, 1000, 8192):
+            s = decode_splits(n, 8, sms, keys)
+            assert 1 <= s <= 32 and s <= max(1, -(-keys // 64))
