@@ -157,6 +157,26 @@ __device__ __forceinline__ void load_kv_rows_pg(uint8_t* ks, uint8_t* vs, int ke
                                                 const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                                                 int nkv, int kvh, int page_size, int page_shift, int lane) {
   constexpr int CH = D / 8;
+  if (page_shift >= 4) {
+    // Pages of 16, 32, 64, ... tokens: the warp's 16 keys (which start at a multiple of 16) lie in
+    // ONE page, so the tile has one base address and every copy a fixed offset from it; only
+    // whether a key is valid still differs from row to row.
+    const int page = __reduce_max_sync(0xffffffffu, lane < 16 ? pg : -1);
+    const size_t base = page >= 0 ? (((size_t)page * nkv + kvh) * page_size + (key_pos0 & (page_size - 1))) * D : 0;
+    const bf16* kb = kcache + base;
+    const bf16* vb = vcache + base;
+#pragma unroll
+    for (int e0 = 0; e0 < 16 * CH; e0 += 32) {
+      const int e = e0 + lane;
+      const int r = e / CH, c = e % CH;                    // compile-time shifts: CH is a power of two
+      const bool valid = __shfl_sync(0xffffffffu, pg, r) >= 0;
+      const int off = valid ? r * D + c * 8 : 0;
+      const uint32_t so = swz<D>(r, c);
+      cp_async16(ks + so, kb + off, valid);
+      cp_async16(vs + so, vb + off, valid);
+    }
+    return;
+  }
 #pragma unroll
   for (int e0 = 0; e0 < 16 * CH; e0 += 32) {
     const int e = e0 + lane;
