@@ -261,6 +261,7 @@ def main() -> int:
                      "frac": round(achieved / hbm_gbs, 4)},
         "points": points,
     }
+    ops.require_kernel_status_ok("bench")   # a kernel whose bounded wait ran out would make every number above void
     print(json.dumps(out))
     return 0
 

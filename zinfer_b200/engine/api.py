@@ -14,6 +14,7 @@ from typing import Optional, Sequence
 
 import torch
 
+from .. import ops
 from ..sampling import Sampler, SamplingParams
 from .batch import StepEntry
 from .runner import ModelRunner
@@ -154,8 +155,14 @@ class Engine:
             if fl.done is not None:
                 fl.done.synchronize()
             sampled = fl.tokens_host.tolist()
+        # a kernel whose bounded wait ran out must not pass unnoticed: checked when a request ends
+        # and every 256 steps (the read of the status word waits for the device)
+        self._resolved_steps = getattr(self, "_resolved_steps", 0) + 1
+        finished = self.scheduler.resolve(fl.plan, sampled)
+        if (finished or self._resolved_steps % 256 == 0) and self.runner.device.type == "cuda":
+            ops.require_kernel_status_ok("Engine.step")
         out = []
-        for r in self.scheduler.resolve(fl.plan, sampled):
+        for r in finished:
             self.sampler.end_request(r.request_id)
             self._live.pop(r.request_id, None)
             out.append(GenerationResult(r.request_id, r.prompt, list(r.output), r.finish_reason, r.preemptions))

@@ -35,6 +35,7 @@ def main(argv=None) -> int:
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
+    from .. import ops
     from .batch import StepEntry
     from .runner import ModelRunner
 
@@ -59,6 +60,7 @@ def main(argv=None) -> int:
         for rid in rec.get("end", []):
             if runner.has_request(rid):
                 runner.end_request(rid)
+        ops.require_kernel_status_ok(f"step {step}")   # a kernel whose bounded wait ran out fails the replay
         sys.stdout.write(f"done {step}\n")
         sys.stdout.flush()
     return 0

@@ -45,6 +45,15 @@ def kernel_status() -> int:
     return int(lib().zi_gemm_tcgen05_status())   # one word for the products, the attention and the whole-layer kernel
 
 
+def require_kernel_status_ok(where: str) -> None:
+    """Raises if a bounded wait inside a tensor-core kernel ran out since the last check (its
+    results are then not to be trusted).  Synchronises; the engine calls it where it waits for
+    the device anyway, and every so many steps."""
+    code = kernel_status()
+    if code != 0:
+        raise KernelError(f"{where}: a wait inside a tensor-core kernel ran out (code {code}); its results are invalid")
+
+
 def library_file() -> str:
     return _build.library_path()
 
