@@ -1,6 +1,6 @@
 // Paged causal flash attention for prompt portions on the 5th-generation tensor cores
 // (head size 128, bfloat16): S = Q K^T and O += P V are tcgen05.mma products with S, P and O in
-// tensor memory; Q, K and V tiles come by TMA (128-byte swizzle, no multicast) straight from the
+// tensor memory; Q, K and V tiles come by TMA (128-byte swizzle, every CTA loads its own tiles) straight from the
 // activation buffer and the cache pages.  V is read as an MN-major operand (its rows are keys,
 // the contraction dimension), K and Q as K-major, P from tensor memory.  The kernel and its warp
 // roles are described at the kernel.  Every mbarrier wait is bounded; a timeout records a code

@@ -1,5 +1,5 @@
 // out[M,N] = x[M,K] * w[N,K]^T in bfloat16 on the 5th-generation tensor cores:
-// TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) fills a ring of shared
+// TMA (cp.async.bulk.tensor, 128-byte swizzle, every CTA loads its own tiles) fills a ring of shared
 // memory stages, one elected thread issues tcgen05.mma with the accumulator in
 // tensor memory, and four warps read it back with tcgen05.ld for the epilogue.
 //
