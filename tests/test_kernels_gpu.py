@@ -341,6 +341,7 @@ def _as_step(args, q_lens, ctx_lens):
     ([1, 1, 1, 1], [0, 63, 64, 700]),                  # decode only, lengths around a tile's edge
     ([300, 17], [0, 130]),                             # prompt portions only, one across several query tiles
     ([1, 37, 2, 1, 129, 1], [70, 0, 15, 0, 48, 255]),  # mixed
+    ([700, 3], [333, 60]),                             # a long portion behind a long context: many key tiles per query tile
 ])
 @pytest.mark.parametrize("prefill_kernel", ["mma", "tcgen05"])
 def test_tensor_core_attention(nq, nkv, d, page, window, q_lens, ctx_lens, prefill_kernel, monkeypatch):
