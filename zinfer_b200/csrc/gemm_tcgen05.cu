@@ -13,7 +13,7 @@
 // Split-K over gridDim.z writes 32-bit partial sums to a workspace; a second kernel
 // adds them in a fixed order.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner and MMA
+// Warp roles (192 threads): warp 0 = TMA producer (a few of its lanes issue side by side), warp 1 = TMEM owner and MMA
 // issuer, warps 2..5 = epilogue (warp w reads TMEM lanes 32*(w%4)..+31).
 // Every wait on an mbarrier is bounded; when it runs out the kernel records a code
 // in `status`, lets copies in flight land, frees its tensor memory and returns.
@@ -113,35 +113,49 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   };
 
   if (warp == 0) {
-    if (lane == 0 && (int)blockIdx.x < total_tiles) {
+    // Issuing a tensor copy holds its thread a few hundred nanoseconds while HBM is busy; copies
+    // issued by several lanes in ONE instruction go out side by side.  So the first tile's
+    // prefetch is one instruction over `pre` lanes (twice: weights before the wait for the kernel
+    // before this one, activations after it), and in the loop lane 0 issues the weight's tile and
+    // lane 1 the activations' in the same instruction.
+    if ((int)blockIdx.x < total_tiles) {
       int a_tile, b_tile, split, kb0, n_kb;
-      // The weight does not depend on the kernel before this one: the first tile's first
-      // weight blocks are requested while that kernel drains; activations only after it.
       decode(blockIdx.x, a_tile, b_tile, split, kb0, n_kb);
       const int pre = min(stages, n_kb);
-      for (int i = 0; i < pre; ++i) {
-        uint8_t* dst = smem + (size_t)i * stage_bytes;
-        mbar_expect_tx(&full[i], (uint32_t)stage_bytes);
-        if (g.a_is_weight) tma_load_2d(dst, &map_a, &full[i], (kb0 + i) * BLOCK_K, a_tile * TILE_A);
-        else tma_load_2d(dst + A_TILE_BYTES, &map_b, &full[i], (kb0 + i) * BLOCK_K, b_tile * BN);
+      // which: 1 = the weight's tile of k-block i into stage s, 0 = the activations'
+      auto issue = [&](int which, int s, int i) {
+        uint8_t* dst = smem + (size_t)s * stage_bytes;
+        const bool use_a = (which != 0) == (g.a_is_weight != 0);
+        tma_load_2d(use_a ? dst : dst + A_TILE_BYTES, use_a ? &map_a : &map_b, &full[s], (kb0 + i) * BLOCK_K,
+                    use_a ? a_tile * TILE_A : b_tile * BN);
+      };
+      if (lane < pre) {
+        mbar_expect_tx(&full[lane], (uint32_t)stage_bytes);
+        issue(1, lane, lane);   // weights do not depend on the kernel before this one
       }
       pdl_wait();
-      uint32_t it = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
-        decode(tile, a_tile, b_tile, split, kb0, n_kb);
-        for (int i = 0; i < n_kb; ++i, ++it) {
-          const int s = it % stages;
-          const uint32_t phase = (it / stages) & 1u;
-          uint8_t* dst = smem + (size_t)s * stage_bytes;
-          const bool preloaded = tile == (int)blockIdx.x && i < pre;
-          if (!preloaded) {
+      if (lane < pre) issue(0, lane, lane);
+      // Few tokens: lanes 0 and 1 walk the k-blocks together (both wait for the stage, lane 0 posts the
+      // byte count, then ONE instruction issues both tiles).  Many tokens: the tensor pipe sets the
+      // pace and one lane issuing both tiles in turn is as fast (and measured slightly faster).
+      const int n_issuers = g.a_is_weight ? 2 : 1;
+      if (lane < n_issuers) {
+        uint32_t it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
+          decode(tile, a_tile, b_tile, split, kb0, n_kb);
+          for (int i = 0; i < n_kb; ++i, ++it) {
+            if (tile == (int)blockIdx.x && i < pre) continue;   // requested above
+            const int s = it % stages;
+            const uint32_t phase = (it / stages) & 1u;
             if (!mbar_wait(&empty[s], phase ^ 1u)) { failed = true; atomicExch(status, 1); break; }
-            mbar_expect_tx(&full[s], (uint32_t)stage_bytes);
-            if (g.a_is_weight) tma_load_2d(dst, &map_a, &full[s], (kb0 + i) * BLOCK_K, a_tile * TILE_A);
-            else tma_load_2d(dst + A_TILE_BYTES, &map_b, &full[s], (kb0 + i) * BLOCK_K, b_tile * BN);
+            if (lane == 0) mbar_expect_tx(&full[s], (uint32_t)stage_bytes);
+            if (n_issuers == 2) {
+              issue(lane == 0 ? 1 : 0, s, i);
+            } else {
+              issue(1, s, i);
+              issue(0, s, i);
+            }
           }
-          if (g.a_is_weight) tma_load_2d(dst + A_TILE_BYTES, &map_b, &full[s], (kb0 + i) * BLOCK_K, b_tile * BN);
-          else tma_load_2d(dst, &map_a, &full[s], (kb0 + i) * BLOCK_K, a_tile * TILE_A);
         }
       }
     }
