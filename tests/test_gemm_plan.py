@@ -23,9 +23,9 @@ def plan():
 
 
 def test_few_tokens_put_the_weight_on_the_lanes_and_split_k(plan):
-    for M in (1, 8, 64):
+    for M in (1, 8, 64, 65, 128):
         p = plan(M, 6144, 4096)
-        assert p["swap"] == 1 and p["BN"] in (16, 32, 64) and p["BN"] >= M
+        assert p["swap"] == 1 and p["BN"] in (16, 32, 64, 128) and M <= p["BN"] < 2 * max(M, 16)
         assert p["splits"] == 4 and p["workspace"] == 4 * M * 6144 * 4      # 48 tiles x 4 = 192 CTAs in one wave
     assert plan(8, 4096, 4096)["splits"] == 8                               # 32 tiles x 8 = 256
     assert plan(8, 4096, 12288)["splits"] == 8
@@ -38,8 +38,9 @@ def test_many_tokens_are_left_whole_and_a_few_hundred_are_split_when_it_pays(pla
     for N, K in [(6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288)]:
         p = plan(2048, N, K)
         assert p["swap"] == 0 and p["BN"] == 256 and p["splits"] == 1
-    assert plan(128, 4096, 12288)["splits"] > 1      # 16 tiles on 148 SMs, 192 k-blocks each
-    assert plan(128, 6144, 4096)["splits"] > 1
+    assert plan(129, 4096, 12288)["swap"] == 0
+    assert plan(160, 4096, 12288)["splits"] > 1      # 64 tiles on 148 SMs, 192 k-blocks each
+    assert plan(160, 4096, 4096)["splits"] > 1
     assert plan(256, 6144, 4096)["splits"] == 1      # 48 tiles: the partial sums would cost what the split saves
     assert plan(512, 24576, 4096)["splits"] == 1
 
