@@ -242,6 +242,35 @@ def test_linear_swiglu_fused_epilogue(M, I, K):
     assert o.kernel_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 1000, 264), (1000, 4096, 512), (2048, 768, 4096),
+                                   (2100, 389 * 2, 160)])
+def test_linear_with_the_kernel_for_cta_pairs(M, N, K):
+    """The product on pairs of CTAs (tcgen05 cta_group::2: tiles of 256 tokens x 256 weight rows, each
+    CTA loading half of the weight rows), which is off unless asked for: plain and with the SwiGLU
+    epilogue, with ragged last tiles on every side, bfloat16 and float32 results."""
+    o = ops()
+    x = rnd(M, K, dtype=torch.bfloat16)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=1)
+    want = x.double() @ w.double().T
+    before = o.gemm_pair_kernel(True)
+    try:
+        got = o.linear(x, w)
+        got32 = o.linear(x, w, out_dtype=torch.float32)
+        if N % 128 == 0:
+            wg, wu = w[:N // 2].contiguous(), w[N // 2:].contiguous()
+            act = o.linear_swiglu(x, o.interleave_gate_up(wg, wu))
+    finally:
+        o.gemm_pair_kernel(before)
+    torch.testing.assert_close(got.double(), want, rtol=8e-3, atol=1e-3)
+    torch.testing.assert_close(got32.double(), want, rtol=1e-5, atol=1e-4)
+    single = o.linear(x, w, out_dtype=torch.float32)
+    torch.testing.assert_close(got32, single, rtol=1e-5, atol=1e-4)
+    if N % 128 == 0:
+        g, u = want[:, :N // 2].float(), want[:, N // 2:].float()
+        torch.testing.assert_close(act.float(), g / (1 + torch.exp(-g)) * u, rtol=1.6e-2, atol=2e-3 * K ** 0.5 * 0.05 + 1e-3)
+    assert o.kernel_status() == 0
+
+
 def _paged_case(dtype, nq, nkv, d, page, q_lens, ctx_lens, seed=0):
     """Random requests laid out in shuffled pages; returns the kernel's arguments."""
     o = ops()

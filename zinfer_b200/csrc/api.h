@@ -41,6 +41,7 @@ int zi_gemm_tcgen05(void* out, int out_dtype, const void* x, const void* w, int 
                     int ldo, float* workspace, long long workspace_bytes, int sm_count, int defer_reduce,
                     cudaStream_t stream);
 int zi_gemm_tcgen05_status();
+int zi_gemm_tcgen05_pair_enable(int on);
 
 int zi_paged_attention_tile_rows();
 int zi_paged_attention(void* out, int out_stride, const void* q, int q_stride, int dtype, const void* kcache,

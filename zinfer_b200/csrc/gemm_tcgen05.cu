@@ -53,6 +53,95 @@ struct GemmArgs {
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
+// One thread's row of an accumulator (TMEM lane `lane_base`, BN columns) to memory: row `a` of the A
+// side against B rows b_tile * BN ...  `a_ok` is false for rows past the end (the thread still
+// takes part in the warp-wide tensor-memory loads).
+template <typename TO, bool SWIGLU>
+__device__ __forceinline__ void drain_accumulator(const GemmArgs& g, TO* __restrict__ out, float* __restrict__ partial,
+                                                  int split, int a, bool a_ok, int b_tile, uint32_t lane_base) {
+  const int BN = g.BN;
+  if (SWIGLU) {
+    // Tokens on the lanes; of every 128 columns the first 64 are gate and the next 64 up.
+    for (int c0 = 0; c0 < BN; c0 += 128) {
+#pragma unroll
+      for (int h = 0; h < 64; h += 32) {
+        float gv[32], uv[32];
+        tmem_load32(lane_base + (uint32_t)(c0 + h), gv);
+        tmem_load32(lane_base + (uint32_t)(c0 + 64 + h), uv);
+        const int f0 = (b_tile * BN + c0) / 2 + h;                 // first output feature of this chunk
+        if (!a_ok) continue;
+        TO* o = out + (long long)a * g.act_ld + f0;
+        if (f0 + 32 <= g.b_rows / 2 && ((uintptr_t)o & 15) == 0 && sizeof(TO) == 2) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 w;
+            w.x = pack2(silu_mul(gv[j], uv[j]), silu_mul(gv[j + 1], uv[j + 1]));
+            w.y = pack2(silu_mul(gv[j + 2], uv[j + 2]), silu_mul(gv[j + 3], uv[j + 3]));
+            w.z = pack2(silu_mul(gv[j + 4], uv[j + 4]), silu_mul(gv[j + 5], uv[j + 5]));
+            w.w = pack2(silu_mul(gv[j + 6], uv[j + 6]), silu_mul(gv[j + 7], uv[j + 7]));
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(o) + j) = w;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (f0 + j < g.b_rows / 2) o[j] = from_f32<TO>(silu_mul(gv[j], uv[j]));
+        }
+      }
+    }
+  } else
+  for (int c0 = 0; c0 < BN; c0 += 32) {
+    float v[32];
+    if (BN - c0 >= 32) {
+      tmem_load32(lane_base + (uint32_t)c0, v);
+    } else {  // BN == 16
+      float v16[16];
+      tmem_load16(lane_base + (uint32_t)c0, v16);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = j < 16 ? v16[j] : 0.f;
+    }
+    const int ncol = min(32, BN - c0);
+    const int b0 = b_tile * BN + c0;
+    if (!a_ok) continue;
+    if (partial) {
+      float* p = partial + (size_t)split * g.a_rows * g.b_rows + (long long)a * g.pa + (long long)b0 * g.pb;
+      if (g.pb == 1 && b0 + ncol <= g.b_rows && ((uintptr_t)p & 15) == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          if (j < ncol) *reinterpret_cast<float4*>(p + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ncol && b0 + j < g.b_rows) p[(long long)j * g.pb] = v[j];
+      }
+    } else {
+      TO* o = out + (long long)a * g.sa + (long long)b0 * g.sb;
+      if (g.sb == 1 && b0 + ncol <= g.b_rows && ((uintptr_t)o & 15) == 0) {
+        if (sizeof(TO) == 2) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (j >= ncol) break;
+            uint4 w;
+            w.x = pack2(v[j], v[j + 1]);
+            w.y = pack2(v[j + 2], v[j + 3]);
+            w.z = pack2(v[j + 4], v[j + 5]);
+            w.w = pack2(v[j + 6], v[j + 7]);
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(o) + j) = w;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            if (j < ncol)
+              *reinterpret_cast<float4*>(reinterpret_cast<float*>(o) + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ncol && b0 + j < g.b_rows) o[(long long)j * g.sb] = from_f32<TO>(v[j]);
+      }
+    }
+  }
+}
+
 // A side: a_rows x K through map_a (box 64 x 128).  B side: b_rows x K through map_b
 // (box 64 x BN).  Persistent: a CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...
 // (A tile fastest, so neighbouring CTAs share the B tile in L2).  Two accumulators in
@@ -199,86 +288,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int a = a_tile * TILE_A + quarter * 32 + lane;
       const uint32_t lane_base = tmem_base + acc * (uint32_t)g.acc_cols + ((uint32_t)(quarter * 32) << 16);
       const bool a_ok = a < g.a_rows;
-      if (SWIGLU) {
-        // Tokens on the lanes; of every 128 columns the first 64 are gate and the next 64 up.
-        for (int c0 = 0; c0 < BN; c0 += 128) {
-#pragma unroll
-          for (int h = 0; h < 64; h += 32) {
-            float gv[32], uv[32];
-            tmem_load32(lane_base + (uint32_t)(c0 + h), gv);
-            tmem_load32(lane_base + (uint32_t)(c0 + 64 + h), uv);
-            const int f0 = (b_tile * BN + c0) / 2 + h;                 // first output feature of this chunk
-            if (!a_ok) continue;
-            TO* o = out + (long long)a * g.act_ld + f0;
-            if (f0 + 32 <= g.b_rows / 2 && ((uintptr_t)o & 15) == 0 && sizeof(TO) == 2) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 w;
-                w.x = pack2(silu_mul(gv[j], uv[j]), silu_mul(gv[j + 1], uv[j + 1]));
-                w.y = pack2(silu_mul(gv[j + 2], uv[j + 2]), silu_mul(gv[j + 3], uv[j + 3]));
-                w.z = pack2(silu_mul(gv[j + 4], uv[j + 4]), silu_mul(gv[j + 5], uv[j + 5]));
-                w.w = pack2(silu_mul(gv[j + 6], uv[j + 6]), silu_mul(gv[j + 7], uv[j + 7]));
-                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(o) + j) = w;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (f0 + j < g.b_rows / 2) o[j] = from_f32<TO>(silu_mul(gv[j], uv[j]));
-            }
-          }
-        }
-      } else
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        float v[32];
-        if (BN - c0 >= 32) {
-          tmem_load32(lane_base + (uint32_t)c0, v);
-        } else {  // BN == 16
-          float v16[16];
-          tmem_load16(lane_base + (uint32_t)c0, v16);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = j < 16 ? v16[j] : 0.f;
-        }
-        const int ncol = min(32, BN - c0);
-        const int b0 = b_tile * BN + c0;
-        if (!a_ok) continue;
-        if (partial) {
-          float* p = partial + (size_t)split * g.a_rows * g.b_rows + (long long)a * g.pa + (long long)b0 * g.pb;
-          if (g.pb == 1 && b0 + ncol <= g.b_rows && ((uintptr_t)p & 15) == 0) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              if (j < ncol) *reinterpret_cast<float4*>(p + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < ncol && b0 + j < g.b_rows) p[(long long)j * g.pb] = v[j];
-          }
-        } else {
-          TO* o = out + (long long)a * g.sa + (long long)b0 * g.sb;
-          if (g.sb == 1 && b0 + ncol <= g.b_rows && ((uintptr_t)o & 15) == 0) {
-            if (sizeof(TO) == 2) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                if (j >= ncol) break;
-                uint4 w;
-                w.x = pack2(v[j], v[j + 1]);
-                w.y = pack2(v[j + 2], v[j + 3]);
-                w.z = pack2(v[j + 4], v[j + 5]);
-                w.w = pack2(v[j + 6], v[j + 7]);
-                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(o) + j) = w;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                if (j < ncol)
-                  *reinterpret_cast<float4*>(reinterpret_cast<float*>(o) + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < ncol && b0 + j < g.b_rows) o[(long long)j * g.sb] = from_f32<TO>(v[j]);
-          }
-        }
-      }
+      drain_accumulator<TO, SWIGLU>(g, out, partial, split, a, a_ok, b_tile, lane_base);
       // this accumulator may be overwritten by the MMAs of the tile after next
       tcgen05_fence_before();
       __syncwarp();
@@ -294,6 +304,159 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (warp == 1) {
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+  }
+}
+
+// ------------------------------------------------------ the kernel for CTA pairs
+// Many tokens: two CTAs of a cluster (one per SM of a pair) share tiles of 256 tokens x 256 weight
+// rows.  Each CTA loads its own 128 tokens (A) and 128 of the 256 weight rows (B); the MMAs
+// (tcgen05 cta_group::2, M = 256, issued by the CTA of rank 0) read both halves of B and leave each
+// CTA's 128 x 256 block of the result in its own tensor memory.  A single CTA's 128 x 256 MMA reads
+// 12 KB of operands from shared memory for 131 cycles of tensor work, which is what bounds it; the
+// pair's reads 8 KB per SM for the same work.
+// Barriers: full[s] lives in rank 0 and counts the bytes of both CTAs' copies; empty[s] and
+// accum_full[i] are signalled in both CTAs by one multicast commit; accum_empty[i] lives in rank 0
+// and counts the epilogue warps of both CTAs.  Every wait is bounded as in the kernel above, and
+// every path ends in the cluster barrier before tensor memory is freed, so that neither CTA's
+// shared memory goes away while the other may still signal into it.
+constexpr int PAIR_TILE = 256;
+constexpr int PAIR_STAGE_BYTES = A_TILE_BYTES + (PAIR_TILE / 2) * BLOCK_K * 2;
+
+template <typename TO, bool SWIGLU>
+__global__ void __launch_bounds__(THREADS)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         TO* __restrict__ out, const GemmArgs g, int* __restrict__ status) {
+  pdl_launch_dependents();
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int stages = g.stages;
+  uint64_t* full = (uint64_t*)(smem + (size_t)stages * PAIR_STAGE_BYTES);
+  uint64_t* empty = full + stages;
+  uint64_t* accum_full = empty + stages;       // [2]
+  uint64_t* accum_empty = accum_full + 2;      // [2]
+  uint32_t* tmem_slot = (uint32_t*)(accum_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int total_tiles = g.a_tiles * g.b_tiles;
+  const uint32_t tmem_cols = 2u * (uint32_t)PAIR_TILE;
+  bool failed = false;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&accum_full[i], 1);
+      mbar_init(&accum_empty[i], 8);   // one arrival per epilogue warp of either CTA
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // the other CTA's barriers exist before anything signals them
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int n_kb = g.k_blocks;
+
+  if (warp == 0) {
+    if (pair < total_tiles) {
+      int b_tile = pair / g.a_tiles, a_tile = pair - b_tile * g.a_tiles;
+      const int pre = min(stages, n_kb);
+      // which: 1 = this CTA's half of the weight rows of k-block i into stage s, 0 = its tokens
+      auto issue = [&](int which, int s, int i) {
+        uint8_t* dst = smem + (size_t)s * PAIR_STAGE_BYTES;
+        const uint32_t bar = cluster_addr_of(&full[s], 0);
+        if (which)
+          tma_load_2d_pair(dst + A_TILE_BYTES, &map_b, bar, i * BLOCK_K, b_tile * PAIR_TILE + (int)rank * (PAIR_TILE / 2));
+        else
+          tma_load_2d_pair(dst, &map_a, bar, i * BLOCK_K, a_tile * PAIR_TILE + (int)rank * TILE_A);
+      };
+      if (lane < pre) {
+        if (rank == 0) mbar_expect_tx(&full[lane], 2u * (uint32_t)PAIR_STAGE_BYTES);
+        issue(1, lane, lane);   // weights do not depend on the kernel before this one
+      }
+      pdl_wait();
+      if (lane < pre) issue(0, lane, lane);
+      if (lane == 0) {
+        uint32_t it = 0;
+        for (int tile = pair; tile < total_tiles && !failed; tile += n_pairs) {
+          b_tile = tile / g.a_tiles;
+          a_tile = tile - b_tile * g.a_tiles;
+          for (int i = 0; i < n_kb; ++i, ++it) {
+            if (tile == pair && i < pre) continue;   // requested above
+            const int s = it % stages;
+            const uint32_t phase = (it / stages) & 1u;
+            if (!mbar_wait(&empty[s], phase ^ 1u)) { failed = true; atomicExch(status, 5); break; }
+            if (rank == 0) mbar_expect_tx(&full[s], 2u * (uint32_t)PAIR_STAGE_BYTES);
+            issue(1, s, i);
+            issue(0, s, i);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = instr_desc_bf16(PAIR_TILE, PAIR_TILE);
+      uint32_t it = 0, lt = 0;
+      for (int tile = pair; tile < total_tiles && !failed; tile += n_pairs, ++lt) {
+        const uint32_t acc = lt & 1u, acc_phase = (lt >> 1) & 1u;
+        if (!mbar_wait(&accum_empty[acc], acc_phase ^ 1u)) { failed = true; atomicExch(status, 8); break; }
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * (uint32_t)PAIR_TILE;
+        for (int i = 0; i < n_kb; ++i, ++it) {
+          const int s = it % stages;
+          const uint32_t phase = (it / stages) & 1u;
+          if (!mbar_wait(&full[s], phase)) { failed = true; atomicExch(status, 6); break; }
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(smem + (size_t)s * PAIR_STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_TILE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+            tcgen05_mma_bf16_pair(d_tmem, smem_desc_sw128(a_addr + k * UMMA_K * 2),
+                                  smem_desc_sw128(b_addr + k * UMMA_K * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+          }
+          tcgen05_commit_pair(&empty[s], 3);   // frees the stage in both CTAs when these MMAs have read it
+        }
+        if (!failed) tcgen05_commit_pair(&accum_full[acc], 3);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;  // the TMEM lanes this warp may read
+    uint32_t lt = 0;
+    for (int tile = pair; tile < total_tiles && !failed; tile += n_pairs, ++lt) {
+      const int b_tile = tile / g.a_tiles, a_tile = tile - b_tile * g.a_tiles;
+      const uint32_t acc = lt & 1u, acc_phase = (lt >> 1) & 1u;
+      if (!mbar_wait(&accum_full[acc], acc_phase)) { failed = true; atomicExch(status, 7); break; }
+      tcgen05_fence_after();
+      const int a = a_tile * PAIR_TILE + (int)rank * TILE_A + quarter * 32 + lane;
+      const uint32_t lane_base = tmem_base + acc * (uint32_t)PAIR_TILE + ((uint32_t)(quarter * 32) << 16);
+      drain_accumulator<TO, SWIGLU>(g, out, nullptr, 0, a, a < g.a_rows, b_tile, lane_base);
+      // this accumulator may be overwritten by the MMAs of the tile after next
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(cluster_addr_of(&accum_empty[acc], 0));
+    }
+  }
+  if (failed) {
+    // let copies that may still be in flight land before shared memory is given up
+    for (int i = 0; i < 64; ++i) __nanosleep(10000);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
 }
 
@@ -464,6 +627,84 @@ extern "C" long long zi_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int
 }
 
 namespace {
+// Whether the product goes to the kernel for CTA pairs: switched on (zi_gemm_tcgen05_pair_enable, or
+// ZINFER_B200_GEMM_PAIR=1 in the environment), tokens on the lanes, 256-row tiles on both sides, no
+// K split, and few enough padding rows (300 tokens would fill 512 rows of pair tiles but 384 of
+// single tiles).  Off by default: in a prefill step both kernels run at the pace the power limit
+// allows (1.2-1.3 PFLOP/s), so the pair's lighter shared-memory traffic buys nothing there.
+int g_pair_enabled = -1;   // -1: ask the environment
+bool use_pair_kernel(const int* plan, int M) {
+  if (g_pair_enabled < 0) {
+    const char* e = getenv("ZINFER_B200_GEMM_PAIR");
+    g_pair_enabled = (e && e[0] == '1') ? 1 : 0;
+  }
+  if (!g_pair_enabled || plan[0] || plan[1] != PAIR_TILE || plan[2] != 1) return false;
+  const int pair_rows = (M + PAIR_TILE - 1) / PAIR_TILE * PAIR_TILE, single_rows = (M + TILE_A - 1) / TILE_A * TILE_A;
+  return pair_rows == single_rows || M >= 1024;
+}
+// Rows of the B side's copy box.
+int b_box_rows(const int* plan, int M) { return use_pair_kernel(plan, M) ? PAIR_TILE / 2 : plan[1]; }
+
+// Launch of the pair kernel: clusters of two CTAs, as many as are resident at once (74 on 148 SMs).
+// Returns -3 when no cluster fits (the caller then has no maps for the single kernel: an error).
+template <typename TO>
+int launch_pair(void* out, const CUtensorMap& map_a, const CUtensorMap& map_b, GemmArgs g, int M, int N, int K,
+                int* status, int swiglu, const char* what, cudaStream_t stream) {
+  g.a_tiles = (M + PAIR_TILE - 1) / PAIR_TILE;
+  g.b_tiles = (N + PAIR_TILE - 1) / PAIR_TILE;
+  g.BN = PAIR_TILE;
+  g.acc_cols = PAIR_TILE;
+  g.splits = 1;
+  g.k_blocks_per_split = g.k_blocks;
+  g.stages = 6;
+  if (g.stages > g.k_blocks) g.stages = g.k_blocks < 2 ? 2 : g.k_blocks;
+  const size_t smem = 1024 + (size_t)g.stages * PAIR_STAGE_BYTES + (2 * g.stages + 4) * sizeof(uint64_t) + 16;
+  auto kern = swiglu ? gemm_tcgen05_pair_kernel<TO, true> : gemm_tcgen05_pair_kernel<TO, false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return zi_refuse("%s: cannot get %zu bytes of shared memory", what, smem);
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  // clusters resident at once: asked once per device, kernel and number of stages (no allocation here:
+  // this path also serves callers that must not allocate)
+  static std::mutex mu;
+  static int resident[64][2][2][8];   // 0 = not asked yet, else the answer + 1
+  int clusters = 0, dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return zi_refuse("%s: no current device", what);
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    int& slot = resident[dev][swiglu ? 1 : 0][sizeof(TO) == 2 ? 1 : 0][g.stages];
+    if (slot == 0) {
+      cfg.gridDim = dim3(2 * 148);
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+      }
+      slot = n + 1;
+    }
+    clusters = slot - 1;
+  }
+  if (clusters <= 0) return zi_refuse("%s: no cluster of two CTAs fits on this GPU", what);
+  const int total_tiles = g.a_tiles * g.b_tiles;
+  if (clusters > total_tiles) clusters = total_tiles;
+  cfg.gridDim = dim3(2 * clusters);
+  cfg.numAttrs = g_zi_pdl_enabled ? 2 : 1;
+  e = cudaLaunchKernelEx(&cfg, kern, map_a, map_b, (TO*)out, g, status);
+  if (e != cudaSuccess) return zi_refuse("%s: launch failed: %s", what, cudaGetErrorString(e));
+  return zi_check_launch(what);
+}
+
 // Launches the product (and, unless deferred, the split-K reduction) with the given
 // tensor maps, partial-sum buffer and status word.  Both entry points end here.
 int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtensorMap& map_b, int M, int N, int K,
@@ -494,6 +735,9 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
   const int total_tiles = g.a_tiles * g.b_tiles * g.splits;
   float* partial = g.splits > 1 ? partial_buf : nullptr;
 
+  if (use_pair_kernel(plan, M)) {
+    ZI_DISPATCH_DTYPE(out_dtype, TO, { return launch_pair<TO>(out, map_a, map_b, g, M, N, K, status, swiglu, what, stream); });
+  }
   ZI_DISPATCH_DTYPE(out_dtype, TO, {
     auto kern = swiglu ? gemm_tcgen05_kernel<TO, true> : gemm_tcgen05_kernel<TO, false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -532,11 +776,11 @@ extern "C" int zi_gemm_tcgen05(void* out, int out_dtype, const void* x, const vo
   int plan[3];
   const long long need = zi_gemm_tcgen05_plan(M, N, K, sm_count, plan);
   if (need > workspace_bytes) return zi_refuse("gemm_tcgen05: split-K needs %lld workspace bytes, got %lld", need, workspace_bytes);
-  const int swap = plan[0], BN = plan[1];
+  const int swap = plan[0];
   const int a_rows = swap ? N : M, b_rows = swap ? M : N;
   CUtensorMap map_a, map_b;
   if (!make_map(&map_a, swap ? w : x, a_rows, K, swap ? ldw : ldx, TILE_A) ||
-      !make_map(&map_b, swap ? x : w, b_rows, K, swap ? ldx : ldw, BN))
+      !make_map(&map_b, swap ? x : w, b_rows, K, swap ? ldx : ldw, b_box_rows(plan, M)))
     return zi_refuse("gemm_tcgen05: cuTensorMapEncodeTiled failed");
   int* status = status_word();
   if (!status) return zi_refuse("gemm_tcgen05: cannot allocate the status word");
@@ -563,16 +807,23 @@ extern "C" int zi_gemm_tcgen05_swiglu(void* out, int out_dtype, const void* x, c
   // while this product's CTAs still hold the shared memory.  (Measured: fused is 6 us per layer slower.)
   if (swap) return -2;
   if (plan[1] < 128) return -2;
-  const int BN = plan[1];
   const int a_rows = swap ? N2 : M, b_rows = swap ? M : N2;
   CUtensorMap map_a, map_b;
   if (!make_map(&map_a, swap ? w : x, a_rows, K, swap ? ldw : ldx, TILE_A) ||
-      !make_map(&map_b, swap ? x : w, b_rows, K, swap ? ldx : ldw, BN))
+      !make_map(&map_b, swap ? x : w, b_rows, K, swap ? ldx : ldw, b_box_rows(plan, M)))
     return zi_refuse("gemm_swiglu: cuTensorMapEncodeTiled failed");
   int* status = status_word();
   if (!status) return zi_refuse("gemm_swiglu: cannot allocate the status word");
   return launch_gemm(out, out_dtype, map_a, map_b, M, N2, K, ldo, plan, nullptr, status, sm_count, 0, "gemm_swiglu",
                      stream, 1);
+}
+
+// Switches the kernel for CTA pairs on (1) or off (0) for products of 256 tokens and more; returns
+// the setting before.
+extern "C" int zi_gemm_tcgen05_pair_enable(int on) {
+  const int before = g_pair_enabled > 0 ? 1 : 0;
+  g_pair_enabled = on ? 1 : 0;
+  return before;
 }
 
 // Reads and clears the status word of the tensor-core kernels (synchronises the
@@ -658,12 +909,12 @@ extern "C" int zi_gemm_tcgen05_static_scratch(void* out, int out_dtype, const vo
   int dev = -1;
   if (!static_scratch_for_current_device(&ss, &dev))
     return zi_refuse("gemm_static_scratch: cudaGetSymbolAddress of the built-in scratch failed on the current device");
-  const int swap = plan[0], BN = plan[1];
+  const int swap = plan[0];
   const int a_rows = swap ? N : M, b_rows = swap ? M : N;
   const int lda = swap ? ldw : ldx, ldb = swap ? ldx : ldw;
   CUtensorMap map_a, map_b;
   if (!encode_map_direct(&map_a, swap ? w : x, a_rows, K, lda, TILE_A) ||
-      !encode_map_direct(&map_b, swap ? x : w, b_rows, K, ldb, BN))
+      !encode_map_direct(&map_b, swap ? x : w, b_rows, K, ldb, b_box_rows(plan, M)))
     return zi_refuse("gemm_static_scratch: cuTensorMapEncodeTiled failed");
   int* status = wait_status ? wait_status : ss.status;
   // the status word must start at zero; the partial sums need no clearing, every

@@ -54,6 +54,15 @@ def require_kernel_status_ok(where: str) -> None:
         raise KernelError(f"{where}: a wait inside a tensor-core kernel ran out (code {code}); its results are invalid")
 
 
+def gemm_pair_kernel(on: bool) -> bool:
+    """Switches the matrix product's kernel for CTA pairs (tcgen05 ``cta_group::2``: two SMs on one
+    tile of 256 tokens x 256 weight rows, each loading half of the weight rows) on or off for
+    products of 256 tokens and more; returns the setting before.  Off unless
+    ``ZINFER_B200_GEMM_PAIR=1``: measured equal to the single-CTA kernel inside a prefill step,
+    where both run at the pace the power limit allows."""
+    return bool(lib().zi_gemm_tcgen05_pair_enable(1 if on else 0))
+
+
 def library_file() -> str:
     return _build.library_path()
 
