@@ -1,7 +1,8 @@
 """Generality of the parts, shown with toy parts that exist only in this test: a mixer
 with a fixed-size state of its own, a model whose layers differ (window attention, the
 stateful mixer, full attention), a schedule that names a layer twice and lets a run
-read the cache another run wrote.  Everything is registered, built and stepped through
+read the cache another run wrote; and a second toy model with a routed feed-forward and a
+position encoding of another formula.  Everything is registered, built and stepped through
 the framework's public interfaces, with no change to its files, and compared with a
 plain whole-sequence computation written here."""
 from dataclasses import asdict, dataclass
@@ -215,4 +216,215 @@ def test_toy_hybrid_model_is_built_and_stepped(toy_registered, dtype):
     table = runner.manager.block_table("w", windowed)
     assert table[:7] == [-1] * 7 and all(p >= 0 for p in table[8:])
     runner.end_request("w")
+    runner.manager.check()
+
+
+# ---------------------------------------------- a routed feed-forward and another position encoding
+def _make_routed_ffn():
+    from zinfer_b200.parts import FeedForward, TensorSpec
+
+    class RoutedFFN(FeedForward):
+        """Top-2 of E experts per token: router logits and the softmax over the two chosen in 32-bit,
+        each expert down(relu(up x)^2).  Written densely (every expert on every token, times a gate
+        that is zero for the others), which is fine for a toy and needs no host-side loop."""
+
+        def __init__(self, params, ctx):
+            super().__init__(params, ctx)
+            self.hidden, self.inter, self.experts = (int(params[k]) for k in ("hidden_size", "intermediate_size", "experts"))
+
+        def tensor_specs(self):
+            return {"router.weight": TensorSpec((self.experts, self.hidden)),
+                    "experts.up": TensorSpec((self.experts, self.inter, self.hidden)),
+                    "experts.down": TensorSpec((self.experts, self.hidden, self.inter))}
+
+        def bind(self, tensors):
+            self.router = tensors["router.weight"].float() * 40.0     # spread the logits: clear choices
+            self.up, self.down = tensors["experts.up"].float(), tensors["experts.down"].float()
+
+        def forward(self, x):
+            xf = x.float()
+            logits = xf @ self.router.T
+            top, idx = torch.topk(logits, 2, dim=-1)
+            gate = torch.zeros_like(logits).scatter_(1, idx, torch.softmax(top, dim=-1))
+            mid = torch.relu(torch.einsum("th,eih->tei", xf, self.up)) ** 2
+            return torch.einsum("tei,ehi,te->th", mid, self.down, gate).to(x.dtype)
+
+    return RoutedFFN
+
+
+def _make_scaled_rotary():
+    from zinfer_b200.parts import PositionEncoding
+
+    class ScaledRotary(PositionEncoding):
+        """Rotary angles of position / factor with a phase per frequency: another position encoding
+        that the attention's kernels take, because all they ask for is ``tables()``."""
+
+        def __init__(self, params, ctx):
+            super().__init__(params, ctx)
+            self.d, self.theta, self.factor = int(params["head_dim"]), float(params["theta"]), float(params["factor"])
+            self.n_positions = min(int(params["max_positions"]), ctx.max_positions)
+            self._tables = None
+
+        def tables(self):
+            if self._tables is None:
+                ang = scaled_rotary_angles(self.n_positions, self.d, self.theta, self.factor)
+                self._tables = (torch.cos(ang).float().to(self.ctx.device), torch.sin(ang).float().to(self.ctx.device))
+            return self._tables
+
+    return ScaledRotary
+
+
+def scaled_rotary_angles(n, d, theta, factor):
+    i = torch.arange(d // 2, dtype=F64)
+    inv = theta ** (-2.0 * i / d)
+    pos = torch.arange(n, dtype=F64) / factor
+    return pos[:, None] * inv[None, :] + 0.1 * i[None, :]
+
+
+@dataclass(frozen=True)
+class RoutedConfig:
+    vocab_size: int = 173
+    hidden_size: int = 96
+    intermediate_size: int = 48
+    dense_intermediate_size: int = 144
+    experts: int = 5
+    num_heads: int = 4
+    num_kv_heads: int = 2
+    head_dim: int = 48
+    eps: float = 1e-5
+    theta: float = 700.0
+    factor: float = 2.5
+    max_positions: int = 256
+    model_type: str = "toy_routed"
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(**{k: v for k, v in d.items() if k in cls.__dataclass_fields__})
+
+    def to_dict(self):
+        return {**asdict(self), "architectures": ["ToyRoutedForCausalLM"]}
+
+
+def routed_model_spec(cfg: RoutedConfig):
+    from zinfer_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+
+    H = cfg.hidden_size
+    norm = PartSpec("rmsnorm", {"size": H, "eps": cfg.eps})
+    positions = [PartSpec("toy_scaled_rotary", {"head_dim": cfg.head_dim, "theta": cfg.theta, "factor": cfg.factor,
+                                                "max_positions": cfg.max_positions}),
+                 None,
+                 PartSpec("rope", {"head_dim": cfg.head_dim, "theta": cfg.theta, "max_positions": cfg.max_positions})]
+    routed = PartSpec("toy_routed_ffn", {"hidden_size": H, "intermediate_size": cfg.intermediate_size, "experts": cfg.experts})
+    dense = PartSpec("swiglu_mlp", {"hidden_size": H, "intermediate_size": cfg.dense_intermediate_size})
+
+    def block(position, ffn):
+        mixer = PartSpec("gqa_attention", {"hidden_size": H, "num_heads": cfg.num_heads, "num_kv_heads": cfg.num_kv_heads,
+                                           "head_dim": cfg.head_dim, "qk_norm_eps": cfg.eps, "window": None,
+                                           "position": position})
+        return PartSpec("prenorm_block", {"mixer": mixer, "mixer_norm": norm, "feed_forward": ffn, "ffn_norm": norm})
+
+    layers = tuple(LayerSpec(block(p, f), prefix=f"layers.{i}.") for i, (p, f) in enumerate(zip(positions, (routed, dense, routed))))
+    return ModelSpec(
+        architecture="ToyRoutedForCausalLM", vocab_size=cfg.vocab_size, hidden_size=H, max_positions=cfg.max_positions,
+        embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab_size, "hidden_size": H, "name": "embed"}),
+        layers=layers, schedule=tuple(ScheduleEntry(i) for i in range(3)),
+        final_norm=PartSpec("rmsnorm", {"size": H, "eps": cfg.eps, "name": "norm"}),
+        head=PartSpec("lm_head", {"vocab_size": cfg.vocab_size, "hidden_size": H, "name": "head", "tied_to": None}))
+
+
+def plain_routed_forward(cfg: RoutedConfig, w, tokens):
+    """Logits [S, V] and, per position, the smallest gap between the second and the third router
+    logit in any layer (how safely its experts were chosen)."""
+    S = len(tokens)
+    ang = scaled_rotary_angles(S, cfg.head_dim, cfg.theta, cfg.factor)
+    tables = [(torch.cos(ang), torch.sin(ang)), None, P.rope_tables(S, cfg.head_dim, cfg.theta)]
+    h = w["embed.weight"][torch.as_tensor(tokens)]
+    margin = torch.full((S,), float("inf"), dtype=F64)
+    for i in range(3):
+        p = f"layers.{i}."
+        x = P.rmsnorm(h, w[p + "mixer_norm.weight"], cfg.eps)
+        q = P.rmsnorm((x @ w[p + "mixer.q_proj.weight"].T).reshape(S, cfg.num_heads, cfg.head_dim), w[p + "mixer.q_norm.weight"], cfg.eps)
+        k = P.rmsnorm((x @ w[p + "mixer.k_proj.weight"].T).reshape(S, cfg.num_kv_heads, cfg.head_dim), w[p + "mixer.k_norm.weight"], cfg.eps)
+        v = (x @ w[p + "mixer.v_proj.weight"].T).reshape(S, cfg.num_kv_heads, cfg.head_dim)
+        if tables[i] is not None:
+            q, k = P.apply_rope(q, *tables[i]), P.apply_rope(k, *tables[i])
+        h = h + P.attention(q, k, v).reshape(S, -1) @ w[p + "mixer.o_proj.weight"].T
+        x = P.rmsnorm(h, w[p + "ffn_norm.weight"], cfg.eps)
+        if i == 1:
+            f = P.swiglu(x @ w[p + "feed_forward.gate_proj.weight"].T, x @ w[p + "feed_forward.up_proj.weight"].T) \
+                @ w[p + "feed_forward.down_proj.weight"].T
+        else:
+            logits = x @ (w[p + "feed_forward.router.weight"] * 40.0).T
+            top, idx = torch.topk(logits, 3, dim=-1)
+            margin = torch.minimum(margin, top[:, 1] - top[:, 2])
+            share = torch.softmax(top[:, :2], dim=-1)
+            f = torch.zeros_like(h)
+            for t in range(S):
+                for j in range(2):
+                    e = int(idx[t, j])
+                    mid = torch.relu(w[p + "feed_forward.experts.up"][e] @ x[t]) ** 2
+                    f[t] += share[t, j] * (w[p + "feed_forward.experts.down"][e] @ mid)
+        h = h + f
+    return (P.rmsnorm(h, w["norm.weight"], cfg.eps) @ w["head.weight"].T).numpy(), margin.numpy()
+
+
+@pytest.fixture
+def routed_registered():
+    from zinfer_b200.config import Family, register_family, unregister_family
+    from zinfer_b200.parts import register_part, unregister_part
+
+    register_part("toy_routed_ffn", _make_routed_ffn())
+    register_part("toy_scaled_rotary", _make_scaled_rotary())
+    register_family(Family("ToyRoutedForCausalLM", "toy_routed", RoutedConfig, routed_model_spec))
+    yield
+    unregister_family("ToyRoutedForCausalLM")
+    unregister_part("toy_scaled_rotary")
+    unregister_part("toy_routed_ffn")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_toy_routed_model_with_another_position_encoding(routed_registered, dtype):
+    """A feed-forward with routing and a position encoding of another formula, both defined here,
+    beside layers without positions and with the dense feed-forward.  A token whose second and third
+    router logits lie closer than bfloat16 can tell apart might choose other experts than the plain
+    computation does, which would be no fault; so the requests are made token by token from random
+    candidates whose choice of experts is clear (a gap of 0.5 between logits that spread over 8)."""
+    import random
+
+    from zinfer_b200.config import family_for
+    from zinfer_b200.engine import DecoderModel, ModelRunner
+    from zinfer_b200.weights import random_tensors
+
+    cfg = RoutedConfig()
+    fam = family_for(cfg.to_dict())
+    model = DecoderModel(fam.model_spec(cfg), dtype, DEV)
+    tensors = random_tensors(model.tensor_specs(), 123, dtype, DEV)
+    model.bind(tensors)
+    runner = ModelRunner(model, page_size=8, max_tokens=320, max_requests=4)
+    assert runner.graphs is not None          # attention everywhere: decode steps are replayed from graphs
+
+    w = {k: v.detach().cpu().to(F64) for k, v in tensors.items()}
+    rng = random.Random(11)
+    reqs = {}
+    for r, n in enumerate((37, 9, 58, 26)):
+        toks = []
+        for _ in range(n):
+            for _ in range(100):
+                cand = rng.randrange(cfg.vocab_size)
+                if plain_routed_forward(cfg, w, toks + [cand])[1][-1] >= 0.5:
+                    toks.append(cand)
+                    break
+            else:
+                raise AssertionError("no candidate token with a clear choice of experts")
+        reqs[f"r{r}"] = toks
+    plain = {}
+    for rid, toks in reqs.items():
+        plain[rid], margin = plain_routed_forward(cfg, w, toks)
+        assert margin.min() >= 0.5
+    tol = dict(rtol=5e-5, atol=1e-6) if dtype == torch.float32 else dict(rtol=3e-2, atol=1e-3)
+    for mode, trace in (("whole", ru.trace_whole(reqs)), ("tail", ru.trace_tail_decode(reqs, 20)),
+                        ("portions", ru.trace_portions(reqs, 5)), ("mixed", ru.trace_mixed(reqs, 11, max_live=3))):
+        got = ru.run_in_process(runner, trace)
+        ru.assert_close(got, plain, what=f"routed/{mode}", argmax_frac=0.0, **tol)
+        assert not runner.manager.requests
     runner.manager.check()
