@@ -1,15 +1,19 @@
 // Sampling from 32-bit logits on the device: greedy (first maximum wins) and the
 // reference's chain of penalties, top-k, temperature, min-p, top-p and one draw
-// (src/sampling/sampler.zig:18-91), one block per row.
+// (src/sampling/sampler.zig:18-91), one thread-block cluster per row.
 //
 // The reference sorts candidates by descending logit and cuts prefixes of that order.
 // Here every cut is a threshold in the order (adjusted logit descending, token id
 // ascending), found by radix selection four bits at a time with the bins in registers
 // (no atomics, so sums do not depend on timing and a draw is reproducible bit for bit).
+#include <cooperative_groups.h>
+
 #include <type_traits>
 
 #include "api.h"
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace {
 constexpr int THREADS = 1024;
@@ -30,20 +34,40 @@ struct RowView {
   const int* counts;  // may be null
   int V;
   float rep, pres, freq;
-  __device__ __forceinline__ float adjusted(int v) const {
-    return adjusted_logit(logits[v], counts ? counts[v] : 0, rep, pres, freq);
-  }
 };
 
+// Calls f(v, adjusted logit of v) for the tokens first, first + stride, ... in rising order.  The
+// loads of four tokens go out together.
+constexpr int VISIT_UNROLL = 4;
+template <typename F>
+__device__ __forceinline__ void for_each_token(const RowView& row, int first, int stride, F&& f) {
+  for (int v0 = first; v0 < row.V; v0 += VISIT_UNROLL * stride) {
+    float lg[VISIT_UNROLL];
+    int cn[VISIT_UNROLL];
+#pragma unroll
+    for (int j = 0; j < VISIT_UNROLL; ++j) {
+      const int v = v0 + j * stride;
+      lg[j] = v < row.V ? row.logits[v] : 0.f;
+      cn[j] = (row.counts && v < row.V) ? row.counts[v] : 0;
+    }
+#pragma unroll
+    for (int j = 0; j < VISIT_UNROLL; ++j) {
+      const int v = v0 + j * stride;
+      if (v < row.V) f(v, adjusted_logit(lg[j], cn[j], row.rep, row.pres, row.freq));
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------- argmax
-__device__ void block_argmax(const RowView& row, float* best_val_out, int* best_idx_out, float* sval, int* sidx) {
+// First maximum among the tokens first, first + stride, ... of every thread of the block.
+__device__ void block_argmax(const RowView& row, int first, int stride, float* best_val_out, int* best_idx_out,
+                             float* sval, int* sidx) {
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int v = threadIdx.x; v < row.V; v += blockDim.x) {
-    float a = row.adjusted(v);
+  for_each_token(row, first, stride, [&](int v, float a) {
     if (a != a) a = -INFINITY;
     if (a > bv || (a == bv && v < bi)) { bv = a; bi = v; }
-  }
+  });
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
@@ -79,7 +103,7 @@ __global__ void __launch_bounds__(THREADS) argmax_kernel(int* __restrict__ out, 
   RowView row{logits + (size_t)blockIdx.x * ld, nullptr, V, 1.f, 0.f, 0.f};
   float bv;
   int bi;
-  block_argmax(row, &bv, &bi, sval, sidx);
+  block_argmax(row, threadIdx.x, blockDim.x, &bv, &bi, sval, sidx);
   if (threadIdx.x == 0) out[blockIdx.x] = bi;
 }
 
@@ -151,9 +175,16 @@ __global__ void argmax_final_kernel(int* __restrict__ out, const float* __restri
 // order-preserving bits of the adjusted logit.  A cut of that order is a pair (key threshold,
 // id limit): a token is inside if its key is above the threshold, or equal to it with an id
 // up to the limit.  Thresholds are found four bits at a time: every thread counts (or sums
-// weights of) its tokens into 16 bins held in registers, the block adds the bins up in a
-// fixed order, and all threads walk the 16 totals from the top.  No atomics: the sums do not
-// depend on timing, so a draw is reproducible bit for bit.
+// weights of) its tokens into 16 bins held in registers, the bins are added up in a fixed
+// order, and all threads walk the 16 totals from the top.  No atomics in any sum: the sums do
+// not depend on timing, so a draw is reproducible bit for bit.
+//
+// A row is always cut into SLICES slices of blockDim.x threads each: thread t of slice s owns the
+// tokens (s * blockDim.x + t) + j * SLICES * blockDim.x.  One pass of one block over 150,000 tokens
+// is bound by instruction issue on its SM (40 us), so the row's slices are spread over the CTAs of
+// a thread-block cluster (8, 4, 2 or 1 CTAs, by the number of rows), which exchange their
+// slices' totals through distributed shared memory.  Every sum is made per slice and the slices
+// are added in order, so the result does not depend on how many CTAs shared the row.
 __device__ __forceinline__ unsigned int order_key(float a) {
   unsigned int b = __float_as_uint(a);
   if (a != a) b = 0xff800000u;  // NaN sorts as -inf
@@ -168,55 +199,123 @@ __device__ __forceinline__ bool inside(const Cut& c, unsigned int key, int v) {
   return key > c.key || (key == c.key && v <= c.id_limit);
 }
 
-// Adds 16 per-thread bins over the block; every thread receives the 16 totals in `tot`.
-template <typename T>
-__device__ __forceinline__ void block_sum16(T (&bins)[16], T* smem /* [32][16] */, T (&tot)[16]) {
+constexpr int SLICES = 8;
+
+// The CTAs that share a row, and the shared memory they exchange totals through (the same
+// variables in every CTA, so that one address serves for all ranks).
+struct Team {
+  cg::cluster_group cl;
+  int rank, per;              // this CTA's rank; slices per CTA (SLICES / CTAs of the cluster)
+  unsigned int pass;          // its parity picks the exchange buffer
+  unsigned int* warp_buf;     // [SLICES][32][16] words: per-warp bins of each of this CTA's slices
+  unsigned int* slice_buf;    // [2][SLICES][16] words: per-slice totals, written by the slice's owner
+  unsigned int* tot_buf;      // [16] words: the row's totals, for all threads of this CTA
+  __device__ __forceinline__ int first(int slice) const { return slice * (int)blockDim.x + (int)threadIdx.x; }
+  __device__ __forceinline__ int stride() const { return SLICES * (int)blockDim.x; }
+};
+
+// One pass over the row: acc(v, adjusted logit, bins) adds token v into the calling thread's 16
+// bins; every thread of every CTA of the team receives the row's 16 totals in `tot`.  Within a
+// slice the bins are added over each warp by shuffles and over the warps in order.
+template <typename T, typename F>
+__device__ __forceinline__ void team_sum16(const RowView& row, Team& tm, T (&tot)[16], F&& acc) {
+  static_assert(sizeof(T) == 4, "bins are 32-bit");
+  T* slices = reinterpret_cast<T*>(tm.slice_buf) + (tm.pass & 1u) * SLICES * 16;
+  T* warps = reinterpret_cast<T*>(tm.warp_buf);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  for (int i = 0; i < tm.per; ++i) {
+    const int slice = tm.rank * tm.per + i;
+    T bins[16];
 #pragma unroll
-  for (int b = 0; b < 16; ++b) {
-    T v = bins[b];
+    for (int b = 0; b < 16; ++b) bins[b] = 0;
+    for_each_token(row, tm.first(slice), tm.stride(), [&](int v, float a) { acc(v, a, bins); });
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    bins[b] = v;
+    for (int b = 0; b < 16; ++b) {
+      T v = bins[b];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      bins[b] = v;
+    }
+    if (lane == 0)
+#pragma unroll
+      for (int b = 0; b < 16; ++b) warps[(i * 32 + warp) * 16 + b] = bins[b];
   }
   __syncthreads();
-  if (lane == 0)
-#pragma unroll
-    for (int b = 0; b < 16; ++b) smem[warp * 16 + b] = bins[b];
-  __syncthreads();
-#pragma unroll
-  for (int b = 0; b < 16; ++b) {
+  if ((int)threadIdx.x < tm.per * 16) {
+    const int i = threadIdx.x >> 4, b = threadIdx.x & 15;
     T t = 0;
-    for (int w = 0; w < nwarp; ++w) t += smem[w * 16 + b];   // fixed order
-    tot[b] = t;
+    for (int w = 0; w < nwarp; ++w) t += warps[(i * 32 + w) * 16 + b];   // fixed order
+    slices[(tm.rank * tm.per + i) * 16 + b] = t;
   }
+  tm.cl.sync();   // every slice's totals are written (and, one pass on, the other buffer is free again)
+  if (threadIdx.x < 16) {
+    T t = 0;
+    for (int s = 0; s < SLICES; ++s) {   // fixed order, whoever made the slice
+      const T* theirs = tm.cl.map_shared_rank(slices, s / tm.per);
+      t += theirs[s * 16 + threadIdx.x];
+    }
+    reinterpret_cast<T*>(tm.tot_buf)[threadIdx.x] = t;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int b = 0; b < 16; ++b) tot[b] = reinterpret_cast<T*>(tm.tot_buf)[b];
+  tm.pass += 1;
+}
+
+// First maximum of the row's adjusted logits, for every thread of the team.
+__device__ void team_argmax(const RowView& row, Team& tm, float* best_val, int* best_idx, float* sval, int* sidx) {
+  unsigned int* slices = tm.slice_buf + (tm.pass & 1u) * SLICES * 16;
+  for (int i = 0; i < tm.per; ++i) {
+    const int slice = tm.rank * tm.per + i;
+    float bv;
+    int bi;
+    block_argmax(row, tm.first(slice), tm.stride(), &bv, &bi, sval, sidx);
+    if (threadIdx.x == 0) {
+      slices[slice * 16] = __float_as_uint(bv);
+      slices[slice * 16 + 1] = (unsigned int)bi;
+    }
+    __syncthreads();   // sval/sidx are reused by the next slice
+  }
+  tm.cl.sync();
+  if (threadIdx.x == 0) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int s = 0; s < SLICES; ++s) {
+      const unsigned int* theirs = tm.cl.map_shared_rank(slices, s / tm.per);
+      const float v = __uint_as_float(theirs[s * 16]);
+      const int idx = (int)theirs[s * 16 + 1];
+      if (v > bv || (v == bv && idx < bi)) { bv = v; bi = idx; }
+    }
+    tm.tot_buf[0] = __float_as_uint(bv);
+    tm.tot_buf[1] = (unsigned int)bi;
+  }
+  __syncthreads();
+  *best_val = __uint_as_float(tm.tot_buf[0]);
+  *best_idx = (int)tm.tot_buf[1];
+  tm.pass += 1;
 }
 
 // The cut with `target` measure inside it (measure(above the cut) < target <= measure(with
-// the cut's own key)).  F(v, key&, weight&) -> bool says whether token v is a candidate and
-// gives its key and weight; WEIGHTED false counts candidates instead.
+// the cut's own key)).  F(v, adjusted logit, key&, weight&) -> bool says whether token v is a
+// candidate and gives its key and weight; WEIGHTED false counts candidates instead.
 template <bool WEIGHTED, typename F>
-__device__ Cut select_cut(const F& cand, int V, double target, void* smem) {
+__device__ Cut select_cut(const RowView& row, Team& tm, const F& cand, double target) {
   using T = typename std::conditional<WEIGHTED, float, int>::type;
   unsigned int prefix = 0, mask = 0;
   double remaining = target;
   double eq_total = 0.0;
   for (int pass = 0; pass < 8; ++pass) {
     const int shift = 28 - 4 * pass;
-    T bins[16];
-#pragma unroll
-    for (int b = 0; b < 16; ++b) bins[b] = 0;
-    for (int v = threadIdx.x; v < V; v += blockDim.x) {
+    T tot[16];
+    team_sum16<T>(row, tm, tot, [&](int v, float a, T (&bins)[16]) {
       unsigned int key;
       float w;
-      if (!cand(v, key, w) || (key & mask) != prefix) continue;
+      if (!cand(v, a, key, w) || (key & mask) != prefix) return;
       const unsigned int d = (key >> shift) & 15u;
       const T inc = WEIGHTED ? (T)w : (T)1;
 #pragma unroll
       for (int b = 0; b < 16; ++b) bins[b] += (d == (unsigned)b) ? inc : (T)0;
-    }
-    T tot[16];
-    block_sum16<T>(bins, reinterpret_cast<T*>(smem), tot);
+    });
     double cum = 0.0;
     int digit = 0;
 #pragma unroll
@@ -237,16 +336,12 @@ __device__ Cut select_cut(const F& cand, int V, double target, void* smem) {
   // how many of those tokens (all of equal weight): all of them unless fewer suffice
   int n_eq = 0, need = 0;
   {
-    int bins[16];
-#pragma unroll
-    for (int b = 0; b < 16; ++b) bins[b] = 0;
-    for (int v = threadIdx.x; v < V; v += blockDim.x) {
+    int tot[16];
+    team_sum16<int>(row, tm, tot, [&](int v, float a, int (&bins)[16]) {
       unsigned int key;
       float w;
-      if (cand(v, key, w) && key == prefix) bins[0] += 1;
-    }
-    int tot[16];
-    block_sum16<int>(bins, reinterpret_cast<int*>(smem), tot);
+      if (cand(v, a, key, w) && key == prefix) bins[0] += 1;
+    });
     n_eq = tot[0];
   }
   if (n_eq <= 1) return cut;
@@ -263,19 +358,15 @@ __device__ Cut select_cut(const F& cand, int V, double target, void* smem) {
   int left = need;
   for (int pass = 0; pass < 5; ++pass) {
     const int shift = 16 - 4 * pass;
-    int bins[16];
-#pragma unroll
-    for (int b = 0; b < 16; ++b) bins[b] = 0;
-    for (int v = threadIdx.x; v < V; v += blockDim.x) {
+    int tot[16];
+    team_sum16<int>(row, tm, tot, [&](int v, float a, int (&bins)[16]) {
       unsigned int key;
       float w;
-      if (!cand(v, key, w) || key != prefix || ((unsigned)v & imask) != iprefix) continue;
+      if (!cand(v, a, key, w) || key != prefix || ((unsigned)v & imask) != iprefix) return;
       const unsigned int d = ((unsigned)v >> shift) & 15u;
 #pragma unroll
       for (int b = 0; b < 16; ++b) bins[b] += (d == (unsigned)b) ? 1 : 0;
-    }
-    int tot[16];
-    block_sum16<int>(bins, reinterpret_cast<int*>(smem), tot);
+    });
     int cum = 0, digit = 15;
 #pragma unroll
     for (int b = 0; b < 16; ++b) {
@@ -296,24 +387,19 @@ __device__ Cut select_cut(const F& cand, int V, double target, void* smem) {
 // A key lower bound `lb` with at least k and (if the data allow) at most `limit` tokens at
 // or above it: the radix descent of select_cut, stopped as soon as the surviving bin is small
 // enough to be listed.  Returns the number of tokens with key >= lb.
-template <typename F>
-__device__ int coarse_lower_bound(const F& key_of, int V, int k, int limit, void* smem, unsigned int& lb) {
+__device__ int coarse_lower_bound(const RowView& row, Team& tm, int k, int limit, unsigned int& lb) {
   unsigned int prefix = 0, mask = 0;
-  int remaining = k, above = 0, n_ge = V;
+  int remaining = k, above = 0, n_ge = row.V;
   for (int pass = 0; pass < 8; ++pass) {
     const int shift = 28 - 4 * pass;
-    int bins[16];
-#pragma unroll
-    for (int b = 0; b < 16; ++b) bins[b] = 0;
-    for (int v = threadIdx.x; v < V; v += blockDim.x) {
-      const unsigned int key = key_of(v);
-      if ((key & mask) != prefix) continue;
+    int tot[16];
+    team_sum16<int>(row, tm, tot, [&](int, float a, int (&bins)[16]) {
+      const unsigned int key = order_key(a);
+      if ((key & mask) != prefix) return;
       const unsigned int d = (key >> shift) & 15u;
 #pragma unroll
       for (int b = 0; b < 16; ++b) bins[b] += (d == (unsigned)b) ? 1 : 0;
-    }
-    int tot[16];
-    block_sum16<int>(bins, reinterpret_cast<int*>(smem), tot);
+    });
     int cum = 0, digit = 0;
 #pragma unroll
     for (int b = 15; b >= 0; --b) {
@@ -355,14 +441,34 @@ struct SampleParams {
   const int* draw_index;          // how many tokens the request has drawn before
 };
 
+// One row per cluster of gridDim.x / rows CTAs (a power of two up to SLICES).
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int ld, int V, SampleParams p) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float sval[32];
   __shared__ int sidx[32];
-  __shared__ double sred[32 * 16 / 2 + 34];   // 32 x 16 four-byte bins, then room for the draw's scan
-  const int r = blockIdx.x;
+  __shared__ unsigned int warp_buf[SLICES * 32 * 16];
+  __shared__ unsigned int slice_buf[2 * SLICES * 16];
+  __shared__ unsigned int tot_buf[16];
+  __shared__ float cand_a[SMALL_K];      // the short list of candidates (used in the CTA of rank 0)
+  __shared__ int cand_v[SMALL_K];
+  __shared__ float sort_a[SMALL_K];
+  __shared__ int sort_v[SMALL_K];
+  __shared__ int n_cand, chosen;
+  __shared__ double scan_buf[SLICES * 32];   // warp totals of this CTA's slices, at [slice][warp]
+  __shared__ double all_tot[SLICES * 32];    // the same of every slice, and their running sums
+  __shared__ double prefix_s[SLICES * 32];
+
+  Team tm{cg::this_cluster(), 0, 0, 0u, warp_buf, slice_buf, tot_buf};
+  const int n_ctas = (int)tm.cl.num_blocks();
+  tm.rank = (int)tm.cl.block_rank();
+  tm.per = SLICES / n_ctas;
+  const int r = blockIdx.x / n_ctas;
+  if (threadIdx.x == 0) {
+    n_cand = 0;
+    chosen = -1;
+  }
   int* my_counts = (p.counts && p.count_rows && p.count_rows[r] >= 0) ? p.counts + (size_t)p.count_rows[r] * V : nullptr;
   RowView row{logits + (size_t)r * ld, my_counts, V, p.rep ? p.rep[r] : 1.f, p.pres ? p.pres[r] : 0.f,
               p.freq ? p.freq[r] : 0.f};
@@ -370,7 +476,7 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int ld, i
   const int top_k = p.top_k ? p.top_k[r] : 0;
   float amax;
   int token;
-  block_argmax(row, &amax, &token, sval, sidx);
+  team_argmax(row, tm, &amax, &token, sval, sidx);   // (its cluster barrier also publishes n_cand and chosen)
 
   if (temperature > 0.f && top_k != 1) {
     const float zmax = amax / temperature;
@@ -379,185 +485,197 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int ld, i
     // top-k with few candidates: a coarse key bound that leaves a short list (at least k long)
     unsigned int lb = 0;
     int n_listed = V;
-    if (top_k > 0 && top_k <= SMALL_K && top_k < V) {
-      auto key_of = [&](int v) { return order_key(row.adjusted(v)); };
-      n_listed = coarse_lower_bound(key_of, V, top_k, SMALL_K, sred, lb);
-    }
+    if (top_k > 0 && top_k <= SMALL_K && top_k < V) n_listed = coarse_lower_bound(row, tm, top_k, SMALL_K, lb);
     const unsigned long long bits = splitmix64(splitmix64(p.seeds[r]) ^ (unsigned long long)(unsigned int)p.draw_index[r]);
     const double u = (double)(bits >> 11) * (1.0 / 9007199254740992.0);
     if (top_k > 0 && top_k < V && n_listed <= SMALL_K) {
-      // Few candidates: gather them, order them as the reference does (logit descending, id
-      // ascending), and let one thread run the reference's loop over that short list.
-      __shared__ float cand_a[SMALL_K];
-      __shared__ int cand_v[SMALL_K];
-      __shared__ float sort_a[SMALL_K];
-      __shared__ int sort_v[SMALL_K];
-      __shared__ int n_cand;
-      if (threadIdx.x == 0) n_cand = 0;
-      __syncthreads();
-      for (int v = threadIdx.x; v < V; v += blockDim.x) {
-        const float a = row.adjusted(v);
-        if (order_key(a) >= lb) {
-          const int slot = atomicAdd(&n_cand, 1);   // the order of arrival does not matter: the list is sorted next
-          if (slot < SMALL_K) {
-            cand_a[slot] = a;
-            cand_v[slot] = v;
-          }
-        }
-      }
-      __syncthreads();
-      const int n_all = min(n_cand, SMALL_K);
-      const int n = min(n_all, top_k);                       // the list is sorted: its first k are the top k
-      for (int i = threadIdx.x; i < n_all; i += blockDim.x) {   // rank sort: the place of i is the number of candidates before it
-        const unsigned int ki = order_key(cand_a[i]);
-        const int vi = cand_v[i];
-        int rank = 0;
-        for (int j = 0; j < n_all; ++j) {
-          const unsigned int kj = order_key(cand_a[j]);
-          rank += (kj > ki || (kj == ki && cand_v[j] < vi)) ? 1 : 0;
-        }
-        sort_a[rank] = cand_a[i];
-        sort_v[rank] = vi;
-      }
-      __syncthreads();
-      if (threadIdx.x == 0 && n > 0) {
-        // src/sampling/sampler.zig:38-90 on the sorted candidates
-        double sum = 0.0;
-        for (int i = 0; i < n; ++i) {
-          const float e = expf(sort_a[i] / temperature - zmax);
-          cand_a[i] = e;
-          sum += (double)e;
-        }
-        int keep = n;
-        if (min_p > 0.f) {
-          const float thr = cand_a[0] * min_p;
-          keep = 0;
-          while (keep < n && cand_a[keep] >= thr) ++keep;
-          keep = max(keep, 1);
-          sum = 0.0;
-          for (int i = 0; i < keep; ++i) sum += (double)cand_a[i];
-        }
-        if (top_p < 1.f) {
-          double cum = 0.0;
-          int np = 0;
-          while (np < keep) {
-            cum += (double)cand_a[np] / sum;
-            ++np;
-            if (cum >= (double)top_p) break;
-          }
-          keep = min(max(np, 1), keep);
-        }
-        double kept = 0.0;
-        for (int i = 0; i < keep; ++i) kept += (double)cand_a[i];
-        int pick = sort_v[0];
-        if (kept > 0.0) {
-          double thr = u * kept;
-          pick = sort_v[keep - 1];
-          for (int i = 0; i < keep; ++i) {
-            thr -= (double)cand_a[i];
-            if (thr <= 0.0) {
-              pick = sort_v[i];
-              break;
+      // Few candidates: every CTA sends its own to the CTA of rank 0, which orders them as the
+      // reference does (logit descending, id ascending) and lets one thread run the reference's
+      // loop over that short list.
+      int* n0 = tm.cl.map_shared_rank(&n_cand, 0);
+      float* a0 = tm.cl.map_shared_rank(cand_a, 0);
+      int* v0 = tm.cl.map_shared_rank(cand_v, 0);
+      for (int i = 0; i < tm.per; ++i) {
+        const int slice = tm.rank * tm.per + i;
+        for_each_token(row, tm.first(slice), tm.stride(), [&](int v, float a) {
+          if (order_key(a) >= lb) {
+            const int slot = atomicAdd(n0, 1);   // the order of arrival does not matter: the list is sorted next
+            if (slot < SMALL_K) {
+              a0[slot] = a;
+              v0[slot] = v;
             }
           }
+        });
+      }
+      tm.cl.sync();
+      if (tm.rank == 0) {
+        const int n_all = min(n_cand, SMALL_K);
+        const int n = min(n_all, top_k);                       // the list is sorted: its first k are the top k
+        for (int i = threadIdx.x; i < n_all; i += blockDim.x) {   // rank sort: the place of i is the number of candidates before it
+          const unsigned int ki = order_key(cand_a[i]);
+          const int vi = cand_v[i];
+          int rank = 0;
+          for (int j = 0; j < n_all; ++j) {
+            const unsigned int kj = order_key(cand_a[j]);
+            rank += (kj > ki || (kj == ki && cand_v[j] < vi)) ? 1 : 0;
+          }
+          sort_a[rank] = cand_a[i];
+          sort_v[rank] = vi;
         }
-        cand_v[0] = pick;
+        __syncthreads();
+        if (threadIdx.x == 0 && n > 0) {
+          // src/sampling/sampler.zig:38-90 on the sorted candidates
+          double sum = 0.0;
+          for (int i = 0; i < n; ++i) {
+            const float e = expf(sort_a[i] / temperature - zmax);
+            cand_a[i] = e;
+            sum += (double)e;
+          }
+          int keep = n;
+          if (min_p > 0.f) {
+            const float thr = cand_a[0] * min_p;
+            keep = 0;
+            while (keep < n && cand_a[keep] >= thr) ++keep;
+            keep = max(keep, 1);
+            sum = 0.0;
+            for (int i = 0; i < keep; ++i) sum += (double)cand_a[i];
+          }
+          if (top_p < 1.f) {
+            double cum = 0.0;
+            int np = 0;
+            while (np < keep) {
+              cum += (double)cand_a[np] / sum;
+              ++np;
+              if (cum >= (double)top_p) break;
+            }
+            keep = min(max(np, 1), keep);
+          }
+          double kept = 0.0;
+          for (int i = 0; i < keep; ++i) kept += (double)cand_a[i];
+          int pick = sort_v[0];
+          if (kept > 0.0) {
+            double thr = u * kept;
+            pick = sort_v[keep - 1];
+            for (int i = 0; i < keep; ++i) {
+              thr -= (double)cand_a[i];
+              if (thr <= 0.0) {
+                pick = sort_v[i];
+                break;
+              }
+            }
+          }
+          cand_v[0] = pick;
+        }
+        __syncthreads();
+        if (n > 0) token = cand_v[0];
       }
-      __syncthreads();
-      if (n > 0) token = cand_v[0];
     } else {
-    // many candidates: the cut with exactly k of them inside, then thresholds over the whole row
-    Cut cut_k{0u, 0x7fffffff};
-    if (top_k > 0 && top_k < V) {
-      auto all = [&](int v, unsigned int& key, float& w) {
-        key = order_key(row.adjusted(v));
-        w = 1.f;
-        return true;
-      };
-      cut_k = select_cut<false>(all, V, (double)top_k, sred);
-    }
-    // candidates after top-k and min-p, with weight exp(z - zmax)
-    auto cand1 = [&](int v, unsigned int& key, float& w) {
-      const float a = row.adjusted(v);
-      key = order_key(a);
-      if (!inside(cut_k, key, v)) return false;
-      w = expf(a / temperature - zmax);
-      return !(min_p > 0.f) || w >= min_p || v == token;
-    };
-    // block sum of a candidate set's weights, in a fixed order
-    auto total_of = [&](auto& cand) -> double {
-      float bins[16];
-#pragma unroll
-      for (int b = 0; b < 16; ++b) bins[b] = 0.f;
-      for (int v = threadIdx.x; v < V; v += blockDim.x) {
-        unsigned int key;
-        float w;
-        if (cand(v, key, w)) bins[0] += w;
+      // many candidates: the cut with exactly k of them inside, then thresholds over the whole row
+      Cut cut_k{0u, 0x7fffffff};
+      if (top_k > 0 && top_k < V) {
+        auto all = [&](int, float a, unsigned int& key, float& w) {
+          key = order_key(a);
+          w = 1.f;
+          return true;
+        };
+        cut_k = select_cut<false>(row, tm, all, (double)top_k);
       }
-      float tot[16];
-      block_sum16<float>(bins, reinterpret_cast<float*>(sred), tot);
-      return (double)tot[0];
-    };
-    Cut cut_p{0u, 0x7fffffff};
-    if (top_p < 1.f) {
-      const double sum1 = total_of(cand1);
-      cut_p = select_cut<true>(cand1, V, fmax((double)top_p * sum1, 1e-30), sred);
-    }
-    auto cand2 = [&](int v, unsigned int& key, float& w) { return cand1(v, key, w) && inside(cut_p, key, v); };
-    // the draw: tokens in the order (thread, then its strided tokens); find where the running
-    // sum of weights passes u * total
-    float mine = 0.f;
-    for (int v = threadIdx.x; v < V; v += blockDim.x) {
-      unsigned int key;
-      float w;
-      if (cand2(v, key, w)) mine += w;
-    }
-    double* scan = sred;                      // [blockDim.x / 32] warp totals after the per-warp scan
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    float incl = mine;                        // inclusive scan within the warp
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const float t = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += t;
-    }
-    const float excl = __shfl_up_sync(0xffffffffu, incl, 1);   // the lane below's end is this lane's start, exactly
-    __syncthreads();
-    if (lane == 31) scan[warp] = (double)incl;
-    __syncthreads();
-    double before = 0.0, kept = 0.0;
-    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) {
-      if (w < warp) before += scan[w];
-      kept += scan[w];
-    }
-    if (kept > 0.0) {
-      const double target = u * kept;
-      const double lo = before + (lane > 0 ? (double)excl : 0.0), hi = before + (double)incl;
-      __shared__ int chosen;
-      if (threadIdx.x == 0) chosen = -1;
-      __syncthreads();
-      // exactly one thread's interval [lo, hi) holds the target (the last non-empty one takes hi == kept)
-      if (mine > 0.f && target >= lo && (target < hi || hi >= kept)) {
-        double run = lo;
-        int pick = -1;
-        for (int v = threadIdx.x; v < V; v += blockDim.x) {
+      // candidates after top-k and min-p, with weight exp(z - zmax)
+      auto cand1 = [&](int v, float a, unsigned int& key, float& w) {
+        key = order_key(a);
+        if (!inside(cut_k, key, v)) return false;
+        w = expf(a / temperature - zmax);
+        return !(min_p > 0.f) || w >= min_p || v == token;
+      };
+      Cut cut_p{0u, 0x7fffffff};
+      if (top_p < 1.f) {
+        // the sum of the candidates' weights, in a fixed order
+        float tot[16];
+        team_sum16<float>(row, tm, tot, [&](int v, float a, float (&bins)[16]) {
           unsigned int key;
           float w;
-          if (!cand2(v, key, w)) continue;
-          pick = v;
-          run += (double)w;
-          if (run > target) break;
+          if (cand1(v, a, key, w)) bins[0] += w;
+        });
+        cut_p = select_cut<true>(row, tm, cand1, fmax((double)top_p * (double)tot[0], 1e-30));
+      }
+      auto cand2 = [&](int v, float a, unsigned int& key, float& w) { return cand1(v, a, key, w) && inside(cut_p, key, v); };
+      // The draw: tokens in the order (slice, thread, the thread's strided tokens); find where the
+      // running sum of weights passes u * total.  A thread's share of a slice, scanned over its warp:
+      const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+      auto scan_slice = [&](int slice, float& mine, float& incl, float& excl) {
+        mine = 0.f;
+        for_each_token(row, tm.first(slice), tm.stride(), [&](int v, float a) {
+          unsigned int key;
+          float w;
+          if (cand2(v, a, key, w)) mine += w;
+        });
+        incl = mine;                               // inclusive scan within the warp
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const float t = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += t;
         }
-        if (pick >= 0) atomicMax(&chosen, pick >= 0 ? pick : -1);
+        excl = __shfl_up_sync(0xffffffffu, incl, 1);   // the lane below's end is this lane's start, exactly
+      };
+      for (int i = 0; i < tm.per; ++i) {
+        const int slice = tm.rank * tm.per + i;
+        float mine, incl, excl;
+        scan_slice(slice, mine, incl, excl);
+        if (lane == 31) scan_buf[slice * 32 + warp] = (double)incl;
+      }
+      tm.cl.sync();
+      const int n_parts = SLICES * 32;            // (slice, warp) totals; warps a block does not have count zero
+      if ((int)threadIdx.x < n_parts) {
+        const int s = threadIdx.x >> 5, w = threadIdx.x & 31;
+        const double* theirs = tm.cl.map_shared_rank(scan_buf, s / tm.per);
+        all_tot[threadIdx.x] = w < (int)(blockDim.x >> 5) ? theirs[threadIdx.x] : 0.0;
       }
       __syncthreads();
-      if (chosen >= 0) token = chosen;
-    }
+      if ((int)threadIdx.x < n_parts) {
+        double before = 0.0;
+        for (int j = 0; j < (int)threadIdx.x; ++j) before += all_tot[j];   // fixed order
+        prefix_s[threadIdx.x] = before;
+      }
+      __syncthreads();
+      const double kept = prefix_s[n_parts - 1] + all_tot[n_parts - 1];
+      if (kept > 0.0) {
+        const double target = u * kept;
+        int* chosen0 = tm.cl.map_shared_rank(&chosen, 0);
+        for (int i = 0; i < tm.per; ++i) {
+          const int slice = tm.rank * tm.per + i;
+          // Only a warp whose share [before, before + its total) holds the target (or ends the
+          // row) can hold the thread that does: the others need not look again.
+          const double before = prefix_s[slice * 32 + warp], mine_w = all_tot[slice * 32 + warp];
+          if (!(mine_w > 0.0 && target >= before && (target < before + mine_w || before + mine_w >= kept))) continue;
+          float mine, incl, excl;
+          scan_slice(slice, mine, incl, excl);     // the same sums again, bit for bit (whole warp, no barrier inside)
+          const double lo = before + (lane > 0 ? (double)excl : 0.0), hi = before + (double)incl;
+          // exactly one thread's interval [lo, hi) holds the target (the last non-empty one takes hi == kept)
+          if (mine > 0.f && target >= lo && (target < hi || hi >= kept)) {
+            double run = lo;
+            int pick = -1;
+            bool passed = false;
+            for_each_token(row, tm.first(slice), tm.stride(), [&](int v, float a) {
+              unsigned int key;
+              float w;
+              if (passed || !cand2(v, a, key, w)) return;
+              pick = v;
+              run += (double)w;
+              passed = run > target;
+            });
+            if (pick >= 0) atomicMax(chosen0, pick);
+          }
+        }
+      }
+      tm.cl.sync();
+      if (tm.rank == 0 && chosen >= 0) token = chosen;
     }  // many candidates
   }
-  if (threadIdx.x == 0) {
+  if (tm.rank == 0 && threadIdx.x == 0) {
     out[r] = token;
     if (my_counts) my_counts[token] += 1;
   }
+  tm.cl.sync();   // no CTA leaves while another may still read its shared memory
 }
 
 __global__ void count_tokens_kernel(int* __restrict__ counts, const int* __restrict__ tokens, int n, int V) {
@@ -599,7 +717,28 @@ extern "C" int zi_sample(int* out, const float* logits, int R, int V, int ld, co
   if (V <= 0) return zi_refuse("sample: empty logits");
   if (!temperature || !seeds || !draw_index) return zi_refuse("sample: temperature, seeds and draw_index are required");
   SampleParams p{temperature, top_k, top_p, min_p, rep, pres, freq, count_rows, counts, seeds, draw_index};
-  zi_launch(sample_kernel, dim3(R), dim3(THREADS), 0, stream, out, logits, ld, V, p);
+  // CTAs per row: as many (8, 4, 2, 1) as still give every CTA an SM of its own
+  int sms = 0, dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+    sms = 148;
+  int n_ctas = SLICES;
+  while (n_ctas > 1 && (long long)R * n_ctas > sms) n_ctas /= 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(R * n_ctas));
+  cfg.blockDim = dim3(THREADS);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)n_ctas;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_zi_pdl_enabled ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, sample_kernel, out, logits, ld, V, p);
+  if (e != cudaSuccess) return zi_refuse("sample: launch failed: %s", cudaGetErrorString(e));
   return zi_check_launch("sample");
 }
 
@@ -609,3 +748,4 @@ extern "C" int zi_count_tokens(int* counts, const int* tokens, int n, int V, cud
   zi_launch(count_tokens_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, counts, tokens, n, V);
   return zi_check_launch("count_tokens");
 }
+
