@@ -131,6 +131,41 @@ def test_sampling_follows_the_kept_distribution(kw):
     assert (other != draws).any()
 
 
+@pytest.mark.parametrize("V", [1000, 151936])
+def test_a_draw_does_not_depend_on_the_rows_beside_it(V):
+    """The kernel spreads a row over 8, 4, 2 or 1 CTAs by the number of rows in the launch; the
+    token drawn for a row must be the same in every case, for each of the kernel's routes (few
+    candidates listed and sorted, many candidates cut by thresholds, with and without penalties)."""
+    from zinfer_b200 import ops
+
+    g = torch.Generator().manual_seed(3)
+    base = (torch.randn(12, V, generator=g) * 2.5).to(DEV)
+    counts_base = (torch.rand(12, V, generator=g) < 0.05).to(torch.int32).to(DEV)
+    routes = [dict(top_k=0, top_p=1.0, min_p=0.0, rep=1.0), dict(top_k=20, top_p=0.9, min_p=0.0, rep=1.1),
+              dict(top_k=min(2000, V - 1), top_p=0.7, min_p=0.0, rep=1.0), dict(top_k=0, top_p=0.9, min_p=0.01, rep=1.2)]
+
+    def draw(rows_total, route):
+        reps = -(-rows_total // 12)
+        logits = base.repeat(reps, 1)[:rows_total].contiguous()
+        counts = counts_base.repeat(reps, 1)[:rows_total].contiguous()
+        n = rows_total
+        f = lambda v: torch.full((n,), v, dtype=torch.float32, device=DEV)
+        idx = torch.arange(n, dtype=torch.int32, device=DEV)
+        out = ops.sample(logits, temperature=f(0.9), seeds=(idx % 12).to(torch.int64) + 100, draw_index=(idx % 12) * 3,
+                         top_k=torch.full((n,), route["top_k"], dtype=torch.int32, device=DEV), top_p=f(route["top_p"]),
+                         min_p=f(route["min_p"]), repetition_penalty=f(route["rep"]), presence_penalty=f(0.1),
+                         frequency_penalty=f(0.05), count_rows=idx, counts=counts)
+        return out.cpu().numpy()
+
+    for route in routes:
+        alone = draw(12, route)                 # 8 CTAs a row
+        assert draw(1, route)[0] == alone[0]
+        for n in (30, 70, 200):                 # 4, 2 and 1 CTAs a row
+            got = draw(n, route)
+            assert (got == np.resize(alone, n)).all(), f"{route}: a draw changed with {n} rows in the launch"
+        assert len(set(alone.tolist())) > 3
+
+
 def test_greedy_rows_penalties_and_counts():
     from zinfer_b200 import ops
 
