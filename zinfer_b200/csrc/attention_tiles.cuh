@@ -308,6 +308,9 @@ __device__ __forceinline__ void attn_decode_unit(
   float* snew = vnew + D;                                            // [16] own key's score per head, exp2 domain
   const bool owner = FUSED && z == splits - 1;
   if (FUSED) {
+    // Everything above read only the step's own arrays and pages that earlier steps wrote; the
+    // projection rows below come from the kernel before this one.
+    pdl_wait();
     constexpr int HALF = D / 2, MAXP = HALF / 32 > 0 ? HALF / 32 : 1;
     const int my_pos = min(fq.positions[token], fq.n_table_pos - 1);
     const float row_scale = fq.row_scale ? fq.row_scale[token] : 1.0f;
