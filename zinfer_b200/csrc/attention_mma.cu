@@ -192,7 +192,7 @@ attn_decode_mma_kernel(bf16* __restrict__ out, int out_stride, float* __restrict
                        const int* __restrict__ dec_seq, int nq, int nkv, int page_size, int page_shift, int window,
                        float scale_log2, int splits, const FusedQK fq) {
   pdl_launch_dependents();
-  if (!FUSED) pdl_wait();   // fused: the unit waits itself, after it has asked for its first keys
+  // (the unit waits for the kernel before this one itself, after it has asked for its first keys)
   extern __shared__ __align__(128) uint8_t smem[];
   attn_decode_unit<D, FUSED, BlockSync>(smem, threadIdx.x, blockIdx.x, blockIdx.y, blockIdx.z, out, out_stride, partial,
                                         q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q, kv_lens, dec_seq,

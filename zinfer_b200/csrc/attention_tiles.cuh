@@ -260,20 +260,7 @@ __device__ __forceinline__ void attn_decode_unit(
   const int t_begin = z * tps, t_end = min(total_tiles, t_begin + tps);
   const int n_tiles = max(0, t_end - t_begin);
 
-  // Q fragments: row = query head within the group
-  uint32_t qf[D / 16][4];
-  if (!FUSED) {
-    const int r0 = lane >> 2, r1 = r0 + 8;
-    const bf16* q0p = q + (size_t)token * q_stride + (size_t)(kvh * g + r0) * D + 2 * (lane & 3);
-    const bf16* q1p = q + (size_t)token * q_stride + (size_t)(kvh * g + r1) * D + 2 * (lane & 3);
-#pragma unroll
-    for (int kk = 0; kk < D / 16; ++kk) {
-      qf[kk][0] = r0 < g ? *reinterpret_cast<const uint32_t*>(q0p + kk * 16) : 0u;
-      qf[kk][1] = r1 < g ? *reinterpret_cast<const uint32_t*>(q1p + kk * 16) : 0u;
-      qf[kk][2] = r0 < g ? *reinterpret_cast<const uint32_t*>(q0p + kk * 16 + 8) : 0u;
-      qf[kk][3] = r1 < g ? *reinterpret_cast<const uint32_t*>(q1p + kk * 16 + 8) : 0u;
-    }
-  }
+  uint32_t qf[D / 16][4];   // Q fragments: row = query head within the group
   float o[D / 8][4];
 #pragma unroll
   for (int t = 0; t < D / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
@@ -291,6 +278,10 @@ __device__ __forceinline__ void attn_decode_unit(
     const int key0 = kt0 + (t_begin + t) * DC_TILE + warp * DC_KEYS;
     load_kv_rows_pg<D>(ks, ks + ROWS_BYTES, key0, pg, kcache, vcache, nkv, kvh, page_size, page_shift, lane);
   };
+  // Not fused: the kernel before this one wrote the newest token's key and value (and q).  The first
+  // tiles are asked for before the wait for it unless they may hold that key.
+  const bool early = !FUSED && kt0 + (t_begin + STAGES - 1) * DC_TILE <= pos;
+  if (!FUSED && !early) pdl_wait();
   int pg_next = lookup(0);
 #pragma unroll
   for (int t = 0; t < STAGES - 1; ++t) {
@@ -298,6 +289,19 @@ __device__ __forceinline__ void attn_decode_unit(
     pg_next = lookup(t + 1);
     if (t < n_tiles) issue(t, pg);
     cp_async_commit();
+  }
+  if (!FUSED) {
+    if (early) pdl_wait();
+    const int r0 = lane >> 2, r1 = r0 + 8;
+    const bf16* q0p = q + (size_t)token * q_stride + (size_t)(kvh * g + r0) * D + 2 * (lane & 3);
+    const bf16* q1p = q + (size_t)token * q_stride + (size_t)(kvh * g + r1) * D + 2 * (lane & 3);
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      qf[kk][0] = r0 < g ? *reinterpret_cast<const uint32_t*>(q0p + kk * 16) : 0u;
+      qf[kk][1] = r1 < g ? *reinterpret_cast<const uint32_t*>(q1p + kk * 16) : 0u;
+      qf[kk][2] = r0 < g ? *reinterpret_cast<const uint32_t*>(q0p + kk * 16 + 8) : 0u;
+      qf[kk][3] = r1 < g ? *reinterpret_cast<const uint32_t*>(q1p + kk * 16 + 8) : 0u;
+    }
   }
   // ---- fused: q (all blocks) and the token's own k, v (block of the last split), while the
   // first tiles are on their way
