@@ -1,5 +1,5 @@
-"""The host-side plan of the tensor-core matrix product (which side the tokens go on, the N
-tile, the K split): decisions only, no GPU.  The library is built by nvcc on first use."""
+"""The host-side plans of the kernels (the matrix product: which side the tokens go on, the N
+tile, the K split; the sampling kernel: CTAs per row): decisions only, no GPU.  The library is built by nvcc on first use."""
 import ctypes
 import shutil
 
@@ -52,3 +52,13 @@ def test_splits_never_leave_a_split_without_k_blocks(plan):
             kb = -(-K // 64)
             assert 1 <= p["splits"] <= kb
             assert (p["workspace"] > 0) == (p["splits"] > 1)
+
+
+def test_sampling_rows_share_clusters_by_the_number_of_rows():
+    if shutil.which("nvcc") is None:
+        pytest.skip("no nvcc to build the kernel library with")
+    from zinfer_b200 import ops
+
+    f = ops.lib().zi_sample_ctas_per_row
+    assert [f(r, 148) for r in (1, 8, 18, 19, 37, 38, 64, 74, 75, 256)] == [8, 8, 8, 4, 4, 2, 2, 2, 1, 1]
+    assert f(1, 4) == 4 and f(5, 4) == 1

@@ -94,6 +94,7 @@ int zi_decode_layers(const void* descs, int n_layers, int B, int hidden, int nq,
 
 int zi_argmax_chunks(int R, int V);
 int zi_argmax(int* out, const float* logits, int R, int V, int ld, void* workspace, cudaStream_t stream);
+int zi_sample_ctas_per_row(int R, int sm_count);
 int zi_sample(int* out, const float* logits, int R, int V, int ld, const float* temperature, const int* top_k,
               const float* top_p, const float* min_p, const float* rep, const float* pres, const float* freq,
               const int* count_rows, int* counts, const unsigned long long* seeds, const int* draw_index,

@@ -709,6 +709,14 @@ extern "C" int zi_argmax(int* out, const float* logits, int R, int V, int ld, vo
   return zi_check_launch("argmax");
 }
 
+// CTAs that share a row of the sampling kernel: as many (8, 4, 2, 1) as still give every CTA an SM
+// of its own.
+extern "C" int zi_sample_ctas_per_row(int R, int sm_count) {
+  int n_ctas = SLICES;
+  while (n_ctas > 1 && (long long)R * n_ctas > sm_count) n_ctas /= 2;
+  return n_ctas;
+}
+
 extern "C" int zi_sample(int* out, const float* logits, int R, int V, int ld, const float* temperature,
                          const int* top_k, const float* top_p, const float* min_p, const float* rep,
                          const float* pres, const float* freq, const int* count_rows, int* counts,
@@ -717,13 +725,11 @@ extern "C" int zi_sample(int* out, const float* logits, int R, int V, int ld, co
   if (V <= 0) return zi_refuse("sample: empty logits");
   if (!temperature || !seeds || !draw_index) return zi_refuse("sample: temperature, seeds and draw_index are required");
   SampleParams p{temperature, top_k, top_p, min_p, rep, pres, freq, count_rows, counts, seeds, draw_index};
-  // CTAs per row: as many (8, 4, 2, 1) as still give every CTA an SM of its own
   int sms = 0, dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess ||
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
     sms = 148;
-  int n_ctas = SLICES;
-  while (n_ctas > 1 && (long long)R * n_ctas > sms) n_ctas /= 2;
+  const int n_ctas = zi_sample_ctas_per_row(R, sms);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(R * n_ctas));
   cfg.blockDim = dim3(THREADS);
