@@ -205,7 +205,7 @@ def test_decode_attention_split_choice():
     from zinfer_b200.ops import decode_splits
 
     sms = 148
-    assert decode_splits(1, 8, sms, 2048) >= 16            # one request: many splits fill the GPU
+    assert 12 <= decode_splits(1, 8, sms, 2048) <= 20      # one request: many splits fill the GPU, but each costs its merge
     assert decode_splits(8, 8, sms, 2048) == 4             # 64 (request, head) pairs x 4 = 256 blocks on 296 slots
     assert decode_splits(32, 8, sms, 2048) == 1            # 256 pairs already fill a wave
     assert decode_splits(48, 8, sms, 2048) in (2, 3)       # 384 pairs: 2 waves whole, 1.3 split in three
