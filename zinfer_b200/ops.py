@@ -437,7 +437,7 @@ def decode_splits(n_dec: int, num_kv_heads: int, sm_count: int, max_kv_len: Opti
     an SM at once, and a block costs a fixed time (``fixed_us``: launch, prologue, merge; more in
     the fused kernel, which also makes q, k and v) plus its share of the walk over the keys
     (about 0.025 us a key for a block's four warps); every split also costs the kernel that
-    merges them about 0.27 us (measured at one request: 16 splits beat both 8 and 32).  The
+    merges them, and the blocks' own fixed work, about 0.2 us (measured at one request: 16 splits beat both 8 and 32).  The
     split count (at most 32, never more than tiles of 64 keys) that makes the sum smallest."""
     slots, units = 2 * sm_count, max(1, n_dec * num_kv_heads)
     keys = max_kv_len if max_kv_len and max_kv_len > 0 else 2048
@@ -446,7 +446,7 @@ def decode_splits(n_dec: int, num_kv_heads: int, sm_count: int, max_kv_len: Opti
     best, best_cost = 1, float("inf")
     for s in range(1, limit + 1):
         waves = -(-units * s // slots)
-        cost = waves * (fixed_us + walk / s) + 0.27 * s
+        cost = waves * (fixed_us + walk / s) + 0.2 * s
         if cost < best_cost * 0.98:     # more splits only for a clear gain
             best, best_cost = s, cost
     return best
