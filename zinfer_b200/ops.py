@@ -447,7 +447,7 @@ def decode_splits(n_dec: int, num_kv_heads: int, sm_count: int, max_kv_len: Opti
     for s in range(1, limit + 1):
         waves = -(-units * s // slots)
         cost = waves * (fixed_us + walk / s) + 0.2 * s
-        if cost < best_cost * 0.98:     # more splits only for a clear gain
+        if cost < best_cost:
             best, best_cost = s, cost
     return best
 
