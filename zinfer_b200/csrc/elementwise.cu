@@ -119,12 +119,18 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restri
                                        const float* __restrict__ w, float eps, TO* __restrict__ out,
                                        const int* __restrict__ rows, int H) {
   pdl_launch_dependents();
-  pdl_wait();
   __shared__ float scratch[33];
+  const int nvec = H >> 2;
+  float4 ww[VPT];   // the norm's weights do not depend on the kernel before this one
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    ww[i] = idx < nvec ? Vec4<float>::load(w + 4 * idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  pdl_wait();
   const int r = blockIdx.x;
   const int row = rows ? rows[r] : r;
   float* hr = h + (size_t)row * H;
-  const int nvec = H >> 2;
   float4 v[VPT];
   float ss = 0.f;
 #pragma unroll
@@ -133,11 +139,20 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restri
     if (idx < nvec) {
       float4 a = Vec4<float>::load(hr + 4 * idx);
       if (dpart) {
-        // the splits are read four at a time so that their loads are in flight together;
-        // they are still added in order of z
+        // the splits are read eight (then four) at a time so that their loads are in flight
+        // together; they are still added in order of z
         float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
         const float* base = dpart + (size_t)row * H + 4 * idx;
         int z = 0;
+        for (; z + 8 <= splits; z += 8) {
+          float4 p[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) p[j] = Vec4<float>::load(base + (size_t)(z + j) * zstride);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            d.x += p[j].x; d.y += p[j].y; d.z += p[j].z; d.w += p[j].w;
+          }
+        }
         for (; z + 4 <= splits; z += 4) {
           const float4 p0 = Vec4<float>::load(base + (size_t)z * zstride);
           const float4 p1 = Vec4<float>::load(base + (size_t)(z + 1) * zstride);
@@ -169,11 +184,9 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restri
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = threadIdx.x + i * blockDim.x;
-    if (idx < nvec) {
-      const float4 ww = Vec4<float>::load(w + 4 * idx);
-      Vec4<TO>::store(o + 4 * idx, make_float4(v[i].x * ww.x * inv, v[i].y * ww.y * inv, v[i].z * ww.z * inv,
-                                               v[i].w * ww.w * inv));
-    }
+    if (idx < nvec)
+      Vec4<TO>::store(o + 4 * idx, make_float4(v[i].x * ww[i].x * inv, v[i].y * ww[i].y * inv, v[i].z * ww[i].z * inv,
+                                               v[i].w * ww[i].w * inv));
   }
 }
 
@@ -278,11 +291,22 @@ __global__ void swiglu_partials_kernel(T* __restrict__ out, const float* __restr
   float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
   int gc, uc;
   gate_up_columns(i, I, interleave, gc, uc);
-  for (int z = 0; z < splits; ++z) {
-    const float* p = part + z * zstride + t * 2 * I;
-    const float4 a = *reinterpret_cast<const float4*>(p + gc), b = *reinterpret_cast<const float4*>(p + uc);
-    g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
-    u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+  for (int z0 = 0; z0 < splits; z0 += 4) {   // four splits' loads in flight together, added in order of z
+    float4 a[4], b[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float* p = part + (size_t)(z0 + j) * zstride + t * 2 * I;
+      const bool on = z0 + j < splits;
+      a[j] = on ? *reinterpret_cast<const float4*>(p + gc) : make_float4(0.f, 0.f, 0.f, 0.f);
+      b[j] = on ? *reinterpret_cast<const float4*>(p + uc) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (z0 + j < splits) {
+        g.x += a[j].x; g.y += a[j].y; g.z += a[j].z; g.w += a[j].w;
+        u.x += b[j].x; u.y += b[j].y; u.z += b[j].z; u.w += b[j].w;
+      }
+    }
   }
   Vec4<T>::store(out + t * I + i, make_float4(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y,
                                               g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w));
