@@ -27,7 +27,7 @@ TINY_A = dict(
     num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16, max_position_embeddings=128,
     rms_norm_eps=1e-6, rope_theta=10000.0, tie_word_embeddings=True, torch_dtype="bfloat16")
 TINY_B = dict(
-    architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=389, hidden_size=96, intermediate_size=160,
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=384, hidden_size=96, intermediate_size=160,
     num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=1, head_dim=32, max_position_embeddings=256,
     rms_norm_eps=1e-5, rope_theta=1000000.0, tie_word_embeddings=False, torch_dtype="bfloat16")
 # a third one with sizes that are no powers of two anywhere: width 72, heads of 48, vocabulary 301
@@ -74,7 +74,7 @@ def cpu_kernels(monkeypatch):
     from zinfer_b200.engine import runner
 
     for name in ("embed_gather", "add_rmsnorm", "residual_add", "swiglu", "rope_table", "qk_norm_rope_store",
-                 "linear", "attention_tile_rows", "attention_prefill_tile_rows", "paged_attention", "attention", "argmax", "patch_tokens", "linear_swiglu", "interleave_gate_up", "decode_fused_ok"):
+                 "linear", "attention_tile_rows", "attention_prefill_tile_rows", "paged_attention", "attention", "argmax", "patch_tokens", "linear_swiglu", "interleave_gate_up", "decode_fused_ok", "sample", "count_tokens"):
         monkeypatch.setattr(ops, name, getattr(kernel_refs, name))
     monkeypatch.setattr(ops, "lib", lambda: None)
     monkeypatch.setattr(runner, "_require_cuda", lambda device: None)

@@ -151,3 +151,44 @@ def patch_tokens(ids, prev, dst, src):
 
 def decode_fused_ok(dtype, num_heads, num_kv_heads, head_dim, step):
     return False
+
+
+def count_tokens(counts_row, tokens):
+    for t in tokens.tolist():
+        counts_row[int(t)] += 1
+
+
+def sample(logits, temperature, seeds, draw_index, top_k=None, top_p=None, min_p=None, repetition_penalty=None,
+           presence_penalty=None, frequency_penalty=None, count_rows=None, counts=None, out=None):
+    """The reference's chain per row (penalties, top-k, temperature, min-p, top-p, draw) with the
+    host sampler of tests/plain_qwen3.py.  The uniform number of a draw comes from (seed, draw
+    index) alone, as on the device, but by another generator: tokens are comparable with the
+    kernel's only where the kept set has one member (greedy rows)."""
+    import hashlib
+
+    import plain_qwen3 as P
+
+    R, V = logits.shape
+    res = torch.empty((R,), dtype=torch.int32)
+    get = lambda t, i, default: default if t is None else t[i].item()
+    for i in range(R):
+        row = logits[i].float().numpy()
+        crow = int(get(count_rows, i, -1))
+        if counts is not None and crow >= 0:
+            hist = np.repeat(np.arange(V), counts[crow].numpy())
+            row = P.adjusted_logits(row, hist.tolist(), get(repetition_penalty, i, 1.0), get(presence_penalty, i, 0.0),
+                                    get(frequency_penalty, i, 0.0))
+        T, k = float(temperature[i]), int(get(top_k, i, 0))
+        if T <= 0.0 or k == 1:
+            tok = int(np.argmax(row))
+        else:
+            p = P.kept_distribution(row, T, k, float(get(top_p, i, 1.0)), float(get(min_p, i, 0.0)))
+            h = hashlib.sha256(f"{int(seeds[i])}:{int(draw_index[i])}".encode()).digest()
+            u = int.from_bytes(h[:8], "little") / 2.0 ** 64
+            tok = int(min(np.searchsorted(np.cumsum(p), u, side="right"), V - 1))
+            if p[tok] == 0.0:
+                tok = int(np.argmax(p))
+        if counts is not None and crow >= 0:
+            counts[crow, tok] += 1
+        res[i] = tok
+    return res

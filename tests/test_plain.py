@@ -85,7 +85,7 @@ def test_forward_is_causal_and_tied_head_is_the_embedding():
     assert P.head_weight(cfg, w) is w["model.embed_tokens.weight"]
     cfg_b, w_b = _model(TINY_B, 4)
     assert P.head_weight(cfg_b, w_b) is w_b["lm_head.weight"]
-    assert P.forward(cfg_b, w_b, [1, 2, 3]).shape == (3, 389)
+    assert P.forward(cfg_b, w_b, [1, 2, 3]).shape == (3, 384)
 
 
 def test_greedy_takes_the_first_maximum_and_feeds_it_back():

@@ -147,7 +147,7 @@ def test_waiting_requests_keep_their_order():
     assert max(len(step) for step in log) <= 2
 
 
-def drain_pipelined(cache, sched, limit=2000):
+def drain_pipelined(cache, sched, limit=2000, plans=None):
     """The engine's pipelined order: a step is launched (advance) before the tokens of the
     step before it are read (resolve), so end-of-sequence is noticed one step late."""
     done, pending = [], None
@@ -155,6 +155,8 @@ def drain_pipelined(cache, sched, limit=2000):
         limit -= 1
         assert limit > 0
         plan = sched.schedule()
+        if plans is not None:
+            plans.append(plan)
         sampled = []
         for s in plan.scheduled:
             assert cache.length(s.request.request_id) == s.start
@@ -197,6 +199,45 @@ def test_pipelined_resolution_gives_the_same_tokens_and_reasons():
         assert by[3].finish_reason == "stop" and by[3].output == []
         assert by[0].finish_reason == "length" and len(by[0].output) == 10
         assert not cache2.requests and cache2.free_pages() == [pages]
+
+
+def test_end_of_sequence_in_flight_when_the_request_is_preempted():
+    """A request draws its end-of-sequence token in step k; before the host has read that token,
+    step k+1's schedule preempts the request (an older one needs its page).  It must be reported
+    once, with reason stop, hold no placeholder, and never be admitted again."""
+    def build(eos_for_b=()):
+        cache, sched = make(num_pages=6, page=4, budget=32, max_running=2)
+        a, b = req("a", 7, 12, ignore_eos=True), req("b", 6, 12)
+        b.eos_token_ids = tuple(eos_for_b)
+        sched.add(a)
+        sched.add(b)
+        return cache, sched, b
+
+    # first without an end token: find the step whose schedule preempts b, and the token b drew
+    # in the step before it (a function of its length, like a seeded draw)
+    cache, sched, b = build()
+    plans = []
+    drain_pipelined(cache, sched, plans=plans)
+    k1 = next(i for i, p in enumerate(plans) if any(r is b for r in p.preempted))
+    before = next(s for s in plans[k1 - 1].scheduled if s.request is b)
+    assert before.samples, "the case is meant to have b's token in flight when it is preempted"
+    eos = fake_token(Request("b", [0] * (before.start + before.count), b.params))
+    n_out = before.start + before.count - 6      # tokens b had emitted before that one
+
+    cache, sched, b = build([eos])
+    plans = []
+    done = drain_pipelined(cache, sched, plans=plans)
+    assert any(r is b for r in plans[k1].preempted), "the end token did not change the schedule before it was read"
+    reports = [r for r in done if r is b]
+    assert len(reports) == 1, f"b was reported {len(reports)} times"
+    assert b.finish_reason == "stop" and len(b.output) <= n_out and -1 not in b.output
+    assert not sched.waiting and not sched.running and not cache.requests and cache.free_pages() == [6]
+    assert all(all(s.request is not b for s in p.scheduled) for p in plans[k1 + 1:]), "b ran again after it had ended"
+    # the same tokens as a host that waits for every step
+    cache2, sched2, b2 = build([eos])
+    sync, _ = drain(cache2, sched2)
+    key = lambda rs: sorted((r.request_id, tuple(r.output), r.finish_reason) for r in rs)
+    assert key(done) == key(sync)
 
 
 def test_decode_attention_split_choice():

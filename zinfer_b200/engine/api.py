@@ -107,8 +107,7 @@ class Engine:
         eos = tuple(params.eos_token_ids) if params.eos_token_ids is not None else self.runner.model.spec.eos_token_ids
         req = Request(rid, [int(t) for t in prompt_ids], params, eos_token_ids=eos)
         self.scheduler.add(req)
-        self.sampler.begin_request(rid, params, req.prompt)
-        self._live[rid] = req
+        self._live[rid] = req      # its row of token counts (penalties) is taken when it is first scheduled
         return rid
 
     # ---------------------------------------------------------------------- step
@@ -116,22 +115,30 @@ class Engine:
         """Builds the plan's batch, runs the model and the sampler, and starts the copy of
         the sampled tokens to the host.  Does not wait for anything."""
         prev = self._inflight
+
+        def on_device(s) -> bool:
+            """The portion's one unread token can be taken from the step in flight."""
+            return s.count == 1 and prev is not None and s.request.request_id in prev.row_of
+
+        if any(Scheduler.PLACEHOLDER in s.request.tokens[s.start:s.start + s.count] and not on_device(s)
+               for s in plan.scheduled):
+            # a longer portion holds a token the host has not read yet: read the step in flight first,
+            # before any entry is built, and drop what that ended (its pages are already given back)
+            self._finished_early += self._resolve()
+            prev = None
+            plan.scheduled[:] = [s for s in plan.scheduled if s.request.status != "finished"]
         entries, rows = [], []
         for s in plan.scheduled:
             r = s.request
             toks = r.tokens[s.start:s.start + s.count]
-            src = None
-            if Scheduler.PLACEHOLDER in toks:
-                if s.count == 1 and prev is not None and r.request_id in prev.row_of:
-                    src = prev.row_of[r.request_id]      # sampled by the step in flight: taken on the device
-                else:
-                    # a longer portion holds a token the host has not read yet: read it first
-                    self._finished_early += self._resolve()
-                    prev = None
-                    toks = r.tokens[s.start:s.start + s.count]
+            src = prev.row_of[r.request_id] if Scheduler.PLACEHOLDER in toks else None   # taken on the device
+            if r.params.has_penalties and not self.sampler.has_request(r.request_id):
+                self.sampler.begin_request(r.request_id, r.params, r.prompt)   # admitted: at most max_requests hold a row
             entries.append(StepEntry(r.request_id, toks, [s.count - 1] if s.samples else [], token_src=src))
             if s.samples:
                 rows.append(r)
+        if not entries:
+            return _InFlight(plan, None, None, None, {})
         logits = self.runner.step(entries, prev_tokens=prev.tokens_dev if prev is not None else None)
         if not rows:
             return _InFlight(plan, None, None, None, {})

@@ -42,7 +42,7 @@ from ..cache.manager import CacheManager
 from ..sampling.params import SamplingParams
 
 
-@dataclass
+@dataclass(eq=False)      # a request is itself, never "equal" to another: queues compare by identity
 class Request:
     request_id: Hashable
     prompt: list[int]
@@ -128,6 +128,9 @@ class Scheduler:
         self._release(r)
         if r in self.running:
             self.running.remove(r)
+        if r in self.waiting:
+            # preempted while the token that ends it was still in flight: it must not be admitted again
+            self.waiting.remove(r)
         self.stats.finished += 1
         if plan is not None:
             plan.finished.append(r)
@@ -195,6 +198,7 @@ class Scheduler:
         # 3. admissions, oldest first; none may overtake a request that does not fit
         while self.waiting and budget > 0 and len(self.running) < self.max_running and not plan.preempted:
             r = self.waiting[0]
+            assert r.status == "waiting", f"request {r.request_id!r} is {r.status} but still queued"
             if r.num_tokens >= self.max_model_len or r.params.max_new_tokens <= len(r.output):
                 self.waiting.popleft()
                 self._finish(r, "length", plan)

@@ -22,18 +22,26 @@ class Sampler:
         self.vocab = vocab_size
         self.device = torch.device(device)
         self.max_requests = max_requests
-        self._counts: Optional[torch.Tensor] = None      # [max_requests, V], made when first needed
-        self._rows = PagePool(max_requests, name="token-count rows")
+        # Rows of token counts, [rows, V], made when first needed.  A request that ended in the step in
+        # flight keeps its row until the host has read that step, while the requests admitted in its
+        # place already hold theirs: twice the running requests is the most that can be held.
+        self._counts: Optional[torch.Tensor] = None
+        self._rows = PagePool(2 * max_requests, name="token-count rows")
         self._row_of: dict[Hashable, int] = {}
 
     # ------------------------------------------------------------ token counts
+    def has_request(self, request_id: Hashable) -> bool:
+        return request_id in self._row_of
+
     def begin_request(self, request_id: Hashable, params: SamplingParams, prompt: Sequence[int]) -> None:
-        """Call once when a request enters.  With penalties on, its prompt is counted
-        as history (src/app/cli/runtime/generator.zig:95-97)."""
-        if not params.has_penalties:
+        """Call once when a request is admitted (not when it is queued: a row of counts is
+        [vocabulary] wide and there are only ``max_requests`` of them).  With penalties on, its
+        prompt is counted as history (src/app/cli/runtime/generator.zig:95-97).  The row is kept
+        until :meth:`end_request`, across preemption, so the counts of generated tokens survive."""
+        if not params.has_penalties or request_id in self._row_of:
             return
         if self._counts is None:
-            self._counts = torch.zeros((self.max_requests, self.vocab), dtype=torch.int32, device=self.device)
+            self._counts = torch.zeros((self._rows.num_pages, self.vocab), dtype=torch.int32, device=self.device)
         row = self._rows.alloc(1)[0]
         self._row_of[request_id] = row
         self._counts[row].zero_()
