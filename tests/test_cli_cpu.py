@@ -77,3 +77,66 @@ def test_generate_matches_plain_greedy_on_cpu(cpu_kernels, model_dirs, name):
     assert tight.scheduler.stats.preemptions > 0 and res2[0].preemptions == 0
     tight.runner.manager.check()
     assert not tight.runner.manager.requests
+
+
+def test_engine_and_run_flags():
+    run = {}
+    s, e = cli.parse_flags(["--num-pages", "12", "--kv-cache-bytes", "1000000", "--gpu-memory-fraction", "0.5",
+                            "--max-model-len", "99", "--max-requests", "3", "--random-weights", "7", "--config", "c.json",
+                            "--max-new-tokens", "5", "--profile", "p.json"], run)
+    assert s == {} and e == dict(num_pages=12, kv_cache_bytes=1000000, gpu_memory_fraction=0.5, max_model_len=99, max_requests=3)
+    assert run == dict(random_weights=7, config="c.json", max_new_tokens=5, profile="p.json")
+    with pytest.raises(cli.CliError, match="go together"):
+        cli.ModelSource("x", {"random_weights": 1})
+
+
+def test_generate_several_prompts_from_random_weights_without_a_folder(cpu_kernels, model_dirs, tmp_path):
+    import os
+
+    cfg_path = os.path.join(model_dirs[("A", "float32")], "config.json")
+    common = ["--random-weights", "11", "--config", cfg_path, "--device", "cpu", "--dtype", "float32", "--ignore-eos",
+              "--temperature", "0"]
+    out = io.StringIO()
+    assert cli.run(["generate", "1,2,3;4,5;9", "--max-new-tokens", "4", *common], out) == 0
+    lines = out.getvalue().splitlines()
+    toks = [ln for ln in lines if ln.startswith("tokens[")]
+    assert len(toks) == 3 and all(ln.count(",") == 3 for ln in toks)
+    assert sum(ln.startswith("finish_reason[") and ln.endswith("length") for ln in lines) == 3
+    # each prompt alone, positional max_new_tokens: the same tokens
+    for i, p in enumerate(("1,2,3", "4,5", "9")):
+        alone = io.StringIO()
+        assert cli.run(["generate", p, "4", *common], alone) == 0
+        assert alone.getvalue().splitlines()[0].split(": ")[1] == toks[i].split(": ")[1]
+    # random-model writes a sharded folder, which the commands read like any other
+    assert cli.run(["random-model", str(tmp_path / "m"), cfg_path, "11", "--shards", "2"], io.StringIO()) == 0
+    folder = io.StringIO()
+    assert cli.run(["generate", str(tmp_path / "m"), "1,2,3", "4", "--device", "cpu", "--dtype", "float32", "--ignore-eos",
+                    "--temperature", "0"], folder) == 0
+    assert folder.getvalue().startswith("tokens: [")
+    out = io.StringIO()
+    assert cli.run(["inspect-weights", str(tmp_path / "m")], out) == 0
+    assert "shard_count: 2" in out.getvalue()
+    assert cli.run(["generate", "1,2", "--random-weights", "1"], io.StringIO()) == 2
+
+
+def test_pool_sizing_from_a_byte_budget(cpu_kernels, model_dirs):
+    from zinfer_b200.cache import bytes_per_page, bytes_per_token, pages_for
+    from zinfer_b200.engine.api import Engine
+    from zinfer_b200.parts import KVCacheNeed
+
+    needs = {"a": KVCacheNeed(2, 16, None), "b": KVCacheNeed(2, 16, None), "c": KVCacheNeed(1, 32, 64)}
+    # two caches share a group; the third has its own: one page id costs a page in each
+    assert bytes_per_page(needs, 16, 2) == (2 * 2 * 2 * 16 * 16 + 1 * 2 * 1 * 16 * 32) * 2
+    assert bytes_per_token(needs, 2) * 16 == bytes_per_page(needs, 16, 2)
+    per = bytes_per_page(needs, 16, 2)
+    assert pages_for(needs, 16, 2, budget_bytes=10 * per + per - 1) == 10
+    assert pages_for(needs, 16, 2, budget_bytes=10 * per, tokens=33) == 3       # capped by what the tokens need
+    assert pages_for(needs, 16, 2, budget_bytes=0) == 1
+    # Tiny A: 2 layers x 2 kv heads x 16 x 4 bytes x 2 = 512 bytes a token in float32
+    eng = Engine(model_dirs[("A", "float32")], dtype="float32", device="cpu", page_size=16, kv_cache_bytes=512 * 16 * 7 + 100,
+                 max_requests=4)
+    assert eng.runner.manager.groups[0].pool.num_pages == 7
+    assert eng.runner.storage.bytes() == 512 * 16 * 7
+    # the default: as many tokens as the requests could fill, where no device memory can be asked
+    eng = Engine(model_dirs[("A", "float32")], dtype="float32", device="cpu", page_size=16, max_requests=4)
+    assert eng.runner.manager.groups[0].pool.num_pages == 4 * 128 // 16

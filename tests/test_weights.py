@@ -139,3 +139,81 @@ def test_tied_head_needs_no_separate_tensor_and_tolerates_one(tmp_path):
     write_safetensors(str(d / "model.safetensors"), t)
     with pytest.raises(WeightsError, match="lm_head.weight"):
         load_tensors(str(d), untied, torch.bfloat16, "cpu")
+
+
+# ------------------------------------------------------------------------- shards
+def test_sharded_folder_loads_back_equal_to_the_single_file(tmp_path):
+    from zinfer_b200.weights import Checkpoint
+
+    cfg = Qwen3Config.from_dict(TINY_B)
+    specs = declared_tensors(qwen3_model_spec(cfg))
+    one = write_model_dir(str(tmp_path / "one"), cfg, seed=9)
+    three = write_model_dir(str(tmp_path / "three"), cfg, seed=9, shards=3)
+    files = sorted(os.listdir(three))
+    assert files == ["config.json", "model-00001-of-00003.safetensors", "model-00002-of-00003.safetensors",
+                     "model-00003-of-00003.safetensors", "model.safetensors.index.json"]
+    index = json.load(open(os.path.join(three, "model.safetensors.index.json")))
+    assert set(index["weight_map"]) == {n for n, s in specs.items() if not s.optional}
+    assert len(set(index["weight_map"].values())) == 3
+    sizes = [os.path.getsize(os.path.join(three, f)) for f in files[1:4]]
+    assert max(sizes) < 2.5 * min(sizes), "the shards are far from equal in size"
+    a, b = load_tensors(one, specs, torch.bfloat16, "cpu"), load_tensors(three, specs, torch.bfloat16, "cpu")
+    assert list(a) == list(b) and all(torch.equal(a[n], b[n]) for n in a)
+    with Checkpoint(three) as ck:
+        assert len(ck.files) == 3 and ck.info("model.norm.weight").shape == (cfg.hidden_size,)
+
+
+def test_one_error_over_all_shards(tmp_path):
+    cfg = Qwen3Config.from_dict(TINY_B)
+    specs = declared_tensors(qwen3_model_spec(cfg))
+    t = random_tensors(specs, 3, torch.bfloat16)
+    del t["model.layers.1.self_attn.k_norm.weight"]                        # would lie in a middle shard
+    del t["lm_head.weight"]                                                 # in the last
+    t["model.embed_tokens.weight"] = torch.zeros(5, 5, dtype=torch.bfloat16)   # in the first
+    t["model.layers.9.extra.weight"] = torch.zeros(2, dtype=torch.bfloat16)
+    from zinfer_b200.weights import write_sharded
+
+    d = tmp_path / "m"
+    d.mkdir()
+    write_sharded(str(d), t, 3)
+    with pytest.raises(WeightsError) as ei:
+        load_tensors(str(d), specs, torch.bfloat16, "cpu")
+    e = ei.value
+    assert e.missing == ["lm_head.weight", "model.layers.1.self_attn.k_norm.weight"]
+    assert e.unexpected == ["model.layers.9.extra.weight"]
+    assert len(e.wrong_shape) == 1 and "embed_tokens" in e.wrong_shape[0]
+
+
+def test_broken_shard_sets_are_refused(tmp_path):
+    from zinfer_b200.weights import Checkpoint, CheckpointError
+
+    cfg = Qwen3Config.from_dict(TINY_A)
+    d = write_model_dir(str(tmp_path / "m"), cfg, seed=2, shards=2)
+    index_path = os.path.join(d, "model.safetensors.index.json")
+    index = json.load(open(index_path))
+    # a shard that the index names is absent
+    os.rename(os.path.join(d, "model-00002-of-00002.safetensors"), os.path.join(d, "elsewhere"))
+    with pytest.raises(CheckpointError, match="model-00002-of-00002.safetensors"):
+        Checkpoint(d)
+    os.rename(os.path.join(d, "elsewhere"), os.path.join(d, "model-00002-of-00002.safetensors"))
+    # the index places a tensor in a shard that does not hold it
+    bad = json.loads(json.dumps(index))
+    bad["weight_map"]["model.norm.weight"] = "model-00001-of-00002.safetensors"
+    json.dump(bad, open(index_path, "w"))
+    with pytest.raises(CheckpointError, match="model.norm.weight"):
+        Checkpoint(d)
+    # an index that is no index
+    open(index_path, "w").write('{"weight_map": []}')
+    with pytest.raises(CheckpointError, match="weight_map"):
+        Checkpoint(d)
+    # a folder without weights
+    with pytest.raises(FileNotFoundError, match="model.safetensors"):
+        Checkpoint(str(tmp_path))
+    # a tensor held by two shards
+    json.dump(index, open(index_path, "w"))
+    import shutil
+    shutil.copy(os.path.join(d, "model-00001-of-00002.safetensors"), os.path.join(d, "copy.safetensors"))
+    index["weight_map"]["model.embed_tokens.weight"] = "copy.safetensors"
+    json.dump(index, open(index_path, "w"))
+    with pytest.raises(CheckpointError, match="two shards"):
+        Checkpoint(d)

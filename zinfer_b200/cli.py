@@ -19,11 +19,15 @@ USAGE = """Usage:
   zinfer inspect-tensor [model_dir] <tensor_name> [count]
   zinfer probe-model [model_dir] <token_id> <top_k>
   zinfer generate-token-ids [model_dir] <seed_ids_csv> <steps>
-  zinfer generate [model_dir] <ids_csv> [max_new_tokens] [flags...]
+  zinfer generate [model_dir] <ids_csv[;ids_csv...]> [max_new_tokens] [flags...]
   zinfer bench [model_dir] <ids_csv> [max_new_tokens] [flags...]
   zinfer bench-batch [model_dir] <ids_csv> <batch_size> [max_new_tokens] [flags...]
   zinfer bench-continuous [model_dir] <ids_csv> <batch_size> <total_requests> [max_new_tokens] [flags...]
-  zinfer random-model <out_dir> <config_json> [seed]
+  zinfer random-model <out_dir> <config_json> [seed] [--shards <usize>]
+
+  Instead of [model_dir], `--random-weights <seed> --config <config_json>` draws the
+  weights on the GPU (no folder is read or written).  Several prompts, separated by
+  `;`, run as one batch.
 
 Defaults:
   model_dir = models/Qwen3-0.6B
@@ -39,12 +43,23 @@ Flags:
   --presence-penalty <f32>
   --frequency-penalty <f32>
   --repetition-penalty <f32>
+  --max-new-tokens <usize>     (same as the positional)
   --ignore-eos
   --dtype <bfloat16|float32>
+  --device <cuda:N>
+  --random-weights <seed>      (with --config)
+  --config <config_json>
   --page-size <usize>
-  --kv-cache-tokens <usize>
+  --num-pages <usize>          (pages per cache group; else:)
+  --kv-cache-tokens <usize>    (else:)
+  --kv-cache-bytes <usize>     (else: --gpu-memory-fraction of what is free, default 0.9)
+  --gpu-memory-fraction <f32>
+  --max-model-len <usize>
+  --max-requests <usize>
   --max-batched-tokens <usize>
   --chunk-size <usize>
+  --profile <path>             (generate, bench*: per-kernel-class device times as JSON;
+                                with --hbm-gbs <f32> --bf16-tflops <f32> also fractions of those peaks)
 """
 
 
@@ -77,12 +92,22 @@ _FLAGS = {
 _ENGINE_FLAGS = {
     "--dtype": ("dtype", str), "--page-size": ("page_size", int), "--kv-cache-tokens": ("kv_cache_tokens", int),
     "--max-batched-tokens": ("max_batched_tokens", int), "--chunk-size": ("chunk_size", int),
+    "--num-pages": ("num_pages", int), "--kv-cache-bytes": ("kv_cache_bytes", int),
+    "--gpu-memory-fraction": ("gpu_memory_fraction", float), "--max-model-len": ("max_model_len", int),
+    "--max-requests": ("max_requests", int), "--device": ("device", str),
+}
+# options of the command itself: where the model comes from, how much to generate, what to record
+_RUN_FLAGS = {
+    "--random-weights": ("random_weights", int), "--config": ("config", str), "--max-new-tokens": ("max_new_tokens", int),
+    "--profile": ("profile", str), "--shards": ("shards", int), "--hbm-gbs": ("hbm_gbs", float),
+    "--bf16-tflops": ("bf16_tflops", float),
 }
 
 
-def parse_flags(args: list[str]) -> tuple[dict, dict]:
-    """(sampling options, engine options); errors carry the reference's names
-    (MissingFlagValue, UnknownFlag, args.zig:395-501)."""
+def parse_flags(args: list[str], run_opts: dict | None = None) -> tuple[dict, dict]:
+    """(sampling options, engine options); options of the command itself go to ``run_opts``
+    when given.  Errors carry the reference's names (MissingFlagValue, UnknownFlag,
+    args.zig:395-501)."""
     sampling, engine = {}, {}
     i = 0
     while i < len(args):
@@ -93,14 +118,15 @@ def parse_flags(args: list[str]) -> tuple[dict, dict]:
             sampling["ignore_eos"] = True
             i += 1
             continue
-        table = _FLAGS if a in _FLAGS else _ENGINE_FLAGS if a in _ENGINE_FLAGS else None
+        table = (_FLAGS if a in _FLAGS else _ENGINE_FLAGS if a in _ENGINE_FLAGS
+                 else _RUN_FLAGS if a in _RUN_FLAGS and run_opts is not None else None)
         if table is None:
             raise CliError(f"UnknownFlag: {a}")
         if i + 1 >= len(args):
             raise CliError(f"MissingFlagValue: {a}")
         key, conv = table[a]
         try:
-            (sampling if table is _FLAGS else engine)[key] = conv(args[i + 1])
+            (sampling if table is _FLAGS else engine if table is _ENGINE_FLAGS else run_opts)[key] = conv(args[i + 1])
         except ValueError:
             raise CliError(f"InvalidFlagValue: {a} {args[i + 1]!r}") from None
         i += 2
@@ -145,30 +171,32 @@ def inspect_config(model_dir: str, out) -> None:
 
 
 def inspect_weights(model_dir: str, out) -> None:
-    from .weights import SafetensorsFile
+    from .weights import Checkpoint
 
-    path = os.path.join(model_dir, "model.safetensors")
-    with SafetensorsFile(path) as f:
+    with Checkpoint(model_dir) as ck:
         print("Zinfer weights inspection", file=out)
-        print(f"weights_path: {path}", file=out)
-        print(f"file_size: {os.path.getsize(path)}", file=out)
-        print(f"header_len: {f.data_start - 8}", file=out)
-        print(f"data_start: {f.data_start}", file=out)
-        print(f"tensor_count: {len(f.tensors)}", file=out)
-        for k, v in f.metadata.items():
-            print(f"metadata.{k}: {v}", file=out)
-        for name, t in f.tensors.items():
+        for fname, f in ck.files.items():
+            print(f"weights_path: {f.path}", file=out)
+            print(f"file_size: {os.path.getsize(f.path)}", file=out)
+            print(f"header_len: {f.data_start - 8}", file=out)
+            print(f"data_start: {f.data_start}", file=out)
+            for k, v in f.metadata.items():
+                print(f"metadata.{k}: {v}", file=out)
+        print(f"shard_count: {len(ck.files)}", file=out)
+        print(f"tensor_count: {len(ck.where)}", file=out)
+        for name in ck.where:
+            t = ck.info(name)
             print(f"tensor {name}: dtype={t.dtype} shape={list(t.shape)} bytes={t.end - t.begin}", file=out)
 
 
 def inspect_tensor(model_dir: str, name: str, count: int, out) -> None:
-    from .weights import SafetensorsFile
+    from .weights import Checkpoint
 
-    with SafetensorsFile(os.path.join(model_dir, "model.safetensors")) as f:
-        if name not in f.tensors:
+    with Checkpoint(model_dir) as ck:
+        if name not in ck.where:
             raise CliError(f"TensorNotFound: {name}")
-        info = f.tensors[name]
-        vals = f.tensor(name).reshape(-1)[:count].float().tolist()
+        info = ck.info(name)
+        vals = ck.tensor(name).reshape(-1)[:count].float().tolist()
         print(f"tensor: {name}", file=out)
         print(f"dtype: {info.dtype}", file=out)
         print(f"shape: {list(info.shape)}", file=out)
@@ -176,11 +204,65 @@ def inspect_tensor(model_dir: str, name: str, count: int, out) -> None:
             print(f"value[{i}]: {v:.8f}", file=out)
 
 
-def _engine(model_dir: str, engine_opts: dict, **defaults):
-    from .engine.api import Engine
+class ModelSource:
+    """Where the weights come from: a model folder, or a configuration file and a seed
+    (``--random-weights <seed> --config <config_json>``: drawn on the GPU, nothing read or written)."""
 
-    opts = {**defaults, **engine_opts}
-    return Engine(model_dir, **opts)
+    def __init__(self, model_dir: str | None, run_opts: dict):
+        self.seed = run_opts.get("random_weights")
+        self.config_path = run_opts.get("config")
+        if (self.seed is None) != (self.config_path is None):
+            raise CliError("InvalidCommand: --random-weights <seed> and --config <config_json> go together")
+        self.model_dir = None if self.seed is not None else model_dir
+
+    @property
+    def label(self) -> str:
+        return self.model_dir if self.model_dir is not None else f"{self.config_path} (random weights, seed {self.seed})"
+
+    def engine(self, engine_opts: dict, **defaults):
+        from .engine.api import Engine
+
+        opts = {**defaults, **engine_opts}
+        if any(k in engine_opts for k in ("num_pages", "kv_cache_bytes", "kv_cache_tokens", "gpu_memory_fraction")):
+            for k in ("num_pages", "kv_cache_bytes", "kv_cache_tokens"):     # the user's choice of pool beats the command's default
+                if k not in engine_opts:
+                    opts.pop(k, None)
+        if self.model_dir is not None:
+            return Engine(self.model_dir, **opts)
+        from .config.registry import family_for
+
+        with open(self.config_path) as f:
+            raw = json.load(f)
+        return Engine(config=family_for(raw).config_class.from_dict(raw), random_weights_seed=self.seed, **opts)
+
+
+def _engine(model, engine_opts: dict, **defaults):
+    if isinstance(model, str):
+        model = ModelSource(model, {})
+    return model.engine(engine_opts, **defaults)
+
+
+def _profiled(run_opts: dict, eng, fn):
+    """Runs ``fn()``; with ``--profile <path>`` under the profiler, whose summary goes to that file."""
+    path = run_opts.get("profile")
+    if not path:
+        return fn()
+    with eng.profile(run_opts.get("hbm_gbs"), run_opts.get("bf16_tflops")) as prof:
+        res = fn()
+    prof.dump(path)
+    return res
+
+
+def _pool_lines(eng, out) -> None:
+    from .cache import bytes_per_token
+
+    kv_needs, _ = eng.runner.model.cache_needs()
+    elt = eng.runner.model.dtype.itemsize
+    print(f"weights_bytes: {eng.runner.model.weight_bytes()}", file=out)
+    print(f"kv_cache_bytes: {eng.runner.storage.bytes()}", file=out)
+    print(f"kv_bytes_per_token: {bytes_per_token(kv_needs, elt)}", file=out)
+    print(f"num_pages: {eng.runner.manager.groups[0].pool.num_pages if eng.runner.manager.groups else 0}", file=out)
+    print(f"page_size: {eng.runner.manager.page_size}", file=out)
 
 
 def probe_model(model_dir: str, token_id: int, top_k: int, engine_opts: dict, out) -> None:
@@ -212,20 +294,25 @@ def generate_token_ids(model_dir: str, ids_csv: str, steps: int, engine_opts: di
     print("tokens: [" + ", ".join(str(t) for t in seed_ids + res.token_ids) + "]", file=out)
 
 
-def generate(model_dir: str, ids_csv: str, max_new: int, sampling: dict, engine_opts: dict, out) -> None:
+def generate(model, ids_csv: str, max_new: int, sampling: dict, engine_opts: dict, out, run_opts: dict | None = None) -> None:
+    """One prompt, or several separated by ``;`` that run as one batch (ids in, ids out)."""
     from .sampling import SamplingParams
 
-    ids = parse_token_ids(ids_csv)
-    if not ids:
+    prompts = [parse_token_ids(part) for part in ids_csv.split(";") if part.strip()]
+    if not prompts or any(not p for p in prompts):
         raise CliError("EmptyPrompt")
-    eng = _engine(model_dir, engine_opts, max_requests=1, kv_cache_tokens=len(ids) + max_new + 64)
-    res = eng.generate([ids], SamplingParams(max_new_tokens=max_new, **sampling))[0]
-    print("tokens: [" + ", ".join(str(t) for t in res.token_ids) + "]", file=out)
-    print(f"finish_reason: {res.finish_reason}", file=out)
+    page = engine_opts.get("page_size", 16)
+    eng = _engine(model, engine_opts, max_requests=max(1, len(prompts)),
+                  kv_cache_tokens=sum(-(-(len(p) + max_new) // page) * page + page for p in prompts))
+    results = _profiled(run_opts or {}, eng, lambda: eng.generate(prompts, SamplingParams(max_new_tokens=max_new, **sampling)))
+    for i, res in enumerate(results):
+        tag = "" if len(results) == 1 else f"[{i}]"
+        print(f"tokens{tag}: [" + ", ".join(str(t) for t in res.token_ids) + "]", file=out)
+        print(f"finish_reason{tag}: {res.finish_reason}", file=out)
 
 
-def bench(model_dir: str, ids_csv: str, batch: int, total: int, max_new: int, sampling: dict, engine_opts: dict,
-          out) -> None:
+def bench(model, ids_csv: str, batch: int, total: int, max_new: int, sampling: dict, engine_opts: dict,
+          out, run_opts: dict | None = None) -> None:
     """Prefill and decode rates in the reference's key: value style
     (src/app/cli/tools/bench/runtime.zig:80-98,198-223,284-309)."""
     import torch
@@ -234,18 +321,19 @@ def bench(model_dir: str, ids_csv: str, batch: int, total: int, max_new: int, sa
     ids = parse_token_ids(ids_csv)
     if not ids:
         raise CliError("EmptyPrompt")
-    eng = _engine(model_dir, engine_opts, max_requests=batch, kv_cache_tokens=batch * (len(ids) + max_new + 64))
+    model = model if isinstance(model, ModelSource) else ModelSource(model, {})
+    eng = _engine(model, engine_opts, max_requests=batch, kv_cache_tokens=batch * (len(ids) + max_new + 64))
     params = SamplingParams(max_new_tokens=max_new, **{"temperature": 0.0, "ignore_eos": True, **sampling})
     eng.generate([ids], params, max_new_tokens=2)   # warm-up
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    results = eng.generate([ids] * total, params)
+    results = _profiled(run_opts or {}, eng, lambda: eng.generate([ids] * total, params))
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     st = eng.scheduler.stats
     decoded = sum(len(r.token_ids) for r in results)
     print("Zinfer benchmark", file=out)
-    print(f"model_dir: {model_dir}", file=out)
+    print(f"model_dir: {model.label}", file=out)
     print(f"batch_size: {batch}", file=out)
     print(f"total_requests: {total}", file=out)
     print(f"prompt_tokens: {len(ids)}", file=out)
@@ -254,19 +342,18 @@ def bench(model_dir: str, ids_csv: str, batch: int, total: int, max_new: int, sa
     print(f"total_tok_s: {(decoded + total * len(ids)) / dt:.2f}", file=out)
     print(f"decode_tok_s: {decoded / dt:.2f}", file=out)
     print(f"preemptions: {st.preemptions}", file=out)
-    print(f"weights_bytes: {eng.runner.model.weight_bytes()}", file=out)
-    print(f"kv_cache_bytes: {eng.runner.storage.bytes()}", file=out)
+    _pool_lines(eng, out)
 
 
-def random_model(out_dir: str, config_json: str, seed: int, out) -> None:
+def random_model(out_dir: str, config_json: str, seed: int, out, shards: int = 1) -> None:
     from .config.registry import family_for
     from .weights import write_model_dir
 
     with open(config_json) as f:
         raw = json.load(f)
     cfg = family_for(raw).config_class.from_dict(raw)
-    write_model_dir(out_dir, cfg, seed)
-    print(f"wrote {out_dir} (seed {seed})", file=out)
+    write_model_dir(out_dir, cfg, seed, shards=shards)
+    print(f"wrote {out_dir} (seed {seed}" + (f", {shards} shards)" if shards > 1 else ")"), file=out)
 
 
 # --------------------------------------------------------------------------- main
@@ -277,14 +364,27 @@ def run(argv: list[str], out=sys.stdout) -> int:
     cmd, rest = argv[0], argv[1:]
     try:
         if cmd == "random-model":
-            pos, _ = _positionals(rest)
+            pos, flags = _positionals(rest)
+            run_opts: dict = {}
+            parse_flags(flags, run_opts)
             if len(pos) < 2:
                 raise CliError("InvalidCommand")
-            random_model(pos[0], pos[1], _int(pos[2], "seed") if len(pos) > 2 else 0, out)
+            random_model(pos[0], pos[1], _int(pos[2], "seed") if len(pos) > 2 else 0, out, shards=run_opts.get("shards", 1))
             return 0
         model_dir, rest = split_model_dir(rest)
         pos, flags = _positionals(rest)
-        sampling, engine_opts = parse_flags(flags)
+        run_opts = {}
+        sampling, engine_opts = parse_flags(flags, run_opts)
+        model = ModelSource(model_dir, run_opts)
+
+        def max_new(index: int, default: int) -> int:
+            """The positional at ``index`` if present, else --max-new-tokens, else the command's default."""
+            if len(pos) > index:
+                return _int(pos[index], "max_new_tokens")
+            return run_opts.get("max_new_tokens", default)
+
+        if cmd in ("inspect-config", "inspect-weights", "inspect-tensor") and model.model_dir is None:
+            raise CliError("InvalidCommand: inspection needs a model folder")
         if cmd == "inspect-config":
             inspect_config(model_dir, out)
         elif cmd == "inspect-weights":
@@ -296,29 +396,29 @@ def run(argv: list[str], out=sys.stdout) -> int:
         elif cmd == "probe-model":
             if len(pos) < 2:
                 raise CliError("InvalidCommand")
-            probe_model(model_dir, _int(pos[0], "token_id"), _int(pos[1], "top_k"), engine_opts, out)
+            probe_model(model, _int(pos[0], "token_id"), _int(pos[1], "top_k"), engine_opts, out)
         elif cmd == "generate-token-ids":
             if len(pos) < 2:
                 raise CliError("InvalidCommand")
-            generate_token_ids(model_dir, pos[0], _int(pos[1], "steps"), engine_opts, out)
+            generate_token_ids(model, pos[0], _int(pos[1], "steps"), engine_opts, out)
         elif cmd == "generate":
             if not pos:
                 raise CliError("InvalidCommand")
-            generate(model_dir, pos[0], _int(pos[1], "max_new_tokens") if len(pos) > 1 else 64, sampling, engine_opts, out)
+            generate(model, pos[0], max_new(1, 64), sampling, engine_opts, out, run_opts)
         elif cmd == "bench":
             if not pos:
                 raise CliError("InvalidCommand")
-            bench(model_dir, pos[0], 1, 1, _int(pos[1], "max_new_tokens") if len(pos) > 1 else 16, sampling, engine_opts, out)
+            bench(model, pos[0], 1, 1, max_new(1, 16), sampling, engine_opts, out, run_opts)
         elif cmd == "bench-batch":
             if len(pos) < 2:
                 raise CliError("InvalidCommand")
             b = _int(pos[1], "batch_size")
-            bench(model_dir, pos[0], b, b, _int(pos[2], "max_new_tokens") if len(pos) > 2 else 16, sampling, engine_opts, out)
+            bench(model, pos[0], b, b, max_new(2, 16), sampling, engine_opts, out, run_opts)
         elif cmd == "bench-continuous":
             if len(pos) < 3:
                 raise CliError("InvalidCommand")
-            bench(model_dir, pos[0], _int(pos[1], "batch_size"), _int(pos[2], "total_requests"),
-                  _int(pos[3], "max_new_tokens") if len(pos) > 3 else 16, sampling, engine_opts, out)
+            bench(model, pos[0], _int(pos[1], "batch_size"), _int(pos[2], "total_requests"), max_new(3, 16), sampling,
+                  engine_opts, out, run_opts)
         else:
             print(f"error: unknown command {cmd!r}", file=sys.stderr)
             out.write(USAGE)

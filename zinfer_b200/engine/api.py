@@ -14,7 +14,7 @@ from typing import Optional, Sequence
 
 import torch
 
-from .. import ops
+from .. import ops, profiling
 from ..sampling import Sampler, SamplingParams
 from .batch import StepEntry
 from .runner import ModelRunner
@@ -48,30 +48,59 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.
 class Engine:
     """Model, cache, scheduler and sampler on one GPU.
 
-    ``Engine(model_dir)`` reads config.json and model.safetensors;
+    ``Engine(model_dir)`` reads config.json and the safetensors file(s);
     ``Engine(config=cfg, random_weights_seed=s)`` draws random weights instead.
-    ``kv_cache_tokens`` sizes the page pool (default: ``max_requests`` requests of
-    ``max_model_len`` tokens, capped by free device memory)."""
+
+    The page pool is sized by the first of these that is given: ``num_pages`` (pages per
+    cache group), ``kv_cache_tokens`` (cached tokens), ``kv_cache_bytes`` (a byte budget for
+    keys and values of all layers).  With none of them the pool takes ``gpu_memory_fraction``
+    of the device memory that is free once the weights are loaded, less what a step's
+    activations need, but never more than ``max_requests`` requests of ``max_model_len``
+    tokens could fill.  (The reference sizes one cache per request for prompt + max_new_tokens,
+    src/app/cli/runtime/generator.zig:70-79; its byte count is
+    src/model/runtime/optimized_kv_cache/cache.zig:423-456.)"""
 
     def __init__(self, model_dir: Optional[str] = None, *, config=None, random_weights_seed: Optional[int] = None,
                  dtype="bfloat16", device="cuda:0", page_size: int = 16, kv_cache_tokens: Optional[int] = None,
-                 num_pages: Optional[int] = None, max_model_len: Optional[int] = None,
+                 num_pages: Optional[int] = None, kv_cache_bytes: Optional[int] = None,
+                 gpu_memory_fraction: float = 0.9, max_model_len: Optional[int] = None,
                  max_batched_tokens: int = 2048, chunk_size: Optional[int] = None, max_requests: int = 64,
                  pipelined: bool = True):
         tdtype = _DTYPES.get(dtype)
         if tdtype is None:
             raise ValueError(f"dtype must be bfloat16 or float32, got {dtype!r}")
-        kw = dict(dtype=tdtype, device=device, max_model_len=max_model_len, page_size=page_size,
-                  max_requests=max_requests)
-        self._pool_args = (kv_cache_tokens, num_pages)
-        sizing = self._size_pool(model_dir, config, tdtype, device, page_size, max_model_len, max_requests)
+        if not 0.0 < gpu_memory_fraction <= 1.0:
+            raise ValueError("gpu_memory_fraction must lie in (0, 1]")
         if model_dir is not None:
-            self.runner = ModelRunner.from_model_dir(model_dir, num_pages=sizing, **kw)
+            from ..config.registry import load_config
+            cfg = load_config(model_dir)[1]
         elif config is not None:
-            self.runner = ModelRunner.from_config(config, 0 if random_weights_seed is None else random_weights_seed,
-                                                  num_pages=sizing, **kw)
+            cfg = config
         else:
             raise ValueError("give a model folder, or a configuration with random_weights_seed")
+        kw = dict(dtype=tdtype, device=device, max_model_len=max_model_len, page_size=page_size,
+                  max_requests=max_requests)
+        if num_pages is not None:
+            kw["num_pages"] = num_pages
+        elif kv_cache_tokens is not None:
+            kw["max_tokens"] = kv_cache_tokens
+        else:
+            limit = min(getattr(cfg, "max_position_embeddings", 4096), max_model_len or 1 << 30)
+            per_request = -(-limit // page_size) * page_size
+            if kv_cache_bytes is not None:
+                kw.update(kv_cache_bytes=kv_cache_bytes, max_tokens=max_requests * per_request)
+            elif torch.device(device).type == "cuda":
+                spec_hidden = getattr(cfg, "hidden_size", 4096)
+                spec_vocab = getattr(cfg, "vocab_size", 1 << 17)
+                workspace = max_batched_tokens * spec_hidden * 64 + 8 * max_requests * spec_vocab * 4 + (1 << 30)
+                kw.update(gpu_memory_fraction=gpu_memory_fraction, workspace_bytes=workspace,
+                          max_tokens=max_requests * per_request)
+            else:
+                kw["max_tokens"] = max_requests * min(per_request, 8192)
+        if model_dir is not None:
+            self.runner = ModelRunner.from_model_dir(model_dir, **kw)
+        else:
+            self.runner = ModelRunner.from_config(config, 0 if random_weights_seed is None else random_weights_seed, **kw)
         model = self.runner.model
         self.scheduler = Scheduler(self.runner.manager, max_batched_tokens=max_batched_tokens,
                                    max_running=max_requests, chunk_size=chunk_size, max_model_len=model.max_positions)
@@ -84,17 +113,6 @@ class Engine:
         pin = torch.cuda.is_available() and model.device.type == "cuda"
         self._token_buffers = [torch.zeros(max_requests, dtype=torch.int32, pin_memory=pin) for _ in range(3)]
         self._token_turn = 0
-
-    def _size_pool(self, model_dir, config, dtype, device, page_size, max_model_len, max_requests) -> int:
-        kv_cache_tokens, num_pages = self._pool_args
-        if num_pages is not None:
-            return num_pages
-        if kv_cache_tokens is None:
-            from ..config.registry import load_config
-            cfg = config if config is not None else load_config(model_dir)[1]
-            limit = min(getattr(cfg, "max_position_embeddings", 4096), max_model_len or 1 << 30)
-            kv_cache_tokens = max_requests * min(limit, 8192)
-        return max(1, -(-kv_cache_tokens // page_size))
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_ids: Sequence[int], params: Optional[SamplingParams] = None, request_id=None):
@@ -193,6 +211,12 @@ class Engine:
 
     def has_unfinished(self) -> bool:
         return self.scheduler.has_unfinished() or self._inflight is not None
+
+    def profile(self, hbm_gbs: Optional[float] = None, bf16_tflops: Optional[float] = None):
+        """``with engine.profile(...) as prof:`` times every kernel launched by the steps inside the
+        block per kernel class (see :mod:`zinfer_b200.profiling`); ``prof.summary()`` or
+        ``prof.dump(path)`` afterwards.  The peaks, when given, turn times into fractions of the roofline."""
+        return profiling.profile(hbm_gbs, bf16_tflops)
 
     # ------------------------------------------------------------------ generate
     def generate(self, prompt_ids: Sequence[Sequence[int]], params=None, **options) -> list[GenerationResult]:

@@ -103,6 +103,8 @@ def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile
     n_groups = len(manager.groups)
     if static is not None:
         assert all(q == 1 for q in q_lens) and n_real <= static.batch
+        assert all(len(manager.block_table(e.request_id, gi)) <= static.width for e in entries for gi in range(n_groups)), \
+            "a request is longer than its bucket's block tables"
         n = static.batch
         widths = [static.width] * n_groups
     else:
@@ -223,8 +225,9 @@ def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile
         n_patch=len(patches),
         logit_rows=view("logit_rows") if R else None, kv_groups=groups, q_lens=q_lens, ctx_lens=ctx_lens,
         max_q_len=max(q_lens, default=0),
-        # a captured graph serves later steps with longer requests: no host-side length may shape its launches
-        max_kv_len=0 if static is not None else max((c + q for c, q in zip(ctx_lens, q_lens)), default=0),
+        # a captured graph serves later steps with longer requests: its launches are shaped by the
+        # bucket's length, never by the lengths of the step that happened to be captured
+        max_kv_len=static.max_kv_len if static is not None else max((c + q for c, q in zip(ctx_lens, q_lens)), default=0),
         all_decode=all(q == 1 for q in q_lens), h2d_bytes=int(total) * 4)
 
 
@@ -233,9 +236,10 @@ class StaticStepBuffers:
     batch-size bucket, so that a captured CUDA graph finds every step's arrays at the
     same place."""
 
-    def __init__(self, batch: int, width: int, device):
+    def __init__(self, batch: int, width: int, device, max_kv_len: int = 0):
         self.batch = batch
-        self.width = width
+        self.width = width                # columns of every block table
+        self.max_kv_len = max_kv_len      # the longest request the bucket serves (0: unknown)
         self.device = device
         self._host = None
         self._dev = None

@@ -16,8 +16,8 @@ from typing import Hashable, Optional, Sequence
 
 import torch
 
-from .. import ops
-from ..cache import CacheManager, CacheStorage, OutOfPages
+from .. import ops, profiling
+from ..cache import CacheManager, CacheStorage, OutOfPages, pages_for
 from ..config.registry import load_config
 from ..weights import load_tensors, random_tensors
 from .batch import PinnedStaging, StepContext, StepEntry, build_step
@@ -35,18 +35,28 @@ def _require_cuda(device: torch.device) -> None:
 
 class ModelRunner:
     def __init__(self, model: DecoderModel, page_size: int = 16, num_pages: Optional[int] = None,
-                 max_tokens: Optional[int] = None, max_requests: int = 64, cuda_graphs: bool = True):
-        """``max_tokens`` sizes each group's pool for that many cached tokens
-        (rounded up to whole pages); ``num_pages`` gives the page count directly."""
+                 max_tokens: Optional[int] = None, max_requests: int = 64, cuda_graphs: bool = True,
+                 kv_cache_bytes: Optional[int] = None, gpu_memory_fraction: Optional[float] = None,
+                 workspace_bytes: int = 0):
+        """The page pool is sized, in this order of precedence, by ``num_pages`` (pages per
+        group), by ``kv_cache_bytes`` (a byte budget for all groups together), by
+        ``gpu_memory_fraction`` (that share of the device memory which is free now, the weights
+        being loaded already, minus ``workspace_bytes`` kept for activations), each capped by
+        ``max_tokens`` cached tokens when that is given too; or by ``max_tokens`` alone."""
         _require_cuda(model.device)
         ops.lib()  # fail now, and loudly, if the kernel library cannot be built or loaded
         self.model = model
         self.device = model.device
-        if num_pages is None:
-            if max_tokens is None:
-                raise ValueError("give num_pages or max_tokens")
-            num_pages = -(-max_tokens // page_size)
         kv_needs, state_needs = model.cache_needs()
+        if num_pages is None:
+            elt = torch.empty((), dtype=model.dtype).element_size()
+            budget = kv_cache_bytes
+            if budget is None and gpu_memory_fraction is not None and model.device.type == "cuda":
+                free, _total = torch.cuda.mem_get_info(model.device)
+                budget = int(free * gpu_memory_fraction) - workspace_bytes
+            if budget is None and max_tokens is None:
+                raise ValueError("give num_pages, kv_cache_bytes, gpu_memory_fraction or max_tokens")
+            num_pages = pages_for(kv_needs, page_size, elt, budget_bytes=budget, tokens=max_tokens)
         self.manager = CacheManager(kv_needs, list(state_needs), page_size, num_pages, max_requests)
         self.storage = CacheStorage(self.manager, state_needs, model.dtype, self.device)
         model.attach(self.storage)
@@ -166,7 +176,9 @@ class ModelRunner:
         if any(e.token_src is not None for e in entries) and prev_tokens is None:
             raise StepError("an entry takes its token from the step before, but no such tokens were given")
         self.reserve(entries)
-        if self.graphs is not None and self.graphs.eligible(entries):
+        if profiling.ACTIVE is not None:
+            profiling.ACTIVE.steps += 1      # profiled steps launch their kernels one by one, never from a graph
+        if self.graphs is not None and profiling.ACTIVE is None and self.graphs.eligible(entries):
             all_rows = self.graphs.run(entries, prev_tokens)
             wanted = [i for i, e in enumerate(entries) if len(e.want)]
             if not wanted:

@@ -14,6 +14,7 @@ from typing import Optional
 
 import torch
 
+from . import profiling as _prof
 from .csrc import build as _build
 
 
@@ -103,6 +104,11 @@ def _need(cond: bool, msg: str) -> None:
         raise KernelError(msg)
 
 
+def _nb(*tensors) -> int:
+    """Bytes of the given tensors (None counts nothing)."""
+    return sum(t.numel() * t.element_size() for t in tensors if t is not None)
+
+
 def _i32(t: torch.Tensor, name: str) -> torch.Tensor:
     _need(t.dtype == torch.int32 and t.is_contiguous(), f"{name} must be a contiguous int32 tensor")
     return t
@@ -143,7 +149,8 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Ten
     _i32(ids, "ids")
     if out is None:
         out = torch.empty((T, H), dtype=torch.float32, device=table.device)
-    _check(lib().zi_embed_gather(_ptr(out), _ptr(table), _tag(table), _ptr(ids), T, H, V, _stream()), "embed_gather")
+    with _prof.region("embed_gather", lambda: T * H * table.element_size() + _nb(out, ids)):
+        _check(lib().zi_embed_gather(_ptr(out), _ptr(table), _tag(table), _ptr(ids), T, H, V, _stream()), "embed_gather")
     return out
 
 
@@ -174,9 +181,11 @@ def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
     n = T if rows is None else _i32(rows, "rows").shape[0]
     if out is None:
         out = torch.empty((n, H), dtype=out_dtype, device=h.device)
-    _check(lib().zi_add_rmsnorm(_ptr(h), _ptr(delta), _tag(delta) if delta is not None else F32, _ptr(part), splits,
-                                ctypes.c_longlong(zstride), _ptr(weight), ctypes.c_float(eps), _ptr(out), _tag(out),
-                                _ptr(rows), n, H, _stream()), "add_rmsnorm")
+    with _prof.region("add_rmsnorm", lambda: (2 if rows is None else 1) * n * H * 4 + _nb(out, weight)
+                      + (n * H * delta.element_size() if delta is not None else 0) + splits * n * H * 4):
+        _check(lib().zi_add_rmsnorm(_ptr(h), _ptr(delta), _tag(delta) if delta is not None else F32, _ptr(part), splits,
+                                    ctypes.c_longlong(zstride), _ptr(weight), ctypes.c_float(eps), _ptr(out), _tag(out),
+                                    _ptr(rows), n, H, _stream()), "add_rmsnorm")
     return out
 
 
@@ -185,8 +194,9 @@ def residual_add(h: torch.Tensor, delta) -> None:
         delta = delta.sum(torch.float32)
     _need(h.dtype == torch.float32 and h.is_contiguous() and delta.is_contiguous() and delta.shape == h.shape,
           "residual_add: shapes must match and be contiguous")
-    _check(lib().zi_residual_add(_ptr(h), _ptr(delta), _tag(delta), ctypes.c_longlong(h.numel()), _stream()),
-           "residual_add")
+    with _prof.region("residual_add", lambda: 2 * _nb(h) + _nb(delta)):
+        _check(lib().zi_residual_add(_ptr(h), _ptr(delta), _tag(delta), ctypes.c_longlong(h.numel()), _stream()),
+               "residual_add")
 
 
 def swiglu(gate_up, out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
@@ -199,8 +209,9 @@ def swiglu(gate_up, out: Optional[torch.Tensor] = None, out_dtype: Optional[torc
         I = two_i // 2
         if I % 4 == 0:
             res = torch.empty((T, I), dtype=out_dtype or torch.bfloat16, device=gate_up.data.device)
-            _check(lib().zi_swiglu_partials(_ptr(res), _tag(res), _ptr(gate_up.data), gate_up.splits,
-                                            ctypes.c_longlong(T * two_i), T, I, interleave, _stream()), "swiglu")
+            with _prof.region("swiglu (partial sums)", lambda: _nb(res, gate_up.data)):
+                _check(lib().zi_swiglu_partials(_ptr(res), _tag(res), _ptr(gate_up.data), gate_up.splits,
+                                                ctypes.c_longlong(T * two_i), T, I, interleave, _stream()), "swiglu")
             return res
         gate_up = gate_up.sum(out_dtype or torch.bfloat16)
     T, two_i = gate_up.shape
@@ -208,7 +219,8 @@ def swiglu(gate_up, out: Optional[torch.Tensor] = None, out_dtype: Optional[torc
     I = two_i // 2
     if out is None:
         out = torch.empty((T, I), dtype=gate_up.dtype, device=gate_up.device)
-    _check(lib().zi_swiglu(_ptr(out), _ptr(gate_up), _tag(gate_up), T, I, interleave, _stream()), "swiglu")
+    with _prof.region("swiglu", lambda: _nb(out, gate_up)):
+        _check(lib().zi_swiglu(_ptr(out), _ptr(gate_up), _tag(gate_up), T, I, interleave, _stream()), "swiglu")
     return out
 
 
@@ -233,8 +245,9 @@ def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out_dtype: Optio
             and x.stride(1) == 1 and w_interleaved.is_contiguous()
             and lib().zi_gemm_tcgen05_supported(_ptr(x), _ptr(w_interleaved), K, x.stride(0), w_interleaved.stride(0))):
         out = torch.empty((M, N2 // 2), dtype=out_dtype or x.dtype, device=x.device)
-        code = lib().zi_gemm_tcgen05_swiglu(_ptr(out), _tag(out), _ptr(x), _ptr(w_interleaved), M, N2, K, x.stride(0),
-                                            w_interleaved.stride(0), out.stride(0), _sm_count(x.device), _stream())
+        with _prof.region(f"linear+swiglu N={N2} K={K}", lambda: _nb(w_interleaved, out) + M * K * 2, 2 * M * N2 * K):
+            code = lib().zi_gemm_tcgen05_swiglu(_ptr(out), _tag(out), _ptr(x), _ptr(w_interleaved), M, N2, K, x.stride(0),
+                                                w_interleaved.stride(0), out.stride(0), _sm_count(x.device), _stream())
         if code != -2:
             _check(code, "linear_swiglu")
             return out
@@ -285,11 +298,13 @@ def qk_norm_rope_store(qkv, num_heads: int, num_kv_heads: int, head_dim: int,
         _need(k_cache is not None and v_cache is not None and slots is not None, "writing needs pages and slots")
         _need(k_cache.dtype == q_out.dtype and v_cache.dtype == q_out.dtype, "cache pages have the activations' dtype")
         _i32(slots, "slots")
-    _check(lib().zi_qk_norm_rope_store(
-        _ptr(src), dtype_tag, T, src_stride, _ptr(part), splits, ctypes.c_longlong(zstride), _ptr(q_out),
-        q_out.stride(0), num_heads, num_kv_heads, head_dim, _ptr(q_weight), _ptr(k_weight), ctypes.c_float(eps),
-        _ptr(cos), _ptr(sin), n_table, _ptr(positions), _ptr(k_cache), _ptr(v_cache), _ptr(slots), page_size,
-        1 if write_kv else 0, _stream()), "qk_norm_rope_store")
+    with _prof.region("qk_norm_rope_store", lambda: (2 * T * width * q_out.element_size() if part is None else
+                                                      _nb(part) + T * width * q_out.element_size())):
+        _check(lib().zi_qk_norm_rope_store(
+            _ptr(src), dtype_tag, T, src_stride, _ptr(part), splits, ctypes.c_longlong(zstride), _ptr(q_out),
+            q_out.stride(0), num_heads, num_kv_heads, head_dim, _ptr(q_weight), _ptr(k_weight), ctypes.c_float(eps),
+            _ptr(cos), _ptr(sin), n_table, _ptr(positions), _ptr(k_cache), _ptr(v_cache), _ptr(slots), page_size,
+            1 if write_kv else 0, _stream()), "qk_norm_rope_store")
     return q_out
 
 
@@ -328,15 +343,18 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
         defer = allow_partials and need > 0 and out is None
         if out is None and not defer:
             out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
-        _check(lib().zi_gemm_tcgen05(_ptr(out), _tag(out) if out is not None else BF16, _ptr(x), _ptr(weight), M, N, K,
-                                     x.stride(0), weight.stride(0), out.stride(0) if out is not None else N, _ptr(ws),
-                                     ctypes.c_longlong(need), sms, 1 if defer else 0, _stream()), "linear (tcgen05)")
+        with _prof.region(f"linear N={N} K={K}", lambda: _nb(weight) + M * K * 2 + (_nb(ws) if defer else _nb(out)),
+                          2 * M * N * K):
+            _check(lib().zi_gemm_tcgen05(_ptr(out), _tag(out) if out is not None else BF16, _ptr(x), _ptr(weight), M, N, K,
+                                         x.stride(0), weight.stride(0), out.stride(0) if out is not None else N, _ptr(ws),
+                                         ctypes.c_longlong(need), sms, 1 if defer else 0, _stream()), "linear (tcgen05)")
         return Partials(ws.view(plan[2], M, N)) if defer else out
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
     _need(out.stride(1) == 1, "linear: output rows must be dense")
-    _check(lib().zi_gemm_simt(_ptr(out), _tag(out), _ptr(x), _tag(x), _ptr(weight), _tag(weight), M, N, K,
-                              x.stride(0), weight.stride(0), out.stride(0), _stream()), "linear")
+    with _prof.region(f"linear (CUDA cores) N={N} K={K}", lambda: _nb(weight, out) + M * K * x.element_size(), 2 * M * N * K):
+        _check(lib().zi_gemm_simt(_ptr(out), _tag(out), _ptr(x), _tag(x), _ptr(weight), _tag(weight), M, N, K,
+                                  x.stride(0), weight.stride(0), out.stride(0), _stream()), "linear")
     return out
 
 
@@ -365,11 +383,12 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         _i32(t, name)
     if out is None:
         out = torch.empty((T, num_heads * head_dim), dtype=q.dtype, device=q.device)
-    _check(lib().zi_paged_attention(
-        _ptr(out), out.stride(0), _ptr(q), q.stride(0), _tag(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
-        block_tables.stride(0), _ptr(cu_q), _ptr(kv_lens), _ptr(tile_seq), _ptr(tile_q0), tile_seq.shape[0],
-        num_heads, num_kv_heads, head_dim, page_size, int(window or 0), ctypes.c_float(scale), _stream()),
-        "paged_attention")
+    with _prof.region("attention (exact, CUDA cores)"):
+        _check(lib().zi_paged_attention(
+            _ptr(out), out.stride(0), _ptr(q), q.stride(0), _tag(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+            block_tables.stride(0), _ptr(cu_q), _ptr(kv_lens), _ptr(tile_seq), _ptr(tile_q0), tile_seq.shape[0],
+            num_heads, num_kv_heads, head_dim, page_size, int(window or 0), ctypes.c_float(scale), _stream()),
+            "paged_attention")
     return out
 
 
@@ -379,6 +398,18 @@ ATTENTION_BACKEND = os.environ.get("ZINFER_B200_ATTENTION", "auto")   # auto | g
 # 2,048 tokens of 32 heads of 128, head size 128 only) with "mma" (mma.sync flash attention, 160 us)
 # for the shapes the first does not take; or "mma" always.
 PREFILL_ATTENTION = os.environ.get("ZINFER_B200_PREFILL_ATTENTION", "tcgen05")
+
+
+def _attention_work(step, decode: bool, num_heads: int, num_kv_heads: int, head_dim: int, elt: int) -> tuple[int, int]:
+    """(bytes, flops) of the attention of a step's decode requests (one token) or of its others:
+    every key and value of those requests once, their queries and outputs; 4 d per (query, key) pair."""
+    nbytes = flops = 0
+    for q, c in zip(step.q_lens, step.ctx_lens):
+        if (q == 1) != decode:
+            continue
+        nbytes += 2 * (c + q) * num_kv_heads * head_dim * elt + 2 * q * num_heads * head_dim * elt
+        flops += 4 * num_heads * head_dim * (q * c + q * (q + 1) // 2)
+    return nbytes, flops
 
 
 def attention_prefill_tile_rows() -> int:
@@ -407,27 +438,32 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, blo
           "cache pages are [pages, kv heads, page, d] in the activations' dtype")
     out = torch.empty((T, num_heads * head_dim), dtype=q.dtype, device=q.device)
     win = int(window or 0)
+    work = lambda decode: _attention_work(step, decode, num_heads, num_kv_heads, head_dim, q.element_size()) \
+        if _prof.ACTIVE is not None else (0, 0)
     if step.n_pf_tiles > 0 and PREFILL_ATTENTION == "tcgen05" and L.zi_attention_prefill_tcgen05_supported(
             num_heads, num_kv_heads, head_dim, page_size, _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache)):
-        _check(L.zi_attention_prefill_tcgen05(
-            _ptr(out), out.stride(0), _ptr(q), q.stride(0), T, _ptr(k_cache), _ptr(v_cache),
-            ctypes.c_longlong(k_cache.shape[0]), _ptr(block_tables), block_tables.stride(0), _ptr(step.cu_q),
-            _ptr(step.kv_lens), _ptr(step.pf_tile_seq), _ptr(step.pf_tile_q0), step.n_pf_tiles, num_heads, num_kv_heads,
-            head_dim, page_size, win, ctypes.c_float(scale), _stream()), "attention (prefill, tcgen05)")
+        with _prof.region("attention (prefill, tcgen05)", *work(False)):
+            _check(L.zi_attention_prefill_tcgen05(
+                _ptr(out), out.stride(0), _ptr(q), q.stride(0), T, _ptr(k_cache), _ptr(v_cache),
+                ctypes.c_longlong(k_cache.shape[0]), _ptr(block_tables), block_tables.stride(0), _ptr(step.cu_q),
+                _ptr(step.kv_lens), _ptr(step.pf_tile_seq), _ptr(step.pf_tile_q0), step.n_pf_tiles, num_heads, num_kv_heads,
+                head_dim, page_size, win, ctypes.c_float(scale), _stream()), "attention (prefill, tcgen05)")
     elif step.n_pf_tiles > 0:
-        _check(L.zi_attention_prefill_mma(
-            _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
-            block_tables.stride(0), _ptr(step.cu_q), _ptr(step.kv_lens), _ptr(step.pf_tile_seq), _ptr(step.pf_tile_q0),
-            step.n_pf_tiles, num_heads, num_kv_heads, head_dim, page_size, win, ctypes.c_float(scale), _stream()),
-            "attention (prefill)")
+        with _prof.region("attention (prefill, mma.sync)", *work(False)):
+            _check(L.zi_attention_prefill_mma(
+                _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+                block_tables.stride(0), _ptr(step.cu_q), _ptr(step.kv_lens), _ptr(step.pf_tile_seq), _ptr(step.pf_tile_q0),
+                step.n_pf_tiles, num_heads, num_kv_heads, head_dim, page_size, win, ctypes.c_float(scale), _stream()),
+                "attention (prefill)")
     if step.n_dec > 0:
         splits = decode_splits(step.n_dec, num_kv_heads, _sm_count(q.device), step.max_kv_len)
         need = L.zi_attention_decode_workspace_floats(step.n_dec, num_heads, num_kv_heads, head_dim, splits)
         ws = torch.empty((need,), dtype=torch.float32, device=q.device) if need else None
-        _check(L.zi_attention_decode_mma(
-            _ptr(out), out.stride(0), _ptr(ws), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
-            block_tables.stride(0), _ptr(step.cu_q), _ptr(step.kv_lens), _ptr(step.dec_seq), step.n_dec, num_heads,
-            num_kv_heads, head_dim, page_size, win, ctypes.c_float(scale), splits, _stream()), "attention (decode)")
+        with _prof.region("attention (decode)", *work(True)):
+            _check(L.zi_attention_decode_mma(
+                _ptr(out), out.stride(0), _ptr(ws), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+                block_tables.stride(0), _ptr(step.cu_q), _ptr(step.kv_lens), _ptr(step.dec_seq), step.n_dec, num_heads,
+                num_kv_heads, head_dim, page_size, win, ctypes.c_float(scale), splits, _stream()), "attention (decode)")
     return out
 
 
@@ -501,12 +537,14 @@ def attention_decode_fused(qkv, num_heads: int, num_kv_heads: int, head_dim: int
     splits = decode_splits(step.n_dec, num_kv_heads, _sm_count(device), step.max_kv_len, fixed_us=8.0)
     need = L.zi_attention_decode_workspace_floats(step.n_dec, num_heads, num_kv_heads, head_dim, splits)
     ws = torch.empty((need,), dtype=torch.float32, device=device) if need else None
-    _check(L.zi_attention_decode_fused(
-        _ptr(out), out.stride(0), _ptr(ws), _ptr(src), src_stride, _ptr(part), psplits, ctypes.c_longlong(pz),
-        _ptr(q_weight), _ptr(k_weight), ctypes.c_float(eps), _ptr(cos), _ptr(sin), n_table, _ptr(step.positions),
-        _ptr(slots), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), block_tables.stride(0), _ptr(step.cu_q),
-        _ptr(step.kv_lens), _ptr(step.dec_seq), step.n_dec, num_heads, num_kv_heads, head_dim, page_size,
-        int(window or 0), ctypes.c_float(scale), splits, _stream()), "attention (fused decode)")
+    work = _attention_work(step, True, num_heads, num_kv_heads, head_dim, 2) if _prof.ACTIVE is not None else (0, 0)
+    with _prof.region("attention (decode, fused with q/k norm, rotary, cache write)", work[0] + _nb(part), work[1]):
+        _check(L.zi_attention_decode_fused(
+            _ptr(out), out.stride(0), _ptr(ws), _ptr(src), src_stride, _ptr(part), psplits, ctypes.c_longlong(pz),
+            _ptr(q_weight), _ptr(k_weight), ctypes.c_float(eps), _ptr(cos), _ptr(sin), n_table, _ptr(step.positions),
+            _ptr(slots), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), block_tables.stride(0), _ptr(step.cu_q),
+            _ptr(step.kv_lens), _ptr(step.dec_seq), step.n_dec, num_heads, num_kv_heads, head_dim, page_size,
+            int(window or 0), ctypes.c_float(scale), splits, _stream()), "attention (fused decode)")
     return out
 
 
@@ -645,7 +683,8 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)
     chunks = lib().zi_argmax_chunks(R, V)
     ws = torch.empty((2 * R * chunks,), dtype=torch.int32, device=logits.device) if chunks else None
-    _check(lib().zi_argmax(_ptr(out), _ptr(logits), R, V, logits.stride(0), _ptr(ws), _stream()), "argmax")
+    with _prof.region("argmax", lambda: R * V * 4):
+        _check(lib().zi_argmax(_ptr(out), _ptr(logits), R, V, logits.stride(0), _ptr(ws), _stream()), "argmax")
     return out
 
 
@@ -673,10 +712,11 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, seeds: torch.Tensor,
         _need(counts.dtype == torch.int32 and counts.shape[1] == V and counts.is_contiguous(), "counts are int32 [slots, V]")
     if out is None:
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)
-    _check(lib().zi_sample(_ptr(out), _ptr(logits), R, V, logits.stride(0), _ptr(temperature), _ptr(top_k),
-                           _ptr(top_p), _ptr(min_p), _ptr(repetition_penalty), _ptr(presence_penalty),
-                           _ptr(frequency_penalty), _ptr(count_rows), _ptr(counts), _ptr(seeds), _ptr(draw_index),
-                           _stream()), "sample")
+    with _prof.region("sample", lambda: R * V * 4 * (2 if counts is not None else 1)):
+        _check(lib().zi_sample(_ptr(out), _ptr(logits), R, V, logits.stride(0), _ptr(temperature), _ptr(top_k),
+                               _ptr(top_p), _ptr(min_p), _ptr(repetition_penalty), _ptr(presence_penalty),
+                               _ptr(frequency_penalty), _ptr(count_rows), _ptr(counts), _ptr(seeds), _ptr(draw_index),
+                               _stream()), "sample")
     return out
 
 

@@ -1,0 +1,108 @@
+"""Device time per kernel class, behind a switch.
+
+While a :class:`Profiler` is active every kernel launch that goes through
+``zinfer_b200.ops`` is bracketed by two CUDA events on the launching stream and filed
+under its class (the operation, and for matrix products their shape) together with
+the bytes it has to move and the floating-point operations it has to do.
+``summary()`` waits for the device and gives, per class: launches, milliseconds,
+bytes, flops, and the fraction of the roofline reached, i.e. the time the class
+would take at the peak rates (the larger of bytes / memory bandwidth and
+flops / tensor throughput) divided by the time it took.
+
+Profiled steps run their kernels one by one: decode steps are not replayed from CUDA
+graphs, and an event between two kernels keeps the second from starting under the
+first's tail as it does in normal operation, so the sum over classes is a little
+above a normal step's time.  The figures are for finding where time goes; the
+benchmark's numbers are never taken under a profiler.
+
+The reference times its phases on the host and prints nanoseconds per operation
+(src/app/cli/tools/bench/runtime.zig:57-71, src/app/cli/tools/bench/ops.zig:531-542).
+"""
+from __future__ import annotations
+
+import json
+from contextlib import contextmanager
+from typing import Optional
+
+import torch
+
+ACTIVE: Optional["Profiler"] = None     # read by ops on every launch; None: no cost beyond this test
+
+
+class Profiler:
+    def __init__(self, hbm_gbs: Optional[float] = None, bf16_tflops: Optional[float] = None):
+        self.hbm_gbs = hbm_gbs
+        self.bf16_tflops = bf16_tflops
+        self._records: list[tuple[str, object, object, int, int]] = []
+        self.steps = 0
+
+    @contextmanager
+    def region(self, name: str, nbytes: int = 0, flops: int = 0):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        try:
+            yield
+        finally:
+            end.record()
+            self._records.append((name, start, end, int(nbytes), int(flops)))
+
+    def summary(self) -> dict:
+        torch.cuda.synchronize()
+        classes: dict[str, dict] = {}
+        for name, start, end, nbytes, flops in self._records:
+            c = classes.setdefault(name, {"class": name, "launches": 0, "ms": 0.0, "bytes": 0, "flops": 0})
+            c["launches"] += 1
+            c["ms"] += start.elapsed_time(end)
+            c["bytes"] += nbytes
+            c["flops"] += flops
+        rows = sorted(classes.values(), key=lambda c: -c["ms"])
+        total = sum(c["ms"] for c in rows)
+        for c in rows:
+            c["ms"] = round(c["ms"], 4)
+            c["share"] = round(c["ms"] / total, 4) if total > 0 else 0.0
+            c["us_per_launch"] = round(1e3 * c["ms"] / c["launches"], 2)
+            floor_ms = 0.0
+            if self.hbm_gbs:
+                floor_ms = max(floor_ms, c["bytes"] / (self.hbm_gbs * 1e9) * 1e3)
+            if self.bf16_tflops:
+                floor_ms = max(floor_ms, c["flops"] / (self.bf16_tflops * 1e12) * 1e3)
+            c["roofline_frac"] = round(floor_ms / c["ms"], 4) if c["ms"] > 0 and floor_ms > 0 else None
+        return {"steps": self.steps, "total_ms": round(total, 4), "peaks": {"hbm_gbs": self.hbm_gbs,
+                "bf16_tflops": self.bf16_tflops}, "classes": rows}
+
+    def dump(self, path: str) -> dict:
+        s = self.summary()
+        with open(path, "w") as f:
+            json.dump(s, f, indent=1)
+        return s
+
+
+@contextmanager
+def profile(hbm_gbs: Optional[float] = None, bf16_tflops: Optional[float] = None):
+    """Activates a profiler for the kernel launches made inside the block."""
+    global ACTIVE
+    prof, before = Profiler(hbm_gbs, bf16_tflops), ACTIVE
+    ACTIVE = prof
+    try:
+        yield prof
+    finally:
+        ACTIVE = before
+
+
+class _Null:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NULL = _Null()
+
+
+def region(name: str, nbytes=0, flops=0):
+    """A timed region if a profiler is active, else a context that does nothing.  ``nbytes``
+    and ``flops`` may be callables, evaluated only when a profiler is active."""
+    if ACTIVE is None:
+        return _NULL
+    return ACTIVE.region(name, nbytes() if callable(nbytes) else nbytes, flops() if callable(flops) else flops)

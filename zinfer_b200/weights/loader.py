@@ -1,4 +1,4 @@
-"""Fills a model's declared tensors from a safetensors file, by tensor name.
+"""Fills a model's declared tensors from a model folder's safetensors file or shards, by tensor name.
 
 The model declares every tensor it needs (name, shape, optional or not).  The
 loader compares that list with the file and raises ONE error naming all missing
@@ -12,12 +12,10 @@ it does not find (src/tensor/storage/store.zig:35-45).
 """
 from __future__ import annotations
 
-import os
-
 import torch
 
 from ..parts.base import TensorSpec
-from .safetensors_io import SafetensorsFile
+from .checkpoint import Checkpoint
 
 
 class WeightsError(ValueError):
@@ -61,17 +59,15 @@ def check_against(path: str, available: dict[str, tuple[tuple[int, ...], torch.d
 
 
 def load_tensors(model_dir: str, specs: dict[str, TensorSpec], run_dtype: torch.dtype, device) -> dict[str, torch.Tensor]:
-    path = os.path.join(model_dir, "model.safetensors")
-    if not os.path.exists(path):
-        raise FileNotFoundError(f"{path}: no such file (a model folder holds config.json and model.safetensors)")
-    with SafetensorsFile(path) as f:
-        available = {n: (t.shape, t.torch_dtype) for n, t in f.tensors.items()}
-        check_against(path, available, specs)
+    """One error (:class:`WeightsError`) for everything missing, unexpected or misshapen, over
+    all shards together; then every declared tensor is copied to ``device``, shard by shard."""
+    with Checkpoint(model_dir) as ck:
+        available = ck.available()
+        check_against(ck.path, available, specs)
         out = {}
-        for name, spec in specs.items():
-            if name not in available:
-                continue
-            src = f.tensor(name)
-            dt = kept_dtype(src.dtype, spec, run_dtype)
+        # shard by shard, so that each mapping is walked once from front to back
+        for name in sorted((n for n in specs if n in available), key=lambda n: (ck.where[n], ck.info(n).begin)):
+            src = ck.tensor(name)
+            dt = kept_dtype(src.dtype, specs[name], run_dtype)
             out[name] = src.to(device=device, dtype=dt, copy=True)
-        return out
+        return {n: out[n] for n in specs if n in out}

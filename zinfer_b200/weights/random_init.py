@@ -51,9 +51,10 @@ def random_tensors(specs: dict[str, TensorSpec], seed: int, dtype: torch.dtype, 
     return {n: random_tensor(n, s, seed, dtype, device) for n, s in specs.items() if include_optional or not s.optional}
 
 
-def write_model_dir(path: str, config, seed: int, dtype: torch.dtype = torch.bfloat16) -> str:
-    """Writes ``config.json`` and ``model.safetensors`` for a typed configuration
-    of a registered architecture; returns ``path``."""
+def write_model_dir(path: str, config, seed: int, dtype: torch.dtype = torch.bfloat16, shards: int = 1) -> str:
+    """Writes ``config.json`` and ``model.safetensors`` (or, with ``shards`` > 1, that many
+    shard files and ``model.safetensors.index.json``) for a typed configuration of a
+    registered architecture; returns ``path``.  The tensors do not depend on ``shards``."""
     from ..config.registry import family_for
     from ..engine.model import declared_tensors
 
@@ -64,6 +65,10 @@ def write_model_dir(path: str, config, seed: int, dtype: torch.dtype = torch.bfl
     os.makedirs(path, exist_ok=True)
     with open(os.path.join(path, "config.json"), "w") as f:
         json.dump(raw, f, indent=2)
-    write_safetensors(os.path.join(path, "model.safetensors"), random_tensors(specs, seed, dtype),
-                      metadata={"format": "pt", "seed": str(seed)})
+    tensors, meta = random_tensors(specs, seed, dtype), {"format": "pt", "seed": str(seed)}
+    if shards > 1:
+        from .checkpoint import write_sharded
+        write_sharded(path, tensors, shards, metadata=meta)
+    else:
+        write_safetensors(os.path.join(path, "model.safetensors"), tensors, metadata=meta)
     return path
