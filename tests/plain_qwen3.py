@@ -110,7 +110,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int | N
     g = nq // nkv
     scale = float(np.float32(1.0) / np.sqrt(np.float32(d)))
     out = torch.empty_like(q)
-    idx = torch.arange(S)
+    idx = torch.arange(S, device=q.device)
     mask = idx[None, :] <= idx[:, None]
     if window is not None:
         mask &= idx[None, :] > idx[:, None] - window
@@ -174,16 +174,21 @@ def head_weight(cfg, w):
     return w["lm_head.weight"]
 
 
-def forward(cfg: dict, w: dict[str, torch.Tensor], tokens) -> torch.Tensor:
-    """Logits [S, V] (float64) for a whole sequence: embedding row, L layers, final
-    norm, output head (src/model/runtime/optimized_decoder/runtime.zig:103-148)."""
-    tokens = torch.as_tensor(tokens, dtype=torch.long)
+def forward(cfg: dict, w: dict[str, torch.Tensor], tokens, rows=None) -> torch.Tensor:
+    """Logits [S, V] for a whole sequence: embedding row, L layers, final norm, output
+    head (src/model/runtime/optimized_decoder/runtime.zig:103-148).  Computed in the
+    weights' dtype (float64 as :func:`load_model` gives them) and on their device; ``rows``
+    restricts the output head to those positions (the layers always see the whole sequence)."""
+    table = w["model.embed_tokens.weight"]
+    tokens = torch.as_tensor(tokens, dtype=torch.long, device=table.device)
     S = tokens.shape[0]
-    cos, sin = rope_tables(S, cfg["head_dim"], cfg["rope_theta"])
-    h = w["model.embed_tokens.weight"][tokens]
+    cos, sin = (t.to(device=table.device, dtype=table.dtype) for t in rope_tables(S, cfg["head_dim"], cfg["rope_theta"]))
+    h = table[tokens]
     for i in range(cfg["num_hidden_layers"]):
         h = decoder_layer(h, w, i, cfg, cos, sin)
     h = rmsnorm(h, w["model.norm.weight"], cfg["rms_norm_eps"])
+    if rows is not None:
+        h = h[torch.as_tensor(list(rows), dtype=torch.long, device=h.device)]
     return h @ head_weight(cfg, w).T
 
 

@@ -48,7 +48,8 @@ def test_greedy_generation_through_the_entry_point(model_dirs, name):
         logits = P.forward(cfg16, w16, p + r.token_ids).numpy()
         for i, t in enumerate(r.token_ids):
             row = logits[len(p) - 1 + i]
-            assert row[t] >= row.max() - 3e-2 * np.abs(row).max(), f"bfloat16 picked token {t} far from the best"
+            # twice the tolerance of the bfloat16 replay: two logits that each moved by it can change places
+            assert row[t] >= row.max() - 2 * 2e-2 * np.abs(row).max(), f"bfloat16 picked token {t} far from the best"
 
 
 def test_tight_pool_preempts_and_keeps_the_tokens(model_dirs):
@@ -63,6 +64,90 @@ def test_tight_pool_preempts_and_keeps_the_tokens(model_dirs):
     assert [r.token_ids for r in got] == want
     assert eng.scheduler.stats.preemptions > 0
     eng.runner.manager.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_end_of_sequence_with_the_pipelined_engine(model_dirs, dtype):
+    """Every request gets an end token of its own, taken from the plain model's greedy continuation, so
+    that the requests stop at different steps.  The engine launches step k+1 before it has read the
+    tokens of step k: the end token is noticed one step late, the token in flight behind it is dropped,
+    and its pages go to the next request at once (the pool holds little more than the live requests).
+    float32: the result is the plain continuation cut at the end token, with and without pipelining.
+    bfloat16 (where two close logits may change places, and with them the moment a request stops): every
+    emitted token, and the end token of a request that stopped, is nearly the best under the plain model
+    given the same history; no end token is ever emitted."""
+    from zinfer_b200.sampling import SamplingParams
+
+    name = "D"
+    d = model_dirs[(name, dtype)]
+    cfg, w = P.load_model(d)
+    V = cfg["vocab_size"]
+    prompts = [[(11 * i + 5 * j) % V for j in range(n)] for i, n in enumerate((9, 30, 3, 17, 44, 1, 25))]
+    full = [P.greedy(cfg, w, p, 12) for p in prompts]
+    stops = [2, 7, 0, 11, 4, 1, 9]
+    params = [SamplingParams(temperature=0.0, max_new_tokens=12, eos_token_ids=(f[s],)) for f, s in zip(full, stops)]
+    want = [f[:f.index(f[s])] for f, s in zip(full, stops)]
+    results = {}
+    for pipelined in (True, False):
+        eng = _engine(d, name, dtype, kv_cache_tokens=160, max_requests=3, pipelined=pipelined)
+        got = eng.generate(prompts, params)
+        eng.runner.manager.check()
+        assert not eng.runner.manager.requests and not eng.scheduler.waiting and not eng.scheduler.running
+        assert eng.runner.manager.groups[0].pool.reused > 0
+        if dtype == "float32":
+            assert [r.token_ids for r in got] == want, f"pipelined={pipelined}"
+            assert all(r.finish_reason == "stop" for r in got)
+        else:
+            assert sum(r.finish_reason == "stop" for r in got) >= 4
+            for p, r, sp in zip(prompts, got, params):
+                eos = sp.eos_token_ids[0]
+                assert eos not in r.token_ids and -1 not in r.token_ids
+                assert r.finish_reason in ("stop", "length") and (r.finish_reason == "stop" or len(r.token_ids) == 12)
+                seq = r.token_ids + ([eos] if r.finish_reason == "stop" else [])
+                logits = P.forward(cfg, w, p + seq).numpy()
+                for i, t in enumerate(seq):
+                    row = logits[len(p) - 1 + i]
+                    assert row[t] >= row.max() - 2 * 2e-2 * np.abs(row).max(), f"token {t} is far from the best"
+        results[pipelined] = [(r.token_ids, r.finish_reason) for r in got]
+    if dtype == "float32":
+        assert results[True] == results[False]
+
+
+@pytest.mark.parametrize("opts", [dict(temperature=0.9, top_k=12, repetition_penalty=1.3, presence_penalty=0.2, frequency_penalty=0.1),
+                                  dict(temperature=0.7, top_k=20, top_p=0.9, min_p=0.05, repetition_penalty=1.1)])
+def test_penalties_and_filters_through_generate(model_dirs, opts):
+    """Sampling options travel through Engine.generate: rows of token counts are taken at admission (there
+    are more prompts than rows of running requests), every drawn token lies in the set the plain sampler
+    keeps for the history so far, and a request's tokens do not depend on what ran beside it."""
+    from zinfer_b200.sampling import SamplingParams
+
+    name = "B"
+    d = model_dirs[(name, "float32")]
+    cfg, w = P.load_model(d)
+    V = cfg["vocab_size"]
+    prompts = [[(7 * i + 3 * j) % V for j in range(n)] for i, n in enumerate((5, 21, 2, 40, 9, 13))]
+    sp = SamplingParams(seed=9, max_new_tokens=10, ignore_eos=True, **opts)
+    eng = _engine(d, name, "float32", max_requests=2)       # 6 penalised prompts, 2 running at a time
+    got = eng.generate(prompts, sp)
+    assert eng.sampler._rows.num_used == 0 and not eng.sampler._row_of
+    for p, r in zip(prompts, got):
+        assert len(r.token_ids) == 10
+        logits = P.forward(cfg, w, p + r.token_ids).numpy()
+        for i, t in enumerate(r.token_ids):
+            hist = p + r.token_ids[:i]
+            adj = P.adjusted_logits(logits[len(p) - 1 + i], hist, opts.get("repetition_penalty", 1.0),
+                                    opts.get("presence_penalty", 0.0), opts.get("frequency_penalty", 0.0))
+            # the plain kept set, widened a little at its edges (the engine's logits differ by rounding)
+            keep = P.kept_distribution(adj, opts["temperature"], opts.get("top_k", 0) + 1, min(1.0, opts.get("top_p", 1.0) + 0.03),
+                                       opts.get("min_p", 0.0) * 0.9)
+            assert keep[t] > 0, f"token {t} (draw {i}) lies outside the kept set"
+    assert len({tuple(r.token_ids) for r in got}) > 3
+    alone = [_engine(d, name, "float32", max_requests=2).generate([p], sp)[0].token_ids for p in prompts[:3]]
+    assert [r.token_ids for r in got[:3]] == alone
+    # penalties change the outcome: without them the same seed draws other tokens somewhere
+    plain_opts = {k: v for k, v in opts.items() if "penalty" not in k}
+    other = _engine(d, name, "float32", max_requests=2).generate(prompts, SamplingParams(seed=9, max_new_tokens=10, ignore_eos=True, **plain_opts))
+    assert [r.token_ids for r in other] != [r.token_ids for r in got]
 
 
 def test_command_line_generate_token_ids(model_dirs):
@@ -88,12 +173,13 @@ def test_long_decoding_and_first_tokens(model_dirs, dtype):
     toks = reqs["r0"]
     trace = [{"step": i, "entries": [{"id": "r0", "tokens": toks[i:i + 1], "want": [0]}], "end": []} for i in range(401)]
     runner = ModelRunner.from_model_dir(d, dtype=getattr(torch, dtype), device=DEV, page_size=32, max_tokens=448)
-    got = ru.run_in_process_keep(runner, trace) if hasattr(ru, "run_in_process_keep") else None
-    if got is None:
-        trace[-1]["end"] = ["r0"]
-        got = ru.run_in_process(runner, trace)
-    tol = dict(rtol=5e-5, atol=1e-6) if dtype == "float32" else dict(rtol=3e-2, atol=1e-3)
-    ru.assert_close(got, ru.plain_logits(cfg, w, reqs), what=f"long decode {dtype}", argmax_frac=0.0, **tol)
+    trace[-1]["end"] = ["r0"]
+    got = ru.run_in_process(runner, trace)
+    # bfloat16: measured 0.9e-2 of the row's largest logit on this configuration; the limit is twice that
+    tol = dict(rtol=5e-5, atol=1e-6) if dtype == "float32" else dict(rtol=2e-2, atol=1e-3)
+    worst = ru.assert_close(got, ru.plain_logits(cfg, w, reqs), what=f"long decode {dtype}",
+                            argmax_frac=1.0 if dtype == "float32" else 0.8, **tol)
+    print(f"measured long decode {dtype}: worst error {worst * tol['rtol']:.2e} of the row's largest logit")
     first = {k: v for k, v in got.items() if k[1] < 3}
     assert len(first) == 3
 

@@ -483,3 +483,23 @@ def test_argmax_first_maximum_wins(R, V):
     want = torch.stack([torch.tensor(int(np.argmax(row))) for row in logits.cpu().numpy()]).to(torch.int32)
     assert torch.equal(got.cpu(), want)
     assert int(got[0]) == 7
+
+
+def test_a_wait_that_runs_out_is_reported_not_survived_silently():
+    """The tensor-core kernels bound every wait; when one runs out they record a code in a device
+    word and return.  Here a one-CTA kernel waits on a barrier nobody arrives at, with a limit of a
+    few thousand tries: it returns normally, the word holds the code, the check that the engine,
+    the replay program and the benchmark make raises, and the library works on afterwards."""
+    o = ops()
+    assert o.kernel_status() == 0
+    o.selftest_wait_runs_out(code=77, tries=4096)
+    torch.cuda.synchronize()
+    with pytest.raises(o.KernelError, match="code 77"):
+        o.require_kernel_status_ok("test")
+    assert o.kernel_status() == 0, "reading the status clears it"
+    x, w = rnd(8, 4096, dtype=torch.bfloat16), rnd(256, 4096, dtype=torch.bfloat16, scale=0.05)
+    got = o.linear(x, w, out_dtype=torch.float32)
+    torch.testing.assert_close(got, x.float() @ w.float().T, rtol=1e-3, atol=1e-2)
+    o.require_kernel_status_ok("after")
+    with pytest.raises(o.KernelError):
+        o.selftest_wait_runs_out(code=0)

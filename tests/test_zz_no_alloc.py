@@ -10,7 +10,9 @@ partial sums in a fixed 8 MiB array inside the library's device image.
 This test calls that function through its exported C symbol, as such a user would,
 twice in a row with different shapes (the second, smaller product must not be
 disturbed by what the first left in the shared array), and compares each result
-with the ordinary entry point's.  It also checks that an oversized product is
+with the ordinary entry point's.  It also checks that the calls leave the amount of
+free device memory unchanged (they allocate nothing), that the library's own status
+word can be read by a caller who passes none, and that an oversized product is
 refused with a clear message instead of overrunning the array.  The file sorts
 last, so a run that stops at the first failure has run every other test before it.
 """
@@ -60,11 +62,18 @@ def test_static_scratch_product_matches_the_ordinary_entry_point():
         torch.testing.assert_close(out.float(), want.float(), **tol)
         ref = x.float() @ w.float().T
         torch.testing.assert_close(out.float(), ref, rtol=1.6e-2, atol=2e-2)
-    # without a status word of the caller's, the library's own is used
+    # without a status word of the caller's, the library's own is used, and can be read
     out2 = torch.empty((M, N), dtype=odt, device=DEV)
-    assert _call(lib, x, w, out2) == 0
+    out3 = torch.empty((M, N), dtype=odt, device=DEV)
     torch.cuda.synchronize()
-    assert torch.equal(out2, out)
+    free_before, _ = torch.cuda.mem_get_info()
+    assert _call(lib, x, w, out2) == 0
+    assert _call(lib, x, w, out3) == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, "the entry point that allocates nothing changed the free device memory"
+    assert lib.zi_gemm_static_scratch_status() == 0
+    assert torch.equal(out2, out) and torch.equal(out3, out)
 
 
 def test_static_scratch_refuses_what_does_not_fit():

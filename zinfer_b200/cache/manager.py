@@ -77,6 +77,9 @@ class CacheManager:
         self.state_caches = list(state_caches)
         self.slots = PagePool(max_requests, name="request slots")
         self.requests: dict[Hashable, RequestCache] = {}
+        # called with (group index, pages) whenever pages go back to their pool: a debugging hook
+        # (the storage can overwrite what they held, so that a read of a stale page shows)
+        self.on_release = None
 
     # ------------------------------------------------------------------ requests
     def add_request(self, request_id: Hashable) -> RequestCache:
@@ -94,8 +97,11 @@ class CacheManager:
         rc = self.requests.pop(request_id, None)
         if rc is None:
             raise KeyError(f"request {request_id!r} is not live (freed twice?)")
-        for g, table in zip(self.groups, rc.tables):
-            g.pool.free([p for p in table if p >= 0])
+        for gi, (g, table) in enumerate(zip(self.groups, rc.tables)):
+            pages = [p for p in table if p >= 0]
+            g.pool.free(pages)
+            if self.on_release is not None and pages:
+                self.on_release(gi, pages)
         self.slots.free([rc.state_slot])
 
     # --------------------------------------------------------------------- pages
@@ -151,6 +157,8 @@ class CacheManager:
             dead = [b for b in range(min(n_dead, len(table))) if table[b] >= 0]
             if dead:
                 g.pool.free([table[b] for b in dead])
+                if self.on_release is not None:
+                    self.on_release(gi, [table[b] for b in dead])
                 for b in dead:
                     released.append((gi, table[b]))
                     table[b] = -1

@@ -20,6 +20,8 @@ class PagePool:
         self.num_pages = num_pages
         self._free = list(range(num_pages - 1, -1, -1))  # pop() gives 0, 1, 2, ... first
         self._used: set[int] = set()
+        self._ever: set[int] = set()     # pages that have been handed out at least once
+        self.reused = 0                  # allocations that returned a page which had been in use before
 
     @property
     def num_free(self) -> int:
@@ -37,6 +39,8 @@ class PagePool:
             raise OutOfPages(f"{self.name}: {n} wanted, {len(self._free)} of {self.num_pages} free")
         out = [self._free.pop() for _ in range(n)]
         self._used.update(out)
+        self.reused += sum(p in self._ever for p in out)
+        self._ever.update(out)
         return out
 
     def free(self, pages) -> None:

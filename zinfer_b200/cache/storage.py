@@ -59,6 +59,13 @@ class CacheStorage:
         for t in self.state.values():
             t[slot].zero_()
 
+    def poison(self, group: int, pages, value: float = 3.0e4) -> None:
+        """Overwrites the keys of ``pages`` with ``value`` and their values with ``-value`` in every
+        cache of the group (debugging: what a freed page held must never reach a result)."""
+        idx = torch.as_tensor(list(pages), dtype=torch.long, device=self.kv[group].device)
+        self.kv[group][:, 0].index_fill_(1, idx, value)
+        self.kv[group][:, 1].index_fill_(1, idx, -value)
+
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.kv) + \
             sum(t.numel() * t.element_size() for t in self.state.values())

@@ -25,13 +25,18 @@
 //    Make that first call before you begin any stream capture.
 //  * All calls on one device share the one array, and it keeps what the last call
 //    left in it.  Nothing in it has to be zero at the start (every partial sum that
-//    is read is written first); the status word is cleared by each call.  Two calls
+//    is read is written first).  Two calls
 //    whose kernels may overlap on the GPU (different streams without an ordering
 //    between them) race on the array: order them yourself.
 //  * The function calls no cudaMalloc, cudaFree or any allocating library routine.
-//  * `wait_status`: a device int of yours that receives a non-zero code if a bounded
-//    wait inside the kernel ran out (never seen in practice), or NULL to use a word
-//    inside the library.
+//  * How a failure shows.  Every wait inside the kernel is bounded; if one ever ran
+//    out (never seen in practice) the kernel stores a non-zero code in a status word
+//    and returns, and its output is not to be trusted.  The word is only ever written
+//    with non-zero codes and never cleared by a call, so a failure of an earlier call
+//    stays visible until you read it.  `wait_status` is a device int of yours (zero it
+//    once, read it when you synchronise anyway), or NULL to use a word inside the
+//    library, which zi_gemm_static_scratch_status() reads and clears (it waits for the
+//    device and allocates nothing).
 //
 // Returns 0, a cudaError_t (> 0) of the launch, or -1 with zi_last_error() set.
 #pragma once
@@ -42,6 +47,10 @@ extern "C" {
 #endif
 
 long long zi_gemm_static_scratch_capacity_bytes();
+
+// The library's own status word on the current device: 0, or the code of a wait that ran out
+// since the last read (then cleared); negative if the word cannot be read.
+int zi_gemm_static_scratch_status();
 
 int zi_gemm_tcgen05_static_scratch(void* out, int out_dtype /* 0 = float32, 1 = bfloat16 */, const void* x,
                                    const void* w, int M, int N, int K, int ldx, int ldw, int ldo, int sm_count,

@@ -838,6 +838,31 @@ extern "C" int zi_gemm_tcgen05_status() {
 }
 
 // ------------------------------------------------------------------------------
+// Self-test of the failure path: one CTA waits, with a limit of `tries`, on an mbarrier at
+// which nobody ever arrives.  The wait runs out, the kernel records `code` in the status word
+// exactly as the products do, and returns normally: nothing faults and nothing hangs.  It lets
+// a test see the whole chain (bounded wait -> status word -> zi_gemm_tcgen05_status -> error).
+namespace {
+__global__ void wait_that_runs_out_kernel(int* __restrict__ status, int code, uint32_t tries) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (!mbar_wait(&bar, 0, tries)) atomicExch(status, code);
+  }
+}
+}  // namespace
+
+extern "C" int zi_selftest_wait_runs_out(int code, int tries, cudaStream_t stream) {
+  if (code == 0 || tries <= 0 || tries > (1 << 20))
+    return zi_refuse("selftest_wait_runs_out: code must be non-zero and tries in 1..2^20");
+  int* status = status_word();
+  if (!status) return zi_refuse("selftest_wait_runs_out: cannot allocate the status word");
+  wait_that_runs_out_kernel<<<1, 32, 0, stream>>>(status, code, (uint32_t)tries);
+  return zi_check_launch("selftest_wait_runs_out");
+}
+
+// ------------------------------------------------------------------------------
 // The same product for callers that cannot allocate device memory (declared in
 // gemm_static_scratch.h).  Split-K partial sums go to a fixed array in the
 // library's own device image instead of a caller's workspace.
@@ -893,6 +918,18 @@ bool encode_map_direct(CUtensorMap* map, const void* ptr, int rows, int cols, in
 
 extern "C" long long zi_gemm_static_scratch_capacity_bytes() { return STATIC_SCRATCH_FLOATS * (long long)sizeof(float); }
 
+// Reads and clears the library's own status word on the current device (the one a call with
+// wait_status == NULL reports into).  Waits for the device; allocates nothing.
+extern "C" int zi_gemm_static_scratch_status() {
+  StaticScratch ss;
+  int dev = -1;
+  if (!static_scratch_for_current_device(&ss, &dev)) return -1;
+  int host = 0;
+  if (cudaMemcpy(&host, ss.status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -2;
+  if (host != 0 && cudaMemset(ss.status, 0, sizeof(int)) != cudaSuccess) return -2;
+  return host;
+}
+
 extern "C" int zi_gemm_tcgen05_static_scratch(void* out, int out_dtype, const void* x, const void* w, int M, int N,
                                               int K, int ldx, int ldw, int ldo, int sm_count, int* wait_status,
                                               cudaStream_t stream) {
@@ -916,11 +953,10 @@ extern "C" int zi_gemm_tcgen05_static_scratch(void* out, int out_dtype, const vo
   if (!encode_map_direct(&map_a, swap ? w : x, a_rows, K, lda, TILE_A) ||
       !encode_map_direct(&map_b, swap ? x : w, b_rows, K, ldb, b_box_rows(plan, M)))
     return zi_refuse("gemm_static_scratch: cuTensorMapEncodeTiled failed");
+  // The status word is only ever written with a non-zero code, never cleared here: a failure of an
+  // earlier call stays visible until it is read.  The partial sums need no clearing either, every
+  // element that the second kernel reads is written by the first.
   int* status = wait_status ? wait_status : ss.status;
-  // the status word must start at zero; the partial sums need no clearing, every
-  // element that the second kernel reads is written by the first
-  cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int), stream);
-  if (e != cudaSuccess) return zi_refuse("gemm_static_scratch: cannot clear the status word: %s", cudaGetErrorString(e));
   return launch_gemm(out, out_dtype, map_a, map_b, M, N, K, ldo, plan, ss.scratch, status, sm_count, 0,
                      "gemm_static_scratch", stream);
 }

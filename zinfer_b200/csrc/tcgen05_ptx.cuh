@@ -19,10 +19,10 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// Bounded wait for the phase with the given parity; false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Bounded wait for the phase with the given parity; false when the limit (tries) ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = WAIT_LIMIT) {
   const uint32_t addr = smem_u32(bar);
-  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+  for (uint32_t it = 0; it < limit; ++it) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"

@@ -37,12 +37,14 @@ class ModelRunner:
     def __init__(self, model: DecoderModel, page_size: int = 16, num_pages: Optional[int] = None,
                  max_tokens: Optional[int] = None, max_requests: int = 64, cuda_graphs: bool = True,
                  kv_cache_bytes: Optional[int] = None, gpu_memory_fraction: Optional[float] = None,
-                 workspace_bytes: int = 0):
+                 workspace_bytes: int = 0, poison_freed_pages: bool = False):
         """The page pool is sized, in this order of precedence, by ``num_pages`` (pages per
         group), by ``kv_cache_bytes`` (a byte budget for all groups together), by
         ``gpu_memory_fraction`` (that share of the device memory which is free now, the weights
         being loaded already, minus ``workspace_bytes`` kept for activations), each capped by
-        ``max_tokens`` cached tokens when that is given too; or by ``max_tokens`` alone."""
+        ``max_tokens`` cached tokens when that is given too; or by ``max_tokens`` alone.
+        ``poison_freed_pages`` (debugging) overwrites every page with huge values when it is
+        given back, so that a kernel which reads a stale page cannot go unnoticed."""
         _require_cuda(model.device)
         ops.lib()  # fail now, and loudly, if the kernel library cannot be built or loaded
         self.model = model
@@ -59,6 +61,8 @@ class ModelRunner:
             num_pages = pages_for(kv_needs, page_size, elt, budget_bytes=budget, tokens=max_tokens)
         self.manager = CacheManager(kv_needs, list(state_needs), page_size, num_pages, max_requests)
         self.storage = CacheStorage(self.manager, state_needs, model.dtype, self.device)
+        if poison_freed_pages:
+            self.manager.on_release = self.storage.poison
         model.attach(self.storage)
         self.tile_rows = ops.attention_tile_rows()
         self.pf_tile_rows = ops.attention_prefill_tile_rows()

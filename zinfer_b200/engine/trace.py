@@ -33,6 +33,8 @@ def main(argv=None) -> int:
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--device", default="cuda:0")
+    ap.add_argument("--poison-freed-pages", action="store_true",
+                    help="debugging: overwrite every page with huge values when it is given back")
     args = ap.parse_args(argv)
 
     from .. import ops
@@ -45,7 +47,8 @@ def main(argv=None) -> int:
     os.makedirs(args.out, exist_ok=True)
     dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[args.dtype]
     runner = ModelRunner.from_model_dir(args.model, dtype=dtype, device=args.device, page_size=args.page_size,
-                                        max_tokens=max(args.max_tokens, args.page_size), max_requests=64)
+                                        max_tokens=max(args.max_tokens, args.page_size), max_requests=64,
+                                        poison_freed_pages=args.poison_freed_pages)
     for line in sys.stdin:
         line = line.strip()
         if not line:
@@ -63,6 +66,8 @@ def main(argv=None) -> int:
         ops.require_kernel_status_ok(f"step {step}")   # a kernel whose bounded wait ran out fails the replay
         sys.stdout.write(f"done {step}\n")
         sys.stdout.flush()
+    reused = sum(g.pool.reused for g in runner.manager.groups)
+    print(f"trace_run: {runner.steps_run} steps, {reused} page allocations returned a page used before", file=sys.stderr)
     return 0
 
 

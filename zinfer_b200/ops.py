@@ -55,6 +55,13 @@ def require_kernel_status_ok(where: str) -> None:
         raise KernelError(f"{where}: a wait inside a tensor-core kernel ran out (code {code}); its results are invalid")
 
 
+def selftest_wait_runs_out(code: int = 77, tries: int = 4096) -> None:
+    """Launches one CTA that waits ``tries`` times on a barrier nobody arrives at, so that the wait
+    runs out and the kernel records ``code`` in the status word, the way a stuck product would.
+    Returns normally (nothing faults or hangs); :func:`require_kernel_status_ok` then raises."""
+    _check(lib().zi_selftest_wait_runs_out(code, tries, _stream()), "selftest_wait_runs_out")
+
+
 def gemm_pair_kernel(on: bool) -> bool:
     """Switches the matrix product's kernel for CTA pairs (tcgen05 ``cta_group::2``: two SMs on one
     tile of 256 tokens x 256 weight rows, each loading half of the weight rows) on or off for
