@@ -25,9 +25,10 @@ SHAPE = dict(
     intermediate_size=12288, num_hidden_layers=LAYERS, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
     max_position_embeddings=40960, rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False,
     torch_dtype="bfloat16")
-# Measured on a B200 (worst row, as a fraction of the row's largest logit): bfloat16 tail 0.0040,
-# mixed 0.0042, 64 requests 0.0036; float32 whole 2.1e-6.  The limits are about twice that.
-TOL = {"bfloat16": dict(rtol=1e-2, atol=1e-3), "float32": dict(rtol=1e-5, atol=1e-6)}
+# Measured on a B200 (worst of all compared rows, as a fraction of the row's largest logit, each row
+# being the worst of 151,936 logits): bfloat16 tail 1.15e-2, mixed 1.11e-2, 64 requests 1.22e-2;
+# float32 whole 6.0e-6.  The limits are twice the largest of these.
+TOL = {"bfloat16": dict(rtol=2.5e-2, atol=1e-3), "float32": dict(rtol=1.2e-5, atol=1e-6)}
 
 
 @pytest.fixture(scope="module")

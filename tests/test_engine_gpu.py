@@ -175,8 +175,8 @@ def test_long_decoding_and_first_tokens(model_dirs, dtype):
     runner = ModelRunner.from_model_dir(d, dtype=getattr(torch, dtype), device=DEV, page_size=32, max_tokens=448)
     trace[-1]["end"] = ["r0"]
     got = ru.run_in_process(runner, trace)
-    # bfloat16: measured 0.9e-2 of the row's largest logit on this configuration; the limit is twice that
-    tol = dict(rtol=5e-5, atol=1e-6) if dtype == "float32" else dict(rtol=2e-2, atol=1e-3)
+    # bfloat16: measured 5.8e-3 of the row's largest logit on this configuration; the limit is twice that
+    tol = dict(rtol=5e-5, atol=1e-6) if dtype == "float32" else dict(rtol=1.2e-2, atol=1e-3)
     worst = ru.assert_close(got, ru.plain_logits(cfg, w, reqs), what=f"long decode {dtype}",
                             argmax_frac=1.0 if dtype == "float32" else 0.8, **tol)
     print(f"measured long decode {dtype}: worst error {worst * tol['rtol']:.2e} of the row's largest logit")

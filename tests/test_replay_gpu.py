@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 # row's largest logit, over all four ways of cutting); the bfloat16 limit is twice that.
 # Beyond the limits, the best token must agree wherever the plain model's lead exceeds
 # twice the tolerance (replay_util.assert_close).
-MEASURED_BF16 = {"A": 1.0e-2, "B": 1.0e-2, "C": 1.0e-2, "D": 1.0e-2, "E": 1.0e-2}
+MEASURED_BF16 = {"A": 6.8e-3, "B": 8.4e-3, "C": 6.7e-3, "D": 1.05e-2, "E": 8.3e-3}
 TOL = {"float32": lambda name: dict(rtol=5e-5, atol=1e-6),
        "bfloat16": lambda name: dict(rtol=2 * MEASURED_BF16[name], atol=1e-3)}
 LENGTHS = {"A": [5, 17, 33, 64, 100], "B": [1, 9, 40, 70, 129, 200], "C": [3, 77, 150, 31],
