@@ -10,8 +10,10 @@ for every request).  Prints ONE JSON line:
 
   value     decoded tokens per second at batch 8, timed on the device with CUDA events
   e2e       the same through the Python entry point (Engine.step), host tokens in
-            and out, with the step's host->device and device->host bytes
-  prefill   one step of 2,048 prompt tokens: tokens/s, ms, fraction of the bf16 peak
+            and out, with the step's host->device and device->host bytes; "points"
+            inside it: the same at batch 1 and 64
+  prefill   one step of 2,048 prompt tokens: tokens/s, ms, fraction of the bf16 peak;
+            "chunks_512" inside it: the same prompt as four steps of 512 tokens
   roofline  bytes the decode step must read (every weight once + the live
             requests' cache) / time, against the measured copy bandwidth
   points    decode tokens/s at batch 1 and 64
@@ -122,6 +124,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="zinfer_b200", choices=["zinfer_b200", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
+    ap.add_argument("--profile", default=None, metavar="PATH",
+                    help="also run one prefill and a few decode steps under the per-kernel-class profiler "
+                         "(uncaptured, outside every timed region) and write its summary there as JSON")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -153,7 +158,7 @@ def main() -> int:
 
     engine = Engine(config=cfg, random_weights_seed=20240, dtype="bfloat16", device="cuda:0", page_size=16,
                     kv_cache_tokens=max_batch * (PROMPT_LEN + steps + warmup + 64) + PREFILL_TOKENS + 64,
-                    max_model_len=CONTEXT_LEN, max_batched_tokens=max(PREFILL_TOKENS, 2048), max_requests=max_batch)
+                    max_batched_tokens=max(PREFILL_TOKENS, 2048), max_requests=max_batch)
     runner = engine.runner
     weight_bytes = runner.model.weight_bytes() - cfg.vocab_size * cfg.hidden_size * 2   # the embedding table is only gathered
     kv_bytes_per_token = 2 * n_layers * cfg.num_key_value_heads * cfg.head_dim * 2
@@ -184,6 +189,17 @@ def main() -> int:
     pf_flops = 2 * PREFILL_TOKENS * matmul_params(cfg, n_layers) + attn_flops + 2 * cfg.vocab_size * cfg.hidden_size
     prefill = {"value": round(PREFILL_TOKENS / (pf_ms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3),
                "frac": round(pf_flops / (pf_ms * 1e-3) / (bf16_tflops * 1e12), 4)}
+
+    def prefill_chunked():
+        for c in range(0, PREFILL_TOKENS, 512):
+            last = c + 512 >= PREFILL_TOKENS
+            runner.step([StepEntry("prefill", prompt[c:c + 512], [511] if last else [])])
+        runner.end_request("prefill")
+
+    prefill_chunked()
+    ck_ms = event_ms(prefill_chunked, 3) / 3
+    prefill["chunks_512"] = {"value": round(PREFILL_TOKENS / (ck_ms * 1e-3), 1), "ms": round(ck_ms, 3),
+                             "frac": round(pf_flops / (ck_ms * 1e-3) / (bf16_tflops * 1e12), 4)}
 
     # ----------------------------------------------------------------- decode
     def decode_point(batch: int, n_steps: int, sample_clocks: bool = False):
@@ -226,22 +242,50 @@ def main() -> int:
             points[f"decode_b{b}"] = round(b / (m * 1e-3), 1)
 
     # ------------------------------------------------- end to end through the API
-    params = SamplingParams(temperature=0.0, max_new_tokens=steps + warmup + 8, ignore_eos=True)
-    for i in range(args.batch):
-        engine.add_request(rand_tokens(PROMPT_LEN), params)
-    while any(r.num_computed < len(r.prompt) for r in engine.scheduler.running) or engine.scheduler.waiting:
-        engine.step()
-    for _ in range(warmup):
-        engine.step()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        engine.step()
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    h2d = runner.last_h2d_bytes if hasattr(runner, "last_h2d_bytes") else 0
-    e2e = {"value": round(args.batch * steps / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
-           "d2h_bytes_per_step": 4 * args.batch}
+    def e2e_point(batch: int, n_steps: int) -> tuple[float, int]:
+        """Decoded tokens a second through Engine.step (host tokens in and out), and the bytes of
+        the step's one host->device copy."""
+        params = SamplingParams(temperature=0.0, max_new_tokens=n_steps + warmup + 8, ignore_eos=True)
+        for i in range(batch):
+            engine.add_request(rand_tokens(PROMPT_LEN), params)
+        while any(r.num_computed < len(r.prompt) for r in engine.scheduler.running) or engine.scheduler.waiting:
+            engine.step()
+        for _ in range(warmup):
+            engine.step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(n_steps):
+            engine.step()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        h2d_bytes = runner.last_h2d_bytes
+        while engine.has_unfinished():
+            engine.step()
+        return batch * n_steps / dt, int(h2d_bytes)
+
+    e2e_value, h2d = e2e_point(args.batch, steps)
+    e2e = {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch}
+    if not args.skip_points:
+        e2e["points"] = {f"decode_b{b}": round(e2e_point(b, min(steps, 32))[0], 1) for b in (1, 64)}
+
+    # -------------------------------- where the time goes (uncaptured, never a timed number)
+    if args.profile:
+        ids = [f"p{i}" for i in range(args.batch)]
+        for rid in ids:
+            runner.step([StepEntry(rid, rand_tokens(PROMPT_LEN), [])])
+        cur = torch.randint(0, cfg.vocab_size, (args.batch,), generator=gen).tolist()
+        with engine.profile(hbm_gbs, bf16_tflops) as prof:
+            for _ in range(4):
+                ops.argmax(runner.step([StepEntry(rid, [t], [0]) for rid, t in zip(ids, cur)]))
+            decode_profile = prof.summary()
+        with engine.profile(hbm_gbs, bf16_tflops) as prof:
+            prefill_once()
+            prefill_profile = prof.summary()
+        for rid in ids:
+            runner.end_request(rid)
+        with open(args.profile, "w") as f:
+            json.dump({"decode": {"batch": args.batch, "context": PROMPT_LEN, **decode_profile},
+                       "prefill": {"tokens": PREFILL_TOKENS, **prefill_profile}}, f, indent=1)
 
     out = {
         "metric": "decode tok/s at batch 8 (Qwen3-8B shape, bf16)", "value": round(value, 1), "unit": "tokens/s",

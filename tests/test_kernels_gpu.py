@@ -394,6 +394,33 @@ def test_tensor_core_attention(nq, nkv, d, page, window, q_lens, ctx_lens, prefi
         torch.testing.assert_close(again.float(), want.float(), rtol=1.6e-2, atol=1.5e-2)
 
 
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(32, 8, 128, 16, None), (6, 1, 64, 8, 37), (8, 1, 128, 32, None),
+                                                   (2, 1, 256, 16, None), (5, 5, 64, 16, 200)])
+def test_decode_attention_both_tile_forms(nq, nkv, d, page, window):
+    """Groups of at most 8 query heads take the tile with the keys on the MMA's rows; the form with
+    the heads on the rows (which larger groups use) must give the same, and both the reference."""
+    o = ops()
+    ctx_lens = [0, 15, 16, 63, 64, 65, 700, 1300]
+    q_lens = [1] * len(ctx_lens)
+    args = _paged_case(torch.bfloat16, nq, nkv, d, page, q_lens, ctx_lens, seed=6)
+    step = _as_step(args, q_lens, ctx_lens)
+    scale = float(1 / np.sqrt(d))
+    want = ref.paged_attention(window=window, scale=scale, **args)
+    outs = {}
+    try:
+        for on in (True, False):
+            o.decode_transposed_tile(on)
+            for forced in (1, 5):
+                step.max_kv_len = 64 * forced
+                got = o.attention(args["q"], args["k_cache"], args["v_cache"], args["block_tables"], step, nq, nkv, d,
+                                  page, window, scale)
+                torch.testing.assert_close(got.float(), want.float(), rtol=1.6e-2, atol=1.5e-2)
+                outs[(on, forced)] = got.float()
+    finally:
+        o.decode_transposed_tile(True)
+    torch.testing.assert_close(outs[(True, 5)], outs[(False, 5)], rtol=1.6e-2, atol=4e-3)
+
+
 @pytest.mark.parametrize("nq,nkv,d,page,window,norm,rope,partial", [
     (32, 8, 128, 16, None, True, True, True), (8, 2, 128, 16, None, True, True, False), (6, 1, 64, 8, 50, True, True, False),
     (5, 5, 64, 32, None, False, True, False), (16, 1, 128, 16, None, True, False, False), (2, 1, 256, 16, None, True, True, False)])

@@ -183,7 +183,7 @@ struct BlockSync {
   static __device__ __forceinline__ void sync() { __syncthreads(); }
 };
 
-template <int D, bool FUSED>
+template <int D, bool FUSED, bool TR>
 __global__ void __launch_bounds__(DC_THREADS)
 attn_decode_mma_kernel(bf16* __restrict__ out, int out_stride, float* __restrict__ partial,
                        const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kcache,
@@ -194,9 +194,9 @@ attn_decode_mma_kernel(bf16* __restrict__ out, int out_stride, float* __restrict
   pdl_launch_dependents();
   // (the unit waits for the kernel before this one itself, after it has asked for its first keys)
   extern __shared__ __align__(128) uint8_t smem[];
-  attn_decode_unit<D, FUSED, BlockSync>(smem, threadIdx.x, blockIdx.x, blockIdx.y, blockIdx.z, out, out_stride, partial,
-                                        q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q, kv_lens, dec_seq,
-                                        nq, nkv, page_size, page_shift, window, scale_log2, splits, fq);
+  attn_decode_unit<D, FUSED, BlockSync, DecodeCfg<D>::STAGES, TR>(
+      smem, threadIdx.x, blockIdx.x, blockIdx.y, blockIdx.z, out, out_stride, partial, q, q_stride, kcache, vcache,
+      block_tables, bt_stride, cu_q, kv_lens, dec_seq, nq, nkv, page_size, page_shift, window, scale_log2, splits, fq);
 }
 
 template <int D>
@@ -226,12 +226,15 @@ int launch_prefill(void* out, int out_stride, const void* q, int q_stride, const
   return zi_check_launch("attention_prefill");
 }
 
+int g_decode_transposed = 1;   // zi_attention_decode_transposed(0) switches the transposed tile off (for comparisons)
+
 template <int D, bool FUSED>
 int launch_decode(void* out, int out_stride, float* partial, const void* q, int q_stride, const void* kc,
                   const void* vc, const int* bt, int bt_stride, const int* cu_q, const int* kv_lens,
                   const int* dec_seq, int n_dec, int nq, int nkv, int page_size, int window, float scale, int splits,
                   const FusedQK& fq, cudaStream_t stream) {
-  auto kern = attn_decode_mma_kernel<D, FUSED>;
+  // groups of at most 8 query heads take the transposed tile (keys on the MMA's rows)
+  auto kern = nq / nkv <= 8 && g_decode_transposed ? attn_decode_mma_kernel<D, FUSED, true> : attn_decode_mma_kernel<D, FUSED, false>;
   const size_t smem = (size_t)DC_WARPS * DecodeCfg<D>::STAGES * 2 * DC_KEYS * D * 2 +
                       (FUSED ? (size_t)16 * D * 2 + (2 * D + 16) * sizeof(float) : 0);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -267,6 +270,14 @@ int dispatch_decode(int d, void* out, int out_stride, float* partial, const void
 }  // namespace
 
 extern "C" int zi_attention_prefill_tile_rows() { return PF_BQ; }
+
+// The decode attention's tile for groups of at most 8 query heads: transposed (1, the default) or
+// row-major as for larger groups (0); returns the setting before.  For tests and timing comparisons.
+extern "C" int zi_attention_decode_transposed(int on) {
+  const int before = g_decode_transposed;
+  g_decode_transposed = on ? 1 : 0;
+  return before;
+}
 
 // Whether the tensor-core kernels take this shape (else the caller uses zi_paged_attention).
 extern "C" int zi_attention_mma_supported(int nq, int nkv, int d, int decode) {

@@ -192,6 +192,49 @@ __device__ __forceinline__ void load_kv_rows_pg(uint8_t* ks, uint8_t* vs, int ke
   }
 }
 
+// ---- the decode tile with the KEYS on the MMA's rows (groups of at most 8 query heads) ----------
+// With one token per request the queries of a kv head are only its group's heads (4 in Qwen3-8B);
+// as MMA rows they would fill 4 of 16.  Transposed, S^T = K Q^T has the 16 keys as rows and the
+// heads as the 8 columns of ONE n-tile, and O^T = V^T P^T has the head size as rows: half the
+// MMAs and a quarter of the exponentials of the row-major form, and half the accumulators.
+
+// Transposes an 8 x 8 matrix of 16-bit values held one row per 4 lanes (lane l: row l / 4,
+// columns 2 (l % 4) and + 1, packed): the C fragment of P^T becomes the B fragment PV needs.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+
+// S^T (16 keys x 8 heads) = K (16 x D, the tile at ks_addr) * Q^T.  qb: the warp's Q^T fragments
+// [D/16][2] (B operand: head lane/4, columns 2 (lane%4) .. of each 8-wide half of the 16 values).
+// Two accumulators take alternate steps so that their MMAs do not wait for each other.
+template <int D>
+__device__ __forceinline__ void qk_16keys_t(float (&s)[4], const uint32_t (&qb)[D / 16][2], uint32_t ks_addr, int lane) {
+  float s2[4] = {0.f, 0.f, 0.f, 0.f};
+  const int mi = lane >> 3;
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    uint32_t a[4];
+    ldmatrix_x4(a, ks_addr + swz<D>((mi & 1) * 8 + (lane & 7), kk * 2 + (mi >> 1)));
+    if (kk & 1) mma_bf16(s2, a, qb[kk][0], qb[kk][1]);
+    else mma_bf16(s, a, qb[kk][0], qb[kk][1]);
+  }
+#pragma unroll
+  for (int c = 0; c < 4; ++c) s[c] += s2[c];
+}
+// O^T (D x 8 heads) += V^T (D x 16 keys, from the tile at vs_addr) * P^T (16 keys x 8 heads: pb0, pb1).
+template <int D>
+__device__ __forceinline__ void pv_16keys_t(float (&ot)[D / 16][4], uint32_t pb0, uint32_t pb1, uint32_t vs_addr, int lane) {
+  const int mi = lane >> 3;
+#pragma unroll
+  for (int np = 0; np < D / 16; ++np) {
+    uint32_t a[4];
+    ldmatrix_x4_trans(a, vs_addr + swz<D>((mi >> 1) * 8 + (lane & 7), np * 2 + (mi & 1)));
+    mma_bf16(ot[np], a, pb0, pb1);
+  }
+}
+
 // ================================================================================ decode
 constexpr int DC_THREADS = 128, DC_WARPS = 4, DC_KEYS = 16, DC_TILE = DC_WARPS * DC_KEYS;
 // stages of a warp's private ring: 3 x 8 KB x 4 warps = 96 KB per CTA at d = 128, two CTAs per SM
@@ -231,7 +274,9 @@ struct FusedQK {
 // STAGES: tiles of a warp's ring (STAGES - 1 in flight); shared memory needed:
 // DC_WARPS * STAGES * 2 * DC_KEYS * D * 2 bytes, and for FUSED 16 * D * 2 + (2 D + 16) * 4 more
 // (behind the rings, or at `fused_area`, 128-byte aligned).
-template <int D, bool FUSED, class Sync, int STAGES = DecodeCfg<D>::STAGES>
+// TR: the transposed tile (keys on the MMA's rows) for groups of at most 8 query heads; the
+// caller chooses it, the results agree with the other form up to rounding.
+template <int D, bool FUSED, class Sync, int STAGES = DecodeCfg<D>::STAGES, bool TR = false>
 __device__ __forceinline__ void attn_decode_unit(
     uint8_t* smem, int tid, int dec, int kvh, int z, bf16* __restrict__ out, int out_stride,
     float* __restrict__ partial, const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kcache,
@@ -260,10 +305,20 @@ __device__ __forceinline__ void attn_decode_unit(
   const int t_begin = z * tps, t_end = min(total_tiles, t_begin + tps);
   const int n_tiles = max(0, t_end - t_begin);
 
-  uint32_t qf[D / 16][4];   // Q fragments: row = query head within the group
-  float o[D / 8][4];
+  // Row-major form: Q fragments with the query heads of the group as rows, O as [16 heads][D].
+  // Transposed form: Q^T fragments (heads as columns), O^T as [D][8 heads]; m and l then belong to
+  // the thread's two head columns 2 (lane % 4) and + 1.
+  uint32_t qf[TR ? 1 : D / 16][4];
+  float o[TR ? 1 : D / 8][4];
+  uint32_t qb[TR ? D / 16 : 1][2];
+  float ot[TR ? D / 16 : 1][4];
+  if constexpr (TR) {
 #pragma unroll
-  for (int t = 0; t < D / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+    for (int t = 0; t < D / 16; ++t) ot[t][0] = ot[t][1] = ot[t][2] = ot[t][3] = 0.f;
+  } else {
+#pragma unroll
+    for (int t = 0; t < D / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+  }
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
   // Lane r (r < 16) looks up the page of key r of a tile one iteration before the tile's
@@ -290,7 +345,17 @@ __device__ __forceinline__ void attn_decode_unit(
     if (t < n_tiles) issue(t, pg);
     cp_async_commit();
   }
-  if (!FUSED) {
+  if (!FUSED && TR) {
+    if (early) pdl_wait();
+    const int hq = lane >> 2;   // the head (column of Q^T) this lane holds
+    const bf16* qp = q + (size_t)token * q_stride + (size_t)(kvh * g + hq) * D + 2 * (lane & 3);
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      qb[kk][0] = hq < g ? *reinterpret_cast<const uint32_t*>(qp + kk * 16) : 0u;
+      qb[kk][1] = hq < g ? *reinterpret_cast<const uint32_t*>(qp + kk * 16 + 8) : 0u;
+    }
+  }
+  if (!FUSED && !TR) {
     if (early) pdl_wait();
     const int r0 = lane >> 2, r1 = r0 + 8;
     const bf16* q0p = q + (size_t)token * q_stride + (size_t)(kvh * g + r0) * D + 2 * (lane & 3);
@@ -451,10 +516,23 @@ __device__ __forceinline__ void attn_decode_unit(
         if (lane == 0) snew[r] = dot * scale_log2;
       }
     }
+    if constexpr (TR) {
+      // rows 0..7 of the q tile are the heads; matrix i of a load is the 16-byte chunk 2 kk + i
 #pragma unroll
-    for (int kk = 0; kk < D / 16; ++kk) {
-      const int mtx = lane >> 3;
-      ldmatrix_x4(qf[kk], smem_addr(fused_smem) + swz<D>((mtx & 1) * 8 + (lane & 7), kk * 2 + (mtx >> 1)));
+      for (int kk = 0; kk < D / 16; kk += 2) {
+        uint32_t r[4];
+        ldmatrix_x4(r, smem_addr(fused_smem) + swz<D>(lane & 7, kk * 2 + (lane >> 3)));
+        qb[kk][0] = r[0];
+        qb[kk][1] = r[1];
+        qb[kk + 1][0] = r[2];
+        qb[kk + 1][1] = r[3];
+      }
+    } else {
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const int mtx = lane >> 3;
+        ldmatrix_x4(qf[kk], smem_addr(fused_smem) + swz<D>((mtx & 1) * 8 + (lane & 7), kk * 2 + (mtx >> 1)));
+      }
     }
   }
 
@@ -471,9 +549,53 @@ __device__ __forceinline__ void attn_decode_unit(
     const int key0 = kt0 + (t_begin + t) * DC_TILE + warp * DC_KEYS;
     if (key0 < kv_hi && key0 + DC_KEYS > kv_lo) {
       const uint32_t ks_addr = smem_addr(ring + (t % STAGES) * 2 * ROWS_BYTES), vs_addr = ks_addr + ROWS_BYTES;
+      const bool need_mask = key0 + DC_KEYS > kv_hi || key0 < kv_lo;
+      if constexpr (TR) {
+        float st[4] = {0.f, 0.f, 0.f, 0.f};   // keys lane/4 (st[0], st[1]) and + 8 (st[2], st[3]) x heads 2 (lane%4), + 1
+        qk_16keys_t<D>(st, qb, ks_addr, lane);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          float v = st[c] * scale_log2;
+          if (need_mask) {
+            const int j = key0 + (lane >> 2) + (c >> 1) * 8;
+            if (j >= kv_hi || j < kv_lo) v = -INFINITY;
+          }
+          st[c] = v;
+        }
+        // online softmax down the key rows: the maximum of a head's column lies across the 8 lanes
+        // that share lane % 4; the sums stay per thread until the end
+        float alpha[2];
+        bool grew = false;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          float mx = fmaxf(st[i], st[2 + i]);
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+          const float m_new = fmaxf(m[i], mx);
+          const float m_use = m_new == -INFINITY ? 0.f : m_new;
+          alpha[i] = fast_exp2(m[i] - m_use);
+          grew |= m_new != m[i];
+          st[i] = fast_exp2(st[i] - m_use);
+          st[2 + i] = fast_exp2(st[2 + i] - m_use);
+          l[i] = l[i] * alpha[i] + st[i] + st[2 + i];
+          m[i] = m_new;
+        }
+        if (__any_sync(0xffffffffu, grew)) {
+#pragma unroll
+          for (int np = 0; np < D / 16; ++np) {
+            ot[np][0] *= alpha[0];
+            ot[np][1] *= alpha[1];
+            ot[np][2] *= alpha[0];
+            ot[np][3] *= alpha[1];
+          }
+        }
+        const uint32_t pb0 = movmatrix_trans(pack_bf16(st[0], st[1]));   // keys 0..7 of the tile
+        const uint32_t pb1 = movmatrix_trans(pack_bf16(st[2], st[3]));   // keys 8..15
+        pv_16keys_t<D>(ot, pb0, pb1, vs_addr, lane);
+      } else {
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       qk_16keys<D>(s, qf, ks_addr, 0, lane);
-      const bool need_mask = key0 + DC_KEYS > kv_hi || key0 < kv_lo;
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
@@ -489,20 +611,44 @@ __device__ __forceinline__ void attn_decode_unit(
       uint32_t pf[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]), pack_bf16(s[1][0], s[1][1]),
                         pack_bf16(s[1][2], s[1][3])};
       pv_16keys<D>(o, pf, vs_addr, 0, lane);
+      }
     }
     __syncwarp();  // the stage is refilled by this warp's next issue
   }
   cp_async_wait<0>();
 
   // merge the four warps: each writes (o, m, l) of its rows to its own ring, then all combine
+  __syncwarp();
+  float* wo = reinterpret_cast<float*>(ring);               // [16][D] then m[16], l[16]
+  static_assert(WARP_BYTES >= (16 * D + 32) * 4, "a warp's ring must hold its partial result");
+  if constexpr (TR) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {   // a head's sum lies across the 8 lanes that share lane % 4
+      l[i] += __shfl_xor_sync(0xffffffffu, l[i], 4);
+      l[i] += __shfl_xor_sync(0xffffffffu, l[i], 8);
+      l[i] += __shfl_xor_sync(0xffffffffu, l[i], 16);
+    }
+    const int h0 = 2 * (lane & 3), d0 = lane >> 2;
+#pragma unroll
+    for (int np = 0; np < D / 16; ++np) {
+      wo[h0 * D + np * 16 + d0] = ot[np][0];
+      wo[(h0 + 1) * D + np * 16 + d0] = ot[np][1];
+      wo[h0 * D + np * 16 + d0 + 8] = ot[np][2];
+      wo[(h0 + 1) * D + np * 16 + d0 + 8] = ot[np][3];
+    }
+    if (lane < 4) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        wo[16 * D + h0 + i] = m[i];
+        wo[16 * D + 16 + h0 + i] = l[i];
+      }
+    }
+  } else {
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
     l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
   }
-  __syncwarp();
-  float* wo = reinterpret_cast<float*>(ring);               // [16][D] then m[16], l[16]
-  static_assert(WARP_BYTES >= (16 * D + 32) * 4, "a warp's ring must hold its partial result");
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int r = (lane >> 2) + i * 8;
@@ -515,6 +661,7 @@ __device__ __forceinline__ void attn_decode_unit(
       wo[16 * D + r] = m[i];
       wo[16 * D + 16 + r] = l[i];
     }
+  }
   }
   Sync::sync();
   for (int e = tid; e < g * D; e += DC_THREADS) {

@@ -495,6 +495,13 @@ def decode_splits(n_dec: int, num_kv_heads: int, sm_count: int, max_kv_len: Opti
     return best
 
 
+def decode_transposed_tile(on: bool) -> bool:
+    """The decode attention's tile for groups of at most 8 query heads: with the keys on the MMA's rows
+    (on, the default: half the MMAs and a quarter of the exponentials) or with the heads on them as
+    for larger groups (off).  Returns the setting before.  For tests and timing comparisons."""
+    return bool(lib().zi_attention_decode_transposed(1 if on else 0))
+
+
 def decode_fused_ok(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int, step) -> bool:
     """Whether a step can use :func:`attention_decode_fused`: bfloat16, every request brings
     one token, and the split-key decode kernel takes the shape."""
