@@ -285,3 +285,37 @@ def test_temperature_generation_is_reproducible_and_independent_of_batching(mode
     assert len({tuple(r.token_ids) for r in together}) == 4
     other = _engine(d, "B", "float32").generate(prompts, SamplingParams(temperature=0.8, seed=43, max_new_tokens=24, ignore_eos=True))
     assert [r.token_ids for r in other] != [r.token_ids for r in together]
+
+
+def test_profile_per_kernel_class(model_dirs, tmp_path):
+    """The profiler brackets every launch of the steps inside its block and files it under its kernel
+    class; decode steps run uncaptured meanwhile and from their graphs again afterwards."""
+    import json
+
+    from zinfer_b200.sampling import SamplingParams
+
+    d = model_dirs[("E", "bfloat16")]
+    eng = _engine(d, "E", "bfloat16", max_batched_tokens=256)
+    sp = SamplingParams(temperature=0.0, max_new_tokens=6, ignore_eos=True)
+    prompts = [[(3 * j + 1) % 700 for j in range(150)], [5, 6, 7]]
+    plain = [r.token_ids for r in eng.generate(prompts, sp)]
+    replays = eng.runner.graphs.replays
+    with eng.profile(hbm_gbs=6500.0, bf16_tflops=1600.0) as prof:
+        profiled = [r.token_ids for r in eng.generate(prompts, sp)]
+    assert profiled == plain, "profiling changed the tokens"
+    assert eng.runner.graphs.replays == replays, "profiled decode steps must not be replayed from a graph"
+    path = tmp_path / "profile.json"
+    summary = prof.dump(str(path))
+    assert json.load(open(path)) == summary
+    classes = {c["class"]: c for c in summary["classes"]}
+    assert summary["steps"] >= 6 and summary["total_ms"] > 0
+    for expected in ("add_rmsnorm", "embed_gather", "argmax", "attention (prefill, tcgen05)"):
+        assert expected in classes, f"{expected} missing from {sorted(classes)}"
+    assert any(k.startswith("linear N=") for k in classes) and any("attention (decode" in k for k in classes)
+    for c in classes.values():
+        assert c["launches"] > 0 and c["ms"] > 0 and c["us_per_launch"] < 5000
+    lin = next(c for k, c in classes.items() if k.startswith("linear N="))
+    assert lin["bytes"] > 0 and lin["flops"] > 0 and 0 < lin["roofline_frac"] < 1.5
+    assert abs(sum(c["share"] for c in classes.values()) - 1.0) < 1e-2
+    eng.generate(prompts, sp)
+    assert eng.runner.graphs.replays > replays

@@ -76,22 +76,6 @@ int zi_attention_decode_fused(void* out, int out_stride, float* workspace, const
                               const int* dec_seq, int n_dec, int nq, int nkv, int d, int page_size, int window,
                               float scale, int splits, cudaStream_t stream);
 
-// Whole layers of a decode step in one persistent kernel (decode_layers.cu).
-int zi_decode_layers_supported(int hidden, int nq, int nkv, int d, int inter);
-long long zi_decode_layers_desc_bytes();
-int zi_decode_layers_grid(int sm_count);
-int zi_decode_layers_layout(int hidden, int nq, int nkv, int d, int inter, int grid, long long* out);
-int zi_decode_layers_fill_desc(void* desc, const void* w_qkv, const void* w_o, const void* w_gu, const void* w_down,
-                               int hidden, int nq, int nkv, int d, int inter, const float* norm1_w,
-                               const float* norm2_w, float eps1, float eps2, const float* q_norm_w,
-                               const float* k_norm_w, float qk_eps, void* kcache, void* vcache, const float* cos_t,
-                               const float* sin_t, int n_table_pos, int window, int kv_group, float scale);
-int zi_decode_layers(const void* descs, int n_layers, int B, int hidden, int nq, int nkv, int d, int inter,
-                     int interleave, float* h, const float* pend, int pend_splits, void* workspace,
-                     long long workspace_bytes, const int* positions, const int* cu_q, const int* kv_lens,
-                     const int* dec_seq, int n_groups, const int* const* group_slots, const int* const* group_tables,
-                     const int* group_strides, int page_size, int grid, cudaStream_t stream);
-
 int zi_argmax_chunks(int R, int V);
 int zi_argmax(int* out, const float* logits, int R, int V, int ld, void* workspace, cudaStream_t stream);
 int zi_sample_ctas_per_row(int R, int sm_count);

@@ -356,7 +356,6 @@ extern "C" int zi_attention_decode_fused(void* out, int out_stride, float* works
   fq.slots = slots;
   fq.kcache_w = (bf16*)kcache;
   fq.vcache_w = (bf16*)vcache;
-  fq.row_scale = nullptr;
   return dispatch_decode<true>(d, out, out_stride, workspace, nullptr, 0, kcache, vcache, block_tables, bt_stride, cu_q,
                                kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, fq, stream);
 }

@@ -259,7 +259,6 @@ struct FusedQK {
   const int* slots;         // [T] where the token's k and v go (page * page_size + offset)
   bf16* kcache_w;           // the same pages as kcache / vcache, written here
   bf16* vcache_w;
-  const float* row_scale;   // [T] a factor on each token's row before anything else, or null
 };
 
 // partial[((dec * nkv + kvh) * splits + z) * g + row] holds D output values, then max, then sum.
@@ -382,7 +381,6 @@ __device__ __forceinline__ void attn_decode_unit(
     pdl_wait();
     constexpr int HALF = D / 2, MAXP = HALF / 32 > 0 ? HALF / 32 : 1;
     const int my_pos = min(fq.positions[token], fq.n_table_pos - 1);
-    const float row_scale = fq.row_scale ? fq.row_scale[token] : 1.0f;
     // Heads of this block: g query heads, then (owner only) the key head and the value head.
     // Warp w takes heads w, w + 4, ...: first ALL loads of all its heads (one trip to memory, not
     // one per head), then the norms and rotations.
@@ -458,8 +456,8 @@ __device__ __forceinline__ void attn_decode_unit(
         for (int j = 0; j < MAXP; ++j) {
           const int i = lane + 32 * j;
           if (i < HALF) {
-            vnew[i] = __bfloat162float(__float2bfloat16_rn(a[k][j] * row_scale));
-            vnew[i + HALF] = __bfloat162float(__float2bfloat16_rn(b[k][j] * row_scale));
+            vnew[i] = __bfloat162float(__float2bfloat16_rn(a[k][j]));
+            vnew[i + HALF] = __bfloat162float(__float2bfloat16_rn(b[k][j]));
           }
         }
         continue;
@@ -467,8 +465,6 @@ __device__ __forceinline__ void attn_decode_unit(
       float ss = 0.f;
 #pragma unroll
       for (int j = 0; j < MAXP; ++j) {
-        a[k][j] *= row_scale;
-        b[k][j] *= row_scale;
         ss = sum_squares_step(ss, a[k][j], b[k][j]);   // lanes beyond HALF hold zeros
       }
       const bool normed = which[k] == 0 ? fq.qw != nullptr : fq.kw != nullptr;

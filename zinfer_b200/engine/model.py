@@ -10,7 +10,6 @@ from typing import Optional
 
 import torch
 
-from .. import ops
 from ..cache.storage import CacheStorage
 from ..config.spec import ModelSpec
 from ..parts.base import BuildContext, KVCacheNeed, StateNeed, TensorSpec, make_part, prefixed, take
@@ -50,7 +49,6 @@ class DecoderModel:
         self.head = make_part(spec.head, self.ctx)
         self.runs = _plan_runs(spec)
         self._views: list = []
-        self._spans: list = []
 
     # ----------------------------------------------------------------- weights
     def _final_norm_prefix(self) -> str:
@@ -114,32 +112,6 @@ class DecoderModel:
                 self._views.append(storage.state_view(run.cache, run.writes))
             else:
                 self._views.append(None)
-        self._plan_spans()
-
-    def _plan_spans(self) -> None:
-        """Groups the scheduled runs into spans: consecutive runs whose blocks the kernel for
-        whole layers of a decode step can take (equal sizes, known kinds of parts) become one
-        launch of it; every other run is a span of its own that goes through its block."""
-        self._spans = []   # (first run, one past the last, prepared layers or None)
-        fields = []
-        if self.dtype == torch.bfloat16 and self.device.type == "cuda" and ops.DECODE_LAYERS:
-            for run, view in zip(self.runs, self._views):
-                f = self.blocks[run.layer].fused_decode_fields(view)
-                fields.append((f, ops.decode_layers_signature(f)) if f is not None else (None, None))
-        else:
-            fields = [(None, None)] * len(self.runs)
-        i = 0
-        while i < len(self.runs):
-            f, sig = fields[i]
-            if sig is None:
-                self._spans.append((i, i + 1, None))
-                i += 1
-                continue
-            j = i
-            while j < len(self.runs) and fields[j][1] == sig:
-                j += 1
-            self._spans.append((i, j, ops.DecodeLayers([fields[k][0] for k in range(i, j)])))
-            i = j
 
     # ------------------------------------------------------------------ forward
     def forward(self, step) -> Optional[torch.Tensor]:
@@ -147,13 +119,8 @@ class DecoderModel:
         and returns 32-bit logits [wanted rows, vocab], or None if none are wanted."""
         h = self.embedding.forward(step.token_ids)
         pending = None
-        whole_layers = ops.decode_layers_ok(step)
-        for first, last, prepared in self._spans or [(0, len(self.runs), None)]:
-            if prepared is not None and whole_layers:
-                pending = ops.decode_layers(prepared, h, pending, step)
-                continue
-            for run, view in zip(self.runs[first:last], self._views[first:last]):
-                pending = self.blocks[run.layer].forward(h, pending, step, view)
+        for run, view in zip(self.runs, self._views):
+            pending = self.blocks[run.layer].forward(h, pending, step, view)
         if step.logit_rows is None or step.logit_rows.numel() == 0:
             return None
         x = self.final_norm.forward(h, pending, rows=step.logit_rows)

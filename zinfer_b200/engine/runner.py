@@ -181,7 +181,7 @@ class ModelRunner:
             raise StepError("an entry takes its token from the step before, but no such tokens were given")
         self.reserve(entries)
         if profiling.ACTIVE is not None:
-            profiling.ACTIVE.steps += 1      # profiled steps launch their kernels one by one, never from a graph
+            profiling.ACTIVE.begin_step()    # profiled steps launch their kernels one by one, never from a graph
         if self.graphs is not None and profiling.ACTIVE is None and self.graphs.eligible(entries):
             all_rows = self.graphs.run(entries, prev_tokens)
             wanted = [i for i, e in enumerate(entries) if len(e.want)]

@@ -43,7 +43,7 @@ def lib() -> ctypes.CDLL:
 def kernel_status() -> int:
     """Reads and clears the status words of the tcgen05 kernels (synchronises).
     0: every bounded wait inside them completed; else the code of the wait that ran out."""
-    return int(lib().zi_gemm_tcgen05_status())   # one word for the products, the attention and the whole-layer kernel
+    return int(lib().zi_gemm_tcgen05_status())   # one word for the products and the tcgen05 attention
 
 
 def require_kernel_status_ok(where: str) -> None:
@@ -252,9 +252,10 @@ def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out_dtype: Optio
             and x.stride(1) == 1 and w_interleaved.is_contiguous()
             and lib().zi_gemm_tcgen05_supported(_ptr(x), _ptr(w_interleaved), K, x.stride(0), w_interleaved.stride(0))):
         out = torch.empty((M, N2 // 2), dtype=out_dtype or x.dtype, device=x.device)
-        with _prof.region(f"linear+swiglu N={N2} K={K}", lambda: _nb(w_interleaved, out) + M * K * 2, 2 * M * N2 * K):
+        with _prof.region(f"linear+swiglu N={N2} K={K}", lambda: _nb(w_interleaved, out) + M * K * 2, 2 * M * N2 * K) as rec:
             code = lib().zi_gemm_tcgen05_swiglu(_ptr(out), _tag(out), _ptr(x), _ptr(w_interleaved), M, N2, K, x.stride(0),
                                                 w_interleaved.stride(0), out.stride(0), _sm_count(x.device), _stream())
+            rec["keep"] = code != -2      # -2: this shape is better served by the product followed by the SwiGLU kernel
         if code != -2:
             _check(code, "linear_swiglu")
             return out
@@ -560,133 +561,6 @@ def attention_decode_fused(qkv, num_heads: int, num_kv_heads: int, head_dim: int
             _ptr(step.kv_lens), _ptr(step.dec_seq), step.n_dec, num_heads, num_kv_heads, head_dim, page_size,
             int(window or 0), ctypes.c_float(scale), splits, _stream()), "attention (fused decode)")
     return out
-
-
-# ------------------------------------------------- whole layers of a decode step
-DECODE_LAYERS = os.environ.get("ZINFER_B200_DECODE_LAYERS", "0") != "0"
-DECODE_LAYERS_MAX_TOKENS = int(os.environ.get("ZINFER_B200_DECODE_LAYERS_MAX_TOKENS", "64"))
-
-
-def decode_layers_signature(fields: dict) -> Optional[tuple]:
-    """The sizes layers must share to run in one launch of :func:`decode_layers`, or None
-    if the kernel does not take them.  ``fields``: a block's ``fused_decode_fields``."""
-    m, f = fields["mixer"], fields["feed_forward"]
-    sig = (m["hidden"], m["nq"], m["nkv"], m["d"], f["inter"], f["interleave"], m["page_size"])
-    if not torch.cuda.is_available() or not m["w_qkv"].is_cuda:
-        return None
-    if not lib().zi_decode_layers_supported(m["hidden"], m["nq"], m["nkv"], m["d"], f["inter"]):
-        return None
-    return sig
-
-
-class DecodeLayers:
-    """Consecutive layers of equal sizes prepared for :func:`decode_layers`: their descriptor
-    table on the device and the kernel's workspace (activations between the products,
-    split-K partial sums, the grid barrier's counter)."""
-
-    def __init__(self, layers: list[dict]):
-        L = lib()
-        L.zi_decode_layers_desc_bytes.restype = ctypes.c_longlong
-        sig = decode_layers_signature(layers[0])
-        _need(sig is not None and all(decode_layers_signature(f) == sig for f in layers),
-              "decode_layers: the layers of one launch share their sizes")
-        self.hidden, self.nq, self.nkv, self.d, self.inter, self.interleave, self.page_size = sig
-        self.n_layers = len(layers)
-        self.device = layers[0]["mixer"]["w_qkv"].device
-        self.grid = int(L.zi_decode_layers_grid(_sm_count(self.device)))
-        nbytes = int(L.zi_decode_layers_desc_bytes())
-        host = (ctypes.c_uint8 * (nbytes * self.n_layers))()
-        self._keep = []   # the tensors the descriptors point into
-        for i, f in enumerate(layers):
-            m, ff, n1, n2 = f["mixer"], f["feed_forward"], f["mixer_norm"], f["ffn_norm"]
-            for t in (m["w_qkv"], m["w_o"], ff["w_gate_up"], ff["w_down"]):
-                _need(t.dtype == torch.bfloat16 and t.is_contiguous(), "decode_layers: weights are contiguous bfloat16")
-            for t in (n1["weight"], n2["weight"], m["q_norm"], m["k_norm"], m["cos"], m["sin"]):
-                _need(t is None or (t.dtype == torch.float32 and t.is_contiguous()), "decode_layers: norm weights and tables are float32")
-            _need(m["k"].is_contiguous() and m["v"].is_contiguous() and m["k"].dtype == torch.bfloat16
-                  and tuple(m["k"].shape[1:]) == (self.nkv, self.page_size, self.d),
-                  "decode_layers: cache pages are bfloat16 [pages, kv heads, page, d]")
-            _need((m["q_norm"] is None) == (m["k_norm"] is None), "decode_layers: q and k norms go together")
-            n_table = m["cos"].shape[0] if m["cos"] is not None else 0
-            if m["cos"] is not None:
-                _need(tuple(m["cos"].shape) == tuple(m["sin"].shape) == (n_table, self.d // 2),
-                      "decode_layers: rotary tables are [positions, head_dim / 2]")
-            dst = ctypes.c_void_p(ctypes.addressof(host) + i * nbytes)
-            code = L.zi_decode_layers_fill_desc(
-                dst, _ptr(m["w_qkv"]), _ptr(m["w_o"]), _ptr(ff["w_gate_up"]), _ptr(ff["w_down"]), self.hidden, self.nq,
-                self.nkv, self.d, self.inter, _ptr(n1["weight"]), _ptr(n2["weight"]), ctypes.c_float(n1["eps"]),
-                ctypes.c_float(n2["eps"]), _ptr(m["q_norm"]), _ptr(m["k_norm"]), ctypes.c_float(m["qk_eps"]),
-                _ptr(m["k"]), _ptr(m["v"]), _ptr(m["cos"]), _ptr(m["sin"]), n_table, int(m["window"] or 0),
-                int(m["group"]), ctypes.c_float(m["scale"]))
-            if code != 0:
-                raise KernelError(f"decode_layers: {L.zi_last_error().decode('utf-8', 'replace')} (code {code})")
-            self._keep.append(f)
-        self.n_groups = 1 + max(int(f["mixer"]["group"]) for f in layers)
-        self.table = torch.frombuffer(bytearray(host), dtype=torch.uint8).to(self.device)
-        out = (ctypes.c_longlong * 16)()
-        code = L.zi_decode_layers_layout(self.hidden, self.nq, self.nkv, self.d, self.inter, self.grid, out)
-        if code != 0:
-            raise KernelError(f"decode_layers: {L.zi_last_error().decode('utf-8', 'replace')} (code {code})")
-        self.workspace_bytes, self.pending_offset, self.pending_splits = int(out[0]), int(out[1]), int(out[2])
-        self.workspace = torch.zeros((self.workspace_bytes,), dtype=torch.uint8, device=self.device)
-        self._layout = [int(v) for v in out]
-
-    def inspect(self, tokens: int) -> dict:
-        """Views of what the last launch left in the workspace (for tests and debugging)."""
-        o, ws = self._layout, self.workspace
-        n = [(self.nq + 2 * self.nkv) * self.d, self.hidden, 2 * self.inter, self.hidden]
-
-        def bf(off, cols):
-            return ws[off:off + 2 * 64 * cols].view(torch.bfloat16).view(64, cols)[:tokens]
-
-        views = {"hw": bf(o[3], self.hidden), "xo": bf(o[4], self.nq * self.d), "act": bf(o[5], self.inter)}
-        for j in range(4):
-            S = o[12 + j]
-            views[f"part{j}"] = ws[o[7 + j]:o[7 + j] + 4 * S * tokens * n[j]].view(torch.float32).view(S, tokens, n[j])
-        return views
-
-
-def decode_layers_ok(step) -> bool:
-    """Whether a step is one that :func:`decode_layers` runs: every request brings one token."""
-    return (DECODE_LAYERS and step.n_pf_tiles == 0 and 0 < step.n_dec == step.n_seqs
-            and step.n_dec <= min(64, DECODE_LAYERS_MAX_TOKENS))
-
-
-def decode_layers(prepared: DecodeLayers, h: torch.Tensor, pending, step) -> Partials:
-    """Runs the prepared layers on a decode step's tokens in ONE persistent kernel: ``h``
-    [tokens, hidden] float32 is updated in place up to the last layer's mixer; the last
-    feed-forward's update comes back as partial sums for the next norm to add.
-    ``pending``: an update not yet added into ``h`` (partial sums, a tensor or None)."""
-    B = h.shape[0]
-    _need(h.dtype == torch.float32 and h.is_contiguous() and h.shape[1] == prepared.hidden, "h is float32 [tokens, hidden]")
-    _need(B == step.n_dec, "every request brings exactly one token")
-    pend, pend_splits = None, 0
-    if isinstance(pending, Partials):
-        _need(tuple(pending.data.shape[1:]) == (B, prepared.hidden) and pending.data.is_contiguous(),
-              "pending partial sums are [splits, tokens, hidden]")
-        pend, pend_splits = pending.data, pending.splits
-    elif pending is not None:
-        residual_add(h, pending)
-    _need(len(step.kv_groups) >= prepared.n_groups, "the step has the cache groups the layers use")
-    n_groups = prepared.n_groups
-    slots = (ctypes.c_void_p * n_groups)()
-    tables = (ctypes.c_void_p * n_groups)()
-    strides = (ctypes.c_int * n_groups)()
-    for gi in range(n_groups):
-        g = step.kv_groups[gi]
-        _i32(g.slot_mapping, "slots")
-        _need(g.block_tables.dtype == torch.int32 and g.block_tables.stride(1) == 1, "block tables are int32 with dense rows")
-        slots[gi], tables[gi], strides[gi] = g.slot_mapping.data_ptr(), g.block_tables.data_ptr(), g.block_tables.stride(0)
-    _check(lib().zi_decode_layers(
-        _ptr(prepared.table), prepared.n_layers, B, prepared.hidden, prepared.nq, prepared.nkv, prepared.d,
-        prepared.inter, prepared.interleave, _ptr(h), _ptr(pend), pend_splits, _ptr(prepared.workspace),
-        ctypes.c_longlong(prepared.workspace_bytes), _ptr(step.positions), _ptr(step.cu_q), _ptr(step.kv_lens),
-        _ptr(step.dec_seq), n_groups, slots, tables, strides, prepared.page_size, prepared.grid, _stream()),
-        "decode_layers")
-    S = prepared.pending_splits
-    n = S * B * prepared.hidden
-    flat = prepared.workspace[prepared.pending_offset:prepared.pending_offset + 4 * n].view(torch.float32)
-    return Partials(flat.view(S, B, prepared.hidden))
 
 
 # ------------------------------------------------------------------------ sampling

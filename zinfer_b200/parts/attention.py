@@ -16,7 +16,6 @@ import torch
 
 from .. import ops
 from .base import KVCacheNeed, Mixer, TensorSpec, make_part
-from .rope import NoPosition, RotaryPosition
 
 
 class GQAttention(Mixer):
@@ -90,17 +89,3 @@ class GQAttention(Mixer):
         o = ops.attention(q, cache.k, cache.v, group.block_tables, step, self.nq, self.nkv, self.d,
                           cache.page_size, self.window, self.scale)
         return ops.linear(o, self.w_o, out_dtype=self.ctx.dtype, allow_partials=True)
-
-    def fused_decode_fields(self, cache):
-        if type(self) is not GQAttention or not cache.writes or self.ctx.dtype != torch.bfloat16:
-            return None
-        if self.w_qkv.dtype != torch.bfloat16 or self.w_o.dtype != torch.bfloat16:
-            return None
-        if self.position is not None and type(self.position) not in (RotaryPosition, NoPosition):
-            return None
-        cos, sin = self.position.tables() if self.position is not None else (None, None)
-        return {"w_qkv": self.w_qkv, "w_o": self.w_o, "hidden": self.hidden, "nq": self.nq, "nkv": self.nkv,
-                "d": self.d, "q_norm": self.q_norm, "k_norm": self.k_norm,
-                "qk_eps": self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, "cos": cos, "sin": sin,
-                "window": self.window, "scale": self.scale, "k": cache.k, "v": cache.v, "group": cache.group,
-                "page_size": cache.page_size}

@@ -19,8 +19,6 @@ Kinds of part and what each must provide:
 ``Block``           ``mixer`` attribute and ``forward(h, pending, step, cache)``:
                     arranges norms, mixer, feed-forward and residual sums; returns
                     the update not yet added into ``h``.
-
-Optional for every kind: ``fused_decode_fields``, see :class:`Part`.
 """
 from __future__ import annotations
 
@@ -85,13 +83,6 @@ class Part:
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         """Receives the device tensors named in :meth:`tensor_specs`."""
-
-    def fused_decode_fields(self, *args) -> Optional[dict]:
-        """What the kernel that runs whole layers of a decode step (``ops.decode_layers``)
-        needs from this part, or None if the part is not of a kind that kernel knows: the
-        layer then runs through ``forward``.  The default is None, so a new part never has
-        to know about that kernel."""
-        return None
 
 
 class Norm(Part):

@@ -41,17 +41,3 @@ class PreNormBlock(Block):
         a = self.mixer.forward(x, step, cache)
         x = self.ffn_norm.forward(h, a)
         return self.feed_forward.forward(x)
-
-    def fused_decode_fields(self, cache):
-        """The layer as h += mixer(norm(h)); h += ffn(norm(h)) for ``ops.decode_layers``, if
-        every part of it is of a kind that kernel knows."""
-        if type(self) is not PreNormBlock:
-            return None
-        fields = {"mixer_norm": self.mixer_norm.fused_decode_fields(), "mixer": self.mixer.fused_decode_fields(cache),
-                  "ffn_norm": self.ffn_norm.fused_decode_fields(), "feed_forward": self.feed_forward.fused_decode_fields()}
-        if any(v is None for v in fields.values()):
-            return None
-        m, f = fields["mixer"], fields["feed_forward"]
-        if not (m["hidden"] == f["hidden"] == fields["mixer_norm"]["size"] == fields["ffn_norm"]["size"]):
-            return None
-        return fields

@@ -42,9 +42,3 @@ class SwiGLUMLP(FeedForward):
             act = ops.swiglu(gu, out_dtype=self.ctx.dtype)
         # the product may come back as split-K partial sums; the next norm adds them with the residual
         return ops.linear(act, self.w_down, out_dtype=self.ctx.dtype, allow_partials=True)
-
-    def fused_decode_fields(self):
-        if type(self) is not SwiGLUMLP or self.w_gate_up.dtype != torch.bfloat16 or self.w_down.dtype != torch.bfloat16:
-            return None
-        return {"w_gate_up": self.w_gate_up, "w_down": self.w_down, "hidden": self.hidden, "inter": self.inter,
-                "interleave": ops.SWIGLU_INTERLEAVE if self.interleaved else 0}

@@ -29,8 +29,3 @@ class RMSNorm(Norm):
     def forward(self, h, delta, rows=None):
         """Adds ``delta`` into the residual ``h`` in place, then norms (the picked rows)."""
         return ops.add_rmsnorm(h, delta, self.weight, self.eps, self.ctx.dtype, rows=rows)
-
-    def fused_decode_fields(self):
-        if type(self) is not RMSNorm:   # a subclass may norm differently
-            return None
-        return {"weight": self.weight, "eps": self.eps, "size": self.size}

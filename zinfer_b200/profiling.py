@@ -12,7 +12,10 @@ flops / tensor throughput) divided by the time it took.
 Profiled steps run their kernels one by one: decode steps are not replayed from CUDA
 graphs, and an event between two kernels keeps the second from starting under the
 first's tail as it does in normal operation, so the sum over classes is a little
-above a normal step's time.  The figures are for finding where time goes; the
+above a normal step's time.  So that the figures are device times and not the host's
+pace of launching, every profiled step first queues a short spin on the device
+(``lead_ms``) behind which the host gets ahead: the step's events and kernels then lie
+back to back in the queue.  The figures are for finding where time goes; the
 benchmark's numbers are never taken under a profiler.
 
 The reference times its phases on the host and prints nanoseconds per operation
@@ -30,21 +33,32 @@ ACTIVE: Optional["Profiler"] = None     # read by ops on every launch; None: no 
 
 
 class Profiler:
-    def __init__(self, hbm_gbs: Optional[float] = None, bf16_tflops: Optional[float] = None):
+    def __init__(self, hbm_gbs: Optional[float] = None, bf16_tflops: Optional[float] = None, lead_ms: float = 8.0):
         self.hbm_gbs = hbm_gbs
         self.bf16_tflops = bf16_tflops
+        self.lead_ms = lead_ms
         self._records: list[tuple[str, object, object, int, int]] = []
         self.steps = 0
 
+    def begin_step(self) -> None:
+        """Called by the step function before a profiled step's first launch."""
+        self.steps += 1
+        if self.lead_ms > 0 and torch.cuda.is_available():
+            torch.cuda._sleep(int(self.lead_ms * 1.5e6))    # cycles of a bounded spin; about lead_ms at 1.5 GHz
+
     @contextmanager
     def region(self, name: str, nbytes: int = 0, flops: int = 0):
+        """Times what is launched inside the block.  The block may set ``rec["keep"] = False``
+        (nothing was launched after all) to drop the record."""
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        rec = {"keep": True}
         start.record()
         try:
-            yield
+            yield rec
         finally:
             end.record()
-            self._records.append((name, start, end, int(nbytes), int(flops)))
+            if rec["keep"]:
+                self._records.append((name, start, end, int(nbytes), int(flops)))
 
     def summary(self) -> dict:
         torch.cuda.synchronize()
@@ -91,7 +105,7 @@ def profile(hbm_gbs: Optional[float] = None, bf16_tflops: Optional[float] = None
 
 class _Null:
     def __enter__(self):
-        return None
+        return {"keep": True}
 
     def __exit__(self, *exc):
         return False
