@@ -127,6 +127,10 @@ def main() -> int:
     ap.add_argument("--profile", default=None, metavar="PATH",
                     help="also run one prefill and a few decode steps under the per-kernel-class profiler "
                          "(uncaptured, outside every timed region) and write its summary there as JSON")
+    ap.add_argument("--timeline", default=None, metavar="PATH",
+                    help="with ZINFER_B200_TRACE=1 in the environment: write the timeline of one decode step at the "
+                         "headline batch (every kernel's start, the completion of what it depends on, and what it adds "
+                         "to the chain) there as JSON, and do nothing else")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -175,6 +179,34 @@ def main() -> int:
         end.record()
         torch.cuda.synchronize()
         return start.elapsed_time(end)
+
+    if args.timeline:
+        from zinfer_b200 import profiling
+
+        ids = [f"t{i}" for i in range(args.batch)]
+        for rid in ids:
+            runner.step([StepEntry(rid, rand_tokens(PROMPT_LEN), [])])
+        cur = torch.randint(0, cfg.vocab_size, (args.batch,), generator=gen).tolist()
+
+        def one_step():
+            ops.argmax(runner.step([StepEntry(rid, [t], [0]) for rid, t in zip(ids, cur)]))
+
+        kernels = profiling.chain_timeline(one_step, warm=4)
+        # the chain of a decode step of this architecture, when its kernel count says that it is the one meant
+        per_layer = ["input norm", "qkv product", "attention (fused)", "attention combine", "o product", "post-attention norm",
+                     "gate_up product", "swiglu", "down product"]
+        names = ["embedding"] + per_layer * n_layers + ["final norm", "output head", "argmax (partial)", "argmax (final)"]
+        for i, k in enumerate(kernels):
+            k["kernel"] = names[i] if len(names) == len(kernels) else f"kernel {i}"
+        with open(args.timeline, "w") as f:
+            json.dump({"batch": args.batch, "context": PROMPT_LEN, "layers": n_layers, "kernels": kernels}, f, indent=1)
+        per = {}
+        for k in kernels:
+            if k["own_us"] is not None:
+                per.setdefault(k["kernel"], []).append(k["own_us"])
+        for name, v in per.items():
+            print(f"{name:24s} {statistics.median(v):8.2f} us (median of {len(v)})")
+        return 0
 
     # ---------------------------------------------------------------- prefill
     def prefill_once():

@@ -249,7 +249,8 @@ def test_decode_attention_split_choice():
     assert 12 <= decode_splits(1, 8, sms, 2048) <= 20      # one request: many splits fill the GPU, but each costs its merge
     assert decode_splits(8, 8, sms, 2048) == 4             # 64 (request, head) pairs x 4 = 256 blocks on 296 slots
     assert decode_splits(32, 8, sms, 2048) == 1            # 256 pairs already fill a wave
-    assert decode_splits(48, 8, sms, 2048) in (2, 3)       # 384 pairs: 2 waves whole, 1.3 split in three
+    assert decode_splits(48, 8, sms, 2048) == 1            # 384 pairs: more than half a wave of few keys is never split
+    assert decode_splits(64, 8, sms, 16384) > 1            # long walks: whole waves matter more than the merge
     assert decode_splits(8, 8, sms, 100) <= 2              # 100 keys are two tiles of 64
     assert decode_splits(8, 8, sms, 0) >= 1 and decode_splits(8, 8, sms, None) >= 1
     for n in range(1, 130):

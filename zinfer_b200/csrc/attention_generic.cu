@@ -157,3 +157,5 @@ extern "C" int zi_paged_attention(void* out, int out_stride, const void* q, int 
   });
   return zi_check_launch("paged_attention");
 }
+
+ZI_TRACE_SETTER(attention_generic)

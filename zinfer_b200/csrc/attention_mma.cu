@@ -204,9 +204,12 @@ __global__ void attn_decode_combine_kernel(bf16* __restrict__ out, int out_strid
                                            const int* __restrict__ cu_q, const int* __restrict__ dec_seq, int nq,
                                            int nkv, int splits) {
   pdl_launch_dependents();
+  // which token this is comes from the step's own arrays (copied before any kernel of the step):
+  // these two dependent loads need not wait for the attention kernel
+  const int token = cu_q[dec_seq[blockIdx.x]];
   pdl_wait();
-  attn_decode_combine_item<D>(blockIdx.x, blockIdx.y, threadIdx.x, blockDim.x, out, out_stride, partial, cu_q, dec_seq,
-                              nq, nkv, splits);
+  attn_decode_combine_item<D>(blockIdx.x, blockIdx.y, threadIdx.x, blockDim.x, out, out_stride, partial, token, nq, nkv,
+                              splits);
 }
 
 
@@ -359,3 +362,5 @@ extern "C" int zi_attention_decode_fused(void* out, int out_stride, float* works
   return dispatch_decode<true>(d, out, out_stride, workspace, nullptr, 0, kcache, vcache, block_tables, bt_stride, cu_q,
                                kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, fq, stream);
 }
+
+ZI_TRACE_SETTER(attention_mma)

@@ -435,3 +435,5 @@ extern "C" int zi_attention_prefill_tcgen05(void* out, int out_stride, const voi
             scale * 1.4426950408889634f, status);
   return zi_check_launch("attention_prefill_tcgen05");
 }
+
+ZI_TRACE_SETTER(attention_tcgen05)

@@ -697,12 +697,9 @@ __device__ __forceinline__ void attn_decode_unit(
 // (`partial` may have been written earlier in the same kernel: no read-only loads of it.)
 template <int D>
 __device__ __forceinline__ void attn_decode_combine_item(int dec, int h, int tid, int nthreads, bf16* __restrict__ out,
-                                                         int out_stride, const float* partial,
-                                                         const int* __restrict__ cu_q,
-                                                         const int* __restrict__ dec_seq, int nq, int nkv,
-                                                         int splits) {
+                                                         int out_stride, const float* partial, int token, int nq,
+                                                         int nkv, int splits) {
   const int g = nq / nkv, kvh = h / g, r = h % g;
-  const int token = cu_q[dec_seq[dec]];
   const float* base = partial + ((((size_t)dec * nkv + kvh) * splits) * g + r) * (D + 2);
   const size_t zstride = (size_t)g * (D + 2);
   if (splits <= 32) {

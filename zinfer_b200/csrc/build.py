@@ -21,10 +21,14 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "libzinfer_b200.so"
+# ZINFER_B200_TRACE=1 builds a second library (in a folder of its own) whose kernels leave time stamps
+# for a timeline of the chain (common.cuh, zinfer_b200.profiling.chain_timeline)
+TRACE = os.environ.get("ZINFER_B200_TRACE", "0") not in ("", "0")
+BUILD_FOLDER = "_build_trace" if TRACE else "_build"
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
-]
+] + (["-DZI_TRACE"] if TRACE else [])
 
 
 def _nvcc() -> str:
@@ -50,7 +54,7 @@ def _fingerprint() -> str:
 
 
 def _build_dir() -> str:
-    local = os.path.join(HERE, "_build")
+    local = os.path.join(HERE, BUILD_FOLDER)
     try:
         os.makedirs(local, exist_ok=True)
         probe = os.path.join(local, f".w{os.getpid()}")
@@ -59,7 +63,7 @@ def _build_dir() -> str:
         os.remove(probe)
         return local
     except OSError:
-        d = os.path.join(tempfile.gettempdir(), f"zinfer_b200_build_{os.getuid()}")
+        d = os.path.join(tempfile.gettempdir(), f"zinfer_b200{BUILD_FOLDER}_{os.getuid()}")
         os.makedirs(d, exist_ok=True)
         return d
 
@@ -67,8 +71,8 @@ def _build_dir() -> str:
 def library_path(build_if_needed: bool = True, verbose: bool = True) -> str:
     """Path of an up-to-date library, building it first if necessary."""
     fp = _fingerprint()
-    candidates = [os.path.join(HERE, "_build")]
-    tmp = os.path.join(tempfile.gettempdir(), f"zinfer_b200_build_{os.getuid()}")
+    candidates = [os.path.join(HERE, BUILD_FOLDER)]
+    tmp = os.path.join(tempfile.gettempdir(), f"zinfer_b200{BUILD_FOLDER}_{os.getuid()}")
     candidates.append(tmp)
     for d in candidates:
         lib, stamp = os.path.join(d, LIB_NAME), os.path.join(d, "fingerprint")

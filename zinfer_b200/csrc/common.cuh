@@ -72,8 +72,39 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 // therefore calls pdl_wait() before it reads anything an earlier kernel wrote (and every
 // kernel calls it once, so that completion stays transitive along the stream), and
 // pdl_launch_dependents() as soon as the next kernel may begin to start.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+//
+// Built with -DZI_TRACE (ZINFER_B200_TRACE=1 when the library is built), both calls also leave a time
+// stamp: thread 0 of a kernel's first block records %globaltimer when the kernel starts (stamp 0) and
+// when the kernels before it have completed (stamp 1) into a buffer given by zi_trace_set_<file>().
+// From these a step's timeline can be read as it runs inside the chain, overlaps included, which
+// no profiler that serialises kernels shows.  Without the flag none of this is compiled.
+#ifdef ZI_TRACE
+constexpr unsigned ZI_TRACE_CAPACITY = 8192;
+static __device__ unsigned long long* zi_trace_ptr = nullptr;   // word 0: number of stamps; then the stamps
+__device__ __forceinline__ void zi_stamp(unsigned what) {
+  unsigned long long* t = zi_trace_ptr;
+  if (t && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+    const unsigned idx = atomicAdd((unsigned*)t, 1u);
+    if (idx < ZI_TRACE_CAPACITY) t[1 + idx] = (now << 2) | what;
+  }
+}
+// one setter per source file (each has its own copy of the pointer)
+#define ZI_TRACE_SETTER(file) \
+  extern "C" int zi_trace_set_##file(void* p) { return (int)cudaMemcpyToSymbol(zi_trace_ptr, &p, sizeof(p)); }
+#else
+__device__ __forceinline__ void zi_stamp(unsigned) {}
+#define ZI_TRACE_SETTER(file)
+#endif
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  zi_stamp(1);
+}
+__device__ __forceinline__ void pdl_launch_dependents() {
+  zi_stamp(0);
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 
 extern int g_zi_pdl_enabled;
 

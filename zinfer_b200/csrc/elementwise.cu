@@ -652,3 +652,5 @@ extern "C" int zi_patch_tokens(int* ids, const int* prev, const int* dst, const 
   zi_launch(patch_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, ids, prev, dst, src, n);
   return zi_check_launch("patch_tokens");
 }
+
+ZI_TRACE_SETTER(elementwise)

@@ -94,3 +94,5 @@ extern "C" int zi_gemm_simt(void* out, int out_dtype, const void* x, int x_dtype
   }
   return zi_refuse("gemm: unknown dtype tags x=%d w=%d out=%d", x_dtype, w_dtype, out_dtype);
 }
+
+ZI_TRACE_SETTER(gemm_simt)

@@ -960,3 +960,5 @@ extern "C" int zi_gemm_tcgen05_static_scratch(void* out, int out_dtype, const vo
   return launch_gemm(out, out_dtype, map_a, map_b, M, N, K, ldo, plan, ss.scratch, status, sm_count, 0,
                      "gemm_static_scratch", stream);
 }
+
+ZI_TRACE_SETTER(gemm_tcgen05)

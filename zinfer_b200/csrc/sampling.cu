@@ -755,3 +755,4 @@ extern "C" int zi_count_tokens(int* counts, const int* tokens, int n, int V, cud
   return zi_check_launch("count_tokens");
 }
 
+ZI_TRACE_SETTER(sampling)

@@ -477,20 +477,24 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, blo
 
 def decode_splits(n_dec: int, num_kv_heads: int, sm_count: int, max_kv_len: Optional[int] = None,
                   fixed_us: float = 3.0) -> int:
-    """Key splits of the decode attention.  Its blocks are (request, kv head, split), two fit on
-    an SM at once, and a block costs a fixed time (``fixed_us``: launch, prologue, merge; more in
-    the fused kernel, which also makes q, k and v) plus its share of the walk over the keys
-    (about 0.025 us a key for a block's four warps); every split also costs the kernel that
-    merges them, and the blocks' own fixed work, about 0.2 us (measured at one request: 16 splits beat both 8 and 32).  The
-    split count (at most 32, never more than tiles of 64 keys) that makes the sum smallest."""
+    """Key splits of the decode attention.  Its blocks are (request, kv head, split), two fit on an SM
+    at once, and a block costs a fixed time (``fixed_us``: launch, prologue, merge; more in the fused
+    kernel, which also makes q, k and v) plus its share of the walk over the keys (about 0.02 us a key
+    for a block's four warps).  Any split costs the kernel that merges the splits: about 5 us in the
+    chain of a decode step, and 0.25 us more per split.  The split count (at most 32, never more than
+    tiles of 64 keys) that makes the sum smallest; one, when the blocks already fill more than half of
+    the GPU and the keys are few (measured at 24 to 128 requests of 2,048 keys: no split is 4 to 6 %
+    of a layer faster than any split; at 16 requests two splits win, at 8 four, at one 12 to 16)."""
     slots, units = 2 * sm_count, max(1, n_dec * num_kv_heads)
     keys = max_kv_len if max_kv_len and max_kv_len > 0 else 2048
+    if 2 * units > slots and keys <= 4096:
+        return 1
     limit = max(1, min(32, -(-keys // 64)))
-    walk = 0.025 * keys
+    walk = 0.02 * keys
     best, best_cost = 1, float("inf")
     for s in range(1, limit + 1):
         waves = -(-units * s // slots)
-        cost = waves * (fixed_us + walk / s) + 0.2 * s
+        cost = waves * (fixed_us + walk / s) + (5.0 + 0.25 * s if s > 1 else 0.0)
         if cost < best_cost:
             best, best_cost = s, cost
     return best

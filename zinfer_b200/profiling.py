@@ -120,3 +120,63 @@ def region(name: str, nbytes=0, flops=0):
     if ACTIVE is None:
         return _NULL
     return ACTIVE.region(name, nbytes() if callable(nbytes) else nbytes, flops() if callable(flops) else flops)
+
+
+# ------------------------------------------------------------------ timeline of a chain
+_TRACE_FILES = ("elementwise", "gemm_tcgen05", "attention_mma", "sampling", "attention_tcgen05", "attention_generic",
+                "gemm_simt")
+
+
+def chain_timeline(run_step, warm: int = 2) -> list[dict]:
+    """The timeline of the kernels that ``run_step()`` launches, as they run inside their chain.
+
+    Needs the kernel library built with time stamps (environment ``ZINFER_B200_TRACE=1`` from the
+    start of the process; it is a second library, built beside the ordinary one).  Every kernel
+    stamps the device's clock when its first block starts and when the kernels before it have
+    completed.  Returns, in launch order, ``{"start_us", "deps_done_us", "own_us"}`` per kernel,
+    times relative to the first stamp: ``start_us`` is when the kernel began (under programmatic
+    dependent launch long before it may read its inputs), ``deps_done_us`` when everything before it
+    had completed, ``own_us`` the time from there until everything before the NEXT kernel had
+    completed, i.e. what this kernel adds to the chain.  Unlike a profiler that runs kernels one at
+    a time, this shows the overlaps (weights of the next product fetched under a small kernel)."""
+    import ctypes
+
+    from . import ops
+    from .csrc import build
+
+    if not build.TRACE:
+        raise RuntimeError("chain_timeline needs ZINFER_B200_TRACE=1 in the environment when the process starts")
+    lib = ops.lib()
+    buf = torch.zeros(8192 + 8, dtype=torch.int64, device="cuda")
+
+    def point_all(ptr):
+        for f in _TRACE_FILES:
+            rc = getattr(lib, "zi_trace_set_" + f)(ctypes.c_void_p(ptr))
+            if rc != 0:
+                raise RuntimeError(f"zi_trace_set_{f} failed with CUDA error {rc}")
+
+    try:
+        for _ in range(warm):
+            run_step()
+        torch.cuda.synchronize()
+        point_all(buf.data_ptr())
+        torch.cuda.synchronize()
+        run_step()
+        torch.cuda.synchronize()
+    finally:
+        point_all(0)
+        torch.cuda.synchronize()
+    raw = buf.cpu().numpy()
+    n = min(int(raw[0]) & 0xFFFFFFFF, 8192)
+    stamps = sorted((int(v) >> 2, int(v) & 3) for v in raw[1:1 + n])
+    if not stamps:
+        return []
+    t0 = stamps[0][0]
+    starts = [(t - t0) / 1e3 for t, w in stamps if w == 0]
+    waits = [(t - t0) / 1e3 for t, w in stamps if w == 1]
+    out = []
+    for i, (s_us, w_us) in enumerate(zip(starts, waits)):
+        nxt = waits[i + 1] if i + 1 < len(waits) else None
+        out.append({"start_us": round(s_us, 2), "deps_done_us": round(w_us, 2),
+                    "own_us": round(nxt - w_us, 2) if nxt is not None else None})
+    return out
