@@ -138,7 +138,7 @@ class Engine:
             """The portion's one unread token can be taken from the step in flight."""
             return s.count == 1 and prev is not None and s.request.request_id in prev.row_of
 
-        if any(Scheduler.PLACEHOLDER in s.request.tokens[s.start:s.start + s.count] and not on_device(s)
+        if any(Scheduler.PLACEHOLDER in s.request.token_slice(s.start, s.count) and not on_device(s)
                for s in plan.scheduled):
             # a longer portion holds a token the host has not read yet: read the step in flight first,
             # before any entry is built, and drop what that ended (its pages are already given back)
@@ -148,7 +148,7 @@ class Engine:
         entries, rows = [], []
         for s in plan.scheduled:
             r = s.request
-            toks = r.tokens[s.start:s.start + s.count]
+            toks = r.token_slice(s.start, s.count)
             src = prev.row_of[r.request_id] if Scheduler.PLACEHOLDER in toks else None   # taken on the device
             if r.params.has_penalties and not self.sampler.has_request(r.request_id):
                 self.sampler.begin_request(r.request_id, r.params, r.prompt)   # admitted: at most max_requests hold a row

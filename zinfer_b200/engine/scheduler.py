@@ -63,6 +63,16 @@ class Request:
     def num_tokens(self) -> int:
         return len(self.prompt) + len(self.output)
 
+    def token_slice(self, start: int, count: int) -> list[int]:
+        """``tokens[start:start + count]`` without joining prompt and output first."""
+        n = len(self.prompt)
+        end = start + count
+        if end <= n:
+            return self.prompt[start:end]
+        if start >= n:
+            return self.output[start - n:end - n]
+        return self.prompt[start:] + self.output[:end - n]
+
 
 @dataclass
 class Scheduled:
@@ -85,11 +95,19 @@ class StepPlan:
 
 @dataclass
 class SchedulerStats:
+    """Totals since the scheduler was made, and the state after the last ``schedule()``."""
+
     steps: int = 0
     prompt_tokens: int = 0
     decode_tokens: int = 0
     preemptions: int = 0
     finished: int = 0
+    # the last step
+    step_tokens: int = 0          # tokens scheduled in it
+    running: int = 0
+    waiting: int = 0
+    pages_used: int = 0           # in the fullest cache group
+    pages_total: int = 0
 
 
 class Scheduler:
@@ -228,7 +246,12 @@ class Scheduler:
                 self._finish(stuck, "capacity", plan)
             else:
                 self._preempt(stuck, plan)
-        self.stats.steps += 1
+        st = self.stats
+        st.steps += 1
+        st.step_tokens, st.running, st.waiting = plan.num_tokens, len(self.running), len(self.waiting)
+        if self.cache.groups:
+            st.pages_total = self.cache.groups[0].pool.num_pages
+            st.pages_used = st.pages_total - self.cache.min_free_pages()
         return plan
 
     # --------------------------------------------------------------------- update
