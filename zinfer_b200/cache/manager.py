@@ -8,8 +8,11 @@ window has passed them.  Beside the pages, each request holds one slot for
 per-request state of fixed size (used by mixers that keep a state instead of keys;
 Qwen3 has none, the slot is still allocated and freed).
 
-This module is bookkeeping on the host and imports no device code; the device
-memory the ids refer to is owned by :class:`zinfer_b200.cache.storage.CacheStorage`.
+This is bookkeeping on the host and touches no device; the device memory the ids
+refer to is owned by :class:`zinfer_b200.cache.storage.CacheStorage`.  The
+bookkeeping itself (pools, block tables, windows) is native code
+(``csrc/host_runtime.cpp``), because every step of every request passes through it;
+this class groups the caches, keeps the names, and is its Python face.
 
 The reference has no counterpart: it preallocates one contiguous cache per request
 (src/model/runtime/optimized_kv_cache/cache.zig:38-84) and only resets a cursor
@@ -17,10 +20,13 @@ when a slot is reused (cache.zig:109-111).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+import ctypes
+import itertools
+from dataclasses import dataclass
 from typing import Hashable, Optional
 
-from .pages import OutOfPages, PagePool
+from ..csrc import host
+from .pages import GroupPool, OutOfPages
 
 
 @dataclass(frozen=True)
@@ -34,20 +40,31 @@ class KVNeedKey:
 class KVGroup:
     key: KVNeedKey
     caches: list[str]          # names of the caches that share this group's pages
-    pool: PagePool
+    pool: GroupPool
 
     @property
     def window(self) -> Optional[int]:
         return self.key.window
 
 
-@dataclass
 class RequestCache:
-    request_id: Hashable
-    state_slot: int
-    length: int = 0                       # tokens committed to the cache
-    reserved: int = 0                     # tokens with pages reserved beyond `length`
-    tables: list[list[int]] = field(default_factory=list)   # per group: page id per block, -1 once released
+    """What a live request holds (read from the native manager when asked)."""
+
+    def __init__(self, manager: "CacheManager", request_id: Hashable, native_id: int, state_slot: int):
+        self._manager = manager
+        self.request_id = request_id
+        self.native_id = native_id
+        self.state_slot = state_slot
+
+    @property
+    def length(self) -> int:
+        """Tokens committed to the cache."""
+        return self._manager.length(self.request_id)
+
+    @property
+    def tables(self) -> list[list[int]]:
+        """Per group: page id per block, -1 once released."""
+        return [self._manager.block_table(self.request_id, gi) for gi in range(len(self._manager.groups))]
 
 
 class CacheManager:
@@ -59,34 +76,86 @@ class CacheManager:
             raise ValueError("page_size must be positive")
         self.page_size = page_size
         self.max_requests = max_requests
-        self.groups: list[KVGroup] = []
+        keys: list[KVNeedKey] = []
+        members: list[list[str]] = []
+        sizes: list[int] = []
         self.group_of: dict[str, tuple[int, int]] = {}   # cache name -> (group, index within the group)
         for name, need in kv_needs.items():
             key = KVNeedKey(need.num_kv_heads, need.head_dim, need.window)
             if key.window is not None and key.window <= 0:
                 raise ValueError(f"cache {name!r}: window must be positive")
-            for gi, g in enumerate(self.groups):
-                if g.key == key:
-                    self.group_of[name] = (gi, len(g.caches))
-                    g.caches.append(name)
-                    break
+            if key in keys:
+                gi = keys.index(key)
+                self.group_of[name] = (gi, len(members[gi]))
+                members[gi].append(name)
             else:
-                n = num_pages[key] if isinstance(num_pages, dict) else num_pages
-                self.groups.append(KVGroup(key, [name], PagePool(n, name=f"kv pages of group {len(self.groups)}")))
-                self.group_of[name] = (len(self.groups) - 1, 0)
+                keys.append(key)
+                members.append([name])
+                sizes.append(int(num_pages[key] if isinstance(num_pages, dict) else num_pages))
+                self.group_of[name] = (len(keys) - 1, 0)
+        if any(n < 0 for n in sizes):
+            raise ValueError("num_pages must be >= 0")
+        self._lib = host.lib()
+        n = len(keys)
+        windows = (ctypes.c_int * max(n, 1))(*[k.window or 0 for k in keys])
+        pages = (ctypes.c_int * max(n, 1))(*sizes)
+        self._handle = self._lib.zi_cache_create(n, windows, pages, page_size, max_requests)
+        if not self._handle:
+            raise ValueError("the cache manager could not be created")
+        self.groups: list[KVGroup] = [
+            KVGroup(key, names, GroupPool(self._handle, gi, f"kv pages of group {gi}"))
+            for gi, (key, names) in enumerate(zip(keys, members))]
         self.state_caches = list(state_caches)
-        self.slots = PagePool(max_requests, name="request slots")
+        self.slots = GroupPool(self._handle, -1, "request slots")
         self.requests: dict[Hashable, RequestCache] = {}
+        self._next_id = itertools.count(1)
+        self._pairs = (ctypes.c_int * 4096)()      # (group, page) pairs that a call gave back
+        self._info = (ctypes.c_int * 3)()
+        self._per_group = (ctypes.c_int * max(n, 1))()
         # called with (group index, pages) whenever pages go back to their pool: a debugging hook
         # (the storage can overwrite what they held, so that a read of a stale page shows)
         self.on_release = None
+
+    def __del__(self):
+        handle, self._handle = getattr(self, "_handle", None), None
+        if handle:
+            self._lib.zi_cache_destroy(handle)
+
+    @property
+    def handle(self):
+        """The native manager (for the native step builder)."""
+        return self._handle
+
+    def native_id(self, request_id: Hashable) -> int:
+        return self._live(request_id).native_id
+
+    def _live(self, request_id: Hashable) -> RequestCache:
+        rc = self.requests.get(request_id)
+        if rc is None:
+            raise KeyError(f"request {request_id!r} is not live (freed twice?)")
+        return rc
+
+    def _released(self, n: int) -> list[tuple[int, int]]:
+        pairs = [(self._pairs[2 * i], self._pairs[2 * i + 1]) for i in range(min(n, len(self._pairs) // 2))]
+        if self.on_release is not None and pairs:
+            by_group: dict[int, list[int]] = {}
+            for gi, page in pairs:
+                by_group.setdefault(gi, []).append(page)
+            for gi, pages in by_group.items():
+                self.on_release(gi, pages)
+        return pairs
 
     # ------------------------------------------------------------------ requests
     def add_request(self, request_id: Hashable) -> RequestCache:
         if request_id in self.requests:
             raise KeyError(f"request {request_id!r} is already live")
-        slot = self.slots.alloc(1)[0]
-        rc = RequestCache(request_id, slot, tables=[[] for _ in self.groups])
+        nid = next(self._next_id)
+        slot = self._lib.zi_cache_add(self._handle, nid)
+        if slot == host.OUT_OF_PAGES:
+            raise OutOfPages(f"request slots: 1 wanted, 0 of {self.max_requests} free")
+        if slot < 0:
+            raise RuntimeError(f"adding request {request_id!r} failed (code {slot})")
+        rc = RequestCache(self, request_id, nid, slot)
         self.requests[request_id] = rc
         return rc
 
@@ -94,81 +163,82 @@ class CacheManager:
         return request_id in self.requests
 
     def free_request(self, request_id: Hashable) -> None:
-        rc = self.requests.pop(request_id, None)
-        if rc is None:
-            raise KeyError(f"request {request_id!r} is not live (freed twice?)")
-        for gi, (g, table) in enumerate(zip(self.groups, rc.tables)):
-            pages = [p for p in table if p >= 0]
-            g.pool.free(pages)
-            if self.on_release is not None and pages:
-                self.on_release(gi, pages)
-        self.slots.free([rc.state_slot])
+        rc = self._live(request_id)
+        if self.on_release is not None:      # the hook wants every page, however many: read the tables first
+            tables = rc.tables
+        n = self._lib.zi_cache_free(self._handle, rc.native_id, self._pairs, len(self._pairs))
+        if n < 0:
+            raise RuntimeError(f"freeing request {request_id!r} failed: {host.last_error()}")
+        del self.requests[request_id]
+        if self.on_release is not None:
+            for gi, table in enumerate(tables):
+                pages = [p for p in table if p >= 0]
+                if pages:
+                    self.on_release(gi, pages)
 
     # --------------------------------------------------------------------- pages
-    def _blocks_for(self, n_tokens: int) -> int:
-        return -(-n_tokens // self.page_size)
-
     def pages_needed(self, request_id: Hashable, n_new: int) -> list[int]:
         """Pages each group must still allocate so that ``n_new`` more tokens fit."""
-        rc = self.requests[request_id]
-        want = self._blocks_for(rc.length + n_new)
-        return [max(0, want - len(t)) for t in rc.tables]
+        self._lib.zi_cache_pages_needed(self._handle, self._live(request_id).native_id, n_new, self._per_group)
+        return list(self._per_group[:len(self.groups)])
 
     def can_reserve(self, request_id: Hashable, n_new: int) -> bool:
-        return all(n <= g.pool.num_free for n, g in zip(self.pages_needed(request_id, n_new), self.groups))
+        return self._lib.zi_cache_can_reserve(self._handle, self._live(request_id).native_id, n_new) == 1
+
+    def _out_of_pages(self, what: str) -> OutOfPages:
+        gi, need, free = self._info[0], self._info[1], self._info[2]
+        return OutOfPages(f"{what}: {need} pages wanted in {self.groups[gi].pool.name}, {free} free")
 
     def reserve(self, request_id: Hashable, n_new: int) -> None:
         """Pages for positions ``length .. length + n_new - 1`` in every group, or
         :class:`OutOfPages` with nothing taken."""
-        rc = self.requests[request_id]
-        need = self.pages_needed(request_id, n_new)
-        for n, g in zip(need, self.groups):
-            if n > g.pool.num_free:
-                raise OutOfPages(f"request {request_id!r}: {n} pages wanted in {g.pool.name}, {g.pool.num_free} free")
-        for n, g, table in zip(need, self.groups, rc.tables):
-            table.extend(g.pool.alloc(n))
-        rc.reserved = max(rc.reserved, n_new)
+        rc = self._lib.zi_cache_reserve(self._handle, self._live(request_id).native_id, n_new, self._info)
+        if rc == host.OUT_OF_PAGES:
+            raise self._out_of_pages(f"request {request_id!r}")
+
+    def reserve_all(self, request_ids, n_new) -> None:
+        """Pages for several requests at once: all of them, or :class:`OutOfPages` with nothing taken."""
+        n = len(request_ids)
+        ids = (ctypes.c_longlong * max(n, 1))(*[self._live(r).native_id for r in request_ids])
+        new = (ctypes.c_longlong * max(n, 1))(*[int(v) for v in n_new])
+        rc = self._lib.zi_cache_reserve_all(self._handle, n, ids, new, self._info)
+        if rc == host.OUT_OF_PAGES:
+            raise self._out_of_pages("the step")
 
     def slots_for(self, request_id: Hashable, group: int, start: int, n: int) -> list[int]:
         """Flat slot (page * page_size + offset) of positions ``start .. start+n-1``."""
-        table = self.requests[request_id].tables[group]
-        ps = self.page_size
-        out = []
-        for pos in range(start, start + n):
-            page = table[pos // ps]
-            if page < 0:
-                raise RuntimeError(f"position {pos} of request {request_id!r} lies in a page already given back")
-            out.append(page * ps + pos % ps)
-        return out
+        out = (ctypes.c_int * max(n, 1))()
+        rc = self._lib.zi_cache_slots_for(self._handle, self._live(request_id).native_id, group, start, n, out)
+        if rc == host.RELEASED:
+            raise RuntimeError(f"request {request_id!r}: {host.last_error()}")
+        if rc < 0:
+            raise IndexError(f"request {request_id!r}: {host.last_error()}")
+        return list(out[:n])
 
     def commit(self, request_id: Hashable, n_new: int) -> list[tuple[int, int]]:
         """The step wrote ``n_new`` tokens.  Gives back the pages that every window
         has passed; returns them as (group, page)."""
-        rc = self.requests[request_id]
-        rc.length += n_new
-        rc.reserved = 0
-        released = []
-        for gi, (g, table) in enumerate(zip(self.groups, rc.tables)):
-            if g.window is None:
-                continue
-            # the next query sits at position `length`; it reads keys > length - window
-            first_needed = rc.length - g.window + 1
-            n_dead = max(0, first_needed // self.page_size)
-            dead = [b for b in range(min(n_dead, len(table))) if table[b] >= 0]
-            if dead:
-                g.pool.free([table[b] for b in dead])
-                if self.on_release is not None:
-                    self.on_release(gi, [table[b] for b in dead])
-                for b in dead:
-                    released.append((gi, table[b]))
-                    table[b] = -1
-        return released
+        n = self._lib.zi_cache_commit(self._handle, self._live(request_id).native_id, n_new, self._pairs, len(self._pairs))
+        if n < 0:
+            raise RuntimeError(f"committing to request {request_id!r} failed: {host.last_error()}")
+        return self._released(n) if n else []
 
     def length(self, request_id: Hashable) -> int:
-        return self.requests[request_id].length
+        return int(self._lib.zi_cache_length(self._handle, self._live(request_id).native_id))
 
     def block_table(self, request_id: Hashable, group: int) -> list[int]:
-        return self.requests[request_id].tables[group]
+        nid = self._live(request_id).native_id
+        n = self._lib.zi_cache_table_len(self._handle, nid, group)
+        if n < 0:
+            raise IndexError(f"no group {group}")
+        out = (ctypes.c_int * max(n, 1))()
+        self._lib.zi_cache_table(self._handle, nid, group, out, n)
+        return list(out[:n])
+
+    def blocks_held(self, request_id: Hashable) -> int:
+        """Blocks (pages, released ones included) that the request's shortest block table spans."""
+        nid = self._live(request_id).native_id
+        return min((self._lib.zi_cache_table_len(self._handle, nid, gi) for gi in range(len(self.groups))), default=0)
 
     # ---------------------------------------------------------------- accounting
     def free_pages(self) -> list[int]:
@@ -179,11 +249,5 @@ class CacheManager:
 
     def check(self) -> None:
         """No page lost, held twice or freed twice; no slot either."""
-        self.slots.check()
-        for gi, g in enumerate(self.groups):
-            g.pool.check()
-            held = [p for rc in self.requests.values() for p in rc.tables[gi] if p >= 0]
-            assert len(held) == len(set(held)), f"group {gi}: a page is held by two block tables"
-            assert set(held) == g.pool._used, f"group {gi}: pages in use and pages in block tables differ"
-        slots = [rc.state_slot for rc in self.requests.values()]
-        assert len(slots) == len(set(slots)) and set(slots) == self.slots._used, "request slots are inconsistent"
+        assert self._lib.zi_cache_check(self._handle) == 0, host.last_error()
+        assert self._lib.zi_cache_num_requests(self._handle) == len(self.requests), "live requests differ from the native manager's"

@@ -1,11 +1,16 @@
 """A pool of equal pages (or slots) with a free list.
 
 Pages freed last are handed out first, so reuse is immediate: a fault that comes
-from stale contents of a reused page shows at once in tests.  The pool keeps the
-set of pages in use and refuses to free a page that is not, so no page is ever
-lost, held twice or freed twice.
+from stale contents of a reused page shows at once in tests.  The pool keeps track
+of the pages in use and refuses to free a page that is not, so no page is ever
+lost, held twice or freed twice.  The bookkeeping itself is native
+(``csrc/host_runtime.cpp``); this class is its Python face.
 """
 from __future__ import annotations
+
+import ctypes
+
+from ..csrc import host
 
 
 class OutOfPages(RuntimeError):
@@ -17,45 +22,77 @@ class PagePool:
         if num_pages < 0:
             raise ValueError("num_pages must be >= 0")
         self.name = name
-        self.num_pages = num_pages
-        self._free = list(range(num_pages - 1, -1, -1))  # pop() gives 0, 1, 2, ... first
-        self._used: set[int] = set()
-        self._ever: set[int] = set()     # pages that have been handed out at least once
-        self.reused = 0                  # allocations that returned a page which had been in use before
+        self._lib = host.lib()
+        self._handle = self._lib.zi_pool_create(num_pages)
+        self._stats_buf = (ctypes.c_longlong * 4)()
+
+    def __del__(self):
+        handle, self._handle = getattr(self, "_handle", None), None
+        if handle:
+            self._lib.zi_pool_destroy(handle)
+
+    def _stats(self):
+        self._lib.zi_pool_stats(self._handle, self._stats_buf)
+        return self._stats_buf
+
+    @property
+    def num_pages(self) -> int:
+        return int(self._stats()[0])
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return int(self._stats()[1])
 
     @property
     def num_used(self) -> int:
-        return len(self._used)
+        return int(self._stats()[2])
+
+    @property
+    def reused(self) -> int:
+        """Allocations that returned a page which had been in use before."""
+        return int(self._stats()[3])
 
     def alloc(self, n: int) -> list[int]:
         """n pages, or :class:`OutOfPages` with the pool unchanged."""
         if n < 0:
             raise ValueError("cannot allocate a negative number of pages")
-        if n > len(self._free):
-            raise OutOfPages(f"{self.name}: {n} wanted, {len(self._free)} of {self.num_pages} free")
-        out = [self._free.pop() for _ in range(n)]
-        self._used.update(out)
-        self.reused += sum(p in self._ever for p in out)
-        self._ever.update(out)
-        return out
+        out = (ctypes.c_int * max(n, 1))()
+        rc = self._lib.zi_pool_alloc(self._handle, n, out)
+        if rc == host.OUT_OF_PAGES:
+            raise OutOfPages(f"{self.name}: {n} wanted, {self.num_free} of {self.num_pages} free")
+        return list(out[:n])
 
     def free(self, pages) -> None:
-        pages = list(pages)
-        for p in pages:
-            if p not in self._used:
-                raise ValueError(f"{self.name}: page {p} is not in use (freed twice, or never allocated)")
-        if len(set(pages)) != len(pages):
-            raise ValueError(f"{self.name}: a page is named twice in one free")
-        for p in pages:
-            self._used.remove(p)
-            self._free.append(p)
+        pages = [int(p) for p in pages]
+        arr = (ctypes.c_int * max(len(pages), 1))(*pages)
+        bad = ctypes.c_int(-1)
+        rc = self._lib.zi_pool_free(self._handle, arr, len(pages), ctypes.byref(bad))
+        if rc == host.BAD_PAGE:
+            raise ValueError(f"{self.name}: page {bad.value} is not in use (freed twice, or never allocated)")
+        if rc == host.NAMED_TWICE:
+            raise ValueError(f"{self.name}: page {bad.value} is named twice in one free")
 
     def check(self) -> None:
         """Every page is either free or in use, exactly once."""
-        assert len(self._free) == len(set(self._free)), "a page is on the free list twice"
-        assert not (set(self._free) & self._used), "a page is both free and in use"
-        assert len(self._free) + len(self._used) == self.num_pages, "a page was lost"
+        assert self._lib.zi_pool_check(self._handle) == 0, f"{self.name}: {host.last_error()}"
+
+
+class GroupPool:
+    """Read-only face of a pool that lives inside the native cache manager (a group's pages,
+    or the request slots): the manager itself allocates and frees."""
+
+    def __init__(self, cache_handle, group: int, name: str):
+        self.name = name
+        self._lib = host.lib()
+        self._cache = cache_handle
+        self._group = group
+        self._stats_buf = (ctypes.c_longlong * 4)()
+
+    def _stats(self):
+        self._lib.zi_cache_pool_stats(self._cache, self._group, self._stats_buf)
+        return self._stats_buf
+
+    num_pages = PagePool.num_pages
+    num_free = PagePool.num_free
+    num_used = PagePool.num_used
+    reused = PagePool.reused

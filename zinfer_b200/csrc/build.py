@@ -39,14 +39,15 @@ def _nvcc() -> str:
 
 
 def sources() -> list[str]:
-    return sorted(f for f in os.listdir(HERE) if f.endswith(".cu"))
+    """The kernels (.cu) and the native host runtime (.cpp); nvcc compiles both."""
+    return sorted(f for f in os.listdir(HERE) if f.endswith((".cu", ".cpp")))
 
 
 def _fingerprint() -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS).encode())
     for f in sorted(os.listdir(HERE)):
-        if f.endswith((".cu", ".cuh", ".h")):
+        if f.endswith((".cu", ".cuh", ".h", ".cpp")):
             h.update(f.encode())
             with open(os.path.join(HERE, f), "rb") as fh:
                 h.update(fh.read())
@@ -107,7 +108,7 @@ def build(verbose: bool = True) -> str:
     hb.start()
     try:
         def compile_one(src: str) -> str:
-            obj = os.path.join(out_dir, src[:-3] + ".o")
+            obj = os.path.join(out_dir, os.path.splitext(src)[0] + ".o")
             cmd = [nvcc, *NVCC_FLAGS, "-I", HERE, "-c", os.path.join(HERE, src), "-o", obj]
             r = subprocess.run(cmd, capture_output=True, text=True)
             if r.returncode != 0:

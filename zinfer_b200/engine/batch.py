@@ -15,6 +15,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
+from ..csrc import host
 
 
 @dataclass
@@ -86,148 +87,96 @@ class PinnedStaging:
             self._copied.record()
 
 
+_ARRAYS = ("token_ids", "positions", "cu_q", "kv_lens", "state_slots", "tile_seq", "tile_q0", "logit_rows", "dec_seq",
+           "pf_tile_seq", "pf_tile_q0", "patch_dst", "patch_src")
+
+
 def build_step(manager: CacheManager, entries: Sequence[StepEntry], device, tile_rows: int, pin: bool = True,
                static: Optional["StaticStepBuffers"] = None, pf_tile_rows: int = 128,
                staging: Optional[PinnedStaging] = None) -> StepContext:
-    """Flattens ``entries``; their pages must already be reserved in ``manager``.
+    """Flattens ``entries``; their pages must already be reserved in ``manager``.  The arrays are
+    filled by the native step builder (``zi_step_build`` in csrc/host_runtime.cpp, which reads the
+    block tables where the native cache manager keeps them) into one pinned buffer.
 
     With ``static`` (decode steps replayed from a CUDA graph) the arrays have the
     fixed capacity and addresses of those buffers: every entry brings one token, the
     batch is padded to ``static.batch`` with requests of one key in no page whose
     key/value write is skipped (slot -1), and block tables have ``static.width``
     columns."""
-    n_real = len(entries)
-    ps = manager.page_size
-    q_lens = [len(e.tokens) for e in entries]
-    ctx_lens = [manager.length(e.request_id) for e in entries]
+    lib = host.lib()
+    n_e = len(entries)
     n_groups = len(manager.groups)
-    if static is not None:
-        assert all(q == 1 for q in q_lens) and n_real <= static.batch
-        assert all(len(manager.block_table(e.request_id, gi)) <= static.width for e in entries for gi in range(n_groups)), \
-            "a request is longer than its bucket's block tables"
-        n = static.batch
-        widths = [static.width] * n_groups
+    q_lens = [len(e.tokens) for e in entries]
+    ids = np.fromiter((manager.native_id(e.request_id) for e in entries), dtype=np.int64, count=n_e)
+    ql = np.asarray(q_lens, dtype=np.int32)
+    if max(q_lens, default=0) == 1:
+        tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=n_e)
     else:
-        n = n_real
-        widths = [max(1, max(len(manager.block_table(e.request_id, gi)) for e in entries)) for gi in range(n_groups)]
-    pad = n - n_real
-    T = int(sum(q_lens)) + pad
-    cu = np.zeros(n + 1, dtype=np.int64)
-    np.cumsum(q_lens + [1] * pad, out=cu[1:])
-    n_tiles_per = [-(-q // tile_rows) for q in q_lens] + [1] * pad
-    n_tiles = int(sum(n_tiles_per))
-    all_q = q_lens + [1] * pad
-    dec_list = [i for i, ql in enumerate(all_q) if ql == 1]
-    pf_tiles = [(i, t * pf_tile_rows) for i, ql in enumerate(all_q) if ql > 1 for t in range(-(-ql // pf_tile_rows))]
-    # the tiles that read the most keys come first: blocks are handed out in this order, so
-    # the long ones do not end up alone at the tail
-    all_ctx = ctx_lens + [0] * pad
-    pf_tiles.sort(key=lambda it: -(all_ctx[it[0]] + min(all_q[it[0]], it[1] + pf_tile_rows)))
-    if static is not None:
-        rows = list(range(n))
-    else:
-        rows = [int(cu[i]) + int(w) for i, e in enumerate(entries) for w in e.want]
-    R = len(rows)
+        tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+    want_counts = np.fromiter((len(e.want) for e in entries), dtype=np.int32, count=n_e)
+    n_want = int(want_counts.sum())
+    want = np.fromiter((int(w) for e in entries for w in e.want), dtype=np.int32, count=n_want) if n_want else np.zeros(1, np.int32)
+    token_src = np.fromiter((-1 if e.token_src is None else int(e.token_src) for e in entries), dtype=np.int32, count=n_e)
+    n_arrays = len(_ARRAYS) + 2 * n_groups
+    layout = np.zeros(2 * n_arrays + 10 + n_groups, dtype=np.int64)
 
-    # layout of the packed buffer
-    sizes = [("token_ids", T), ("positions", T), ("cu_q", n + 1), ("kv_lens", n), ("state_slots", n),
-             ("tile_seq", n_tiles), ("tile_q0", n_tiles), ("logit_rows", R), ("dec_seq", len(dec_list)),
-             ("pf_tile_seq", len(pf_tiles)), ("pf_tile_q0", len(pf_tiles))]
-    patches = [(int(cu[i]), int(e.token_src)) for i, e in enumerate(entries) if e.token_src is not None]
-    n_patch_cap = n if static is not None else len(patches)
-    sizes += [("patch_dst", n_patch_cap), ("patch_src", n_patch_cap)]
-    for gi in range(n_groups):
-        sizes += [(f"slots{gi}", T), (f"bt{gi}", n * widths[gi])]
-    offs, total = {}, 0
-    for name, sz in sizes:
-        offs[name] = (total, sz)
-        total += -(-sz // 4) * 4   # keep every array 16-byte aligned
+    def call(buf_ptr, capacity):
+        return lib.zi_step_build(manager.handle, n_e, ids.ctypes.data, ql.ctypes.data, tokens.ctypes.data,
+                                 want_counts.ctypes.data, want.ctypes.data, token_src.ctypes.data,
+                                 static.batch if static is not None else 0, static.width if static is not None else 0,
+                                 tile_rows, pf_tile_rows, buf_ptr, capacity, layout.ctypes.data)
+
+    total = call(None, 0)
+    if total < 0:
+        raise RuntimeError(f"the step cannot be built: {host.last_error()}")
     if static is not None:
-        host = static.host_buffer(total)
+        hostbuf = static.host_buffer(total)
     elif staging is not None:
-        host = staging.get(max(total, 4))
+        hostbuf = staging.get(max(total, 4))
     else:
-        host = torch.empty(max(total, 4), dtype=torch.int32, pin_memory=pin and torch.cuda.is_available())
-    buf = host.numpy()
-
-    def arr(name):
-        o, s = offs[name]
-        return buf[o:o + s]
-
-    tok, pos = arr("token_ids"), arr("positions")
-    tseq, tq0 = arr("tile_seq"), arr("tile_q0")
-    tok[:] = 0
-    pos[:] = 0
-    ti = 0
-    for i in range(n):
-        a, b = int(cu[i]), int(cu[i + 1])
-        if i < n_real:
-            tok[a:b] = np.maximum(np.asarray(entries[i].tokens, dtype=np.int64), 0)   # placeholders are patched on the device
-            pos[a:b] = np.arange(ctx_lens[i], ctx_lens[i] + q_lens[i])
-        for t in range(n_tiles_per[i]):
-            tseq[ti] = i
-            tq0[ti] = t * tile_rows
-            ti += 1
-    arr("cu_q")[:] = cu
-    arr("dec_seq")[:] = dec_list
-    if n_patch_cap:
-        arr("patch_dst")[:] = -1
-        arr("patch_src")[:] = 0
-        arr("patch_dst")[:len(patches)] = [d for d, _ in patches]
-        arr("patch_src")[:len(patches)] = [s_ for _, s_ in patches]
-    arr("pf_tile_seq")[:] = [i for i, _ in pf_tiles]
-    arr("pf_tile_q0")[:] = [t for _, t in pf_tiles]
-    kv = arr("kv_lens")
-    kv[:] = 1
-    if n_real:
-        kv[:n_real] = np.asarray(ctx_lens) + np.asarray(q_lens)
-    ss = arr("state_slots")
-    ss[:] = 0
-    ss[:n_real] = [manager.requests[e.request_id].state_slot for e in entries]
-    if R:
-        arr("logit_rows")[:] = rows
+        hostbuf = torch.empty(max(total, 4), dtype=torch.int32, pin_memory=pin and torch.cuda.is_available())
+    rc = call(hostbuf.data_ptr(), hostbuf.numel())
+    if rc < 0:
+        raise RuntimeError(f"the step cannot be built: {host.last_error()}")
+    offs = {name: (int(layout[2 * i]), int(layout[2 * i + 1])) for i, name in enumerate(_ARRAYS)}
     for gi in range(n_groups):
-        W = widths[gi]
-        bt = arr(f"bt{gi}").reshape(n, W)
-        bt[:] = -1
-        sl = arr(f"slots{gi}")
-        sl[:] = -1
-        for i, e in enumerate(entries):
-            table = np.asarray(manager.block_table(e.request_id, gi), dtype=np.int64)
-            bt[i, :len(table)] = table
-            a, b = int(cu[i]), int(cu[i + 1])
-            p = pos[a:b].astype(np.int64)
-            pages = table[p // ps]
-            if (pages < 0).any():
-                raise RuntimeError(f"request {e.request_id!r}: a token would be written to a page already given back")
-            sl[a:b] = pages * ps + p % ps
+        for j, name in enumerate((f"slots{gi}", f"bt{gi}")):
+            k = len(_ARRAYS) + 2 * gi + j
+            offs[name] = (int(layout[2 * k]), int(layout[2 * k + 1]))
+    tail = layout[2 * n_arrays:]
+    n, T, R, n_dec, n_pf, n_patch = int(tail[1]), int(tail[2]), int(tail[3]), int(tail[4]), int(tail[5]), int(tail[7])
+    widths = [int(w) for w in tail[10:10 + n_groups]]
+    o, sz = offs["kv_lens"]
+    kv = hostbuf[o:o + n_e].tolist()
+    ctx_lens = [k - q for k, q in zip(kv, q_lens)]
 
     if static is not None:
         dev = static.device_buffer(total)
-        dev.copy_(host[:total], non_blocking=True)
+        dev.copy_(hostbuf[:total], non_blocking=True)
         static.mark_copied()
     else:
-        dev = host.to(device, non_blocking=True)
+        dev = hostbuf[:max(total, 4)].to(device, non_blocking=True)
         if staging is not None:
             staging.mark_copied()
 
     def view(name):
-        o, s = offs[name]
-        return dev[o:o + s]
+        o, s_ = offs[name]
+        return dev[o:o + s_]
 
+    n_patch_cap = offs["patch_dst"][1]
     groups = [KVGroupStep(view(f"slots{gi}"), view(f"bt{gi}").view(n, widths[gi])) for gi in range(n_groups)]
     return StepContext(
         n_seqs=n, n_tokens=T, token_ids=view("token_ids"), positions=view("positions"), cu_q=view("cu_q"),
         kv_lens=view("kv_lens"), state_slots=view("state_slots"), tile_seq=view("tile_seq"), tile_q0=view("tile_q0"),
         dec_seq=view("dec_seq"), pf_tile_seq=view("pf_tile_seq"), pf_tile_q0=view("pf_tile_q0"),
-        n_dec=len(dec_list), n_pf_tiles=len(pf_tiles),
+        n_dec=n_dec, n_pf_tiles=n_pf,
         patch_dst=view("patch_dst") if n_patch_cap else None, patch_src=view("patch_src") if n_patch_cap else None,
-        n_patch=len(patches),
+        n_patch=n_patch,
         logit_rows=view("logit_rows") if R else None, kv_groups=groups, q_lens=q_lens, ctx_lens=ctx_lens,
         max_q_len=max(q_lens, default=0),
         # a captured graph serves later steps with longer requests: its launches are shaped by the
         # bucket's length, never by the lengths of the step that happened to be captured
-        max_kv_len=static.max_kv_len if static is not None else max((c + q for c, q in zip(ctx_lens, q_lens)), default=0),
+        max_kv_len=static.max_kv_len if static is not None else int(tail[9]),
         all_decode=all(q == 1 for q in q_lens), h2d_bytes=int(total) * 4)
 
 

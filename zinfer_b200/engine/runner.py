@@ -148,23 +148,13 @@ class ModelRunner:
 
     def reserve(self, entries: Sequence[StepEntry]) -> None:
         """Pages for all entries, or :class:`OutOfPages` with nothing kept."""
-        added, done = [], []
+        added = []
         try:
             for e in entries:
                 if not self.manager.has_request(e.request_id):
                     self.add_request(e.request_id)
                     added.append(e.request_id)
-            # all-or-nothing across entries: count first, then take
-            need = [0] * len(self.manager.groups)
-            for e in entries:
-                for gi, n in enumerate(self.manager.pages_needed(e.request_id, len(e.tokens))):
-                    need[gi] += n
-            for gi, g in enumerate(self.manager.groups):
-                if need[gi] > g.pool.num_free:
-                    raise OutOfPages(f"the step needs {need[gi]} pages in {g.pool.name}, {g.pool.num_free} are free")
-            for e in entries:
-                self.manager.reserve(e.request_id, len(e.tokens))
-                done.append(e)
+            self.manager.reserve_all([e.request_id for e in entries], [len(e.tokens) for e in entries])
         except OutOfPages:
             for rid in added:
                 self.manager.free_request(rid)

@@ -167,7 +167,7 @@ class Scheduler:
         if self.cache.can_reserve(r.request_id, want):
             return want
         ps = self.cache.page_size
-        have = min(len(t) for t in self.cache.requests[r.request_id].tables) * ps if self.cache.groups else 1 << 30
+        have = self.cache.blocks_held(r.request_id) * ps if self.cache.groups else 1 << 30
         room = have + self.cache.min_free_pages() * ps - self.cache.length(r.request_id)
         return max(0, min(want, room))
 
