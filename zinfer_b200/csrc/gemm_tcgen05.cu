@@ -599,17 +599,17 @@ extern "C" long long zi_gemm_tcgen05_plan(int M, int N, int K, int sm_count, int
     // A few hundred tokens: the tiles leave most SMs idle, and a CTA walks all of K at the pace
     // of its own copies (about 0.45 us a k-block).  Splitting K spreads the walk over more CTAs
     // until L2 cannot feed them (about 10 TB/s), and costs the partial sums' round trip through
-    // memory and a kernel to add them.  Split when that model promises a quarter or more (it is
-    // optimistic about the partial sums, and a product that is left whole loses little).
+    // memory and a kernel to add them (about 8 us in all, measured at 256 to 512 tokens).  Split when
+    // that model promises a tenth or more (512 tokens x 4096 x 12288: 78 us whole, 61 us in two).
     const double stage_b = (double)(A_TILE_BYTES + BN * BLOCK_K * 2);
     auto walk = [&](int s) {   // us for one CTA's share of K with s splits
       const double per_kb = tiles * s * stage_b / 10e6;
       return ((double)k_blocks / s) * (per_kb > 0.45 ? per_kb : 0.45);
     };
     const double unsplit = walk(1);
-    double best = unsplit * 0.75;
+    double best = unsplit * 0.9;
     for (int s = 2; s <= 16 && tiles * s <= sm_count && k_blocks / s >= 8; ++s) {
-      const double t = walk(s) + 2.0 * s * (double)M * N * 4.0 / 5e6 + 3.0;
+      const double t = walk(s) + 2.0 * s * (double)M * N * 4.0 / 5e6 + 8.0;
       if (t < best) {
         best = t;
         splits = s;
