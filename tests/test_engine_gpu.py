@@ -319,3 +319,46 @@ def test_profile_per_kernel_class(model_dirs, tmp_path):
     assert abs(sum(c["share"] for c in classes.values()) - 1.0) < 1e-2
     eng.generate(prompts, sp)
     assert eng.runner.graphs.replays > replays
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_random_workloads_through_the_engine_match_plain_greedy(model_dirs, seed):
+    """Requests of random lengths arriving while others run, in a pool so small that requests are
+    preempted and recomputed, with prompts cut into portions: every request's tokens are the plain
+    model's greedy continuation (float32), whatever ran beside it."""
+    import random
+
+    from zinfer_b200.sampling import SamplingParams
+
+    rng = random.Random(100 + seed)
+    name = "AB"[seed]
+    d = model_dirs[(name, "float32")]
+    cfg, w = P.load_model(d)
+    V = cfg["vocab_size"]
+    limit = cfg["max_position_embeddings"]
+    eng = _engine(d, name, "float32", kv_cache_tokens=None, num_pages=(7 if name == "A" else 13), max_batched_tokens=24,
+                  chunk_size=rng.choice([5, 16]), max_requests=4)
+    pending = []
+    for i in range(14):
+        n = rng.choice([1, 2, 7, 15, 16, 17, 31, 40])
+        new = rng.choice([1, 3, 9, 20])
+        pending.append(([rng.randrange(V) for _ in range(min(n, limit - new - 1))], new))
+    ids, done = {}, {}
+    while pending or eng.has_unfinished():
+        for _ in range(rng.randint(0, 2)):        # arrivals between steps
+            if pending:
+                prompt, new = pending.pop()
+                rid = eng.add_request(prompt, SamplingParams(temperature=0.0, max_new_tokens=new, ignore_eos=True))
+                ids[rid] = (prompt, new)
+        for res in eng.step():
+            done[res.request_id] = res
+    assert set(done) == set(ids)
+    for rid, (prompt, new) in ids.items():
+        res = done[rid]
+        if res.finish_reason == "capacity":      # alone and larger than the pool: as many tokens as fitted
+            assert res.token_ids == P.greedy(cfg, w, prompt, len(res.token_ids))
+        else:
+            assert res.finish_reason == "length" and res.token_ids == P.greedy(cfg, w, prompt, new), f"request {rid}"
+    assert eng.scheduler.stats.preemptions > 0, "the pool was meant to be too small for all requests at once"
+    eng.runner.manager.check()
+    assert not eng.runner.manager.requests and eng.runner.manager.groups[0].pool.num_used == 0
