@@ -398,7 +398,8 @@ def test_tensor_core_attention(nq, nkv, d, page, window, q_lens, ctx_lens, prefi
                                                    (2, 1, 256, 16, None), (5, 5, 64, 16, 200)])
 def test_decode_attention_both_tile_forms(nq, nkv, d, page, window):
     """Groups of at most 8 query heads take the tile with the keys on the MMA's rows; the form with
-    the heads on the rows (which larger groups use) must give the same, and both the reference."""
+    the heads on the rows (which larger groups use) must give the same, and both the reference; each
+    with the keys and values brought by TMA page boxes and by cp.async."""
     o = ops()
     ctx_lens = [0, 15, 16, 63, 64, 65, 700, 1300]
     q_lens = [1] * len(ctx_lens)
@@ -408,17 +409,22 @@ def test_decode_attention_both_tile_forms(nq, nkv, d, page, window):
     want = ref.paged_attention(window=window, scale=scale, **args)
     outs = {}
     try:
-        for on in (True, False):
-            o.decode_transposed_tile(on)
-            for forced in (1, 5):
-                step.max_kv_len = 64 * forced
-                got = o.attention(args["q"], args["k_cache"], args["v_cache"], args["block_tables"], step, nq, nkv, d,
-                                  page, window, scale)
-                torch.testing.assert_close(got.float(), want.float(), rtol=1.6e-2, atol=1.5e-2)
-                outs[(on, forced)] = got.float()
+        for tma in (True, False):
+            o.decode_tma(tma)
+            for on in (True, False):
+                o.decode_transposed_tile(on)
+                for forced in (1, 5):
+                    step.max_kv_len = 64 * forced
+                    got = o.attention(args["q"], args["k_cache"], args["v_cache"], args["block_tables"], step, nq, nkv, d,
+                                      page, window, scale)
+                    torch.testing.assert_close(got.float(), want.float(), rtol=1.6e-2, atol=1.5e-2)
+                    outs[(tma, on, forced)] = got.float()
     finally:
         o.decode_transposed_tile(True)
-    torch.testing.assert_close(outs[(True, 5)], outs[(False, 5)], rtol=1.6e-2, atol=4e-3)
+        o.decode_tma(1)
+    torch.testing.assert_close(outs[(True, True, 5)], outs[(True, False, 5)], rtol=1.6e-2, atol=4e-3)
+    assert torch.equal(outs[(True, True, 5)], outs[(False, True, 5)]), "the same tile read from TMA boxes and from cp.async rows differs"
+    o.require_kernel_status_ok("decode attention")
 
 
 @pytest.mark.parametrize("nq,nkv,d,page,window,norm,rope,partial", [

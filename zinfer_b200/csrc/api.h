@@ -64,14 +64,14 @@ int zi_attention_prefill_tcgen05(void* out, int out_stride, const void* q, int q
                                  float scale, cudaStream_t stream);
 long long zi_attention_decode_workspace_floats(int n_dec, int nq, int nkv, int d, int splits);
 int zi_attention_decode_mma(void* out, int out_stride, float* workspace, const void* q, int q_stride,
-                            const void* kcache, const void* vcache, const int* block_tables, int bt_stride,
+                            const void* kcache, const void* vcache, long long n_pages, const int* block_tables, int bt_stride,
                             const int* cu_q, const int* kv_lens, const int* dec_seq, int n_dec, int nq, int nkv, int d,
                             int page_size, int window, float scale, int splits, cudaStream_t stream);
 
 int zi_attention_decode_fused(void* out, int out_stride, float* workspace, const void* qkv, int qkv_stride,
                               const float* partials, int part_splits, long long part_zstride, const float* qw,
                               const float* kw, float eps, const float* cos_t, const float* sin_t, int n_table_pos,
-                              const int* positions, const int* slots, void* kcache, void* vcache,
+                              const int* positions, const int* slots, void* kcache, void* vcache, long long n_pages,
                               const int* block_tables, int bt_stride, const int* cu_q, const int* kv_lens,
                               const int* dec_seq, int n_dec, int nq, int nkv, int d, int page_size, int window,
                               float scale, int splits, cudaStream_t stream);

@@ -16,8 +16,11 @@
 // [key][d] with the 16-byte chunks of a row XOR-swizzled by (key & 7) so that
 // ldmatrix reads are free of bank conflicts.  Keys outside the request (beyond its
 // length, in pages it does not hold) are zero-filled and masked.
+#include <string.h>
+
 #include "api.h"
 #include "common.cuh"
+#include "gemm_internal.h"
 #include "attention_tiles.cuh"
 
 namespace {
@@ -183,9 +186,10 @@ struct BlockSync {
   static __device__ __forceinline__ void sync() { __syncthreads(); }
 };
 
-template <int D, bool FUSED, bool TR>
+template <int D, bool FUSED, bool TR, bool TMA>
 __global__ void __launch_bounds__(DC_THREADS)
-attn_decode_mma_kernel(bf16* __restrict__ out, int out_stride, float* __restrict__ partial,
+attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       int* __restrict__ status, bf16* __restrict__ out, int out_stride, float* __restrict__ partial,
                        const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kcache,
                        const bf16* __restrict__ vcache, const int* __restrict__ block_tables, int bt_stride,
                        const int* __restrict__ cu_q, const int* __restrict__ kv_lens,
@@ -193,10 +197,16 @@ attn_decode_mma_kernel(bf16* __restrict__ out, int out_stride, float* __restrict
                        float scale_log2, int splits, const FusedQK fq) {
   pdl_launch_dependents();
   // (the unit waits for the kernel before this one itself, after it has asked for its first keys)
-  extern __shared__ __align__(128) uint8_t smem[];
-  attn_decode_unit<D, FUSED, BlockSync, DecodeCfg<D>::STAGES, TR>(
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  // tiles that TMA fills with the 128-byte swizzle start on 1024-byte boundaries
+  uint8_t* smem = TMA ? (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023) : smem_raw;
+  constexpr int RING_BYTES = DC_WARPS * DecodeCfg<D>::STAGES * 2 * DC_KEYS * D * 2;
+  constexpr int FUSED_BYTES = FUSED ? 16 * D * 2 + (2 * D + 16) * (int)sizeof(float) : 0;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + RING_BYTES + ((FUSED_BYTES + 15) & ~15));
+  attn_decode_unit<D, FUSED, BlockSync, DecodeCfg<D>::STAGES, TR, TMA>(
       smem, threadIdx.x, blockIdx.x, blockIdx.y, blockIdx.z, out, out_stride, partial, q, q_stride, kcache, vcache,
-      block_tables, bt_stride, cu_q, kv_lens, dec_seq, nq, nkv, page_size, page_shift, window, scale_log2, splits, fq);
+      block_tables, bt_stride, cu_q, kv_lens, dec_seq, nq, nkv, page_size, page_shift, window, scale_log2, splits, fq,
+      nullptr, &map_k, &map_v, bars, status);
 }
 
 template <int D>
@@ -231,21 +241,60 @@ int launch_prefill(void* out, int out_stride, const void* q, int q_stride, const
 
 int g_decode_transposed = 1;   // zi_attention_decode_transposed(0) switches the transposed tile off (for comparisons)
 
-template <int D, bool FUSED>
-int launch_decode(void* out, int out_stride, float* partial, const void* q, int q_stride, const void* kc,
-                  const void* vc, const int* bt, int bt_stride, const int* cu_q, const int* kv_lens,
-                  const int* dec_seq, int n_dec, int nq, int nkv, int page_size, int window, float scale, int splits,
-                  const FusedQK& fq, cudaStream_t stream) {
-  // groups of at most 8 query heads take the transposed tile (keys on the MMA's rows)
-  auto kern = nq / nkv <= 8 && g_decode_transposed ? attn_decode_mma_kernel<D, FUSED, true> : attn_decode_mma_kernel<D, FUSED, false>;
-  const size_t smem = (size_t)DC_WARPS * DecodeCfg<D>::STAGES * 2 * DC_KEYS * D * 2 +
-                      (FUSED ? (size_t)16 * D * 2 + (2 * D + 16) * sizeof(float) : 0);
+int g_decode_tma = 1;          // see zi_attention_decode_tma
+
+template <int D, bool FUSED, bool TR, bool TMA>
+int launch_decode_as(void* out, int out_stride, float* partial, const void* q, int q_stride, const void* kc,
+                     const void* vc, long long n_pages, const int* bt, int bt_stride, const int* cu_q,
+                     const int* kv_lens, const int* dec_seq, int n_dec, int nq, int nkv, int page_size, int window,
+                     float scale, int splits, const FusedQK& fq, cudaStream_t stream) {
+  auto kern = attn_decode_mma_kernel<D, FUSED, TR, TMA>;
+  CUtensorMap map_k, map_v;
+  memset(&map_k, 0, sizeof(map_k));
+  memset(&map_v, 0, sizeof(map_v));
+  int* status = nullptr;
+  if (TMA) {
+    const long long rows = n_pages * nkv * page_size;
+    const int box_rows = page_size >= 16 ? 16 : page_size;
+    if (!zi_internal_make_map(&map_k, kc, (int)rows, D, D, box_rows) || !zi_internal_make_map(&map_v, vc, (int)rows, D, D, box_rows))
+      return zi_refuse("attention_decode: cuTensorMapEncodeTiled failed");
+    status = zi_internal_status_word();
+    if (!status) return zi_refuse("attention_decode: cannot allocate the status word");
+  }
+  const size_t ring = (size_t)DC_WARPS * DecodeCfg<D>::STAGES * 2 * DC_KEYS * D * 2;
+  const size_t fused = FUSED ? (size_t)16 * D * 2 + (2 * D + 16) * sizeof(float) : 0;
+  const size_t smem = ring + ((fused + 15) & ~(size_t)15) + (TMA ? (size_t)DC_WARPS * DecodeCfg<D>::STAGES * 8 + 1024 : 0);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return zi_refuse("attention_decode: cannot get %zu bytes of shared memory", smem);
   dim3 grid(n_dec, nkv, splits);
-  zi_launch(kern, dim3(grid), dim3(DC_THREADS), smem, stream, (bf16*)out, out_stride, splits > 1 ? partial : nullptr,
-            (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, bt, bt_stride, cu_q, kv_lens, dec_seq, nq, nkv,
-            page_size, log2_or_minus1(page_size), window, scale * 1.4426950408889634f, splits, fq);
+  zi_launch(kern, dim3(grid), dim3(DC_THREADS), smem, stream, map_k, map_v, status, (bf16*)out, out_stride,
+            splits > 1 ? partial : nullptr, (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, bt, bt_stride, cu_q,
+            kv_lens, dec_seq, nq, nkv, page_size, log2_or_minus1(page_size), window, scale * 1.4426950408889634f, splits, fq);
+  return 0;
+}
+
+template <int D, bool FUSED>
+int launch_decode(void* out, int out_stride, float* partial, const void* q, int q_stride, const void* kc,
+                  const void* vc, long long n_pages, const int* bt, int bt_stride, const int* cu_q, const int* kv_lens,
+                  const int* dec_seq, int n_dec, int nq, int nkv, int page_size, int window, float scale, int splits,
+                  const FusedQK& fq, cudaStream_t stream) {
+  // Groups of at most 8 query heads take the transposed tile (keys on the MMA's rows).  Keys and values come by
+  // TMA (page boxes, pages of 8, 16, 32, ... tokens whose rows a tensor map can address) while the requests
+  // are few, and by cp.async from every lane when they are many.  Measured per 36-layer step (Qwen3-8B
+  // sizes, 2,048 keys): TMA 3.285 against 3.295 ms at 1 request and 3.66 against 3.68 at 8, but 4.47 against
+  // 4.42 at 24 and 6.79 against 6.74 at 64: where the kernel is bound by memory, 32 lanes asking for 16 bytes
+  // each keep slightly more in flight than boxes of 2 KB (g_decode_tma: 0 never, 1 by this rule, 2 always).
+  const bool tr = nq / nkv <= 8 && g_decode_transposed;
+  const int shift = log2_or_minus1(page_size);
+  const bool tma = g_decode_tma && (g_decode_tma == 2 || n_dec <= 16) && shift >= 3 && n_pages > 0 &&
+                   n_pages * nkv * page_size <= 0x7fffffffll && (uintptr_t)kc % 16 == 0 && (uintptr_t)vc % 16 == 0;
+#define ZI_DECODE_AS(TR_, TMA_)                                                                                        \
+  launch_decode_as<D, FUSED, TR_, TMA_>(out, out_stride, partial, q, q_stride, kc, vc, n_pages, bt, bt_stride, cu_q, kv_lens, \
+                                        dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, fq, stream)
+  int rc0 = tr ? (tma ? ZI_DECODE_AS(true, true) : ZI_DECODE_AS(true, false))
+               : (tma ? ZI_DECODE_AS(false, true) : ZI_DECODE_AS(false, false));
+#undef ZI_DECODE_AS
+  if (rc0) return rc0;
   int rc = zi_check_launch("attention_decode");
   if (rc) return rc;
   if (splits > 1) {
@@ -258,16 +307,16 @@ int launch_decode(void* out, int out_stride, float* partial, const void* q, int 
 
 template <bool FUSED>
 int dispatch_decode(int d, void* out, int out_stride, float* partial, const void* q, int q_stride, const void* kc,
-                    const void* vc, const int* bt, int bt_stride, const int* cu_q, const int* kv_lens,
+                    const void* vc, long long n_pages, const int* bt, int bt_stride, const int* cu_q, const int* kv_lens,
                     const int* dec_seq, int n_dec, int nq, int nkv, int page_size, int window, float scale, int splits,
                     const FusedQK& fq, cudaStream_t stream) {
   if (d == 64)
-    return launch_decode<64, FUSED>(out, out_stride, partial, q, q_stride, kc, vc, bt, bt_stride, cu_q, kv_lens, dec_seq,
+    return launch_decode<64, FUSED>(out, out_stride, partial, q, q_stride, kc, vc, n_pages, bt, bt_stride, cu_q, kv_lens, dec_seq,
                                     n_dec, nq, nkv, page_size, window, scale, splits, fq, stream);
   if (d == 128)
-    return launch_decode<128, FUSED>(out, out_stride, partial, q, q_stride, kc, vc, bt, bt_stride, cu_q, kv_lens,
+    return launch_decode<128, FUSED>(out, out_stride, partial, q, q_stride, kc, vc, n_pages, bt, bt_stride, cu_q, kv_lens,
                                      dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, fq, stream);
-  return launch_decode<256, FUSED>(out, out_stride, partial, q, q_stride, kc, vc, bt, bt_stride, cu_q, kv_lens, dec_seq,
+  return launch_decode<256, FUSED>(out, out_stride, partial, q, q_stride, kc, vc, n_pages, bt, bt_stride, cu_q, kv_lens, dec_seq,
                                    n_dec, nq, nkv, page_size, window, scale, splits, fq, stream);
 }
 }  // namespace
@@ -276,6 +325,14 @@ extern "C" int zi_attention_prefill_tile_rows() { return PF_BQ; }
 
 // The decode attention's tile for groups of at most 8 query heads: transposed (1, the default) or
 // row-major as for larger groups (0); returns the setting before.  For tests and timing comparisons.
+// Keys and values of the decode attention by TMA: 1 (the default) for up to 16 requests, 2 always, 0 never
+// (cp.async from every lane); returns the setting before.  For tests and timing comparisons.
+extern "C" int zi_attention_decode_tma(int mode) {
+  const int before = g_decode_tma;
+  g_decode_tma = mode < 0 ? 0 : (mode > 2 ? 2 : mode);
+  return before;
+}
+
 extern "C" int zi_attention_decode_transposed(int on) {
   const int before = g_decode_transposed;
   g_decode_transposed = on ? 1 : 0;
@@ -309,8 +366,9 @@ extern "C" long long zi_attention_decode_workspace_floats(int n_dec, int nq, int
   return splits > 1 ? (long long)n_dec * nq * splits * (d + 2) : 0;
 }
 
+// n_pages: pages of each cache (their rows are addressed through a tensor map when they come by TMA).
 extern "C" int zi_attention_decode_mma(void* out, int out_stride, float* workspace, const void* q, int q_stride,
-                                       const void* kcache, const void* vcache, const int* block_tables,
+                                       const void* kcache, const void* vcache, long long n_pages, const int* block_tables,
                                        int bt_stride, const int* cu_q, const int* kv_lens, const int* dec_seq,
                                        int n_dec, int nq, int nkv, int d, int page_size, int window, float scale,
                                        int splits, cudaStream_t stream) {
@@ -320,7 +378,7 @@ extern "C" int zi_attention_decode_mma(void* out, int out_stride, float* workspa
   if (splits < 1 || (splits > 1 && !workspace)) return zi_refuse("attention_decode: %d splits need a workspace", splits);
   if (q_stride % 2) return zi_refuse("attention_decode: q rows must be 4-byte aligned");
   FusedQK none = {};
-  return dispatch_decode<false>(d, out, out_stride, workspace, q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q,
+  return dispatch_decode<false>(d, out, out_stride, workspace, q, q_stride, kcache, vcache, n_pages, block_tables, bt_stride, cu_q,
                                 kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, none, stream);
 }
 
@@ -332,8 +390,8 @@ extern "C" int zi_attention_decode_fused(void* out, int out_stride, float* works
                                          const float* partials, int part_splits, long long part_zstride,
                                          const float* qw, const float* kw, float eps, const float* cos_t,
                                          const float* sin_t, int n_table_pos, const int* positions,
-                                         const int* slots, void* kcache, void* vcache, const int* block_tables,
-                                         int bt_stride, const int* cu_q, const int* kv_lens, const int* dec_seq,
+                                         const int* slots, void* kcache, void* vcache, long long n_pages,
+                                         const int* block_tables, int bt_stride, const int* cu_q, const int* kv_lens, const int* dec_seq,
                                          int n_dec, int nq, int nkv, int d, int page_size, int window, float scale,
                                          int splits, cudaStream_t stream) {
   if (n_dec <= 0) return 0;
@@ -359,7 +417,7 @@ extern "C" int zi_attention_decode_fused(void* out, int out_stride, float* works
   fq.slots = slots;
   fq.kcache_w = (bf16*)kcache;
   fq.vcache_w = (bf16*)vcache;
-  return dispatch_decode<true>(d, out, out_stride, workspace, nullptr, 0, kcache, vcache, block_tables, bt_stride, cu_q,
+  return dispatch_decode<true>(d, out, out_stride, workspace, nullptr, 0, kcache, vcache, n_pages, block_tables, bt_stride, cu_q,
                                kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, fq, stream);
 }
 

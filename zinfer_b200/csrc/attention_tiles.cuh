@@ -5,6 +5,7 @@
 // runs whole layers of a decode step are made of.
 #pragma once
 #include "common.cuh"
+#include "tcgen05_ptx.cuh"
 
 namespace {
 using bf16 = __nv_bfloat16;
@@ -45,29 +46,37 @@ template <int D> __device__ __forceinline__ uint32_t swz(int r, int c) {
   return (uint32_t)(r * D * 2 + ((c ^ (r & 7)) << 4));
 }
 
+// The same for a tile that TMA filled (TL): one box of [16 rows][64 values = 128 bytes] per 64 columns
+// with the hardware's 128-byte swizzle (chunk ^ (row & 7) within a row of 128 bytes), the boxes of
+// a tile one after the other.  A tile's base is 1024-byte aligned.
+template <int D, bool TL> __device__ __forceinline__ uint32_t tile_off(int r, int c) {
+  if (TL) return (uint32_t)((c >> 3) * 2048 + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+  return swz<D>(r, c);
+}
+
 // S (16 x 16 keys) += Q (16 x D) * K^T for the 16 keys at rows key0.. of tile `ks`.
 // qf: the warp's Q fragments, [D/16][4].  s: two n-tiles of 8 keys.
-template <int D>
+template <int D, bool TL = false>
 __device__ __forceinline__ void qk_16keys(float (&s)[2][4], const uint32_t (&qf)[D / 16][4], uint32_t ks_addr,
                                           int key0, int lane) {
 #pragma unroll
   for (int kk = 0; kk < D / 16; ++kk) {
     uint32_t b[4];
     const int m = lane >> 3;
-    ldmatrix_x4(b, ks_addr + swz<D>(key0 + (m >> 1) * 8 + (lane & 7), kk * 2 + (m & 1)));
+    ldmatrix_x4(b, ks_addr + tile_off<D, TL>(key0 + (m >> 1) * 8 + (lane & 7), kk * 2 + (m & 1)));
     mma_bf16(s[0], qf[kk], b[0], b[1]);
     mma_bf16(s[1], qf[kk], b[2], b[3]);
   }
 }
 // O (16 x D) += P (16 x 16 keys) * V for the 16 keys at rows key0.. of tile `vs`.
-template <int D>
+template <int D, bool TL = false>
 __device__ __forceinline__ void pv_16keys(float (&o)[D / 8][4], const uint32_t (&pf)[4], uint32_t vs_addr, int key0,
                                           int lane) {
 #pragma unroll
   for (int np = 0; np < D / 16; ++np) {
     uint32_t b[4];
     const int m = lane >> 3;
-    ldmatrix_x4_trans(b, vs_addr + swz<D>(key0 + (m & 1) * 8 + (lane & 7), np * 2 + (m >> 1)));
+    ldmatrix_x4_trans(b, vs_addr + tile_off<D, TL>(key0 + (m & 1) * 8 + (lane & 7), np * 2 + (m >> 1)));
     mma_bf16(o[2 * np], pf, b[0], b[1]);
     mma_bf16(o[2 * np + 1], pf, b[2], b[3]);
   }
@@ -209,14 +218,14 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
 // S^T (16 keys x 8 heads) = K (16 x D, the tile at ks_addr) * Q^T.  qb: the warp's Q^T fragments
 // [D/16][2] (B operand: head lane/4, columns 2 (lane%4) .. of each 8-wide half of the 16 values).
 // Two accumulators take alternate steps so that their MMAs do not wait for each other.
-template <int D>
+template <int D, bool TL = false>
 __device__ __forceinline__ void qk_16keys_t(float (&s)[4], const uint32_t (&qb)[D / 16][2], uint32_t ks_addr, int lane) {
   float s2[4] = {0.f, 0.f, 0.f, 0.f};
   const int mi = lane >> 3;
 #pragma unroll
   for (int kk = 0; kk < D / 16; ++kk) {
     uint32_t a[4];
-    ldmatrix_x4(a, ks_addr + swz<D>((mi & 1) * 8 + (lane & 7), kk * 2 + (mi >> 1)));
+    ldmatrix_x4(a, ks_addr + tile_off<D, TL>((mi & 1) * 8 + (lane & 7), kk * 2 + (mi >> 1)));
     if (kk & 1) mma_bf16(s2, a, qb[kk][0], qb[kk][1]);
     else mma_bf16(s, a, qb[kk][0], qb[kk][1]);
   }
@@ -224,14 +233,65 @@ __device__ __forceinline__ void qk_16keys_t(float (&s)[4], const uint32_t (&qb)[
   for (int c = 0; c < 4; ++c) s[c] += s2[c];
 }
 // O^T (D x 8 heads) += V^T (D x 16 keys, from the tile at vs_addr) * P^T (16 keys x 8 heads: pb0, pb1).
-template <int D>
+template <int D, bool TL = false>
 __device__ __forceinline__ void pv_16keys_t(float (&ot)[D / 16][4], uint32_t pb0, uint32_t pb1, uint32_t vs_addr, int lane) {
   const int mi = lane >> 3;
 #pragma unroll
   for (int np = 0; np < D / 16; ++np) {
     uint32_t a[4];
-    ldmatrix_x4_trans(a, vs_addr + swz<D>((mi >> 1) * 8 + (lane & 7), np * 2 + (mi & 1)));
+    ldmatrix_x4_trans(a, vs_addr + tile_off<D, TL>((mi >> 1) * 8 + (lane & 7), np * 2 + (mi & 1)));
     mma_bf16(ot[np], a, pb0, pb1);
+  }
+}
+
+// One warp's 16 keys (K and V) by TMA: boxes of [min(page_size, 16) keys][64 values] straight from the
+// pages into a tile laid out for tile_off<D, true>, completion counted in bytes on `bar`.  Pages of 8
+// tokens take two boxes per 64 columns, pages of 16, 32, ... one.  Lane r < 16 holds the page of key r
+// (-1: outside the request or its window, or a page given back): a box is fetched when any of its keys
+// has a page, else its rows are zeroed (what shared memory held before must never meet the MMA, where
+// 0 x NaN would not be 0).  Called by the whole warp; lane 0 issues.
+template <int D>
+__device__ __forceinline__ void tma_kv_tile(uint8_t* ks, uint8_t* vs, uint64_t* bar, int key_pos0, int pg,
+                                            const CUtensorMap* map_k, const CUtensorMap* map_v, int nkv, int kvh,
+                                            int page_size, int lane) {
+  constexpr int COLS = D / 64;                       // boxes side by side
+  const int box_rows = page_size >= 16 ? 16 : page_size;
+  const int n_boxes = 16 / box_rows;
+  int box_page[2];
+#pragma unroll
+  for (int b = 0; b < 2; ++b) {
+    // the page of a box: that of any of its keys (they share it); -1 if none has one
+    const int lo = b * box_rows, hi = lo + box_rows;
+    const int mine = (b < n_boxes && lane >= lo && lane < hi && lane < 16) ? pg : -1;
+    box_page[b] = __reduce_max_sync(0xffffffffu, mine);
+  }
+  int fetched = 0;
+#pragma unroll
+  for (int b = 0; b < 2; ++b)
+    if (b < n_boxes && box_page[b] >= 0) ++fetched;
+  if (lane == 0) mbar_expect_tx(bar, (uint32_t)(fetched * 2 * COLS * box_rows * 128));
+  __syncwarp();   // the byte count is posted before any copy can complete
+  // The copies go out side by side, one per lane in ONE instruction (a thread that issues a tensor copy is
+  // held a few hundred nanoseconds while memory is busy): lane = (box, 64-column part, K or V).
+  const int per_box = COLS * 2;
+  if (lane < n_boxes * per_box) {
+    const int bx = lane / per_box, rem = lane % per_box, c = rem >> 1, is_v = rem & 1;
+    const int page = bx == 0 ? box_page[0] : box_page[1];
+    if (page >= 0) {
+      const int row = (page * nkv + kvh) * page_size + ((key_pos0 + bx * box_rows) & (page_size - 1));
+      tma_load_2d((is_v ? vs : ks) + c * 2048 + bx * box_rows * 128, is_v ? map_v : map_k, bar, c * 64, row);
+    }
+  }
+#pragma unroll
+  for (int bx = 0; bx < 2; ++bx) {
+    if (bx >= n_boxes || box_page[bx] >= 0) continue;
+    for (int e = lane; e < COLS * box_rows * 8; e += 32) {   // 16-byte chunks of the box's rows
+      const int c = e / (box_rows * 8), rem = e % (box_rows * 8);
+      const uint32_t off = (uint32_t)(c * 2048 + bx * box_rows * 128 + rem * 16);
+      *reinterpret_cast<uint4*>(ks + off) = make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(vs + off) = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // before a later copy lands on these rows
   }
 }
 
@@ -275,14 +335,19 @@ struct FusedQK {
 // (behind the rings, or at `fused_area`, 128-byte aligned).
 // TR: the transposed tile (keys on the MMA's rows) for groups of at most 8 query heads; the
 // caller chooses it, the results agree with the other form up to rounding.
-template <int D, bool FUSED, class Sync, int STAGES = DecodeCfg<D>::STAGES, bool TR = false>
+// TMA: the keys and values come by cp.async.bulk.tensor (tma_kv_tile; pages of 8, 16, 32, ... tokens),
+// one lane issuing, completion on a barrier per warp and stage (`bars`, DC_WARPS * STAGES of them, which
+// the caller places in shared memory; `smem` is then 1024-byte aligned) with a bounded wait that records
+// a code in `status`; else by cp.async from every lane.
+template <int D, bool FUSED, class Sync, int STAGES = DecodeCfg<D>::STAGES, bool TR = false, bool TMA = false>
 __device__ __forceinline__ void attn_decode_unit(
     uint8_t* smem, int tid, int dec, int kvh, int z, bf16* __restrict__ out, int out_stride,
     float* __restrict__ partial, const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kcache,
     const bf16* __restrict__ vcache, const int* __restrict__ block_tables, int bt_stride,
     const int* __restrict__ cu_q, const int* __restrict__ kv_lens, const int* __restrict__ dec_seq, int nq, int nkv,
     int page_size, int page_shift, int window, float scale_log2, int splits, const FusedQK& fq,
-    uint8_t* fused_area = nullptr) {
+    uint8_t* fused_area = nullptr, const CUtensorMap* map_k = nullptr, const CUtensorMap* map_v = nullptr,
+    uint64_t* bars = nullptr, int* status = nullptr) {
 
   constexpr int ROWS_BYTES = DC_KEYS * D * 2;                  // one warp's 16 keys of K (or V)
   constexpr int WARP_BYTES = STAGES * 2 * ROWS_BYTES;          // a warp's private ring
@@ -327,10 +392,23 @@ __device__ __forceinline__ void attn_decode_unit(
     if (t >= n_tiles || j < kv_lo || j >= kv_hi) return -1;
     return __ldg(bt + (page_shift >= 0 ? (j >> page_shift) : (j / page_size)));
   };
+  uint64_t* my_bars = TMA ? bars + warp * STAGES : nullptr;
+  if (TMA) {
+    if (lane == 0) {
+#pragma unroll
+      for (int st = 0; st < STAGES; ++st) mbar_init(&my_bars[st], 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncwarp();
+  }
   auto issue = [&](int t, int pg) {   // this warp's 16 keys of tile t into stage t % STAGES
     uint8_t* ks = ring + (t % STAGES) * 2 * ROWS_BYTES;
     const int key0 = kt0 + (t_begin + t) * DC_TILE + warp * DC_KEYS;
-    load_kv_rows_pg<D>(ks, ks + ROWS_BYTES, key0, pg, kcache, vcache, nkv, kvh, page_size, page_shift, lane);
+    if constexpr (TMA)
+      tma_kv_tile<D>(ks, ks + ROWS_BYTES, &my_bars[t % STAGES], key0, pg, map_k, map_v, nkv, kvh, page_size, lane);
+    else
+      load_kv_rows_pg<D>(ks, ks + ROWS_BYTES, key0, pg, kcache, vcache, nkv, kvh, page_size, page_shift, lane);
   };
   // Not fused: the kernel before this one wrote the newest token's key and value (and q).  The first
   // tiles are asked for before the wait for it unless they may hold that key.
@@ -342,7 +420,7 @@ __device__ __forceinline__ void attn_decode_unit(
     const int pg = pg_next;
     pg_next = lookup(t + 1);
     if (t < n_tiles) issue(t, pg);
-    cp_async_commit();
+    if constexpr (!TMA) cp_async_commit();
   }
   if (!FUSED && TR) {
     if (early) pdl_wait();
@@ -539,8 +617,17 @@ __device__ __forceinline__ void attn_decode_unit(
       pg_next = lookup(tt + 1);
       if (tt < n_tiles) issue(tt, pg);
     }
-    cp_async_commit();
-    cp_async_wait<STAGES - 1>();
+    if constexpr (TMA) {
+      // the tile's bytes have landed when its barrier's phase completes (bounded wait)
+      if (!mbar_wait(&my_bars[t % STAGES], (uint32_t)(t / STAGES) & 1u)) {
+        if (lane == 0 && status) atomicExch(status, 21);
+        for (int i = 0; i < 64; ++i) __nanosleep(10000);   // let copies in flight land before the ring is reused
+        break;
+      }
+    } else {
+      cp_async_commit();
+      cp_async_wait<STAGES - 1>();
+    }
     __syncwarp();
     const int key0 = kt0 + (t_begin + t) * DC_TILE + warp * DC_KEYS;
     if (key0 < kv_hi && key0 + DC_KEYS > kv_lo) {
@@ -548,7 +635,7 @@ __device__ __forceinline__ void attn_decode_unit(
       const bool need_mask = key0 + DC_KEYS > kv_hi || key0 < kv_lo;
       if constexpr (TR) {
         float st[4] = {0.f, 0.f, 0.f, 0.f};   // keys lane/4 (st[0], st[1]) and + 8 (st[2], st[3]) x heads 2 (lane%4), + 1
-        qk_16keys_t<D>(st, qb, ks_addr, lane);
+        qk_16keys_t<D, TMA>(st, qb, ks_addr, lane);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           float v = st[c] * scale_log2;
@@ -588,10 +675,10 @@ __device__ __forceinline__ void attn_decode_unit(
         }
         const uint32_t pb0 = movmatrix_trans(pack_bf16(st[0], st[1]));   // keys 0..7 of the tile
         const uint32_t pb1 = movmatrix_trans(pack_bf16(st[2], st[3]));   // keys 8..15
-        pv_16keys_t<D>(ot, pb0, pb1, vs_addr, lane);
+        pv_16keys_t<D, TMA>(ot, pb0, pb1, vs_addr, lane);
       } else {
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-      qk_16keys<D>(s, qf, ks_addr, 0, lane);
+      qk_16keys<D, TMA>(s, qf, ks_addr, 0, lane);
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
@@ -606,12 +693,12 @@ __device__ __forceinline__ void attn_decode_unit(
       softmax_step<2, D / 8>(s, o, m, l);
       uint32_t pf[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]), pack_bf16(s[1][0], s[1][1]),
                         pack_bf16(s[1][2], s[1][3])};
-      pv_16keys<D>(o, pf, vs_addr, 0, lane);
+      pv_16keys<D, TMA>(o, pf, vs_addr, 0, lane);
       }
     }
     __syncwarp();  // the stage is refilled by this warp's next issue
   }
-  cp_async_wait<0>();
+  if constexpr (!TMA) cp_async_wait<0>();
 
   // merge the four warps: each writes (o, m, l) of its rows to its own ring, then all combine
   __syncwarp();

@@ -469,7 +469,8 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, blo
         ws = torch.empty((need,), dtype=torch.float32, device=q.device) if need else None
         with _prof.region("attention (decode)", *work(True)):
             _check(L.zi_attention_decode_mma(
-                _ptr(out), out.stride(0), _ptr(ws), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+                _ptr(out), out.stride(0), _ptr(ws), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache),
+                ctypes.c_longlong(k_cache.shape[0]), _ptr(block_tables),
                 block_tables.stride(0), _ptr(step.cu_q), _ptr(step.kv_lens), _ptr(step.dec_seq), step.n_dec, num_heads,
                 num_kv_heads, head_dim, page_size, win, ctypes.c_float(scale), splits, _stream()), "attention (decode)")
     return out
@@ -498,6 +499,15 @@ def decode_splits(n_dec: int, num_kv_heads: int, sm_count: int, max_kv_len: Opti
         if cost < best_cost:
             best, best_cost = s, cost
     return best
+
+
+def decode_tma(mode) -> int:
+    """The decode attention's keys and values by TMA (``cp.async.bulk.tensor`` page boxes, a few lanes
+    issuing side by side; pages of 8, 16, 32, ... tokens) or by ``cp.async`` from every lane: 1 (the
+    default) TMA for up to 16 requests, where it measured slightly faster, 2 or True always, 0 or False
+    never.  Returns the setting before.  For tests and timing comparisons."""
+    mode = 2 if mode is True else (0 if mode is False else int(mode))
+    return int(lib().zi_attention_decode_tma(mode))
 
 
 def decode_transposed_tile(on: bool) -> bool:
@@ -561,7 +571,8 @@ def attention_decode_fused(qkv, num_heads: int, num_kv_heads: int, head_dim: int
         _check(L.zi_attention_decode_fused(
             _ptr(out), out.stride(0), _ptr(ws), _ptr(src), src_stride, _ptr(part), psplits, ctypes.c_longlong(pz),
             _ptr(q_weight), _ptr(k_weight), ctypes.c_float(eps), _ptr(cos), _ptr(sin), n_table, _ptr(step.positions),
-            _ptr(slots), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), block_tables.stride(0), _ptr(step.cu_q),
+            _ptr(slots), _ptr(k_cache), _ptr(v_cache), ctypes.c_longlong(k_cache.shape[0]), _ptr(block_tables),
+            block_tables.stride(0), _ptr(step.cu_q),
             _ptr(step.kv_lens), _ptr(step.dec_seq), step.n_dec, num_heads, num_kv_heads, head_dim, page_size,
             int(window or 0), ctypes.c_float(scale), splits, _stream()), "attention (fused decode)")
     return out
