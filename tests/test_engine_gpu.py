@@ -362,3 +362,33 @@ def test_random_workloads_through_the_engine_match_plain_greedy(model_dirs, seed
     assert eng.scheduler.stats.preemptions > 0, "the pool was meant to be too small for all requests at once"
     eng.runner.manager.check()
     assert not eng.runner.manager.requests and eng.runner.manager.groups[0].pool.num_used == 0
+
+
+def test_command_line_generate_with_a_byte_budget_and_a_profile(model_dirs, tmp_path):
+    """Several prompts in one call, the pool sized from a byte budget, per-kernel-class times written."""
+    import json
+
+    d = model_dirs[("D", "bfloat16")]
+    prof = tmp_path / "p.json"
+    r = subprocess.run([sys.executable, os.path.join(REPO, "bin", "zinfer"), "generate", d, "5,17,3;9,9,9,9;1", "--max-new-tokens", "5",
+                        "--temperature", "0", "--ignore-eos", "--kv-cache-bytes", "4000000", "--profile", str(prof)],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("tokens[")]
+    assert len(lines) == 3 and all(ln.count(",") == 4 for ln in lines)
+    summary = json.load(open(prof))
+    assert summary["steps"] >= 5 and any(c["class"].startswith("linear") for c in summary["classes"])
+
+
+def test_default_pool_takes_what_the_device_has_free_but_no_more_than_the_requests_can_fill(model_dirs):
+    from zinfer_b200.cache import bytes_per_token
+    from zinfer_b200.engine.api import Engine
+
+    d = model_dirs[("A", "bfloat16")]
+    eng = Engine(d, dtype="bfloat16", device=DEV, page_size=16, max_requests=8)       # nothing said about the pool
+    pages = eng.runner.manager.groups[0].pool.num_pages
+    assert pages == 8 * 128 // 16, "a tiny model's pool is capped by max_requests x max_position_embeddings"
+    kv_needs, _ = eng.runner.model.cache_needs()
+    assert eng.runner.storage.bytes() == pages * 16 * bytes_per_token(kv_needs, 2)
+    tiny = Engine(d, dtype="bfloat16", device=DEV, page_size=16, max_requests=8, kv_cache_bytes=3 * 16 * bytes_per_token(kv_needs, 2) + 5)
+    assert tiny.runner.manager.groups[0].pool.num_pages == 3
