@@ -189,13 +189,13 @@ def main() -> int:
         cur = torch.randint(0, cfg.vocab_size, (args.batch,), generator=gen).tolist()
 
         def one_step():
-            ops.argmax(runner.step([StepEntry(rid, [t], [0]) for rid, t in zip(ids, cur)]))
+            runner.step_argmax([StepEntry(rid, [t], [0]) for rid, t in zip(ids, cur)])
 
         kernels = profiling.chain_timeline(one_step, warm=4)
         # the chain of a decode step of this architecture, when its kernel count says that it is the one meant
         per_layer = ["input norm", "qkv product", "attention (fused)", "attention combine", "o product", "post-attention norm",
                      "gate_up product", "swiglu", "down product"]
-        names = ["embedding"] + per_layer * n_layers + ["final norm", "output head", "argmax (partial)", "argmax (final)"]
+        names = ["embedding"] + per_layer * n_layers + ["final norm", "output head", "argmax (candidates)"]
         for i, k in enumerate(kernels):
             k["kernel"] = names[i] if len(names) == len(kernels) else f"kernel {i}"
         with open(args.timeline, "w") as f:
@@ -244,9 +244,7 @@ def main() -> int:
 
         def one():
             nonlocal cur
-            logits = runner.step([StepEntry(rid, [t], [0]) for rid, t in zip(ids, cur)])
-            nxt = ops.argmax(logits)
-            return nxt
+            return runner.step_argmax([StepEntry(rid, [t], [0]) for rid, t in zip(ids, cur)])[1]
 
         for _ in range(warmup):
             one()
@@ -308,7 +306,7 @@ def main() -> int:
         cur = torch.randint(0, cfg.vocab_size, (args.batch,), generator=gen).tolist()
         with engine.profile(hbm_gbs, bf16_tflops) as prof:
             for _ in range(4):
-                ops.argmax(runner.step([StepEntry(rid, [t], [0]) for rid, t in zip(ids, cur)]))
+                runner.step_argmax([StepEntry(rid, [t], [0]) for rid, t in zip(ids, cur)])
             decode_profile = prof.summary()
         with engine.profile(hbm_gbs, bf16_tflops) as prof:
             prefill_once()

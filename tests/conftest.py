@@ -74,7 +74,7 @@ def cpu_kernels(monkeypatch):
     from zinfer_b200.engine import runner
 
     for name in ("embed_gather", "add_rmsnorm", "residual_add", "swiglu", "rope_table", "qk_norm_rope_store",
-                 "linear", "attention_tile_rows", "attention_prefill_tile_rows", "paged_attention", "attention", "argmax", "patch_tokens", "linear_swiglu", "interleave_gate_up", "decode_fused_ok", "sample", "count_tokens"):
+                 "linear", "attention_tile_rows", "attention_prefill_tile_rows", "paged_attention", "attention", "argmax", "linear_argmax", "patch_tokens", "linear_swiglu", "interleave_gate_up", "decode_fused_ok", "sample", "count_tokens"):
         monkeypatch.setattr(ops, name, getattr(kernel_refs, name))
     monkeypatch.setattr(ops, "lib", lambda: None)
     monkeypatch.setattr(runner, "_require_cuda", lambda device: None)

@@ -138,6 +138,11 @@ def argmax(logits, out=None):
     return torch.argmax(logits, dim=-1).to(torch.int32)
 
 
+def linear_argmax(x, weight):
+    logits = linear(x, weight, out_dtype=torch.float32)
+    return logits, argmax(logits)
+
+
 def attention(q, k_cache, v_cache, block_tables, step, num_heads, num_kv_heads, head_dim, page_size, window, scale):
     return paged_attention(q, k_cache, v_cache, block_tables, step.cu_q, step.kv_lens, step.tile_seq, step.tile_q0,
                            num_heads, num_kv_heads, head_dim, page_size, window, scale)

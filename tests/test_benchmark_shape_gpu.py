@@ -122,6 +122,31 @@ def test_sixty_four_requests_decode_together(shape_model):
     ops.require_kernel_status_ok("8B shape")
 
 
+@pytest.mark.parametrize("n", [3, 64])
+def test_greedy_ids_from_the_heads_epilogue(shape_model, n):
+    """Greedy decoding takes the row maxima that the output head's product leaves per 32 weight rows
+    (151,936 weight rows: 4,748 candidates a token): the ids are the first maxima of the logits
+    returned beside them, and the logits are those of the plain step; uncaptured, captured, replayed."""
+    from zinfer_b200.engine import StepEntry
+
+    cfg, tensors, _ = shape_model
+    runner = _runner(cfg, tensors, torch.bfloat16, max_tokens=n * 64, max_requests=n)
+    twin = _runner(cfg, tensors, torch.bfloat16, max_tokens=n * 64, max_requests=n)
+    reqs = ru.make_requests(cfg.vocab_size, [9 + (i * 5) % 17 for i in range(n)], seed=11)
+    for r in (runner, twin):
+        for rid, toks in reqs.items():
+            r.add_request(rid)
+        r.step([StepEntry(rid, toks[:-1], []) for rid, toks in reqs.items()])
+    cur = [toks[-1] for toks in reqs.values()]
+    for _ in range(3):
+        entries = [StepEntry(rid, [t], [0]) for rid, t in zip(reqs, cur)]
+        logits, ids = runner.step_argmax(entries)
+        assert ids.dtype == torch.int32 and torch.equal(ids.long(), torch.argmax(logits, dim=-1))
+        assert torch.equal(logits, twin.step(entries))
+        cur = ids.tolist()
+    assert runner.graphs.replays >= 1
+
+
 def test_float32_whole_prompts(shape_model):
     """The true 32-bit path at these sizes: CUDA-core products over K = 12288 and the exact attention."""
     cfg, tensors, plain_w = shape_model

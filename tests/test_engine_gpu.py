@@ -309,8 +309,9 @@ def test_profile_per_kernel_class(model_dirs, tmp_path):
     assert json.load(open(path)) == summary
     classes = {c["class"]: c for c in summary["classes"]}
     assert summary["steps"] >= 6 and summary["total_ms"] > 0
-    for expected in ("add_rmsnorm", "embed_gather", "argmax", "attention (prefill, tcgen05)"):
+    for expected in ("add_rmsnorm", "embed_gather", "attention (prefill, tcgen05)"):
         assert expected in classes, f"{expected} missing from {sorted(classes)}"
+    assert any(k.startswith("argmax") for k in classes), "greedy rows end in an argmax, fused with the head or not"
     assert any(k.startswith("linear N=") for k in classes) and any("attention (decode" in k for k in classes)
     for c in classes.values():
         assert c["launches"] > 0 and c["ms"] > 0 and c["us_per_launch"] < 5000

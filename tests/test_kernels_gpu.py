@@ -518,6 +518,41 @@ def test_argmax_first_maximum_wins(R, V):
     assert int(got[0]) == 7
 
 
+@pytest.mark.parametrize("M,N,K,fused", [(1, 301, 72, True), (8, 5000, 256, True), (64, 1000, 136, True),
+                                           (128, 389, 64, True), (3, 151936, 64, True), (16, 20000, 1024, True), (16, 4133, 4096, False),
+                                           (130, 389, 64, False), (8, 256, 4096, False)])
+def test_argmax_in_the_output_heads_epilogue(M, N, K, fused):
+    """The head's product leaves one candidate per 32 weight rows and a small kernel picks among
+    them: the ids are those of the argmax kernel over the same logits (first maximum, NaN as -inf),
+    the logits are bit for bit the plain product's.  More than 128 rows, or a K that is split, take
+    the two kernels instead (src/sampling/sampler.zig:93-105)."""
+    o = ops()
+    x, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.1)
+    w[N - 1] = w[5] = (x[0].float() * 4).to(torch.bfloat16)      # a tie inside one warp's rows or across tiles
+    if N > 200:
+        w[200] = w[5]
+    w[9] = float("nan")                                           # a row of NaN logits never wins
+    x[M - 1] = 0                                                  # a row of zeros: every finite logit ties, id 0 wins
+    from zinfer_b200 import profiling
+    with profiling.profile() as prof:
+        logits, ids = o.linear_argmax(x, w)
+    classes = {c["class"] for c in prof.summary()["classes"]}
+    assert ("argmax (candidates)" in classes) == fused and ("argmax" in classes) != fused
+    plain = o.linear(x, w, out_dtype=torch.float32)
+    assert torch.equal(logits.nan_to_num(nan=-7.0), plain.nan_to_num(nan=-7.0))
+    assert torch.equal(ids, o.argmax(plain))
+    assert int(ids[0]) == 5 or M == 1                             # (with one row, row 0 is the row of zeros)
+    assert int(ids[M - 1]) == 0
+    # all logits negative, and -0 beside +0
+    xn = torch.ones((M, K), dtype=torch.bfloat16, device="cuda")
+    wn = -rnd(N, K, dtype=torch.bfloat16, scale=0.1).abs() - 0.01
+    wn[N // 2] = 0.0
+    wn[3] = -0.0
+    logits, ids = o.linear_argmax(xn, wn)
+    assert torch.equal(ids, o.argmax(logits)) and int(ids[0]) == 3
+    o.require_kernel_status_ok("linear_argmax")
+
+
 def test_a_wait_that_runs_out_is_reported_not_survived_silently():
     """The tensor-core kernels bound every wait; when one runs out they record a code in a device
     word and return.  Here a one-CTA kernel waits on a barrier nobody arrives at, with a limit of a

@@ -25,6 +25,9 @@ int zi_swiglu_partials(void* out, int dtype, const float* partials, int splits, 
                        int interleave, cudaStream_t stream);
 int zi_gemm_tcgen05_swiglu(void* out, int out_dtype, const void* x, const void* w, int M, int N2, int K, int ldx,
                            int ldw, int ldo, int sm_count, cudaStream_t stream);
+int zi_gemm_argmax_units(int N);
+int zi_gemm_tcgen05_argmax(float* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldw, int ldo,
+                           float* cand_val, int* cand_idx, int sm_count, cudaStream_t stream);
 int zi_rope_table(float* cos_t, float* sin_t, int n_pos, int d, float theta, cudaStream_t stream);
 int zi_qk_norm_rope_store(const void* src, int dtype, int T, int src_stride, const float* partials, int splits,
                           long long split_stride, void* q_out, int q_stride, int nq, int nkv, int d, const float* qw,
@@ -78,6 +81,7 @@ int zi_attention_decode_fused(void* out, int out_stride, float* workspace, const
 
 int zi_argmax_chunks(int R, int V);
 int zi_argmax(int* out, const float* logits, int R, int V, int ld, void* workspace, cudaStream_t stream);
+int zi_argmax_candidates(int* out, const float* cand_val, const int* cand_idx, int R, int units, cudaStream_t stream);
 int zi_sample_ctas_per_row(int R, int sm_count);
 int zi_sample(int* out, const float* logits, int R, int V, int ld, const float* temperature, const int* top_k,
               const float* top_p, const float* min_p, const float* rep, const float* pres, const float* freq,

@@ -49,17 +49,26 @@ struct GemmArgs {
   // (64 gate rows, then the 64 up rows of the same features); the kernel writes
   // silu(gate) * up, half as many columns, with this row pitch.
   long long act_ld;
+  // Argmax epilogue (weight rows on the lanes, one token per column): beside the 32-bit results,
+  // every warp leaves the first maximum of its 32 weight rows for each token as
+  // cand_val/cand_idx[token * cand_units + a / 32]; a second, small kernel picks among them.
+  float* cand_val;
+  int* cand_idx;
+  int cand_units;
 };
+
+constexpr int EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2;
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
 // One thread's row of an accumulator (TMEM lane `lane_base`, BN columns) to memory: row `a` of the A
 // side against B rows b_tile * BN ...  `a_ok` is false for rows past the end (the thread still
 // takes part in the warp-wide tensor-memory loads).
-template <typename TO, bool SWIGLU>
+template <typename TO, int EPI>
 __device__ __forceinline__ void drain_accumulator(const GemmArgs& g, TO* __restrict__ out, float* __restrict__ partial,
                                                   int split, int a, bool a_ok, int b_tile, uint32_t lane_base) {
   const int BN = g.BN;
+  constexpr bool SWIGLU = EPI == EPI_SWIGLU;
   if (SWIGLU) {
     // Tokens on the lanes; of every 128 columns the first 64 are gate and the next 64 up.
     for (int c0 = 0; c0 < BN; c0 += 128) {
@@ -101,6 +110,28 @@ __device__ __forceinline__ void drain_accumulator(const GemmArgs& g, TO* __restr
     }
     const int ncol = min(32, BN - c0);
     const int b0 = b_tile * BN + c0;
+    if (EPI == EPI_ARGMAX) {
+      // Floats as unsigned keys in the same order (NaN counts as -inf, -0 as +0; rows past the end
+      // get key 0, below every number): one warp-wide maximum and one vote per token, and the
+      // first lane that holds the maximum, the lowest weight row, writes it.
+      const int lane = threadIdx.x & 31;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (j >= ncol || b0 + j >= g.b_rows) break;
+        float x = v[j];
+        if (x != x) x = -INFINITY;
+        if (x == 0.f) x = 0.f;
+        const uint32_t bits = __float_as_uint(x);
+        const uint32_t key = a_ok ? ((bits >> 31) ? ~bits : (bits | 0x80000000u)) : 0u;
+        const uint32_t top = __reduce_max_sync(0xffffffffu, key);
+        const int who = __ffs(__ballot_sync(0xffffffffu, key == top)) - 1;
+        if (lane == who) {
+          const long long at = (long long)(b0 + j) * g.cand_units + (a >> 5);
+          g.cand_val[at] = top ? x : -INFINITY;
+          g.cand_idx[at] = top ? a : 0x7fffffff;
+        }
+      }
+    }
     if (!a_ok) continue;
     if (partial) {
       float* p = partial + (size_t)split * g.a_rows * g.b_rows + (long long)a * g.pa + (long long)b0 * g.pb;
@@ -146,8 +177,9 @@ __device__ __forceinline__ void drain_accumulator(const GemmArgs& g, TO* __restr
 // (box 64 x BN).  Persistent: a CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...
 // (A tile fastest, so neighbouring CTAs share the B tile in L2).  Two accumulators in
 // tensor memory let the epilogue of one tile run under the MMAs of the next.
-// SWIGLU: the epilogue writes silu(gate) * up (tokens on the lanes only).
-template <typename TO, bool SWIGLU>
+// EPI_SWIGLU: the epilogue writes silu(gate) * up (tokens on the lanes only).  EPI_ARGMAX: it also
+// leaves each token's largest result per 32 weight rows (weight rows on the lanes only).
+template <typename TO, int EPI>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     TO* __restrict__ out, float* __restrict__ partial, const GemmArgs g, int* __restrict__ status) {
@@ -288,7 +320,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int a = a_tile * TILE_A + quarter * 32 + lane;
       const uint32_t lane_base = tmem_base + acc * (uint32_t)g.acc_cols + ((uint32_t)(quarter * 32) << 16);
       const bool a_ok = a < g.a_rows;
-      drain_accumulator<TO, SWIGLU>(g, out, partial, split, a, a_ok, b_tile, lane_base);
+      drain_accumulator<TO, EPI>(g, out, partial, split, a, a_ok, b_tile, lane_base);
       // this accumulator may be overwritten by the MMAs of the tile after next
       tcgen05_fence_before();
       __syncwarp();
@@ -440,7 +472,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       tcgen05_fence_after();
       const int a = a_tile * PAIR_TILE + (int)rank * TILE_A + quarter * 32 + lane;
       const uint32_t lane_base = tmem_base + acc * (uint32_t)PAIR_TILE + ((uint32_t)(quarter * 32) << 16);
-      drain_accumulator<TO, SWIGLU>(g, out, nullptr, 0, a, a < g.a_rows, b_tile, lane_base);
+      drain_accumulator<TO, SWIGLU ? EPI_SWIGLU : EPI_PLAIN>(g, out, nullptr, 0, a, a < g.a_rows, b_tile, lane_base);
       // this accumulator may be overwritten by the MMAs of the tile after next
       tcgen05_fence_before();
       __syncwarp();
@@ -705,13 +737,37 @@ int launch_pair(void* out, const CUtensorMap& map_a, const CUtensorMap& map_b, G
   return zi_check_launch(what);
 }
 
+// One launch of the single-CTA kernel: as many CTAs as fit on the GPU at once, by shared memory and
+// by tensor memory (512 columns per SM), or one per tile if those are fewer.
+template <typename TO, int EPI>
+int launch_single(void* out, const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& g, float* partial,
+                  int* status, int sm_count, size_t smem, int total_tiles, const char* what, cudaStream_t stream) {
+  auto kern = gemm_tcgen05_kernel<TO, EPI>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return zi_refuse("%s: cannot get %zu bytes of shared memory", what, smem);
+  int per_sm = (int)((227 * 1024) / (smem + 1024));
+  per_sm = per_sm < 1 ? 1 : per_sm;
+  const int by_tmem = 512 / (2 * g.acc_cols);
+  if (per_sm > by_tmem) per_sm = by_tmem;
+  if (per_sm > 2) per_sm = 2;
+  int grid = per_sm * (sm_count > 0 ? sm_count : 148);
+  if (grid > total_tiles) grid = total_tiles;
+  zi_launch(kern, dim3(grid), dim3(THREADS), smem, stream, map_a, map_b, (TO*)out, partial, g, status);
+  return zi_check_launch(what);
+}
+
 // Launches the product (and, unless deferred, the split-K reduction) with the given
 // tensor maps, partial-sum buffer and status word.  Both entry points end here.
 int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtensorMap& map_b, int M, int N, int K,
                 int ldo, const int* plan, float* partial_buf, int* status, int sm_count, int defer_reduce,
-                const char* what, cudaStream_t stream, int swiglu = 0) {
+                const char* what, cudaStream_t stream, int epi = EPI_PLAIN, float* cand_val = nullptr,
+                int* cand_idx = nullptr) {
   const int swap = plan[0], BN = plan[1], splits = plan[2];
+  const int swiglu = epi == EPI_SWIGLU;
   GemmArgs g;
+  g.cand_val = cand_val;
+  g.cand_idx = cand_idx;
+  g.cand_units = swap ? (N + TILE_A - 1) / TILE_A * (TILE_A / 32) : 0;
   g.a_rows = swap ? N : M;
   g.b_rows = swap ? M : N;
   g.a_tiles = (g.a_rows + TILE_A - 1) / TILE_A;
@@ -738,20 +794,14 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
   if (use_pair_kernel(plan, M)) {
     ZI_DISPATCH_DTYPE(out_dtype, TO, { return launch_pair<TO>(out, map_a, map_b, g, M, N, K, status, swiglu, what, stream); });
   }
+  if (epi == EPI_ARGMAX) {
+    if (out_dtype != ZI_F32 || !swap || g.splits != 1 || !cand_val || !cand_idx)
+      return zi_refuse("%s: the argmax epilogue takes 32-bit results of an unsplit product of at most 128 tokens", what);
+    return launch_single<float, EPI_ARGMAX>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream);
+  }
   ZI_DISPATCH_DTYPE(out_dtype, TO, {
-    auto kern = swiglu ? gemm_tcgen05_kernel<TO, true> : gemm_tcgen05_kernel<TO, false>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return zi_refuse("%s: cannot get %zu bytes of shared memory", what, smem);
-    // CTAs that fit on the GPU at once: by shared memory, and by tensor memory (512 columns per SM)
-    int per_sm = (int)((227 * 1024) / (smem + 1024));
-    per_sm = per_sm < 1 ? 1 : per_sm;
-    const int by_tmem = 512 / (2 * g.acc_cols);
-    if (per_sm > by_tmem) per_sm = by_tmem;
-    if (per_sm > 2) per_sm = 2;
-    int grid = per_sm * (sm_count > 0 ? sm_count : 148);
-    if (grid > total_tiles) grid = total_tiles;
-    zi_launch(kern, dim3(grid), dim3(THREADS), smem, stream, map_a, map_b, (TO*)out, partial, g, status);
-    int rc = zi_check_launch(what);
+    int rc = swiglu ? launch_single<TO, EPI_SWIGLU>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream)
+                    : launch_single<TO, EPI_PLAIN>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream);
     if (rc) return rc;
     if (partial && !defer_reduce) {
       const size_t total = (size_t)M * N;
@@ -815,7 +865,34 @@ extern "C" int zi_gemm_tcgen05_swiglu(void* out, int out_dtype, const void* x, c
   int* status = status_word();
   if (!status) return zi_refuse("gemm_swiglu: cannot allocate the status word");
   return launch_gemm(out, out_dtype, map_a, map_b, M, N2, K, ldo, plan, nullptr, status, sm_count, 0, "gemm_swiglu",
-                     stream, 1);
+                     stream, EPI_SWIGLU);
+}
+
+// Rows of candidates per token that zi_gemm_tcgen05_argmax leaves: one per 32 weight rows,
+// rounded up to whole tiles of 128.
+extern "C" int zi_gemm_argmax_units(int N) { return (N + TILE_A - 1) / TILE_A * (TILE_A / 32); }
+
+// The product into 32-bit `out` [M, N] as zi_gemm_tcgen05 makes it, and beside it, for every token, the
+// first maximum of each 32 weight rows as cand_val/cand_idx [M, units] (units from
+// zi_gemm_argmax_units): what an argmax over the row needs, without reading the row again.
+// Returns -2 (without launching) when the product would not run with the weight rows on the lanes
+// and K whole (more than 128 tokens, or so few weight rows that K is split): the caller then
+// takes the plain product and the argmax kernel.
+extern "C" int zi_gemm_tcgen05_argmax(float* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldw,
+                                      int ldo, float* cand_val, int* cand_idx, int sm_count, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (!zi_gemm_tcgen05_supported(x, w, K, ldx, ldw))
+    return zi_refuse("gemm_argmax: operands must be 16-byte aligned bfloat16 with row pitches in multiples of 8");
+  int plan[3];
+  zi_gemm_tcgen05_plan(M, N, K, sm_count, plan);
+  if (!plan[0] || plan[2] > 1) return -2;
+  CUtensorMap map_a, map_b;
+  if (!make_map(&map_a, w, N, K, ldw, TILE_A) || !make_map(&map_b, x, M, K, ldx, plan[1]))
+    return zi_refuse("gemm_argmax: cuTensorMapEncodeTiled failed");
+  int* status = status_word();
+  if (!status) return zi_refuse("gemm_argmax: cannot allocate the status word");
+  return launch_gemm(out, ZI_F32, map_a, map_b, M, N, K, ldo, plan, nullptr, status, sm_count, 0, "gemm_argmax", stream,
+                     EPI_ARGMAX, cand_val, cand_idx);
 }
 
 // Switches the kernel for CTA pairs on (1) or off (0) for products of 256 tokens and more; returns

@@ -149,14 +149,18 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(float* __restrict__
   }
 }
 
-__global__ void argmax_final_kernel(int* __restrict__ out, const float* __restrict__ pval,
-                                    const int* __restrict__ pidx, int chunks) {
+// Picks among `chunks` candidates per row (value, token id): the largest value, and of equal values
+// the lowest id.  Any block of whole warps.
+__global__ void __launch_bounds__(256) argmax_final_kernel(int* __restrict__ out, const float* __restrict__ pval,
+                                                           const int* __restrict__ pidx, int chunks) {
   pdl_launch_dependents();
   pdl_wait();
-  const int r = blockIdx.x;
+  __shared__ float sval[8];
+  __shared__ int sidx[8];
+  const size_t r = blockIdx.x;
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int c = threadIdx.x; c < chunks; c += 32) {
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
     const float v = pval[r * chunks + c];
     const int i = pidx[r * chunks + c];
     if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
@@ -166,6 +170,20 @@ __global__ void argmax_final_kernel(int* __restrict__ out, const float* __restri
     const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
     const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
     if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  if (blockDim.x > 32) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    if (lane == 0) { sval[warp] = bv; sidx[warp] = bi; }
+    __syncthreads();
+    if (warp != 0) return;
+    bv = lane < nwarp ? sval[lane] : -INFINITY;
+    bi = lane < nwarp ? sidx[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
   }
   if (threadIdx.x == 0) out[r] = bi == 0x7fffffff ? 0 : bi;
 }
@@ -707,6 +725,16 @@ extern "C" int zi_argmax(int* out, const float* logits, int R, int V, int ld, vo
   }
   zi_launch(argmax_kernel, dim3(R), dim3(THREADS), 0, stream, out, logits, ld, V);
   return zi_check_launch("argmax");
+}
+
+// The argmax of R rows from `units` candidates per row, as the output head's product leaves them
+// (zi_gemm_tcgen05_argmax): cand_val/cand_idx [R, units].
+extern "C" int zi_argmax_candidates(int* out, const float* cand_val, const int* cand_idx, int R, int units,
+                                    cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (units <= 0) return zi_refuse("argmax: no candidates");
+  zi_launch(argmax_final_kernel, dim3(R), dim3(units > 256 ? 256 : 32), 0, stream, out, cand_val, cand_idx, units);
+  return zi_check_launch("argmax (candidates)");
 }
 
 // CTAs that share a row of the sampling kernel: as many (8, 4, 2, 1) as still give every CTA an SM

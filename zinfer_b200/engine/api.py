@@ -157,11 +157,15 @@ class Engine:
                 rows.append(r)
         if not entries:
             return _InFlight(plan, None, None, None, {})
-        logits = self.runner.step(entries, prev_tokens=prev.tokens_dev if prev is not None else None)
+        prev_tokens = prev.tokens_dev if prev is not None else None
+        if rows and self.sampler.all_greedy([r.params for r in rows]):
+            logits, greedy_ids = self.runner.step_argmax(entries, prev_tokens=prev_tokens)
+        else:
+            logits, greedy_ids = self.runner.step(entries, prev_tokens=prev_tokens), None
         if not rows:
             return _InFlight(plan, None, None, None, {})
         tokens = self.sampler.sample(logits, [r.request_id for r in rows], [r.params for r in rows],
-                                     [len(r.output) for r in rows])
+                                     [len(r.output) for r in rows], greedy_ids=greedy_ids)
         host = self._token_buffers[self._token_turn % len(self._token_buffers)]
         self._token_turn += 1
         host[:len(rows)].copy_(tokens, non_blocking=True)     # the step's one read back to the host

@@ -59,9 +59,9 @@ class DecodeGraphs:
         return (len(entries) <= self.max_batch and all(len(e.tokens) == 1 for e in entries)
                 and self.bucket_for(len(entries)) is not None)
 
-    def run(self, entries: Sequence[StepEntry], prev_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Logits [bucket, vocab] (a buffer that the next replay overwrites); the
-        first len(entries) rows belong to the entries, in order."""
+    def run(self, entries: Sequence[StepEntry], prev_tokens: Optional[torch.Tensor] = None):
+        """Logits [bucket, vocab] and their rows' first maxima [bucket] (buffers that the next
+        replay overwrites); the first len(entries) rows belong to the entries, in order."""
         runner = self.runner
         b = self.bucket_for(len(entries))
         ps = runner.manager.page_size
@@ -85,7 +85,7 @@ class DecodeGraphs:
                 # first use: run uncaptured, so that one-time set-up (function attributes,
                 # rotary tables, the kernels' status word) happens outside a capture
                 state["warm"] += 1
-                return runner.model.forward(ctx)
+                return runner.model.forward(ctx, argmax=True)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             before = ops.LAUNCHES
@@ -94,7 +94,7 @@ class DecodeGraphs:
             if self._pool is None:
                 self._pool = torch.cuda.graph_pool_handle()
             with torch.cuda.graph(graph, pool=self._pool, capture_error_mode="relaxed"):
-                state["logits"] = runner.model.forward(ctx)
+                state["logits"] = runner.model.forward(ctx, argmax=True)
             self.captures += 1
             state["launches"] = ops.LAUNCHES - before
             ops.LAUNCHES = before

@@ -10,6 +10,7 @@ from typing import Optional
 
 import torch
 
+from .. import ops
 from ..cache.storage import CacheStorage
 from ..config.spec import ModelSpec
 from ..parts.base import BuildContext, KVCacheNeed, StateNeed, TensorSpec, make_part, prefixed, take
@@ -114,17 +115,23 @@ class DecoderModel:
                 self._views.append(None)
 
     # ------------------------------------------------------------------ forward
-    def forward(self, step) -> Optional[torch.Tensor]:
+    def forward(self, step, argmax: bool = False):
         """Runs the step's tokens through every scheduled layer (filling the caches)
-        and returns 32-bit logits [wanted rows, vocab], or None if none are wanted."""
+        and returns 32-bit logits [wanted rows, vocab], or None if none are wanted.
+        With ``argmax`` it returns the pair (logits, first maximum of every row as int32)."""
         h = self.embedding.forward(step.token_ids)
         pending = None
         for run, view in zip(self.runs, self._views):
             pending = self.blocks[run.layer].forward(h, pending, step, view)
         if step.logit_rows is None or step.logit_rows.numel() == 0:
-            return None
+            return (None, None) if argmax else None
         x = self.final_norm.forward(h, pending, rows=step.logit_rows)
-        return self.head.forward(x)
+        if not argmax:
+            return self.head.forward(x)
+        if hasattr(self.head, "forward_argmax"):     # a head may find the maxima while it makes the logits
+            return self.head.forward_argmax(x)
+        logits = self.head.forward(x)
+        return logits, ops.argmax(logits)
 
 
 def declared_tensors(spec: ModelSpec) -> dict[str, TensorSpec]:

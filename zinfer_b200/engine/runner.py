@@ -164,8 +164,16 @@ class ModelRunner:
         """Runs the entries as one batch; returns logits [wanted, vocab] in the order
         of the entries and of each entry's ``want`` (None if nothing is wanted).
         ``prev_tokens`` (int32, on the device) is read by entries with ``token_src``."""
+        return self._step(entries, prev_tokens, False)[0]
+
+    def step_argmax(self, entries: Sequence[StepEntry], prev_tokens: Optional[torch.Tensor] = None):
+        """As :meth:`step`, and beside the logits the first maximum of every wanted row (int32, on
+        the device): greedy decoding without a second pass over the logits."""
+        return self._step(entries, prev_tokens, True)
+
+    def _step(self, entries: Sequence[StepEntry], prev_tokens: Optional[torch.Tensor], argmax: bool):
         if not entries:
-            return None
+            return None, None
         self.validate(entries)
         if any(e.token_src is not None for e in entries) and prev_tokens is None:
             raise StepError("an entry takes its token from the step before, but no such tokens were given")
@@ -173,22 +181,26 @@ class ModelRunner:
         if profiling.ACTIVE is not None:
             profiling.ACTIVE.begin_step()    # profiled steps launch their kernels one by one, never from a graph
         if self.graphs is not None and profiling.ACTIVE is None and self.graphs.eligible(entries):
-            all_rows = self.graphs.run(entries, prev_tokens)
+            all_rows, all_ids = self.graphs.run(entries, prev_tokens)
             wanted = [i for i, e in enumerate(entries) if len(e.want)]
             if not wanted:
-                logits = None
+                logits = ids = None
             elif len(wanted) == len(entries):
-                logits = all_rows[:len(entries)]
+                logits, ids = all_rows[:len(entries)], all_ids[:len(entries)]
             else:
-                logits = all_rows[torch.tensor(wanted, device=self.device)]
+                pick = torch.tensor(wanted, device=self.device)
+                logits, ids = all_rows[pick], (all_ids[pick] if argmax else None)
         else:
             ctx = build_step(self.manager, entries, self.device, self.tile_rows, pf_tile_rows=self.pf_tile_rows,
                              staging=self._staging)
             self.last_h2d_bytes = ctx.h2d_bytes
             if ctx.n_patch:
                 ops.patch_tokens(ctx.token_ids, prev_tokens, ctx.patch_dst, ctx.patch_src)
-            logits = self.model.forward(ctx)
+            if argmax:
+                logits, ids = self.model.forward(ctx, argmax=True)
+            else:
+                logits, ids = self.model.forward(ctx), None
         for e in entries:
             self.manager.commit(e.request_id, len(e.tokens))
         self.steps_run += 1
-        return logits
+        return logits, ids

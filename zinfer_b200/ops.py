@@ -366,6 +366,35 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     return out
 
 
+def linear_argmax(x: torch.Tensor, weight: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """The 32-bit product ``x [M, K] @ weight [N, K]^T`` and each row's argmax (first maximum, NaN
+    counted as -inf, as :func:`argmax` has it).  For up to 128 rows on the tensor-core path the
+    product's epilogue leaves one candidate per 32 weight rows and a small kernel picks among them,
+    so the [M, N] result is not read again; otherwise the product is followed by the argmax kernel."""
+    M, K = x.shape
+    N = weight.shape[0]
+    if (GEMM_BACKEND != "simt" and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and M > 0
+            and x.stride(1) == 1 and weight.is_contiguous()
+            and lib().zi_gemm_tcgen05_supported(_ptr(x), _ptr(weight), K, x.stride(0), weight.stride(0))):
+        units = lib().zi_gemm_argmax_units(N)
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+        cand_val = torch.empty((M, units), dtype=torch.float32, device=x.device)
+        cand_idx = torch.empty((M, units), dtype=torch.int32, device=x.device)
+        with _prof.region(f"linear+argmax N={N} K={K}", lambda: _nb(weight, out) + M * K * 2, 2 * M * N * K) as rec:
+            code = lib().zi_gemm_tcgen05_argmax(_ptr(out), _ptr(x), _ptr(weight), M, N, K, x.stride(0), weight.stride(0),
+                                                out.stride(0), _ptr(cand_val), _ptr(cand_idx), _sm_count(x.device), _stream())
+            rec["keep"] = code != -2      # -2: more than 128 rows, or K would be split
+        if code != -2:
+            _check(code, "linear_argmax")
+            ids = torch.empty((M,), dtype=torch.int32, device=x.device)
+            with _prof.region("argmax (candidates)", lambda: _nb(cand_val, cand_idx)):
+                _check(lib().zi_argmax_candidates(_ptr(ids), _ptr(cand_val), _ptr(cand_idx), M, units, _stream()),
+                       "argmax (candidates)")
+            return out, ids
+    out = linear(x, weight, out_dtype=torch.float32)
+    return out, argmax(out)
+
+
 # ----------------------------------------------------------------------- attention
 def attention_tile_rows() -> int:
     return int(lib().zi_paged_attention_tile_rows())

@@ -69,13 +69,19 @@ class Sampler:
         self._turn += 1
         return buf
 
+    @staticmethod
+    def all_greedy(params: Sequence[SamplingParams]) -> bool:
+        """Whether these rows need nothing but their logits' first maximum."""
+        return all(p.greedy and not p.has_penalties for p in params)
+
     def sample(self, logits: torch.Tensor, request_ids: Sequence[Hashable], params: Sequence[SamplingParams],
-               draw_index: Sequence[int]) -> torch.Tensor:
-        """One token (int32, on the device) per row of ``logits``."""
+               draw_index: Sequence[int], greedy_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One token (int32, on the device) per row of ``logits``.  ``greedy_ids``: the rows' first
+        maxima where the model's step has already found them."""
         R = logits.shape[0]
         assert R == len(request_ids) == len(params) == len(draw_index)
-        if all(p.greedy and not p.has_penalties for p in params):
-            return ops.argmax(logits)
+        if self.all_greedy(params):
+            return greedy_ids if greedy_ids is not None else ops.argmax(logits)
         any_pen = any(p.has_penalties for p in params)
         # all per-row parameters travel in one pinned buffer and one copy
         host = self._staging(R)
