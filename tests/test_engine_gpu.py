@@ -217,6 +217,32 @@ def test_sampling_follows_the_kept_distribution(kw):
     assert (other != draws).any()
 
 
+@pytest.mark.parametrize("case", ["one bin of thousands", "a flood of equal logits", "everything equal"])
+def test_top_k_when_the_first_count_of_keys_does_not_settle_it(case):
+    """Top-k with a short list first counts the keys by their top 12 bits.  When the bin that holds
+    the k-th key holds more tokens than can be listed, the row is counted again by the next bits;
+    when even equal logits are too many, the cut falls to the thresholds over the whole row (ties
+    are cut by token id, src/sampling/sampler.zig:93-105)."""
+    V, k, n = 20000, 20, 3000
+    g = torch.Generator().manual_seed(1)
+    row = torch.randn(V, generator=g)
+    ulp = 2.0 ** -20                                            # of a float in [8, 16)
+    if case == "one bin of thousands":
+        row[100:5100] = 9.0 + torch.arange(5000, dtype=torch.float64).mul(ulp).float()   # 5,000 tokens in [9, 9.005)
+        expected = set(range(5100 - k, 5100))
+    elif case == "a flood of equal logits":
+        row[100:3100] = 9.0
+        row[[7, 19000, 4000, 12, 15000]] = 9.5
+        expected = {7, 19000, 4000, 12, 15000} | set(range(100, 115))
+    else:
+        row[:] = 1.25
+        expected = set(range(k))
+    draws = _sample_many(row, n, temperature=5.0, top_k=k)
+    p = P.kept_distribution(row.numpy(), 5.0, k, 1.0, 0.0)
+    assert set(np.nonzero(p)[0]) == expected
+    assert set(draws.tolist()) == expected, "with nearly equal weights, 3,000 draws reach every one of the 20 tokens"
+
+
 @pytest.mark.parametrize("V", [1000, 151936])
 def test_a_draw_does_not_depend_on_the_rows_beside_it(V):
     """The kernel spreads a row over 8, 4, 2 or 1 CTAs by the number of rows in the launch; the

@@ -402,38 +402,136 @@ __device__ Cut select_cut(const RowView& row, Team& tm, const F& cand, double ta
   return cut;
 }
 
-// A key lower bound `lb` with at least k and (if the data allow) at most `limit` tokens at
-// or above it: the radix descent of select_cut, stopped as soon as the surviving bin is small
-// enough to be listed.  Returns the number of tokens with key >= lb.
-__device__ int coarse_lower_bound(const RowView& row, Team& tm, int k, int limit, unsigned int& lb) {
+// A key lower bound `lb` with at least k and (if the data allow) at most `limit` tokens at or
+// above it, and the row's first maximum, in as few passes over the row as the data allow: usually
+// one.  Every CTA counts its tokens by the top 12 bits of their keys into 4,096 bins in shared
+// memory (integer atomics: a count does not depend on the order of its increments), keeping the
+// running maximum on the way; after a cluster barrier every thread adds four bins over the CTAs,
+// and a block-wide sum from the top finds the bin in which the k-th key lies.  Only if that bin
+// holds more tokens than may be listed is the row read again, for the next 12 bits (and once more
+// for the last 8).  Returns the number of tokens with key >= lb.  `hist` is this CTA's 4,096 words.
+constexpr int HIST_BINS = 4096;   // four per thread of a block of THREADS
+__device__ int hist_lower_bound(const RowView& row, Team& tm, int k, int limit, unsigned int& lb, unsigned int* hist,
+                                float* best_val, int* best_idx, float* sval, int* sidx) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int n_ctas = SLICES / tm.per;
   unsigned int prefix = 0, mask = 0;
   int remaining = k, above = 0, n_ge = row.V;
-  for (int pass = 0; pass < 8; ++pass) {
-    const int shift = 28 - 4 * pass;
-    int tot[16];
-    team_sum16<int>(row, tm, tot, [&](int, float a, int (&bins)[16]) {
-      const unsigned int key = order_key(a);
-      if ((key & mask) != prefix) return;
-      const unsigned int d = (key >> shift) & 15u;
-#pragma unroll
-      for (int b = 0; b < 16; ++b) bins[b] += (d == (unsigned)b) ? 1 : 0;
-    });
-    int cum = 0, digit = 0;
-#pragma unroll
-    for (int b = 15; b >= 0; --b) {
-      if (cum + tot[b] >= remaining || b == 0) {
-        digit = b;
-        break;
-      }
-      cum += tot[b];
+  for (int pass = 0; pass < 3; ++pass) {
+    const int shift = pass == 0 ? 20 : pass == 1 ? 8 : 0;
+    const unsigned int width = pass == 2 ? 0xffu : 0xfffu;
+    for (int b = threadIdx.x; b < HIST_BINS; b += blockDim.x) hist[b] = 0u;
+    __syncthreads();
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = 0; i < tm.per; ++i) {
+      const int slice = tm.rank * tm.per + i;
+      for_each_token(row, tm.first(slice), tm.stride(), [&](int v, float a) {
+        const unsigned int key = order_key(a);
+        if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & width], 1u);
+        if (pass == 0) {
+          if (a != a) a = -INFINITY;
+          if (a > bv || (a == bv && v < bi)) { bv = a; bi = v; }
+        }
+      });
     }
+    if (pass == 0) {
+      // this CTA's first maximum: over each warp by shuffles, over the warps by warp 0
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      }
+      if (lane == 0) { sval[warp] = bv; sidx[warp] = bi; }
+      __syncthreads();
+      if (warp == 0) {
+        bv = lane < nwarp ? sval[lane] : -INFINITY;
+        bi = lane < nwarp ? sidx[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+          const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+          if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) {
+          unsigned int* mine = tm.slice_buf + (tm.pass & 1u) * SLICES * 16;
+          mine[0] = __float_as_uint(bv);
+          mine[1] = (unsigned int)bi;
+        }
+      }
+    }
+    tm.cl.sync();   // every CTA's bins (and maximum) are complete
+    // four neighbouring bins per thread, added over the CTAs; the highest bins in the highest threads
+    int t[4] = {0, 0, 0, 0};
+    if ((int)threadIdx.x * 4 < HIST_BINS) {
+      for (int c = 0; c < n_ctas; ++c) {
+        const uint4 theirs = *reinterpret_cast<const uint4*>(tm.cl.map_shared_rank(hist, c) + threadIdx.x * 4);
+        t[0] += (int)theirs.x;
+        t[1] += (int)theirs.y;
+        t[2] += (int)theirs.z;
+        t[3] += (int)theirs.w;
+      }
+    }
+    if (pass == 0 && threadIdx.x == 0) {
+      float gv = -INFINITY;
+      int gi = 0x7fffffff;
+      for (int c = 0; c < n_ctas; ++c) {
+        const unsigned int* theirs = tm.cl.map_shared_rank(tm.slice_buf + (tm.pass & 1u) * SLICES * 16, c);
+        const float v = __uint_as_float(theirs[0]);
+        const int idx = (int)theirs[1];
+        if (v > gv || (v == gv && idx < gi)) { gv = v; gi = idx; }
+      }
+      tm.tot_buf[0] = __float_as_uint(gv);
+      tm.tot_buf[1] = (unsigned int)(gi == 0x7fffffff ? 0 : gi);
+    }
+    tm.cl.sync();   // nobody reads another CTA's bins after this: they may be cleared or reused
+    if (pass == 0) tm.pass += 1;
+    // tokens in bins above this thread's four: within the warp (higher lanes), then the warps above
+    const int mine = t[0] + t[1] + t[2] + t[3];
+    int incl = mine;   // this lane and the lanes above it
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_down_sync(0xffffffffu, incl, o);
+      if (lane + o < 32) incl += up;
+    }
+    if (lane == 0) sidx[warp] = incl;   // the warp's total
+    if (threadIdx.x == 0) tm.tot_buf[2] = 0xffffffffu;
+    __syncthreads();
+    int higher = incl - mine;
+    for (int w = warp + 1; w < nwarp; ++w) higher += sidx[w];
+    // exactly one thread's bins hold the place where the count from the top reaches `remaining`
+    if (higher < remaining && higher + mine >= remaining) {
+      int cum = higher;
+#pragma unroll
+      for (int b = 3; b >= 0; --b) {
+        if (cum + t[b] >= remaining) {
+          tm.tot_buf[2] = (unsigned int)(threadIdx.x * 4 + b);
+          tm.tot_buf[3] = (unsigned int)cum;
+          tm.tot_buf[4] = (unsigned int)t[b];
+          break;
+        }
+        cum += t[b];
+      }
+    }
+    __syncthreads();
+    unsigned int digit = tm.tot_buf[2];
+    int cum = (int)tm.tot_buf[3], in_bin = (int)tm.tot_buf[4];
+    if (digit == 0xffffffffu) {   // fewer tokens than asked for: everything is inside
+      digit = 0u;
+      cum = 0;
+      in_bin = 0;
+    }
+    __syncthreads();   // tot_buf and sidx are free again
     remaining -= cum;
     above += cum;
-    prefix |= (unsigned)digit << shift;
-    mask |= 15u << shift;
-    n_ge = above + tot[digit];
+    prefix |= digit << shift;
+    mask |= width << shift;
+    n_ge = above + in_bin;
     if (n_ge <= limit) break;
   }
+  *best_val = __uint_as_float(tm.tot_buf[0]);
+  *best_idx = (int)tm.tot_buf[1];
   lb = prefix;
   return n_ge;
 }
@@ -466,7 +564,7 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int ld, i
   pdl_wait();
   __shared__ float sval[32];
   __shared__ int sidx[32];
-  __shared__ unsigned int warp_buf[SLICES * 32 * 16];
+  __shared__ __align__(16) unsigned int warp_buf[SLICES * 32 * 16];   // (also the 4,096 bins of hist_lower_bound)
   __shared__ unsigned int slice_buf[2 * SLICES * 16];
   __shared__ unsigned int tot_buf[16];
   __shared__ float cand_a[SMALL_K];      // the short list of candidates (used in the CTA of rank 0)
@@ -494,16 +592,19 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int ld, i
   const int top_k = p.top_k ? p.top_k[r] : 0;
   float amax;
   int token;
-  team_argmax(row, tm, &amax, &token, sval, sidx);   // (its cluster barrier also publishes n_cand and chosen)
+  // top-k with few candidates: a coarse key bound that leaves a short list (at least k long), found
+  // in the pass that finds the maximum
+  const bool few = temperature > 0.f && top_k > 1 && top_k <= SMALL_K && top_k < V;
+  unsigned int lb = 0;
+  int n_listed = V;
+  // (the cluster barrier inside either also publishes n_cand and chosen)
+  if (few) n_listed = hist_lower_bound(row, tm, top_k, SMALL_K, lb, warp_buf, &amax, &token, sval, sidx);
+  else team_argmax(row, tm, &amax, &token, sval, sidx);
 
   if (temperature > 0.f && top_k != 1) {
     const float zmax = amax / temperature;
     const float min_p = fminf(fmaxf(p.min_p ? p.min_p[r] : 0.f, 0.f), 1.f);
     const float top_p = fminf(fmaxf(p.top_p ? p.top_p[r] : 1.f, 0.f), 1.f);
-    // top-k with few candidates: a coarse key bound that leaves a short list (at least k long)
-    unsigned int lb = 0;
-    int n_listed = V;
-    if (top_k > 0 && top_k <= SMALL_K && top_k < V) n_listed = coarse_lower_bound(row, tm, top_k, SMALL_K, lb);
     const unsigned long long bits = splitmix64(splitmix64(p.seeds[r]) ^ (unsigned long long)(unsigned int)p.draw_index[r]);
     const double u = (double)(bits >> 11) * (1.0 / 9007199254740992.0);
     if (top_k > 0 && top_k < V && n_listed <= SMALL_K) {
