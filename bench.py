@@ -272,10 +272,10 @@ def main() -> int:
             points[f"decode_b{b}"] = round(b / (m * 1e-3), 1)
 
     # ------------------------------------------------- end to end through the API
-    def e2e_point(batch: int, n_steps: int) -> tuple[float, int]:
+    def e2e_point(batch: int, n_steps: int, **sampling) -> tuple[float, int]:
         """Decoded tokens a second through Engine.step (host tokens in and out), and the bytes of
-        the step's one host->device copy."""
-        params = SamplingParams(temperature=0.0, max_new_tokens=n_steps + warmup + 8, ignore_eos=True)
+        the step's one host->device copy.  Greedy unless sampling options are given."""
+        params = SamplingParams(**{"temperature": 0.0, **sampling}, max_new_tokens=n_steps + warmup + 8, ignore_eos=True)
         for i in range(batch):
             engine.add_request(rand_tokens(PROMPT_LEN), params)
         while any(r.num_computed < len(r.prompt) for r in engine.scheduler.running) or engine.scheduler.waiting:
@@ -297,6 +297,10 @@ def main() -> int:
     e2e = {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch}
     if not args.skip_points:
         e2e["points"] = {f"decode_b{b}": round(e2e_point(b, min(steps, 32))[0], 1) for b in (1, 64)}
+        # the same with the reference's default sampling options instead of greedy (src/app/cli/args.zig:364-370)
+        e2e["sampled"] = {"value": round(e2e_point(args.batch, min(steps, 32), temperature=0.7, top_k=20, top_p=0.8,
+                                                   repetition_penalty=1.1, seed=7)[0], 1),
+                          "options": "temperature 0.7, top-k 20, top-p 0.8, repetition penalty 1.1"}
 
     # -------------------------------- where the time goes (uncaptured, never a timed number)
     if args.profile:
