@@ -140,3 +140,24 @@ def test_pool_sizing_from_a_byte_budget(cpu_kernels, model_dirs):
     # the default: as many tokens as the requests could fill, where no device memory can be asked
     eng = Engine(model_dirs[("A", "float32")], dtype="float32", device="cpu", page_size=16, max_requests=4)
     assert eng.runner.manager.groups[0].pool.num_pages == 4 * 128 // 16
+
+
+def test_stop_and_stream_flags(cpu_kernels, model_dirs):
+    """--stop (repeatable, ids for the reference's text) and --stream through the command line."""
+    run = {}
+    s, _ = cli.parse_flags(["--stop", "5,6", "--stop", "7", "--stream"], run)
+    assert s == dict(stop_sequences=[[5, 6], [7]]) and run == dict(stream=True)
+    with pytest.raises(cli.CliError, match="MissingFlagValue"):
+        cli.parse_flags(["--stop"], {})
+    d = model_dirs[("A", "float32")]
+    cfg, w = plain_qwen3.load_model(d)
+    full = plain_qwen3.greedy(cfg, w, [3, 9, 27], 8)
+    stop = ",".join(map(str, full[4:6]))
+    cut = next(i for i in range(7) if full[i:i + 2] == full[4:6])
+    out = io.StringIO()
+    assert cli.run(["generate", d, "3,9,27", "8", "--device", "cpu", "--dtype", "float32", "--temperature", "0", "--ignore-eos",
+                    "--stop", stop, "--stream"], out) == 0
+    text = out.getvalue()
+    streamed = [int(t) for line in text.splitlines() if line.startswith("stream[0]: ") for t in line.split(": ")[1].split()]
+    assert streamed == full[:cut]
+    assert "tokens: [" + ", ".join(map(str, full[:cut])) + "]" in text and "finish_reason: stop" in text

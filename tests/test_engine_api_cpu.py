@@ -54,3 +54,58 @@ def test_more_penalised_prompts_than_count_rows(cpu_kernels, model_dirs):
     assert eng.sampler._rows.num_used == 0 and not eng.sampler._row_of
     alone = [_engine(model_dirs, "A", max_requests=2).generate([p], sp)[0].token_ids for p in prompts]
     assert [r.token_ids for r in got] == alone, "a request's tokens depend on what ran beside it"
+
+
+def test_stop_analysis_on_ids():
+    """The reference's two cases (src/app/cli/runtime/streaming.zig:68-87) with ids for bytes, and
+    the order of several stop sequences."""
+    from zinfer_b200.sampling import analyze_generated
+
+    hello_today = [7, 4, 11, 11, 14, 99, 19, 14, 3, 0, 24, 50]      # "Hello today?"
+    today = hello_today[6:]
+    a = analyze_generated(hello_today, [today])
+    assert (a.stop_hit, a.printable_len, a.response_len) == (True, 6, 6)
+    a = analyze_generated(hello_today[:8], [today])                 # "Hello to": a prefix of the stop is held back
+    assert (a.stop_hit, a.printable_len, a.response_len) == (False, 6, 8)
+    a = analyze_generated([1, 2, 3], [[], [9], [2, 3, 4], [3, 5, 5]])
+    assert (a.stop_hit, a.printable_len, a.response_len) == (False, 1, 3)   # the longest tail that may still grow
+    a = analyze_generated([1, 2, 3], [[3], [2, 3]])
+    assert (a.stop_hit, a.response_len) == (True, 2)                # the first sequence that matches, in the order given
+    assert analyze_generated([], [[1]]) == analyze_generated([], [])
+
+
+@pytest.mark.parametrize("pipelined", [True, False])
+def test_stop_sequences_and_streaming_through_the_engine(cpu_kernels, model_dirs, pipelined):
+    """Stop sequences cut from the plain greedy continuation: the response ends before the
+    sequence, whatever was in flight is dropped, and the streamed pieces add up to the response
+    without ever showing a tail that became a stop sequence."""
+    from zinfer_b200.sampling import SamplingParams
+
+    cfg, w = P.load_model(model_dirs[("A", "float32")])
+    prompts = _prompts(cfg["vocab_size"])
+    full = [P.greedy(cfg, w, p, 12) for p in prompts]
+    # request i stops on the two ids at positions cut[i], cut[i]+1 of its continuation; the last has a
+    # stop sequence that never occurs, and one whose first id alone occurs (held back, then shown)
+    cut = [3, 0, 7, 10]
+    params = [SamplingParams(temperature=0.0, max_new_tokens=12, ignore_eos=True, stop_sequences=[[4242, 1], f[c:c + 2]])
+              for f, c in zip(full, cut)]
+    params.append(SamplingParams(temperature=0.0, max_new_tokens=12, ignore_eos=True,
+                                 stop_sequences=[[full[4][5], cfg["vocab_size"] + 5]]))
+    def first_hit(f, stop):
+        return next((i for i in range(len(f) - 1) if f[i:i + 2] == stop), None)
+    want = [f[:first_hit(f, f[c:c + 2])] for f, c in zip(full, cut)] + [full[4]]
+    eng = _engine(model_dirs, "A", kv_cache_tokens=96, pipelined=pipelined)
+    got = eng.generate(prompts, params)
+    assert [r.token_ids for r in got] == want
+    assert [r.finish_reason for r in got] == ["stop"] * 4 + ["length"]
+    eng.runner.manager.check()
+    assert not eng.runner.manager.requests and not eng.scheduler.waiting and not eng.scheduler.running
+    pieces = {i: [] for i in range(5)}
+    ended = {}
+    for i, new_ids, res in eng.generate_stream(prompts, params):
+        assert i not in ended, "nothing comes after the event that ends a request"
+        pieces[i] += new_ids
+        assert pieces[i] == want[i][:len(pieces[i])], "a token was shown that is not part of the response"
+        if res is not None:
+            ended[i] = res
+    assert [pieces[i] for i in range(5)] == want and [ended[i].token_ids for i in range(5)] == want

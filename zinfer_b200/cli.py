@@ -45,6 +45,10 @@ Flags:
   --repetition-penalty <f32>
   --max-new-tokens <usize>     (same as the positional)
   --ignore-eos
+  --stop <ids_csv>             (repeatable: generation ends when the generated ids end with these; they are not
+                                part of the response)
+  --stream                     (generate: print ids as they are generated, `stream[i]: ...`, holding back a tail
+                                that may still become a stop sequence)
   --dtype <bfloat16|float32>
   --device <cuda:N>
   --random-weights <seed>      (with --config)
@@ -117,6 +121,16 @@ def parse_flags(args: list[str], run_opts: dict | None = None) -> tuple[dict, di
         if a == "--ignore-eos":
             sampling["ignore_eos"] = True
             i += 1
+            continue
+        if a == "--stream" and run_opts is not None:
+            run_opts["stream"] = True
+            i += 1
+            continue
+        if a == "--stop":                       # repeatable, like the reference's (args.zig:462-466); ids instead of text
+            if i + 1 >= len(args):
+                raise CliError(f"MissingFlagValue: {a}")
+            sampling.setdefault("stop_sequences", []).append(parse_token_ids(args[i + 1]))
+            i += 2
             continue
         table = (_FLAGS if a in _FLAGS else _ENGINE_FLAGS if a in _ENGINE_FLAGS
                  else _RUN_FLAGS if a in _RUN_FLAGS and run_opts is not None else None)
@@ -304,7 +318,18 @@ def generate(model, ids_csv: str, max_new: int, sampling: dict, engine_opts: dic
     page = engine_opts.get("page_size", 16)
     eng = _engine(model, engine_opts, max_requests=max(1, len(prompts)),
                   kv_cache_tokens=sum(-(-(len(p) + max_new) // page) * page + page for p in prompts))
-    results = _profiled(run_opts or {}, eng, lambda: eng.generate(prompts, SamplingParams(max_new_tokens=max_new, **sampling)))
+    params = SamplingParams(max_new_tokens=max_new, **sampling)
+
+    def streamed():
+        done = {}
+        for i, new_ids, res in eng.generate_stream(prompts, params):
+            if new_ids:
+                print(f"stream[{i}]: " + " ".join(str(t) for t in new_ids), file=out, flush=True)
+            if res is not None:
+                done[i] = res
+        return [done[i] for i in range(len(prompts))]
+
+    results = _profiled(run_opts or {}, eng, streamed if (run_opts or {}).get("stream") else lambda: eng.generate(prompts, params))
     for i, res in enumerate(results):
         tag = "" if len(results) == 1 else f"[{i}]"
         print(f"tokens{tag}: [" + ", ".join(str(t) for t in res.token_ids) + "]", file=out)

@@ -15,7 +15,7 @@ from typing import Optional, Sequence
 import torch
 
 from .. import ops, profiling
-from ..sampling import Sampler, SamplingParams
+from ..sampling import Sampler, SamplingParams, analyze_generated
 from .batch import StepEntry
 from .runner import ModelRunner
 from .scheduler import Request, Scheduler, StepPlan
@@ -242,6 +242,40 @@ class Engine:
             for res in self.step():
                 done[res.request_id] = res
         return [done[i] for i in ids]
+
+
+    def generate_stream(self, prompt_ids: Sequence[Sequence[int]], params=None, **options):
+        """As :meth:`generate`, but yields ``(index of the prompt, new token ids, result or None)``
+        as tokens reach the host: ``new token ids`` continue what was yielded for that prompt
+        before, and ``result`` is its :class:`GenerationResult` in the event that ends it.  A tail
+        that may still grow into one of the request's stop sequences is held back until it has
+        not (src/app/cli/runtime/streaming.zig:42-66 on ids)."""
+        if prompt_ids and isinstance(prompt_ids[0], int):
+            prompt_ids = [prompt_ids]
+        if params is None or isinstance(params, SamplingParams):
+            params = [params or SamplingParams()] * len(prompt_ids)
+        if len(params) != len(prompt_ids):
+            raise ValueError("one SamplingParams per prompt, or one for all")
+        if options:
+            params = [replace(p, **options) for p in params]
+        ids = [self.add_request(p, sp) for p, sp in zip(prompt_ids, params)]
+        index = {rid: i for i, rid in enumerate(ids)}
+        live = {rid: self._live[rid] for rid in ids}
+        shown = {rid: 0 for rid in ids}
+        while self.has_unfinished():
+            finished = {res.request_id: res for res in self.step()}
+            for rid in list(live):
+                res = finished.get(rid)
+                if res is not None:
+                    del live[rid]
+                    yield index[rid], res.token_ids[shown[rid]:], res
+                    continue
+                out = live[rid].output
+                known = next((i for i, t in enumerate(out) if t == Scheduler.PLACEHOLDER), len(out))
+                upto = analyze_generated(out[:known], live[rid].params.stop_sequences or ()).printable_len
+                if upto > shown[rid]:
+                    yield index[rid], list(out[shown[rid]:upto]), None
+                    shown[rid] = upto
 
 
 def generate(model_dir: str, prompt_ids, params: Optional[SamplingParams] = None, *, dtype="bfloat16",

@@ -40,6 +40,7 @@ from typing import Hashable, Optional, Sequence
 
 from ..cache.manager import CacheManager
 from ..sampling.params import SamplingParams
+from ..sampling.stop import stop_hit_at
 
 
 @dataclass(eq=False)      # a request is itself, never "equal" to another: queues compare by identity
@@ -300,6 +301,15 @@ class Scheduler:
                 continue
             if idx < len(r.output):
                 r.output[idx] = tok
+                hit = stop_hit_at(r.output, idx + 1, r.params.stop_sequences) if r.params.stop_sequences else 0
+                if hit:
+                    del r.output[idx + 1 - hit:]         # the stop sequence and anything in flight after it
+                    if r.status != "finished":
+                        self._finish(r, "stop")
+                    else:
+                        r.finish_reason = "stop"
+                    finished.append(r)
+                    continue
             if r.status == "finished" and r.finish_reason == "length" and idx == len(r.output) - 1:
                 finished.append(r)
         return finished

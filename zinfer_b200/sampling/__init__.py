@@ -1,4 +1,5 @@
 from .params import SamplingParams
 from .sampler import Sampler
+from .stop import StopAnalysis, analyze_generated
 
-__all__ = ["Sampler", "SamplingParams"]
+__all__ = ["Sampler", "SamplingParams", "StopAnalysis", "analyze_generated"]

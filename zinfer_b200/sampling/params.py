@@ -19,6 +19,10 @@ class SamplingParams:
     seed: int = 0
     max_new_tokens: int = 64          # the reference's default for `generate` (src/app/cli/args.zig:100)
     eos_token_ids: Optional[Sequence[int]] = None   # None: the model family's own
+    # Sequences of token ids that end the response when the generated ids end with one of them; the
+    # sequence itself is not part of the response (the reference's --stop strings, args.zig:462-466,
+    # streaming.zig:11-40, on ids).
+    stop_sequences: Optional[Sequence[Sequence[int]]] = None
     ignore_eos: bool = False
 
     @property
