@@ -274,24 +274,31 @@ def main() -> int:
     # ------------------------------------------------- end to end through the API
     def e2e_point(batch: int, n_steps: int, **sampling) -> tuple[float, int]:
         """Decoded tokens a second through Engine.step (host tokens in and out), and the bytes of
-        the step's one host->device copy.  Greedy unless sampling options are given."""
-        params = SamplingParams(**{"temperature": 0.0, **sampling}, max_new_tokens=n_steps + warmup + 8, ignore_eos=True)
-        for i in range(batch):
-            engine.add_request(rand_tokens(PROMPT_LEN), params)
+        the step's one host->device copy.  Greedy unless sampling options are given.  Prompts are
+        admitted one a step, so the first request has decoded `batch` tokens before the last one is
+        in: every request may generate enough to stay live through the timed steps, and the tokens
+        counted are the ones the requests really gained."""
+        params = SamplingParams(**{"temperature": 0.0, **sampling}, max_new_tokens=batch + n_steps + warmup + 8, ignore_eos=True)
+        rids = [engine.add_request(rand_tokens(PROMPT_LEN), params) for _ in range(batch)]
+        reqs = [engine._live[rid] for rid in rids]
         while any(r.num_computed < len(r.prompt) for r in engine.scheduler.running) or engine.scheduler.waiting:
             engine.step()
         for _ in range(warmup):
             engine.step()
         torch.cuda.synchronize()
+        before = sum(len(r.output) for r in reqs)
         t0 = time.perf_counter()
         for _ in range(n_steps):
             engine.step()
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
+        gained = sum(len(r.output) for r in reqs) - before
+        if gained != batch * n_steps or len(engine.scheduler.running) != batch:
+            raise RuntimeError(f"e2e at batch {batch}: {gained} tokens in {n_steps} steps, {len(engine.scheduler.running)} requests live")
         h2d_bytes = runner.last_h2d_bytes
         while engine.has_unfinished():
             engine.step()
-        return batch * n_steps / dt, int(h2d_bytes)
+        return gained / dt, int(h2d_bytes)
 
     e2e_value, h2d = e2e_point(args.batch, steps)
     e2e = {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch}
