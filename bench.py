@@ -319,11 +319,11 @@ def main() -> int:
             for _ in range(4):
                 runner.step_argmax([StepEntry(rid, [t], [0]) for rid, t in zip(ids, cur)])
             decode_profile = prof.summary()
+        for rid in ids:
+            runner.end_request(rid)
         with engine.profile(hbm_gbs, bf16_tflops) as prof:
             prefill_once()
             prefill_profile = prof.summary()
-        for rid in ids:
-            runner.end_request(rid)
         with open(args.profile, "w") as f:
             json.dump({"decode": {"batch": args.batch, "context": PROMPT_LEN, **decode_profile},
                        "prefill": {"tokens": PREFILL_TOKENS, **prefill_profile}}, f, indent=1)
