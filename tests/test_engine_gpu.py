@@ -113,6 +113,37 @@ def test_end_of_sequence_with_the_pipelined_engine(model_dirs, dtype):
         assert results[True] == results[False]
 
 
+def test_stop_sequences_and_streaming_with_the_pipelined_engine(model_dirs):
+    """Stop sequences of two ids cut from the plain greedy continuation (float32, so that the engine's
+    tokens are the plain model's): the response ends before the sequence although the step behind it
+    is already in flight, streaming never shows an id that is not part of the response, and pages of
+    stopped requests go to the next ones at once."""
+    from zinfer_b200.sampling import SamplingParams
+
+    name = "D"
+    d = model_dirs[(name, "float32")]
+    cfg, w = P.load_model(d)
+    V = cfg["vocab_size"]
+    prompts = [[(11 * i + 5 * j) % V for j in range(n)] for i, n in enumerate((9, 30, 3, 17, 44, 1, 25))]
+    full = [P.greedy(cfg, w, p, 12) for p in prompts]
+    cut = [2, 7, 0, 10, 4, 1, 9]
+    params = [SamplingParams(temperature=0.0, max_new_tokens=12, ignore_eos=True, stop_sequences=[[V + 3], f[c:c + 2]])
+              for f, c in zip(full, cut)]
+    want = [f[:next(i for i in range(11) if f[i:i + 2] == f[c:c + 2])] for f, c in zip(full, cut)]
+    for pipelined in (True, False):
+        eng = _engine(d, name, "float32", kv_cache_tokens=160, max_requests=3, pipelined=pipelined)
+        got = eng.generate(prompts, params)
+        assert [r.token_ids for r in got] == want and all(r.finish_reason == "stop" for r in got), f"pipelined={pipelined}"
+        eng.runner.manager.check()
+        assert not eng.runner.manager.requests and eng.runner.manager.groups[0].pool.reused > 0
+        pieces = {i: [] for i in range(len(prompts))}
+        for i, new_ids, res in eng.generate_stream(prompts, params):
+            pieces[i] += new_ids
+            assert pieces[i] == want[i][:len(pieces[i])]
+            assert res is None or res.token_ids == want[i]
+        assert [pieces[i] for i in range(len(prompts))] == want
+
+
 @pytest.mark.parametrize("opts", [dict(temperature=0.9, top_k=12, repetition_penalty=1.3, presence_penalty=0.2, frequency_penalty=0.1),
                                   dict(temperature=0.7, top_k=20, top_p=0.9, min_p=0.05, repetition_penalty=1.1)])
 def test_penalties_and_filters_through_generate(model_dirs, opts):
