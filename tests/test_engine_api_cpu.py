@@ -109,3 +109,37 @@ def test_stop_sequences_and_streaming_through_the_engine(cpu_kernels, model_dirs
         if res is not None:
             ended[i] = res
     assert [pieces[i] for i in range(5)] == want and [ended[i].token_ids for i in range(5)] == want
+
+
+@pytest.mark.parametrize("pipelined", [True, False])
+def test_abort_gives_everything_back_and_disturbs_nobody(cpu_kernels, model_dirs, pipelined):
+    """A running request (with a token in flight when the engine is pipelined) and a waiting one are
+    aborted between steps: their pages, slots and count rows are free at once, they are reported once,
+    with the tokens that had reached the host, and the other requests' tokens are the plain model's."""
+    from zinfer_b200.sampling import SamplingParams
+
+    cfg, w = P.load_model(model_dirs[("A", "float32")])
+    prompts = _prompts(cfg["vocab_size"], lengths=(5, 17, 9, 12))
+    want = [P.greedy(cfg, w, p, 8) for p in prompts]
+    eng = _engine(model_dirs, "A", kv_cache_tokens=96, max_requests=2, pipelined=pipelined)
+    sp = SamplingParams(temperature=0.0, max_new_tokens=8, ignore_eos=True, repetition_penalty=1.0)
+    pen = SamplingParams(temperature=0.0, max_new_tokens=8, ignore_eos=True, presence_penalty=1e-9)   # takes a count row
+    ids = [eng.add_request(p, pen if i == 1 else sp) for i, p in enumerate(prompts)]
+    done = {}
+    for _ in range(4):                                   # requests 0 and 1 run, 2 and 3 wait
+        for res in eng.step():
+            done[res.request_id] = res
+    assert [r.request_id for r in eng.scheduler.running] == ids[:2] and len(eng.scheduler.waiting) == 2
+    a = eng.abort(ids[1])
+    b = eng.abort(ids[3])
+    assert eng.abort(ids[1]) is None and eng.abort("nobody") is None
+    assert a.finish_reason == b.finish_reason == "abort" and b.token_ids == []
+    assert -1 not in a.token_ids and a.token_ids == want[1][:len(a.token_ids)] and 0 < len(a.token_ids) < 8
+    assert not eng.runner.manager.has_request(ids[1]) and not eng.sampler.has_request(ids[1])
+    while eng.has_unfinished():
+        for res in eng.step():
+            assert res.request_id not in (ids[1], ids[3]), "an aborted request was reported again"
+            done[res.request_id] = res
+    assert done[ids[0]].token_ids == want[0] and done[ids[2]].token_ids == want[2]
+    eng.runner.manager.check()
+    assert not eng.runner.manager.requests and not eng.scheduler.waiting and not eng.scheduler.running

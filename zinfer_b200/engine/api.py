@@ -37,7 +37,7 @@ class GenerationResult:
     request_id: object
     prompt_token_ids: list[int]
     token_ids: list[int]
-    finish_reason: str            # stop | length | capacity
+    finish_reason: str            # stop | length | capacity | abort
     preemptions: int = 0
 
 
@@ -127,6 +127,17 @@ class Engine:
         self.scheduler.add(req)
         self._live[rid] = req      # its row of token counts (penalties) is taken when it is first scheduled
         return rid
+
+    def abort(self, request_id) -> Optional[GenerationResult]:
+        """Ends a request at once: its pages, its slot and its row of token counts are free for the
+        next step.  Returns its result (``finish_reason`` "abort", the tokens that have reached the
+        host), or None if it is not live.  A step of it that is in flight completes unnoticed."""
+        r = self.scheduler.abort(request_id)
+        if r is None:
+            return None
+        self.sampler.end_request(request_id)
+        self._live.pop(request_id, None)
+        return GenerationResult(r.request_id, r.prompt, list(r.output), r.finish_reason, r.preemptions)
 
     # ---------------------------------------------------------------------- step
     def _launch(self, plan: StepPlan) -> Optional[_InFlight]:

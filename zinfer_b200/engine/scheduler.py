@@ -137,6 +137,18 @@ class Scheduler:
     def has_unfinished(self) -> bool:
         return bool(self.waiting or self.running)
 
+    def abort(self, request_id: Hashable) -> Optional[Request]:
+        """Ends a waiting or running request now (``finish_reason`` "abort") and gives back what it
+        holds; the request is returned with the tokens that have reached the host.  A token of it
+        that is still in flight is dropped when its step is resolved.  None if no such request lives."""
+        r = next((x for x in list(self.running) + list(self.waiting) if x.request_id == request_id), None)
+        if r is None:
+            return None
+        known = next((i for i, t in enumerate(r.output) if t == self.PLACEHOLDER), len(r.output))
+        del r.output[known:]
+        self._finish(r, "abort")
+        return r
+
     # -------------------------------------------------------------------- helpers
     def _release(self, r: Request) -> None:
         if self.cache.has_request(r.request_id):
@@ -288,8 +300,8 @@ class Scheduler:
                 continue
             r = s.request
             tok = int(next(it))
-            if r.finish_reason == "stop":
-                continue                                 # ended by an earlier token; this one is dropped
+            if r.finish_reason in ("stop", "abort"):
+                continue                                 # ended by an earlier token, or aborted; this one is dropped
             idx = s.start + s.count - len(r.prompt)      # which output this step sampled
             if not r.params.ignore_eos and tok in r.eos_token_ids:
                 del r.output[idx:]                       # the end token and anything in flight after it
