@@ -11,7 +11,8 @@ for every request).  Prints ONE JSON line:
   value     decoded tokens per second at batch 8, timed on the device with CUDA events
   e2e       the same through the Python entry point (Engine.step), host tokens in
             and out, with the step's host->device and device->host bytes; "points"
-            inside it: the same at batch 1 and 64
+            inside it: the same at batch 1 and 64; "sampled": the same at batch 8 with
+            the reference's default sampling options instead of greedy
   prefill   one step of 2,048 prompt tokens: tokens/s, ms, fraction of the bf16 peak;
             "chunks_512" inside it: the same prompt as four steps of 512 tokens
   roofline  bytes the decode step must read (every weight once + the live
