@@ -8,8 +8,6 @@ every cache of the group.  For each state cache one tensor
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional
-
 import torch
 
 from .manager import CacheManager

@@ -20,7 +20,7 @@ from .. import ops, profiling
 from ..cache import CacheManager, CacheStorage, OutOfPages, pages_for
 from ..config.registry import load_config
 from ..weights import load_tensors, random_tensors
-from .batch import PinnedStaging, StepContext, StepEntry, build_step
+from .batch import PinnedStaging, StepEntry, build_step
 from .model import DecoderModel
 
 

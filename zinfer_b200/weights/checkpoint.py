@@ -15,7 +15,7 @@ from typing import Optional
 
 import torch
 
-from .safetensors_io import SafetensorsError, SafetensorsFile, TensorInfo, write_safetensors
+from .safetensors_io import SafetensorsFile, TensorInfo, write_safetensors
 
 SINGLE_FILE = "model.safetensors"
 INDEX_FILE = "model.safetensors.index.json"
