@@ -20,12 +20,16 @@ F64 = torch.float64
 
 
 # ----------------------------------------------------------------- the toy mixer
-def _make_ema_mixer():
+def _make_ema_mixer(on_device: bool = False):
     from zinfer_b200.parts import Mixer, StateNeed, TensorSpec
 
     class EmaMixer(Mixer):
         """s_t = decay * s_{t-1} + W_in x_t ; y_t = W_out s_t.  Its only memory is s, one
-        vector per request, kept in the cache manager's per-request state slots."""
+        vector per request, kept in the cache manager's per-request state slots.
+        ``on_device``: steps in which every request brings one token touch the state with device
+        operations alone (gather by ``state_slots``, update, scatter), so they can be captured."""
+
+        graph_safe = on_device
 
         def __init__(self, params, ctx):
             super().__init__(params, ctx)
@@ -45,6 +49,11 @@ def _make_ema_mixer():
 
         def forward(self, x, step, cache):
             u = x.float() @ self.w_in.T
+            if on_device and step.n_pf_tiles == 0 and step.n_dec == step.n_seqs:
+                slots = step.state_slots.long()              # rows that pad a captured batch name the spare slot
+                s = self.decay * cache.state.index_select(0, slots) + u
+                cache.state.index_copy_(0, slots, s)
+                return (s @ self.w_out.T).to(x.dtype)
             y = torch.empty_like(u)
             slots = step.state_slots.tolist()
             start = 0
@@ -216,6 +225,51 @@ def test_toy_hybrid_model_is_built_and_stepped(toy_registered, dtype):
     table = runner.manager.block_table("w", windowed)
     assert table[:7] == [-1] * 7 and all(p >= 0 for p in table[8:])
     runner.end_request("w")
+    runner.manager.check()
+
+
+@pytest.fixture
+def toy_on_device_registered():
+    from zinfer_b200.config import Family, register_family, unregister_family
+    from zinfer_b200.parts import register_part, unregister_part
+
+    register_part("toy_ema_mixer", _make_ema_mixer(on_device=True))
+    register_family(Family("ToyHybridForCausalLM", "toy_hybrid", ToyConfig, toy_model_spec))
+    yield
+    unregister_family("ToyHybridForCausalLM")
+    unregister_part("toy_ema_mixer")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_toy_mixer_with_state_decodes_from_a_graph(toy_on_device_registered, dtype):
+    """The same toy model with a mixer whose decode steps use device operations only: the runner
+    captures them, three live requests fill a bucket of four (the row that pads it names the spare
+    state slot, so nobody's state is touched), and the logits are the plain model's."""
+    from zinfer_b200.config import family_for
+    from zinfer_b200.engine import DecoderModel, ModelRunner
+    from zinfer_b200.weights import random_tensors
+
+    cfg = ToyConfig()
+    model = DecoderModel(family_for(cfg.to_dict()).model_spec(cfg), dtype, DEV)
+    tensors = random_tensors(model.tensor_specs(), 77, dtype, DEV)
+    model.bind(tensors)
+    runner = ModelRunner(model, page_size=4, max_tokens=192, max_requests=3)
+    assert runner.graphs is not None
+    w = {k: v.detach().cpu().to(F64) for k, v in tensors.items()}
+    reqs = ru.make_requests(cfg.vocab_size, [41, 30, 52], seed=8)
+    plain = {rid: plain_toy_forward(cfg, w, toks) for rid, toks in reqs.items()}
+    tol = dict(rtol=5e-5, atol=1e-6) if dtype == torch.float32 else dict(rtol=3e-2, atol=1e-3)
+    # prompts without their last 16 tokens in one step, then 16 steps of one token for all three together
+    ids = list(reqs)
+    trace = [{"step": 0, "end": [], "entries": [{"id": r, "tokens": reqs[r][:-16], "want": []} for r in ids]}]
+    for k in range(16, 0, -1):
+        trace.append({"step": len(trace), "end": ids if k == 1 else [],
+                      "entries": [{"id": r, "tokens": reqs[r][len(reqs[r]) - k:len(reqs[r]) - k + 1], "want": [0]} for r in ids]})
+    got = ru.run_in_process(runner, trace)
+    assert runner.graphs.replays >= 10 and len(got) == 3 * 16
+    ru.assert_close(got, plain, what="toy/graph", argmax_frac=0.0, **tol)
+    for name, t in runner.storage.state.items():
+        assert t.shape[0] == 4, "three request slots and the spare one"
     runner.manager.check()
 
 

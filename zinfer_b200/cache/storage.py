@@ -3,7 +3,9 @@
 For each group one tensor ``[caches, 2, pages, kv heads, page_size, head_dim]``
 (keys at index 0, values at index 1) in the run's dtype: a page id is valid for
 every cache of the group.  For each state cache one tensor
-``[request slots, *shape]``, zeroed for a slot when a request takes it.
+``[request slots + 1, *shape]``, zeroed for a slot when a request takes it.  The last
+slot belongs to no request: the rows that pad a captured decode batch name it, so a
+mixer that updates ``state[state_slots]`` with device operations alone harms nobody.
 """
 from __future__ import annotations
 
@@ -29,7 +31,7 @@ class StateView:
     """What a mixer with fixed-size state gets: ``state[slot]`` belongs to the
     request whose slot is ``slot`` (StepContext.state_slots)."""
 
-    state: torch.Tensor      # [request slots, *shape]
+    state: torch.Tensor      # [request slots + 1, *shape]; the last slot is the padding rows' scratch
     writes: bool = True
 
 
@@ -41,7 +43,7 @@ class CacheStorage:
             shape = (len(g.caches), 2, g.pool.num_pages, g.key.num_kv_heads, manager.page_size, g.key.head_dim)
             self.kv.append(torch.zeros(shape, dtype=dtype, device=device))
         self.state: dict[str, torch.Tensor] = {
-            name: torch.zeros((manager.max_requests, *need.shape), dtype=need.dtype, device=device)
+            name: torch.zeros((manager.max_requests + 1, *need.shape), dtype=need.dtype, device=device)
             for name, need in state_needs.items()
         }
 

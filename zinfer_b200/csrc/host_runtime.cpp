@@ -409,7 +409,8 @@ extern "C" int zi_cache_check(void* h) {
 //   9 pf_tile_seq [pf]  10 pf_tile_q0 [pf]  11 patch_dst [P]    12 patch_src [P]
 //  13 + 2g slots_g [T]  14 + 2g block_table_g [n * width_g]
 // n = max(n_entries, static_batch): with static_batch > 0 (a decode step replayed from a CUDA graph)
-// the batch is padded with requests of one key in no page whose key/value write is skipped, every
+// the batch is padded with requests of one key in no page whose key/value write is skipped and whose
+// state slot is the spare one behind the requests' slots (index max_requests), every
 // entry brings one token, logits are wanted for all n rows, block tables have static_width columns and
 // P = n.  Otherwise width_g is the longest block table of the entries in group g (at least 1).
 // The pages of the entries' tokens must have been reserved.
@@ -539,7 +540,7 @@ extern "C" long long zi_step_build(void* h, int n_entries, const long long* ids,
       src += ql[i];
     }
     kv[i] = real ? (int)(ctx[i] + ql[i]) : 1;
-    ss[i] = real ? reqs[i]->slot : 0;
+    ss[i] = real ? reqs[i]->slot : c->max_requests;   // padding rows: the spare slot that belongs to no request
     for (int q0 = 0; q0 < ql[i]; q0 += tile_rows) {
       tseq[ti] = i;
       tq0[ti] = q0;
