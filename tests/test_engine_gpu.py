@@ -422,6 +422,78 @@ def test_random_workloads_through_the_engine_match_plain_greedy(model_dirs, seed
     assert not eng.runner.manager.requests and eng.runner.manager.groups[0].pool.num_used == 0
 
 
+def test_a_mixed_workload_with_aborts_keeps_its_books_and_its_greedy_tokens(model_dirs):
+    """Eighty requests of every kind the entry point takes (greedy, temperature, the reference's default
+    filters with a repetition penalty, greedy with penalties, stop sequences) arrive at random while
+    others run in a small pool, and some are aborted between steps.  No request is reported twice, no
+    placeholder and no token outside the vocabulary comes out, nothing is left in the cache manager,
+    no bounded wait ran out, and the greedy requests that were not aborted (float32) have the plain
+    model's tokens, cut at their stop sequence."""
+    import random
+
+    from zinfer_b200 import ops
+    from zinfer_b200.sampling import SamplingParams
+
+    rnd = random.Random(7)
+    name = "B"
+    d = model_dirs[(name, "float32")]
+    cfg, w = P.load_model(d)
+    V = cfg["vocab_size"]
+    eng = _engine(d, name, "float32", kv_cache_tokens=None, num_pages=40, max_batched_tokens=96, chunk_size=37, max_requests=6)
+    pending = []
+    for i in range(80):
+        prompt = [rnd.randrange(V) for _ in range(rnd.choice([1, 2, 5, 17, 40, 90, 150]))]
+        new = rnd.choice([1, 3, 9, 20, 33])
+        kind = rnd.choice(["greedy", "greedy", "temperature", "default", "penalised", "stop"])
+        sp = {"greedy": SamplingParams(temperature=0.0, max_new_tokens=new, ignore_eos=True),
+              "temperature": SamplingParams(temperature=0.9, seed=i, max_new_tokens=new),
+              "default": SamplingParams(temperature=0.7, top_k=20, top_p=0.8, repetition_penalty=1.1, seed=i, max_new_tokens=new),
+              "penalised": SamplingParams(temperature=0.0, presence_penalty=0.3, frequency_penalty=0.1, max_new_tokens=new, ignore_eos=True),
+              "stop": SamplingParams(temperature=0.0, max_new_tokens=new, ignore_eos=True,
+                                     stop_sequences=[[rnd.randrange(V)], [rnd.randrange(V), rnd.randrange(V)]])}[kind]
+        pending.append((prompt, sp, kind))
+    asked, done, aborted = {}, {}, set()
+    steps = 0
+    while pending or eng.has_unfinished():
+        while pending and rnd.random() < 0.4:
+            prompt, sp, kind = pending.pop()
+            asked[eng.add_request(prompt, sp)] = (prompt, sp, kind)
+        live = [rid for rid in asked if rid not in done]
+        if live and rnd.random() < 0.04:
+            res = eng.abort(rnd.choice(live))
+            if res is not None:
+                assert res.finish_reason == "abort"
+                aborted.add(res.request_id)
+                done[res.request_id] = res
+        for res in eng.step():
+            assert res.request_id not in done, "a request was reported twice"
+            done[res.request_id] = res
+        steps += 1
+        if steps % 64 == 0:
+            eng.runner.manager.check()
+        assert steps < 5000
+    assert set(done) == set(asked) and aborted
+    eng.runner.manager.check()
+    assert not eng.runner.manager.requests and not eng.scheduler.running and not eng.scheduler.waiting
+    assert eng.scheduler.stats.preemptions > 0 and eng.runner.graphs.replays > 0
+    ops.require_kernel_status_ok("mixed workload")
+    compared = 0
+    for rid, res in done.items():
+        prompt, sp, kind = asked[rid]
+        assert -1 not in res.token_ids and len(res.token_ids) <= sp.max_new_tokens and all(0 <= t < V for t in res.token_ids)
+        if kind in ("greedy", "stop") and rid not in aborted and res.finish_reason != "capacity":
+            full = P.greedy(cfg, w, prompt, sp.max_new_tokens)
+            cut = len(full)
+            for i in range(len(full)):
+                hit = next((s_ for s_ in (sp.stop_sequences or []) if i + 1 >= len(s_) and full[i + 1 - len(s_):i + 1] == list(s_)), None)
+                if hit is not None:
+                    cut = i + 1 - len(hit)
+                    break
+            assert res.token_ids == full[:cut], f"request {rid} ({kind})"
+            compared += 1
+    assert compared >= 20
+
+
 def test_command_line_generate_with_a_byte_budget_and_a_profile(model_dirs, tmp_path):
     """Several prompts in one call, the pool sized from a byte budget, per-kernel-class times written."""
     import json
