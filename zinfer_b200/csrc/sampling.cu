@@ -411,6 +411,7 @@ __device__ Cut select_cut(const RowView& row, Team& tm, const F& cand, double ta
 // holds more tokens than may be listed is the row read again, for the next 12 bits (and once more
 // for the last 8).  Returns the number of tokens with key >= lb.  `hist` is this CTA's 4,096 words.
 constexpr int HIST_BINS = 4096;   // four per thread of a block of THREADS
+static_assert(HIST_BINS == 4 * THREADS, "every thread adds four neighbouring bins");
 __device__ int hist_lower_bound(const RowView& row, Team& tm, int k, int limit, unsigned int& lb, unsigned int* hist,
                                 float* best_val, int* best_idx, float* sval, int* sidx) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
