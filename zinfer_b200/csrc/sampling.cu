@@ -5,7 +5,9 @@
 // The reference sorts candidates by descending logit and cuts prefixes of that order.
 // Here every cut is a threshold in the order (adjusted logit descending, token id
 // ascending), found by radix selection four bits at a time with the bins in registers
-// (no atomics, so sums do not depend on timing and a draw is reproducible bit for bit).
+// (no atomics in any sum of weights, so sums do not depend on timing and a draw is reproducible
+// bit for bit).  Only the bound for a short top-k list counts keys with integer atomics in
+// shared memory, 12 bits at a time: a count is the same in whatever order it is made.
 #include <cooperative_groups.h>
 
 #include <type_traits>
