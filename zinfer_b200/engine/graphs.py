@@ -73,7 +73,7 @@ class DecodeGraphs:
             while len(self._buckets) >= MAX_GRAPHS:
                 self._buckets.popitem(last=False)
             static = StaticStepBuffers(b, -(-ctx_bucket // ps), runner.device, max_kv_len=ctx_bucket)
-            state = self._buckets[key] = {"static": static, "graph": None, "logits": None, "launches": 0, "warm": 0}
+            state = self._buckets[key] = {"static": static, "graph": None, "outputs": None, "launches": 0, "warm": 0}
         self._buckets.move_to_end(key)
         ctx = build_step(runner.manager, entries, runner.device, runner.tile_rows, static=state["static"],
                          pf_tile_rows=runner.pf_tile_rows)
@@ -94,7 +94,7 @@ class DecodeGraphs:
             if self._pool is None:
                 self._pool = torch.cuda.graph_pool_handle()
             with torch.cuda.graph(graph, pool=self._pool, capture_error_mode="relaxed"):
-                state["logits"] = runner.model.forward(ctx, argmax=True)
+                state["outputs"] = runner.model.forward(ctx, argmax=True)
             self.captures += 1
             state["launches"] = ops.LAUNCHES - before
             ops.LAUNCHES = before
@@ -102,4 +102,4 @@ class DecodeGraphs:
         state["graph"].replay()
         self.replays += 1
         self.launches += state["launches"]
-        return state["logits"]
+        return state["outputs"]
