@@ -757,6 +757,13 @@ int launch_single(void* out, const CUtensorMap& map_a, const CUtensorMap& map_b,
   if (per_sm > 2) per_sm = 2;
   int grid = per_sm * (sm_count > 0 ? sm_count : 148);
   if (grid > total_tiles) grid = total_tiles;
+  if (g.a_is_weight && total_tiles > grid) {
+    // Few tokens, more tiles than CTA slots (the output head: 1,187 tiles on 296 slots): as many CTAs as give
+    // every one the same number of tiles (238 with five each), instead of all slots with a last round of three
+    // tiles, which three CTAs would walk alone at the pace of their own copies (1 % of a step at one request).
+    const int rounds = (total_tiles + grid - 1) / grid;
+    grid = (total_tiles + rounds - 1) / rounds;
+  }
   zi_launch(kern, dim3(grid), dim3(THREADS), smem, stream, map_a, map_b, (TO*)out, partial, g, status);
   return zi_check_launch(what);
 }
