@@ -55,14 +55,15 @@ class Sampler:
             self._rows.free([row])
 
     # ----------------------------------------------------------------- sampling
-    _FIELDS = ("temperature", "top_p", "min_p", "rep", "pres", "freq", "top_k", "draw_index", "count_rows", "seed_lo", "seed_hi")
+    _FIELDS = ("temperature", "top_p", "min_p", "rep", "pres", "freq", "top_k", "draw_index", "count_rows")
 
-    def _staging(self, rows: int):
-        """A pinned buffer [fields, rows] of 32-bit words from a small ring (so a buffer is
-        not overwritten while its copy to the device may still be in flight)."""
+    def _staging(self):
+        """A flat pinned buffer of 32-bit words from a small ring (so a buffer is not overwritten
+        while its copy to the device may still be in flight): for R rows its first 2 R words hold the
+        seeds (64-bit each), the next len(_FIELDS) * R the per-row fields, field by field."""
         if not hasattr(self, "_ring"):
             pin = torch.cuda.is_available() and self.device.type == "cuda"
-            self._ring = [torch.zeros((len(self._FIELDS), self.max_requests), dtype=torch.int32, pin_memory=pin)
+            self._ring = [torch.zeros(((2 + len(self._FIELDS)) * self.max_requests,), dtype=torch.int32, pin_memory=pin)
                           for _ in range(4)]
             self._turn = 0
         buf = self._ring[self._turn % len(self._ring)]
@@ -83,10 +84,15 @@ class Sampler:
         if self.all_greedy(params):
             return greedy_ids if greedy_ids is not None else ops.argmax(logits)
         any_pen = any(p.has_penalties for p in params)
-        # all per-row parameters travel in one pinned buffer and one copy
-        host = self._staging(R)
+        # all per-row parameters travel in one pinned buffer and one contiguous copy; the tensors the
+        # kernel takes are views of that copy
+        nf = len(self._FIELDS)
+        words = self._staging()[:(2 + nf) * R]
+        seeds_h = words[:2 * R].view(torch.int64)
+        host = words[2 * R:].view(nf, R)
         f = host.view(torch.float32)
         for i, (rid, p) in enumerate(zip(request_ids, params)):
+            seeds_h[i] = p.seed
             f[0, i] = 0.0 if p.greedy else p.temperature
             f[1, i] = p.top_p
             f[2, i] = p.min_p
@@ -96,13 +102,10 @@ class Sampler:
             host[6, i] = p.top_k
             host[7, i] = int(draw_index[i])
             host[8, i] = self._row_of.get(rid, -1) if p.has_penalties else -1
-            host[9, i] = (p.seed & 0xFFFFFFFF) - (1 << 32 if p.seed & 0x80000000 else 0)
-            host[10, i] = (p.seed >> 32) & 0x7FFFFFFF
-        dev = host[:, :R].to(self.device, non_blocking=True) if self.device.type == "cuda" else host[:, :R].clone()
-        dev = dev.contiguous()
+        dev_words = words.to(self.device, non_blocking=True) if self.device.type == "cuda" else words.clone()
+        seeds = dev_words[:2 * R].view(torch.int64)
+        dev = dev_words[2 * R:].view(nf, R)
         fl = dev.view(torch.float32)
-        # seeds as int64 [R]: low and high words side by side
-        seeds = torch.stack([dev[9], dev[10]], dim=1).contiguous().view(torch.int64).reshape(R)
         return ops.sample(
             logits, temperature=fl[0], seeds=seeds, draw_index=dev[7], top_k=dev[6], top_p=fl[1], min_p=fl[2],
             repetition_penalty=fl[3] if any_pen else None, presence_penalty=fl[4] if any_pen else None,
